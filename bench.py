@@ -1,0 +1,330 @@
+#!/usr/bin/env python
+"""Headline benchmark: 1-bit decode attention over a group-format quantized KV cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--bits 1] [--context 32768] [--batch 8]
+
+A *step* is one decode-attention pass (all batch rows, all 32 query / 8 KV heads) over one
+resident quantized cache.  The workload is the reference configuration "quantize+pack sweep"
+at its largest point: batch 8, 8 KV heads, head_dim 128, context 32768, whole context
+quantized, fp16.  Several caches are kept resident and visited round-robin so that every step
+reads its cache from HBM, not from L2 (each cache alone exceeds the 126 MB L2).
+
+value   = algorithmic bytes per step / device time per step  (GB/s, inputs resident in HBM)
+e2e     = same metric through the public Python API with the step's query coming from pinned
+          host memory and the output going back to host memory inside the timed region
+roofline= achieved GB/s of the decode call against the measured HBM copy peak
+cpu_baseline = the CPU oracle (a PyTorch port of the reference arithmetic) on a bounded
+          sample of the same workload, on this host's cores
+
+N > 1 (torchrun): batch-sharded replicas, no collective on the data path; every rank holds
+its own batch of 8 rows (weak scaling); value aggregates all ranks over the max rank time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HQ, HKV, D = 32, 8, 128
+GROUP = 32
+L2_BYTES = 126 * 1024 * 1024
+
+
+def algorithmic_bytes(batch, t_vis, t_fp, bits):
+    """Bytes one step must move: K and V codes + scale + min once per KV head (GQA reuse),
+    fp16 K/V of full-precision tokens, q in and o out."""
+    per_vis_tok = 2 * (D * bits // 8 + (D // GROUP) * 4)        # 64 / 96 / 160 B
+    kv = batch * HKV * (t_vis * per_vis_tok + t_fp * D * 2 * 2)
+    qo = batch * HQ * D * 2 * 2
+    return kv + qo
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return json.load(open(p))["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, device_index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = torch.cuda.get_device_properties(device_index).uuid
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _reason_names(self, bits):
+        nv = self.nv
+        table = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        return {n for n, b in table.items() if bits & b}
+
+    def _sample(self):
+        nv = self.nv
+        self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+        try:
+            bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            self.reasons |= self._reason_names(bits)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self._sample()
+            except Exception:
+                break
+            self._stop.wait(0.02)
+
+    def start(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if not self.nv:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "NVML unavailable"}
+        self._stop.set()
+        self._thread.join()
+        if not self.samples:
+            self._sample()
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def build_caches(batch, t_vis, t_fp, bits, n_caches, device, seed):
+    """Synthetic caches with the reference generator's value distribution (K ~ N(0,1) times a
+    per-channel lognormal factor, V ~ N(0,1)), generated and packed on the device."""
+    from calibquant_b200 import ops
+    g = torch.Generator(device=device).manual_seed(seed)
+    caches = []
+    for _ in range(n_caches):
+        f = torch.exp(torch.randn(D, generator=g, device=device))
+        k = (torch.randn(batch, HKV, t_vis, D, generator=g, device=device) * f).half()
+        kp = ops.pack_k_per_channel(k, GROUP, bits)
+        del k
+        v = torch.randn(batch, HKV, t_vis, D, generator=g, device=device).half()
+        vp = ops.pack_last_dim(v, GROUP, bits)
+        del v
+        if t_fp:
+            kf = torch.randn(batch, HKV, t_fp, D, generator=g, device=device).half()
+            vf = torch.randn(batch, HKV, t_fp, D, generator=g, device=device).half()
+        else:
+            kf = vf = None
+        caches.append((kp, vp, kf, vf))
+    return caches
+
+
+def run_ours(args, rank, world, device):
+    from calibquant_b200 import ops
+    t_vis, t_fp, bits, batch = args.context, args.fp_tokens, args.bits, args.batch
+    step_bytes = algorithmic_bytes(batch, t_vis, t_fp, bits)
+    n_caches = max(3, -(-3 * L2_BYTES // step_bytes))
+    n_caches = min(n_caches, 64)
+    caches = build_caches(batch, t_vis, t_fp, bits, n_caches, device, seed=1234 + rank)
+    g = torch.Generator(device=device).manual_seed(99 + rank)
+    q_dev = torch.randn(batch, HQ, 1, D, generator=g, device=device).half()
+    out = torch.empty(batch, HQ, D, dtype=torch.float16, device=device)
+    t_sys = min(41, t_fp)
+
+    def step(i, q):
+        kp, vp, kf, vf = caches[i % n_caches]
+        return ops.decode_attention(q, kp, vp, kf, vf, t_sys, bits, out=out)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i, q_dev)
+    # ---- device-resident timing -------------------------------------------------------------
+    sampler = ClockSampler(device.index)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    ev0.record()
+    for i in range(args.steps):
+        step(i, q_dev)
+    ev1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = ev0.elapsed_time(ev1)
+    # ---- end to end: query from pinned host memory, output back to host, every step ----------
+    q_host = q_dev.cpu().pin_memory()
+    o_host = torch.empty(batch, HQ, D, dtype=torch.float16).pin_memory()
+    q_stage = torch.empty_like(q_dev)
+    for i in range(min(3, args.warmup)):
+        q_stage.copy_(q_host, non_blocking=True)
+        o_host.copy_(step(i, q_stage).view(batch, HQ, D), non_blocking=True)
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        q_stage.copy_(q_host, non_blocking=True)
+        o = step(i, q_stage)
+        o_host.copy_(o.view(batch, HQ, D), non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # a decode loop needs the result each step
+    ev1.record()
+    barrier()
+    ms_e2e = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms, ms_e2e = t.tolist()
+    per_step_ms = ms / args.steps
+    gbs = world * step_bytes / (per_step_ms * 1e-3) / 1e9
+    gbs_e2e = world * step_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    launches_per_step = 4
+    line = {
+        "metric": f"decode_attn_{bits}bit_GBps", "value": round(gbs, 2), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(per_step_ms, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {
+            "workload": f"decode attention, batch {batch}/GPU, {HQ}q/{HKV}kv heads, head_dim {D}, "
+                        f"context {t_vis} quantized at {bits} bit (group 32) + {t_fp} fp16 tokens",
+            "batch_per_gpu": batch, "context": t_vis, "fp_tokens": t_fp, "bits": bits,
+            "l2": f"{n_caches} resident caches of {step_bytes / 1e6:.1f} MB visited round-robin "
+                  f"(each larger than the 126 MB L2)" if step_bytes > L2_BYTES else
+                  f"{n_caches} resident caches visited round-robin (together {n_caches * step_bytes / 1e6:.0f} MB > 3x L2)",
+            "parallelism": f"batch-sharded x{world}, no collective",
+            "pct_of_8TBps": round(100 * gbs / world / 8000, 2),
+        },
+        "roofline": {"bound": "hbm", "achieved": round(gbs / world, 2), "peak": peak, "unit": "GB/s",
+                     "frac": round(gbs / world / peak, 4), "traffic": None,
+                     "peak_kind": peak_kind, "bytes_per_launch": step_bytes,
+                     "kernel": "cq_decode_attn (scores + stats + attn.V + combine launches)"},
+        "e2e": {"value": round(gbs_e2e, 2), "unit": "GB/s",
+                "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": o_host.numel() * 2,
+                "ms_per_step": round(ms_e2e / args.steps, 5)},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args, reps=2)
+    return line
+
+
+def cpu_baseline(args, reps, rows=1):
+    """Time the CPU oracle (PyTorch port of the reference decode step) on `rows` batch rows of
+    the workload; report GB/s with the same algorithmic byte count."""
+    from oracle import generator
+    from oracle import group_format as gf
+    torch.set_num_threads(os.cpu_count())
+    t_vis, t_fp, bits = args.context, args.fp_tokens, args.bits
+    T = t_vis + t_fp
+    sys_len = min(41, t_fp)
+    k, v, q = generator.make_kvq(rows, HQ, HKV, T, seed=0)
+    k_sys, k_vis, k_txt = generator.split_spans(k, t_vis, sys_len)
+    v_sys, v_vis, v_txt = generator.split_spans(v, t_vis, sys_len)
+    kp = gf.quantize_and_pack_last_dim(k_vis.transpose(2, 3).contiguous(), GROUP, bits)
+    vp = gf.quantize_and_pack_last_dim(v_vis.contiguous(), GROUP, bits)
+    gf.decode_attention(q, kp, vp, k_sys, k_txt, v_sys, v_txt, bits)      # warm-up
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        gf.decode_attention(q, kp, vp, k_sys, k_txt, v_sys, v_txt, bits)
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    gbs = algorithmic_bytes(rows, t_vis, t_fp, bits) / sec / 1e9
+    return {"value": round(gbs, 4), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{rows} of {args.batch} batch rows, full context, median of {reps} passes "
+                      f"({sec * 1e3:.1f} ms per pass)", "ms_per_sample": round(sec * 1e3, 2)}
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's decode-step arithmetic on this host's CPU cores (its CUDA
+    extension and Triton kernels need a GPU toolchain that the port replaces; the CPU oracle is
+    the PyTorch restatement pinned against the reference's own outputs)."""
+    if rank != 0:
+        return None
+    rows = 1
+    t0 = time.perf_counter()
+    base = cpu_baseline(args, reps=max(1, min(args.steps, 5)), rows=rows)
+    step_ms = base["ms_per_sample"] * args.batch / rows
+    return {
+        "impl": "reference", "metric": f"decode_attn_{args.bits}bit_GBps", "value": base["value"],
+        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(step_ms, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"decode attention, batch {args.batch}, {HQ}q/{HKV}kv heads, head_dim {D}, "
+                               f"context {args.context} quantized at {args.bits} bit (group 32) + "
+                               f"{args.fp_tokens} fp16 tokens",
+                   "note": "CPU, sampled: ms_per_step extrapolates the sampled rows to the full batch"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": round(time.perf_counter() - t0, 1),
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--bits", type=int, default=1)
+    ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--fp-tokens", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        line = run_reference(args, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product path has no CPU fallback)")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+    try:
+        line = run_ours(args, rank, world, device)
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+    finally:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

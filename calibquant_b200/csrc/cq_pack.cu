@@ -1,0 +1,216 @@
+// Group-wise min-max quantize + bit-pack (group format), one pass over the data.
+//
+// Arithmetic contract (what makes the result bit-identical to qjl/new_pack.py:53-82 of the
+// reference, whose torch ops each compute in fp32 and round to the tensor dtype):
+//   r     = rnd(mx - mn)                  scale = rnd(r / (2^b - 1))
+//   d     = rnd(x - mn)                   y     = rnd(d / scale)      (IEEE division)
+//   code  = rint_half_even(clamp(y, 0, 2^b - 1))
+// word w of a row holds elements w*fpi .. w*fpi+fpi-1, element i in bits [i*b, (i+1)*b).
+#include "cq_common.cuh"
+
+namespace cq {
+
+template <typename T>
+__device__ __forceinline__ void group_params(float mn, float mx, int levels, float& scale) {
+  float r = rnd<T>(mx - mn);
+  scale = rnd<T>(__fdiv_rn(r, (float)levels));
+}
+
+template <typename T>
+__device__ __forceinline__ unsigned quantize_one(float x, float mn, float scale, int levels) {
+  float d = rnd<T>(x - mn);
+  float y = rnd<T>(__fdiv_rn(d, scale));
+  y = fminf(fmaxf(y, 0.f), (float)levels);
+  return (unsigned)__float2int_rn(y);
+}
+
+// ---- rows of L contiguous elements; a thread owns 8 consecutive elements (one 128-bit load),
+// ---- four neighbouring lanes own one group of 32.
+template <typename T, int BITS>
+__global__ void __launch_bounds__(256)
+pack_last_dim_kernel(const T* __restrict__ data, int64_t n_chunks, int32_t* __restrict__ code,
+                     T* __restrict__ scale_out, T* __restrict__ mn_out) {
+  constexpr int LEVELS = (1 << BITS) - 1;
+  const int64_t chunk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = chunk < n_chunks;   // n_chunks is a multiple of 4, so quads are uniform
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (live) raw = __ldg(reinterpret_cast<const uint4*>(data) + chunk);
+  float x[8];
+  {
+    const typename Elem<T>::T2* p = reinterpret_cast<const typename Elem<T>::T2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = Elem<T>::to_f2(p[i]);
+      x[2 * i] = f.x;
+      x[2 * i + 1] = f.y;
+    }
+  }
+  float mn = x[0], mx = x[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) {
+    mn = fminf(mn, x[i]);
+    mx = fmaxf(mx, x[i]);
+  }
+  mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 1));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+  mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 2));
+  mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+  float scale;
+  group_params<T>(mn, mx, LEVELS, scale);
+  unsigned local = 0;
+  if (mx != mn) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) local |= quantize_one<T>(x[i], mn, scale, LEVELS) << (i * BITS);
+  }
+  // BITS*8 bits per thread; 32/(BITS*8) threads make one word.
+  constexpr int THREADS_PER_WORD = 4 / BITS;   // 4, 2, 1
+  const int lane = threadIdx.x & 31;
+  if (THREADS_PER_WORD > 1) {
+    const int pos = lane % THREADS_PER_WORD;
+    local <<= pos * 8 * BITS;
+#pragma unroll
+    for (int o = 1; o < THREADS_PER_WORD; o <<= 1) local |= __shfl_xor_sync(0xffffffffu, local, o);
+  }
+  if (!live) return;
+  if (lane % THREADS_PER_WORD == 0) code[chunk / THREADS_PER_WORD] = (int32_t)local;
+  if ((lane & 3) == 0) {
+    scale_out[chunk >> 2] = Elem<T>::from_f(scale);
+    mn_out[chunk >> 2] = Elem<T>::from_f(mn);
+  }
+}
+
+// ---- K per channel, transpose fused: a CTA stages 128 tokens x 128 channels in shared memory
+// ---- with coalesced 128-bit loads, then each thread walks 32 tokens of two adjacent channels.
+constexpr int KT_TOKENS = 128;
+
+template <typename T, int BITS>
+__global__ void __launch_bounds__(256)
+pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
+                          int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                          int32_t* __restrict__ code, T* __restrict__ scale_out,
+                          T* __restrict__ mn_out) {
+  constexpr int LEVELS = (1 << BITS) - 1;
+  constexpr int FPI = 32 / BITS;
+  constexpr int WORDS_PER_GROUP = BITS;  // 32 tokens * BITS / 32
+  __shared__ __align__(16) T tile[KT_TOKENS][kHeadDim];
+
+  const int bh = blockIdx.y;
+  const int b = bh / heads, h = bh % heads;
+  const int64_t t0 = (int64_t)blockIdx.x * KT_TOKENS;
+  const T* src = k + b * stride_b + h * stride_h;
+  const int n_tok = (int)min((int64_t)KT_TOKENS, T_len - t0);   // multiple of 32
+
+  for (int i = threadIdx.x; i < KT_TOKENS * (kHeadDim / 8); i += blockDim.x) {
+    const int row = i / (kHeadDim / 8), col = i % (kHeadDim / 8);
+    if (row < n_tok) {
+      uint4 v = __ldg(reinterpret_cast<const uint4*>(src + (t0 + row) * stride_t) + col);
+      *reinterpret_cast<uint4*>(&tile[row][col * 8]) = v;
+    }
+  }
+  __syncthreads();
+
+  const int gq = threadIdx.x / 64;        // group (of 32 tokens) inside the tile
+  const int cp = threadIdx.x % 64;        // channel pair
+  if (gq * 32 >= n_tok) return;
+  float xa[32], xb[32];
+#pragma unroll
+  for (int t = 0; t < 32; ++t) {
+    float2 f = Elem<T>::to_f2(*reinterpret_cast<const typename Elem<T>::T2*>(&tile[gq * 32 + t][cp * 2]));
+    xa[t] = f.x;
+    xb[t] = f.y;
+  }
+  const int64_t G = t0 / 32 + gq;
+  const int64_t n_groups = T_len / 32;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    float* x = c == 0 ? xa : xb;
+    float mn = x[0], mx = x[0];
+#pragma unroll
+    for (int t = 1; t < 32; ++t) {
+      mn = fminf(mn, x[t]);
+      mx = fmaxf(mx, x[t]);
+    }
+    float scale;
+    group_params<T>(mn, mx, LEVELS, scale);
+    const int64_t row = (int64_t)bh * kHeadDim + cp * 2 + c;
+    const bool constant = (mx == mn);
+#pragma unroll
+    for (int w = 0; w < WORDS_PER_GROUP; ++w) {
+      unsigned word = 0;
+      if (!constant) {
+#pragma unroll
+        for (int i = 0; i < FPI; ++i)
+          word |= quantize_one<T>(x[w * FPI + i], mn, scale, LEVELS) << (i * BITS);
+      }
+      code[row * (n_groups * WORDS_PER_GROUP) + G * WORDS_PER_GROUP + w] = (int32_t)word;
+    }
+    scale_out[row * n_groups + G] = Elem<T>::from_f(scale);
+    mn_out[row * n_groups + G] = Elem<T>::from_f(mn);
+  }
+}
+
+template <typename T>
+int launch_pack_last_dim(const void* data, int64_t rows, int64_t L, int bits, int32_t* code,
+                         void* scale, void* mn, cudaStream_t st) {
+  const int64_t n_chunks = rows * L / 8;
+  const int64_t blocks = (n_chunks + 255) / 256;
+  if (blocks > 0x7fffffffLL) return CQ_ERR_UNSUPPORTED;
+  const T* d = static_cast<const T*>(data);
+  T* s = static_cast<T*>(scale);
+  T* m = static_cast<T*>(mn);
+  switch (bits) {
+    case 1: pack_last_dim_kernel<T, 1><<<(unsigned)blocks, 256, 0, st>>>(d, n_chunks, code, s, m); break;
+    case 2: pack_last_dim_kernel<T, 2><<<(unsigned)blocks, 256, 0, st>>>(d, n_chunks, code, s, m); break;
+    default: pack_last_dim_kernel<T, 4><<<(unsigned)blocks, 256, 0, st>>>(d, n_chunks, code, s, m); break;
+  }
+  return check_launch();
+}
+
+template <typename T>
+int launch_pack_k(const void* k, int batch, int heads, int64_t T_len, int64_t sb, int64_t sh,
+                  int64_t st_, int bits, int32_t* code, void* scale, void* mn, cudaStream_t st) {
+  dim3 grid((unsigned)((T_len + KT_TOKENS - 1) / KT_TOKENS), (unsigned)(batch * heads));
+  const T* d = static_cast<const T*>(k);
+  T* s = static_cast<T*>(scale);
+  T* m = static_cast<T*>(mn);
+  switch (bits) {
+    case 1: pack_k_per_channel_kernel<T, 1><<<grid, 256, 0, st>>>(d, heads, T_len, sb, sh, st_, code, s, m); break;
+    case 2: pack_k_per_channel_kernel<T, 2><<<grid, 256, 0, st>>>(d, heads, T_len, sb, sh, st_, code, s, m); break;
+    default: pack_k_per_channel_kernel<T, 4><<<grid, 256, 0, st>>>(d, heads, T_len, sb, sh, st_, code, s, m); break;
+  }
+  return check_launch();
+}
+
+}  // namespace cq
+
+extern "C" int cq_pack_last_dim(const void* data, int64_t rows, int64_t L, int group_size,
+                                int bits, int dtype, int32_t* code, void* scale, void* mn,
+                                void* stream) {
+  if (!data || !code || !scale || !mn || rows < 0 || L < 0) return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (bits != 1 && bits != 2 && bits != 4) return CQ_ERR_UNSUPPORTED;
+  if (group_size != cq::kGroup || L % 32 != 0) return CQ_ERR_UNSUPPORTED;
+  if (!cq::aligned16(data)) return CQ_ERR_BAD_ARG;
+  if (rows == 0 || L == 0) return CQ_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CQ_DTYPE_F16)
+    return cq::launch_pack_last_dim<__half>(data, rows, L, bits, code, scale, mn, st);
+  return cq::launch_pack_last_dim<__nv_bfloat16>(data, rows, L, bits, code, scale, mn, st);
+}
+
+extern "C" int cq_pack_k_per_channel(const void* k, int batch, int heads, int64_t T, int D,
+                                     int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                                     int group_size, int bits, int dtype, int32_t* code,
+                                     void* scale, void* mn, void* stream) {
+  if (!k || !code || !scale || !mn || batch < 0 || heads < 0 || T < 0) return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (bits != 1 && bits != 2 && bits != 4) return CQ_ERR_UNSUPPORTED;
+  if (group_size != cq::kGroup || T % 32 != 0 || D != cq::kHeadDim) return CQ_ERR_UNSUPPORTED;
+  if (!cq::aligned16(k) || stride_b % 8 || stride_h % 8 || stride_t % 8) return CQ_ERR_BAD_ARG;
+  if (batch == 0 || heads == 0 || T == 0) return CQ_OK;
+  if ((int64_t)batch * heads > 65535) return CQ_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CQ_DTYPE_F16)
+    return cq::launch_pack_k<__half>(k, batch, heads, T, stride_b, stride_h, stride_t, bits, code, scale, mn, st);
+  return cq::launch_pack_k<__nv_bfloat16>(k, batch, heads, T, stride_b, stride_h, stride_t, bits, code, scale, mn, st);
+}

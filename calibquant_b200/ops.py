@@ -1,0 +1,183 @@
+"""Tensor-level entry points over the C ABI.
+
+torch is used here for device memory and streams only: every function hands raw
+device pointers of CUDA tensors to ``libcalibquant_b200.so`` on torch's current
+stream.  CPU tensors are rejected -- there is no fallback implementation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import DecodeArgs, check, lib
+
+_DTYPES = {torch.float16: _lib.CQ_DTYPE_F16, torch.bfloat16: _lib.CQ_DTYPE_BF16}
+
+
+def _dtype_enum(t: torch.Tensor) -> int:
+    if t.dtype not in _DTYPES:
+        raise TypeError(f"unsupported dtype {t.dtype}; expected float16 or bfloat16")
+    return _DTYPES[t.dtype]
+
+
+def _need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("calibquant_b200 runs on CUDA tensors only (no CPU fallback)")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+_workspaces = {}
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    """Grow-only scratch buffer per (device, stream)."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def pack_last_dim(data: torch.Tensor, group_size: int, bits: int):
+    """Group-wise quantize + pack along the last dim of a 4-D tensor.
+
+    Returns (code int32 [B,nh,R,L*bits/32], scale [B,nh,R,L/g], mn [B,nh,R,L/g]).
+    """
+    _need_cuda(data)
+    assert data.dim() == 4
+    B, nh, R, L = data.shape
+    assert L % group_size == 0
+    data = data.contiguous()
+    rows = B * nh * R
+    code = torch.empty((B, nh, R, L * bits // 32), dtype=torch.int32, device=data.device)
+    scale = torch.empty((B, nh, R, L // group_size), dtype=data.dtype, device=data.device)
+    mn = torch.empty_like(scale)
+    with torch.cuda.device(data.device):
+        rc = lib().cq_pack_last_dim(_ptr(data), rows, L, group_size, bits, _dtype_enum(data),
+                                    _ptr(code), _ptr(scale), _ptr(mn), _stream())
+    check(rc, "cq_pack_last_dim")
+    return code, scale, mn
+
+
+def pack_k_per_channel(k: torch.Tensor, group_size: int, bits: int):
+    """Per-channel quantize + pack of K given as [B,H,T,D] (any batch/head/token strides,
+    channels contiguous), as if ``pack_last_dim(k.transpose(2,3).contiguous())``.
+
+    Returns (code [B,H,D,T*bits/32], scale [B,H,D,T/g], mn [B,H,D,T/g]).
+    """
+    _need_cuda(k)
+    assert k.dim() == 4
+    B, H, T, D = k.shape
+    assert T % group_size == 0
+    if k.stride(3) != 1 or any(s % 8 for s in k.stride()[:3]) or k.data_ptr() % 16:
+        k = k.contiguous()
+    code = torch.empty((B, H, D, T * bits // 32), dtype=torch.int32, device=k.device)
+    scale = torch.empty((B, H, D, T // group_size), dtype=k.dtype, device=k.device)
+    mn = torch.empty_like(scale)
+    with torch.cuda.device(k.device):
+        rc = lib().cq_pack_k_per_channel(_ptr(k), B, H, T, D, k.stride(0), k.stride(1), k.stride(2),
+                                         group_size, bits, _dtype_enum(k),
+                                         _ptr(code), _ptr(scale), _ptr(mn), _stream())
+    check(rc, "cq_pack_k_per_channel")
+    return code, scale, mn
+
+
+def qbmm(group_size: int, fA: torch.Tensor, qB: torch.Tensor, scales: torch.Tensor,
+         zeros: torch.Tensor, bits: int) -> torch.Tensor:
+    """out[b,h,0,n] = sum_k fA[b,h,0,k]*(scales*code+zeros)[b,h//n_rep,k,n].
+
+    fA [B,Hq,1,K]; qB [B,Hkv,K,N*bits/32]; scales, zeros [B,Hkv,K,N/g].  Hkv may equal Hq
+    (operands already expanded, as the reference passes them) or divide it (GQA).
+    """
+    _need_cuda(fA, qB, scales, zeros)
+    assert fA.dim() == 4 and qB.dim() == 4
+    B, Hq, M, K = fA.shape
+    if M != 1:
+        raise ValueError("only M == 1 (one query row) is implemented")
+    Hkv = qB.shape[1]
+    N = qB.shape[-1] * (32 // bits)
+    fA, qB = fA.contiguous(), qB.contiguous()
+    scales, zeros = scales.contiguous(), zeros.contiguous()
+    out = torch.empty((B, Hq, 1, N), dtype=fA.dtype, device=fA.device)
+    nbytes = lib().cq_qbmm_workspace_bytes(B, Hq, K, N)
+    ws = _workspace(nbytes, fA.device)
+    with torch.cuda.device(fA.device):
+        rc = lib().cq_qbmm(_ptr(fA), _ptr(qB), _ptr(scales), _ptr(zeros), _ptr(out), B, Hq, Hkv,
+                           K, N, group_size, bits, _dtype_enum(fA), _ptr(ws), ws.numel(), _stream())
+    check(rc, "cq_qbmm")
+    return out
+
+
+def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
+                     calibrate=None, mask=None, out=None, t_fp=None):
+    """One decode step over [sys | visual (quantized) | text].
+
+    q [B,Hq,1,D] or [B,Hq,D]; k_pack/v_pack = (code, scale, mn) in the group format (K per
+    channel, V per token) or None when there are no quantized tokens; k_fp/v_fp [B,Hkv,T_fp,D]
+    (token rows contiguous; batch/head strides free) hold the system tokens followed by the
+    text tokens; ``t_fp`` limits how many of their rows are valid (default: all).
+    ``mask``: optional additive [B, T_fp+T_vis] in key order [sys | visual | text].
+    Returns o with q's shape.
+    """
+    _need_cuda(q, k_fp, v_fp, mask)
+    shape = q.shape
+    B, Hq, D = shape[0], shape[1], shape[-1]
+    q2 = q.reshape(B, Hq, D).contiguous()
+    Hkv = k_fp.shape[1] if k_fp is not None else k_pack[0].shape[1]
+    a = DecodeArgs()
+    a.batch, a.n_q_heads, a.n_kv_heads, a.head_dim = B, Hq, Hkv, D
+    a.bits, a.group_size, a.dtype = bits, group_size, _dtype_enum(q)
+    a.calibrate = int(bits <= 2 if calibrate is None else calibrate)
+    keep = [q2]
+    if k_pack is not None and k_pack[0].numel() > 0:
+        kc, ks, kmn = (t.contiguous() for t in k_pack)
+        vc, vs, vmn = (t.contiguous() for t in v_pack)
+        keep += [kc, ks, kmn, vc, vs, vmn]
+        a.t_vis = vc.shape[2]
+        a.k_code, a.k_scale, a.k_mn = kc.data_ptr(), ks.data_ptr(), kmn.data_ptr()
+        a.v_code, a.v_scale, a.v_mn = vc.data_ptr(), vs.data_ptr(), vmn.data_ptr()
+    else:
+        a.t_vis = 0
+    if k_fp is not None and k_fp.shape[2] > 0:
+        for t in (k_fp, v_fp):
+            if t.stride(3) != 1 or t.stride(2) != D:
+                raise ValueError("k_fp/v_fp token rows must be contiguous ([.., T, D] with stride D)")
+        if k_fp.stride() != v_fp.stride():
+            raise ValueError("k_fp and v_fp must share strides")
+        a.t_fp = k_fp.shape[2] if t_fp is None else t_fp
+        a.k_fp, a.v_fp = k_fp.data_ptr(), v_fp.data_ptr()
+        a.fp_stride_b, a.fp_stride_h = k_fp.stride(0), k_fp.stride(1)
+    else:
+        a.t_fp = 0
+    a.t_sys = min(t_sys, a.t_fp)
+    if mask is not None:
+        mask = mask.reshape(B, -1)
+        if mask.dtype != q.dtype or mask.stride(1) != 1:
+            mask = mask.to(q.dtype).contiguous()
+        if mask.shape[1] != a.t_vis + a.t_fp:
+            raise ValueError(f"Attention mask should cover {a.t_vis + a.t_fp} keys, but covers {mask.shape[1]}")
+        keep.append(mask)
+        a.mask, a.mask_stride_b = mask.data_ptr(), mask.stride(0)
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=q.dtype, device=q.device)
+    a.out = out.data_ptr()
+    nbytes = lib().cq_decode_attn_workspace_bytes(ctypes.byref(a))
+    if nbytes == 0:
+        check(lib().cq_decode_attn(ctypes.byref(a), None, 0, _stream()), "cq_decode_attn")
+    ws = _workspace(nbytes, q.device)
+    with torch.cuda.device(q.device):
+        rc = lib().cq_decode_attn(ctypes.byref(a), _ptr(ws), ws.numel(), _stream())
+    check(rc, "cq_decode_attn")
+    return out.reshape(shape)

@@ -1,0 +1,134 @@
+/*
+ * calibquant_b200 -- C ABI of the B200 (sm_100a) quantized-KV attention path.
+ *
+ * Every entry point takes raw DEVICE pointers, extents and a CUDA stream, returns
+ * 0 (CQ_OK) or a negative CQ_ERR_* code, never throws, never synchronises and
+ * never allocates: the caller owns every output and workspace buffer.  Work is
+ * ordered only by the stream that is passed (`stream` is a cudaStream_t cast to
+ * void*; NULL is the legacy default stream).  All entry points are re-entrant.
+ *
+ * Each declaration names the reference (ActiveSky/calibquant) interface it
+ * replaces, as file:line inside that project.
+ *
+ * Data formats
+ *   "group format" (qjl/new_pack.py): groups of `group_size` consecutive elements of
+ *   the last dimension; per group scale and minimum in the data dtype; 32/bits codes
+ *   per int32 word, element i of a word in bits [i*bits, (i+1)*bits).
+ *     K per channel : code [B,Hkv,D,T*bits/32]  scale,mn [B,Hkv,D,T/group]
+ *     V per token   : code [B,Hkv,T,D*bits/32]  scale,mn [B,Hkv,T,D/group]
+ *   dequantised value = scale*code + mn.
+ */
+#ifndef CALIBQUANT_B200_H_
+#define CALIBQUANT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CQ_OK 0
+#define CQ_ERR_BAD_ARG (-1)      /* null pointer, non-positive extent, bad enum            */
+#define CQ_ERR_UNSUPPORTED (-2)  /* legal request outside what the kernels implement        */
+#define CQ_ERR_LAUNCH (-3)       /* cudaGetLastError() reported a failure after the launch  */
+#define CQ_ERR_WORKSPACE (-4)    /* workspace pointer null or smaller than required         */
+#define CQ_ERR_TIMEOUT (-5)      /* a bounded device-side wait ran out (see status word)    */
+
+#define CQ_DTYPE_F16 0
+#define CQ_DTYPE_BF16 1
+
+/* Library version (major*10000 + minor*100 + patch). */
+int cq_version(void);
+
+/* Static, human-readable text for a status code. */
+const char* cq_status_string(int status);
+
+/*
+ * Quantize-and-pack along the last dimension (group format).
+ * Replaces qjl/new_pack.py:53-82 triton_quantize_and_pack_along_last_dim(data, group_size, bit)
+ * together with its Triton kernels (:7-28, :32-50) and the torch elementwise chain (:69-72).
+ *   data  : [rows, L] contiguous, dtype f16/bf16        (rows = B*nh*R of the 4-D input)
+ *   code  : [rows, L*bits/32] int32      scale, mn : [rows, L/group_size] in the data dtype
+ * Requirements: group_size == 32, bits in {1,2,4}, L % 32 == 0, data 16-byte aligned.
+ * Arithmetic reproduces the reference's per-operation rounding, so code/scale/mn are
+ * bit-identical to it.  A constant group (max == min) yields scale 0 and code 0.
+ */
+int cq_pack_last_dim(const void* data, int64_t rows, int64_t L, int group_size, int bits,
+                     int dtype, int32_t* code, void* scale, void* mn, void* stream);
+
+/*
+ * Per-channel K quantize-and-pack with the transpose fused in.
+ * Same result as cq_pack_last_dim applied to K transposed to [B,Hkv,D,T]
+ * (qjl/new_pack.py:53-82 on `K.transpose(2,3).contiguous()`), without materialising it.
+ *   k     : element (b,h,t,d) at k[b*stride_b + h*stride_h + t*stride_t + d], strides in
+ *           elements, last dimension contiguous, D == 128, every row 16-byte aligned
+ *   code  : [B,H,D,T*bits/32] int32      scale, mn : [B,H,D,T/32]
+ * Requirements: T % 32 == 0, group_size == 32, bits in {1,2,4}.
+ */
+int cq_pack_k_per_channel(const void* k, int batch, int heads, int64_t T, int D,
+                          int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                          int group_size, int bits, int dtype,
+                          int32_t* code, void* scale, void* mn, void* stream);
+
+/*
+ * Quantized batched vector-matrix product with dequantize-on-the-fly (M == 1).
+ * Replaces qjl/matmul.py:4-35 cuda_quantized_bmm_dynamic and the CUDA kernel
+ * qjl/csrc/quantization.cu:67-169 (batchedQuantizedMultiplyAccumulate<T>).
+ *   out[b,h,n] = sum_k fA[b,h,k] * (scales[b,hk,k,n/g]*code[b,hk,k,n] + zeros[b,hk,k,n/g]),
+ *   hk = h / n_rep   (GQA: the packed operand is NOT expanded to the query heads; this
+ *   replaces repeat_kv_quant, qjl/qjl_utils.py:6-11, and the reference's `mqa` flag).
+ *   fA [B*Hq, K]   qB [B*Hkv, K, N*bits/32]   scales, zeros [B*Hkv, K, N/32]   out [B*Hq, N]
+ * fp32 accumulation, result rounded to `dtype`.  Unlike the reference, bits == 1 works.
+ * Requirements: group_size == 32, bits in {1,2,4}, N % 32 == 0, n_rep in [1,8].
+ * `workspace` must hold cq_qbmm_workspace_bytes(...) bytes (fp32 partial sums).
+ */
+size_t cq_qbmm_workspace_bytes(int batch, int n_q_heads, int64_t K, int64_t N);
+int cq_qbmm(const void* fA, const int32_t* qB, const void* scales, const void* zeros,
+            void* out, int batch, int n_q_heads, int n_kv_heads, int64_t K, int64_t N,
+            int group_size, int bits, int dtype, void* workspace, size_t workspace_bytes,
+            void* stream);
+
+/*
+ * One decode step of attention over [system | visual (quantized) | text] keys.
+ * Replaces the q_len == 1 branch of the patched attention forward:
+ * patch_internvl.py:556-592 (scores, softmax, packed attn.V, fp16 side segments), with the
+ * logit calibration of patch_internvl.py:376-385 applied to the visual logits when
+ * `calibrate` != 0, and replaces per call: repeat_kv / repeat_kv_quant copies
+ * (patch_internvl.py:97-106, 581-583), the transposes of qjl/matmul.py:16-22 and both
+ * cuda_quantized_bmm_dynamic launches.
+ */
+typedef struct cq_decode_args {
+  /* extents */
+  int32_t batch, n_q_heads, n_kv_heads, head_dim;   /* head_dim must be 128            */
+  int32_t t_vis;        /* quantized (visual) tokens, multiple of 32, may be 0          */
+  int32_t t_fp;         /* full-precision tokens (system + text), may be 0              */
+  int32_t t_sys;        /* how many of the t_fp tokens precede the visual span; only    */
+                        /* used to index `mask` in the original key order               */
+  int32_t bits, group_size, dtype;
+  int32_t calibrate;    /* 1: remap visual logits (patch_internvl.py:376-385)           */
+  int32_t reserved;
+  /* operands (device pointers) */
+  const void* q;                 /* [B,Hq,D]                                            */
+  const int32_t* k_code;         /* [B,Hkv,D,t_vis*bits/32]                             */
+  const void* k_scale;           /* [B,Hkv,D,t_vis/32]                                  */
+  const void* k_mn;
+  const int32_t* v_code;         /* [B,Hkv,t_vis,D*bits/32]                             */
+  const void* v_scale;           /* [B,Hkv,t_vis,D/32]                                  */
+  const void* v_mn;
+  const void* k_fp;              /* token (b,h,t,:) at k_fp + b*fp_stride_b + h*fp_stride_h + t*D */
+  const void* v_fp;
+  int64_t fp_stride_b, fp_stride_h;  /* in elements */
+  const void* mask;              /* optional additive mask [B, t_fp + t_vis] in `dtype`, */
+  int64_t mask_stride_b;         /* key order [sys | visual | text]; NULL = none         */
+  void* out;                     /* [B,Hq,D] in `dtype`                                 */
+} cq_decode_args;
+
+size_t cq_decode_attn_workspace_bytes(const cq_decode_args* args);
+int cq_decode_attn(const cq_decode_args* args, void* workspace, size_t workspace_bytes,
+                   void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CALIBQUANT_B200_H_ */

@@ -1,0 +1,184 @@
+"""Decode-step attention and the stand-alone quantized product vs the CPU oracle.
+
+Tolerance: attention outputs rel-L2 <= 1e-2 in fp16/bf16 (the bar the path is specified
+with); the quantized product alone is held to 2e-3."""
+
+import pytest
+import torch
+
+from oracle import generator
+from oracle import group_format as gf
+from gpu_util import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+TOL_ATTN = 1e-2
+TOL_QBMM = 2e-3
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from calibquant_b200 import ops as _ops
+    return _ops
+
+
+def _cuda(pack):
+    return tuple(t.cuda() for t in pack)
+
+
+def _run_case(ops, B, Hq, Hkv, t_vis, t_txt, bits, dtype, seed, sys_len=generator.SYS_LEN,
+              calibrated=None, with_mask=False):
+    T = sys_len + t_vis + t_txt
+    k, v, q = generator.make_kvq(B, Hq, Hkv, T, seed=seed, dtype=dtype)
+    k_sys, k_vis, k_txt = generator.split_spans(k, t_vis, sys_len)
+    v_sys, v_vis, v_txt = generator.split_spans(v, t_vis, sys_len)
+    k_pack = gf.quantize_and_pack_last_dim(k_vis.transpose(2, 3).contiguous(), 32, bits)
+    v_pack = gf.quantize_and_pack_last_dim(v_vis.contiguous(), 32, bits)
+    if with_mask:
+        mask = torch.zeros(B, 1, 1, T, dtype=dtype)
+        mask[0, ..., :7] = torch.finfo(dtype).min          # left padding on row 0
+        mask[-1, ..., sys_len + 3] = torch.finfo(dtype).min
+    else:
+        mask = None
+    ref = _oracle_with_mask(q, k_pack, v_pack, k_sys, k_txt, v_sys, v_txt, bits, calibrated, mask)
+    k_fp = torch.cat([k_sys, k_txt], dim=2).cuda()
+    v_fp = torch.cat([v_sys, v_txt], dim=2).cuda()
+    out = ops.decode_attention(q.cuda(), _cuda(k_pack), _cuda(v_pack), k_fp, v_fp, sys_len, bits,
+                               calibrate=calibrated, mask=None if mask is None else mask.cuda())
+    torch.cuda.synchronize()
+    return out.cpu(), ref
+
+
+def _oracle_with_mask(q, k_pack, v_pack, k_sys, k_txt, v_sys, v_txt, bits, calibrated, mask):
+    if mask is None:
+        return gf.decode_attention(q, k_pack, v_pack, k_sys, k_txt, v_sys, v_txt, bits,
+                                   calibrated=calibrated)
+    # same composition with the additive mask applied before the softmax
+    import math
+    n_rep = q.shape[1] // k_sys.shape[1]
+    rep = lambda t: gf.repeat_kv(t, n_rep)
+    if calibrated is None:
+        calibrated = bits <= 2
+    sd = math.sqrt(q.shape[-1])
+    s_vis = gf.qbmm(32, q, rep(k_pack[0]), rep(k_pack[1]), rep(k_pack[2]), bits) / sd
+    s_sys = torch.matmul(q, rep(k_sys).transpose(2, 3)) / sd
+    s_txt = torch.matmul(q, rep(k_txt).transpose(2, 3)) / sd
+    if calibrated:
+        s_vis = gf.calibrate(s_vis)
+    att = torch.softmax(torch.cat([s_sys, s_vis, s_txt], -1) + mask, -1, dtype=torch.float32).to(q.dtype)
+    ns, nv = s_sys.shape[-1], s_vis.shape[-1]
+    o = gf.qbmm(32, att[..., ns:ns + nv], rep(v_pack[0]), rep(v_pack[1]), rep(v_pack[2]), bits)
+    return o + (torch.matmul(att[..., ns + nv:], rep(v_txt)) + torch.matmul(att[..., :ns], rep(v_sys)))
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4])
+def test_config0(ops, bits):
+    """B=1, 32 q / 8 KV heads, 41 + 3328 + 727 tokens, seed 0, fp16."""
+    out, ref = _run_case(ops, 1, 32, 8, 3328, 727, bits, torch.float16, seed=0)
+    assert out.shape == ref.shape
+    assert rel_l2(out, ref) <= TOL_ATTN, rel_l2(out, ref)
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_small_batched(ops, bits, dtype):
+    out, ref = _run_case(ops, 3, 8, 2, 544, 70, bits, dtype, seed=3 + bits)
+    tol = TOL_ATTN if dtype == torch.float16 else 2e-2   # bf16 keeps 8 mantissa bits per rounded op
+    assert rel_l2(out, ref) <= tol, rel_l2(out, ref)
+
+
+def test_n_rep_6(ops):
+    """48 q / 8 KV heads (the 20B backbone's grouping)."""
+    out, ref = _run_case(ops, 2, 12, 2, 256, 40, 1, torch.float16, seed=9)
+    assert rel_l2(out, ref) <= TOL_ATTN
+
+
+def test_without_calibration_and_with_mask(ops):
+    out, ref = _run_case(ops, 2, 8, 2, 320, 33, 1, torch.float16, seed=4, calibrated=False)
+    assert rel_l2(out, ref) <= TOL_ATTN
+    out, ref = _run_case(ops, 2, 8, 2, 320, 33, 2, torch.float16, seed=5, with_mask=True)
+    assert rel_l2(out, ref) <= TOL_ATTN
+
+
+def test_edge_segments(ops):
+    # no text tokens yet, a single group of visual tokens
+    out, ref = _run_case(ops, 1, 4, 1, 32, 0, 1, torch.float16, seed=6)
+    assert rel_l2(out, ref) <= TOL_ATTN
+    # no visual tokens at all: plain fp attention over sys + text
+    k, v, q = generator.make_kvq(2, 8, 2, 100, seed=7)
+    out = ops.decode_attention(q.cuda(), None, None, k.cuda(), v.cuda(), 41, 1)
+    s = torch.matmul(q.float(), gf.repeat_kv(k, 4).float().transpose(2, 3)) / 128 ** 0.5
+    ref = torch.matmul(torch.softmax(s, -1), gf.repeat_kv(v, 4).float())
+    assert rel_l2(out.cpu(), ref) <= 2e-3
+    # no fp tokens at all
+    k, v, q = generator.make_kvq(1, 4, 1, 64, seed=8)
+    kp = gf.quantize_and_pack_last_dim(k.transpose(2, 3).contiguous(), 32, 2)
+    vp = gf.quantize_and_pack_last_dim(v.contiguous(), 32, 2)
+    out = ops.decode_attention(q.cuda(), _cuda(kp), _cuda(vp), None, None, 0, 2)
+    e = torch.zeros(1, 1, 0, 128, dtype=torch.float16)
+    ref = gf.decode_attention(q, kp, vp, e, e, e, e, 2)
+    assert rel_l2(out.cpu(), ref) <= TOL_ATTN
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4])
+def test_qbmm_both_orientations(ops, bits):
+    k, v, q = generator.make_kvq(2, 8, 2, 384, seed=20 + bits)
+    kp = gf.quantize_and_pack_last_dim(k.transpose(2, 3).contiguous(), 32, bits)
+    vp = gf.quantize_and_pack_last_dim(v.contiguous(), 32, bits)
+    rep = lambda t: gf.repeat_kv(t, 4)
+    # q.K : [B,Hq,1,D] x [B,Hkv,D,T]
+    ref = gf.qbmm(32, q, rep(kp[0]), rep(kp[1]), rep(kp[2]), bits)
+    got = ops.qbmm(32, q.cuda(), *_cuda(kp), bits)
+    assert rel_l2(got.cpu(), ref) <= TOL_QBMM
+    # same with operands already expanded to the q heads, as the reference passes them
+    got2 = ops.qbmm(32, q.cuda(), rep(kp[0]).cuda(), rep(kp[1]).cuda(), rep(kp[2]).cuda(), bits)
+    assert torch.equal(got2, got)
+    # att.V : [B,Hq,1,T] x [B,Hkv,T,D]
+    g = torch.Generator().manual_seed(1)
+    att = torch.softmax(torch.randn(2, 8, 1, 384, generator=g) * 2, -1).half()
+    ref = gf.qbmm(32, att, rep(vp[0]), rep(vp[1]), rep(vp[2]), bits)
+    got = ops.qbmm(32, att.cuda(), *_cuda(vp), bits)
+    assert rel_l2(got.cpu(), ref) <= TOL_QBMM
+
+
+def test_drop_in_module_names(ops):
+    """The reference's import surface for this path resolves to the CUDA kernels."""
+    from calibquant_b200.qjl.matmul import cuda_quantized_bmm_dynamic
+    from calibquant_b200.qjl.new_pack import triton_quantize_and_pack_along_last_dim
+    k, v, q = generator.make_kvq(1, 4, 1, 64, seed=2)
+    code, scale, mn = triton_quantize_and_pack_along_last_dim(v.cuda(), 32, 2)
+    ref = gf.quantize_and_pack_last_dim(v, 32, 2)
+    assert torch.equal(code.cpu(), ref[0])
+    att = torch.softmax(torch.randn(1, 4, 1, 64), -1).half()
+    out = cuda_quantized_bmm_dynamic(32, att.cuda(), code, scale, mn, 2)
+    assert rel_l2(out.cpu(), gf.qbmm(32, att, *[gf.repeat_kv(t, 4) for t in ref], 2)) <= TOL_QBMM
+    with pytest.raises(TypeError):
+        cuda_quantized_bmm_dynamic(32, att.cuda().float(), code, scale, mn, 2)
+
+
+@pytest.mark.parametrize("bits", [1, 2])
+def test_full_size_properties(ops, bits):
+    """Config-1 size (B=8, T=32768): properties that need no oracle.
+    (1) permuting whole 32-token groups of the visual span leaves the output unchanged
+        (softmax/attn.V are permutation invariant, calibration uses only min/max);
+    (2) rows of the batch are independent: row 0 alone equals row 0 of the batch."""
+    torch.manual_seed(11)
+    B, Hq, Hkv, T, D = 8, 32, 8, 32768, 128
+    k = torch.randn(B, Hkv, T, D, device="cuda", dtype=torch.float16)
+    v = torch.randn(B, Hkv, T, D, device="cuda", dtype=torch.float16)
+    q = torch.randn(B, Hq, 1, D, device="cuda", dtype=torch.float16)
+    kf = torch.randn(B, Hkv, 64, D, device="cuda", dtype=torch.float16)
+    vf = torch.randn(B, Hkv, 64, D, device="cuda", dtype=torch.float16)
+    kp = ops.pack_k_per_channel(k, 32, bits)
+    vp = ops.pack_last_dim(v, 32, bits)
+    o = ops.decode_attention(q, kp, vp, kf, vf, 41, bits)
+    perm = torch.randperm(T // 32, device="cuda")
+    idx = (perm[:, None] * 32 + torch.arange(32, device="cuda")[None]).reshape(-1)
+    kp2 = ops.pack_k_per_channel(k[:, :, idx], 32, bits)
+    vp2 = ops.pack_last_dim(v[:, :, idx].contiguous(), 32, bits)
+    o2 = ops.decode_attention(q, kp2, vp2, kf, vf, 41, bits)
+    assert rel_l2(o2, o) <= 1e-3
+    o0 = ops.decode_attention(q[:1], tuple(t[:1] for t in kp), tuple(t[:1] for t in vp),
+                              kf[:1], vf[:1], 41, bits)
+    assert torch.equal(o0, o[:1])
+    assert torch.isfinite(o.float()).all()
