@@ -186,12 +186,13 @@ int launch_pack_k(const void* k, int batch, int heads, int64_t T_len, int64_t sb
 extern "C" int cq_pack_last_dim(const void* data, int64_t rows, int64_t L, int group_size,
                                 int bits, int dtype, int32_t* code, void* scale, void* mn,
                                 void* stream) {
-  if (!data || !code || !scale || !mn || rows < 0 || L < 0) return CQ_ERR_BAD_ARG;
+  if (rows < 0 || L < 0) return CQ_ERR_BAD_ARG;
   if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
   if (bits != 1 && bits != 2 && bits != 4) return CQ_ERR_UNSUPPORTED;
   if (group_size != cq::kGroup || L % 32 != 0) return CQ_ERR_UNSUPPORTED;
+  if (rows == 0 || L == 0) return CQ_OK;   // empty input: nothing to read or write
+  if (!data || !code || !scale || !mn) return CQ_ERR_BAD_ARG;
   if (!cq::aligned16(data)) return CQ_ERR_BAD_ARG;
-  if (rows == 0 || L == 0) return CQ_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == CQ_DTYPE_F16)
     return cq::launch_pack_last_dim<__half>(data, rows, L, bits, code, scale, mn, st);
@@ -202,12 +203,13 @@ extern "C" int cq_pack_k_per_channel(const void* k, int batch, int heads, int64_
                                      int64_t stride_b, int64_t stride_h, int64_t stride_t,
                                      int group_size, int bits, int dtype, int32_t* code,
                                      void* scale, void* mn, void* stream) {
-  if (!k || !code || !scale || !mn || batch < 0 || heads < 0 || T < 0) return CQ_ERR_BAD_ARG;
+  if (batch < 0 || heads < 0 || T < 0) return CQ_ERR_BAD_ARG;
   if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
   if (bits != 1 && bits != 2 && bits != 4) return CQ_ERR_UNSUPPORTED;
   if (group_size != cq::kGroup || T % 32 != 0 || D != cq::kHeadDim) return CQ_ERR_UNSUPPORTED;
+  if (batch == 0 || heads == 0 || T == 0) return CQ_OK;   // empty input
+  if (!k || !code || !scale || !mn) return CQ_ERR_BAD_ARG;
   if (!cq::aligned16(k) || stride_b % 8 || stride_h % 8 || stride_t % 8) return CQ_ERR_BAD_ARG;
-  if (batch == 0 || heads == 0 || T == 0) return CQ_OK;
   if ((int64_t)batch * heads > 65535) return CQ_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == CQ_DTYPE_F16)

@@ -140,6 +140,7 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
     a.batch, a.n_q_heads, a.n_kv_heads, a.head_dim = B, Hq, Hkv, D
     a.bits, a.group_size, a.dtype = bits, group_size, _dtype_enum(q)
     a.calibrate = int(bits <= 2 if calibrate is None else calibrate)
+    a.q = q2.data_ptr()
     keep = [q2]
     if k_pack is not None and k_pack[0].numel() > 0:
         kc, ks, kmn = (t.contiguous() for t in k_pack)

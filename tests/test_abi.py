@@ -53,6 +53,7 @@ def test_argument_validation_needs_no_gpu(handle):
     from calibquant_b200 import _lib
     lib = _lib.lib()
     assert lib.cq_pack_last_dim(None, 1, 32, 32, 1, 0, None, None, None, None) == _lib.CQ_ERR_BAD_ARG
+    assert lib.cq_pack_last_dim(None, 0, 32, 32, 1, 0, None, None, None, None) == _lib.CQ_OK   # empty
     buf = ctypes.create_string_buffer(64)
     p = ctypes.cast(buf, ctypes.c_void_p)
     p16 = ctypes.c_void_p((p.value + 15) // 16 * 16)
