@@ -18,6 +18,7 @@ CQ_ERR_UNSUPPORTED = -2
 CQ_ERR_LAUNCH = -3
 CQ_ERR_WORKSPACE = -4
 CQ_ERR_TIMEOUT = -5
+CQ_ERR_TOO_LARGE = -6
 
 CQ_DTYPE_F16 = 0
 CQ_DTYPE_BF16 = 1
@@ -53,6 +54,9 @@ SIGNATURES = {
     "cq_qbmm_workspace_bytes": (_sz, [_c.c_int, _c.c_int, _i64, _i64]),
     "cq_qbmm": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _i64, _i64,
                            _c.c_int, _c.c_int, _c.c_int, _vp, _sz, _vp]),
+    "cq_qbmm_static_capacity_bytes": (_sz, []),
+    "cq_qbmm_static": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _i64, _i64,
+                                  _c.c_int, _c.c_int, _c.c_int, _vp]),
     "cq_decode_attn_workspace_bytes": (_sz, [_c.POINTER(DecodeArgs)]),
     "cq_decode_attn": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _sz, _vp]),
 }

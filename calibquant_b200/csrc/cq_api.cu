@@ -11,6 +11,7 @@ extern "C" const char* cq_status_string(int status) {
     case CQ_ERR_LAUNCH: return "CUDA reported an error at kernel launch";
     case CQ_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
     case CQ_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case CQ_ERR_TOO_LARGE: return "problem needs more scratch than this fixed-capacity entry point holds";
     default: return "unknown status";
   }
 }

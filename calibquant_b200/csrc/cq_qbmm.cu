@@ -123,3 +123,58 @@ extern "C" int cq_qbmm(const void* fA, const int32_t* qB, const void* scales, co
     return cq::launch_qbmm<__half>(fA, qB, scales, zeros, out, batch, n_q_heads, n_kv_heads, K, N, bits, ws, st);
   return cq::launch_qbmm<__nv_bfloat16>(fA, qB, scales, zeros, out, batch, n_q_heads, n_kv_heads, K, N, bits, ws, st);
 }
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant: the fp32 partial sums live in a fixed array inside the library image.
+//
+// Who needs it: a serving process that has handed every remaining byte of HBM to its KV-cache
+// pool, or that must not stall its other streams, cannot call cudaMalloc in the decode loop
+// (the call can fail for lack of memory, and it synchronises the whole device).  Such a caller
+// still owns its inputs and outputs; only the scratch is taken off its hands.
+//
+// Cost: every GPU that loads this library keeps QB_STATIC_BYTES (8 MiB) of device memory until
+// the process exits, whether or not this entry point is ever called.
+// ------------------------------------------------------------------------------------------
+#include <mutex>
+
+namespace cq {
+
+constexpr size_t QB_STATIC_BYTES = (size_t)8 << 20;   // 8 MiB = 2 Mi fp32 partial sums
+constexpr int QB_MAX_DEVICES = 64;
+
+static __device__ __align__(256) unsigned char qbmm_static_scratch[QB_STATIC_BYTES];
+
+// In host code `qbmm_static_scratch` is only a handle for the runtime, not a device address,
+// so the address is asked for once per device (with that device current) and cached.
+static int static_scratch_address(float** out) {
+  static std::mutex mu;
+  static void* cached[QB_MAX_DEVICES] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= QB_MAX_DEVICES) return CQ_ERR_LAUNCH;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, qbmm_static_scratch) != cudaSuccess || !p) return CQ_ERR_LAUNCH;
+    cached[dev] = p;
+  }
+  *out = static_cast<float*>(cached[dev]);
+  return CQ_OK;
+}
+
+}  // namespace cq
+
+extern "C" size_t cq_qbmm_static_capacity_bytes(void) { return cq::QB_STATIC_BYTES; }
+
+extern "C" int cq_qbmm_static(const void* fA, const int32_t* qB, const void* scales,
+                              const void* zeros, void* out, int batch, int n_q_heads,
+                              int n_kv_heads, int64_t K, int64_t N, int group_size, int bits,
+                              int dtype, void* stream) {
+  if (batch > 0 && n_q_heads > 0 && K > 0 && N > 0 &&
+      cq_qbmm_workspace_bytes(batch, n_q_heads, K, N) > cq::QB_STATIC_BYTES)
+    return CQ_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = cq::static_scratch_address(&scratch);
+  if (rc != CQ_OK) return rc;
+  return cq_qbmm(fA, qB, scales, zeros, out, batch, n_q_heads, n_kv_heads, K, N, group_size, bits,
+                 dtype, scratch, cq::QB_STATIC_BYTES, stream);
+}

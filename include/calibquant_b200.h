@@ -34,6 +34,7 @@ extern "C" {
 #define CQ_ERR_LAUNCH (-3)       /* cudaGetLastError() reported a failure after the launch  */
 #define CQ_ERR_WORKSPACE (-4)    /* workspace pointer null or smaller than required         */
 #define CQ_ERR_TIMEOUT (-5)      /* a bounded device-side wait ran out (see status word)    */
+#define CQ_ERR_TOO_LARGE (-6)    /* problem needs more scratch than a fixed-capacity variant has */
 
 #define CQ_DTYPE_F16 0
 #define CQ_DTYPE_BF16 1
@@ -88,6 +89,33 @@ int cq_qbmm(const void* fA, const int32_t* qB, const void* scales, const void* z
             void* out, int batch, int n_q_heads, int n_kv_heads, int64_t K, int64_t N,
             int group_size, int bits, int dtype, void* workspace, size_t workspace_bytes,
             void* stream);
+
+/*
+ * cq_qbmm without any allocation by anybody: the fp32 partial sums go to a fixed array that
+ * is part of the library image (no counterpart in the reference, whose extension allocates
+ * its output through torch on every call).
+ *
+ * For callers that cannot allocate device memory once they are serving: a process that has
+ * given all remaining HBM to its KV-cache pool (cudaMalloc would fail), or one that must not
+ * stall its other streams (cudaMalloc synchronises the device).  Inputs and `out` are still the
+ * caller's; the entry point itself calls no cudaMalloc/cudaFree or other allocating routine.
+ *
+ * Limits and rules
+ *   - capacity: cq_qbmm_static_capacity_bytes() == 8 MiB, i.e. the call is accepted only while
+ *     cq_qbmm_workspace_bytes(batch, n_q_heads, K, N) <= 8 MiB (ceil(K/256)*batch*n_q_heads*N
+ *     fp32 values); a larger problem returns CQ_ERR_TOO_LARGE and launches nothing;
+ *   - every GPU that loads the library holds those 8 MiB until the process exits;
+ *   - the first call on each device looks the array's device address up (cudaGetSymbolAddress,
+ *     with that device current) and caches it; make that first call before any stream capture;
+ *   - all calls share the one array.  Nothing in it has to start at zero (each call overwrites
+ *     the part it later reads), but two calls that overlap on the GPU -- different streams, or
+ *     different host threads on different streams -- race on it.  Order them on one stream.
+ * Same arguments, requirements and result as cq_qbmm otherwise.
+ */
+size_t cq_qbmm_static_capacity_bytes(void);
+int cq_qbmm_static(const void* fA, const int32_t* qB, const void* scales, const void* zeros,
+                   void* out, int batch, int n_q_heads, int n_kv_heads, int64_t K, int64_t N,
+                   int group_size, int bits, int dtype, void* stream);
 
 /*
  * One decode step of attention over [system | visual (quantized) | text] keys.
