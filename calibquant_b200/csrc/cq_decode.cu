@@ -17,6 +17,7 @@
 //   3 attn.V  : split over tokens, fp32 partial outputs -> workspace
 //   4 combine : add the splits, round to the dtype
 #include "cq_common.cuh"
+#include "cq_decode_shared.cuh"
 
 namespace cq {
 
@@ -362,8 +363,8 @@ static DecodeDims make_dims(const cq_decode_args* a) {
 static WsLayout make_layout(const DecodeDims& dm) {
   WsLayout w;
   const size_t rows = (size_t)dm.batch * dm.hq;
-  w.scores_off = 0;
-  w.stats_off = align_up(rows * (size_t)dm.t_all * 2, 256);
+  w.scores_off = 256;   // the first 256 bytes are the sticky device status word of the workspace
+  w.stats_off = w.scores_off + align_up(rows * (size_t)dm.t_all * 2, 256);
   w.partial_off = w.stats_off + align_up(rows * STATS_FLOATS * sizeof(float), 256);
   w.total = w.partial_off + rows * (size_t)(dm.n_vis_splits + dm.n_fp_splits) * kHeadDim * sizeof(float);
   return w;
@@ -436,6 +437,7 @@ static int run_decode_bits(const cq_decode_args* a, const DecodeDims& dm, const 
 
 extern "C" size_t cq_decode_attn_workspace_bytes(const cq_decode_args* args) {
   if (cq::validate(args) != CQ_OK) return 0;
+  if (cq::mma_path_eligible(args)) return cq::mma_path_workspace_bytes(args);
   return cq::make_layout(cq::make_dims(args)).total;
 }
 
@@ -443,10 +445,15 @@ extern "C" int cq_decode_attn(const cq_decode_args* args, void* workspace, size_
                               void* stream) {
   int rc = cq::validate(args);
   if (rc != CQ_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cq::mma_path_eligible(args)) {
+    if (!workspace || workspace_bytes < cq::mma_path_workspace_bytes(args) || !cq::aligned16(workspace))
+      return CQ_ERR_WORKSPACE;
+    return cq::mma_path_run(args, workspace, st);
+  }
   const cq::DecodeDims dm = cq::make_dims(args);
   const cq::WsLayout w = cq::make_layout(dm);
   if (!workspace || workspace_bytes < w.total || !cq::aligned16(workspace)) return CQ_ERR_WORKSPACE;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   if (args->dtype == CQ_DTYPE_F16) return cq::run_decode_bits<__half>(args, dm, w, ws, st);
   return cq::run_decode_bits<__nv_bfloat16>(args, dm, w, ws, st);

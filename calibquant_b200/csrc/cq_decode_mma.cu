@@ -1,0 +1,815 @@
+// Decode-step attention, fast path: persistent CTAs, TMA-staged K/V tiles, packed-code dot
+// products on the warp-level fp16 tensor-core MMA.
+//
+// Why a tensor-core instruction on an HBM-bound path: with GQA every packed K/V bit is used by
+// n_rep (4..8) query heads, i.e. 16 multiply-adds per byte at 1 bit.  At HBM speed that is
+// ~100 T multiply-adds/s, three times the fp32 FMA rate of the SMs, so a CUDA-core inner loop is
+// instruction-issue bound at a fraction of the memory roofline.  The packed codes are therefore
+// expanded *in registers* into fp16 MMA operands and contracted with m16n8k16:
+//   * a byte permute (PRMT) drops one byte of two code words (two adjacent contraction indices)
+//     into the low bytes of the two fp16 halves of a register, and one AND keeps the b-bit field of
+//     the row this lane owns.  The surviving pattern c << s (c the code, s < 8) read as fp16 is the
+//     subnormal c * 2^(s-24): exact, and linear in c.  The 2^(24-s) factor is applied to the fp32
+//     accumulator of that row afterwards.  Two rows of a lane (adjacent tokens / channels) share
+//     the PRMT, so an A operand register costs 1.5 integer instructions.
+//   * "post-scaling": the other operand carries the scales, never the codes:
+//       scores : B[d][h] = q[h][d] * ks[d,G]          (per 32-token group G)
+//       attn.V : B[t][h] = p[h][t] * vs[t,g]          (per 32-channel group g)
+//     and the minima fold into one extra small MMA per tile (sum_d q*kmn, sum_t p*vmn), whose spare
+//     column also yields sum_t p (the softmax denominator).
+//
+// Three launches per decode step on the caller's stream (all persistent, grid = resident CTAs):
+//   K1 scores   : logits (fp16-rounded exactly where the reference rounds) -> workspace, plus
+//                 per-tile min/max of the visual logits for the calibration
+//   K2 attn.V   : per 1024-token chunk: calibrate, exp relative to the chunk max, accumulate,
+//                 write (max, sum, acc[128]) partials
+//   K3 combine  : merge the chunk partials (online-softmax rescale), round to the output dtype
+//
+// Eligibility (otherwise cq_decode_attn uses the general kernels): fp16, t_vis % 256 == 0,
+// no additive mask, 16-byte aligned operands.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "cq_common.cuh"
+#include "cq_ptx.cuh"
+#include "cq_decode_shared.cuh"
+
+namespace cq {
+namespace mma {
+
+using namespace ptx;
+
+constexpr int THREADS = 128;
+constexpr int TILE_G = 32;             // 32-token groups per K tile (1024 tokens)
+constexpr int CHUNK_TOK = 1024;        // tokens per attn.V work item
+constexpr int VT_TOK = 256;            // tokens per V tile
+constexpr uint32_t WAIT_TRIES = 1u << 22;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__host__ __device__ constexpr int k1_stages(int bits) { return bits == 1 ? 3 : 2; }
+__host__ __device__ constexpr int k1_stage_bytes(int bits) { return bits * 16384 + 2 * 8192; }
+__host__ __device__ constexpr int k2_stages(int) { return 4; }
+__host__ __device__ constexpr int k2_stage_bytes(int bits) { return VT_TOK * 16 * bits + 2 * VT_TOK * 8; }
+
+struct Dims {
+  int batch, hq, hkv, n_rep, t_vis, t_fp, calibrate;
+  int n_groups;        // t_vis / 32
+  int n_ktiles;        // ceil(n_groups / 32)
+  int n_chunks;        // ceil(t_vis / 1024)
+  int n_fp_chunks;     // ceil(t_fp / 128)
+  int n_slots;         // n_chunks + n_fp_chunks
+  int pitch;           // score row pitch in elements (multiple of 8)
+  int n_mm;            // min/max entries per row: n_ktiles * 4
+  int64_t fp_stride_b, fp_stride_h;
+};
+
+// ---- per-lane constants for expanding packed codes into MMA A operands -------------------------
+// A lane (g = lane/4) owns rows g and g+8 of a 16-row m-tile; they are mapped to the adjacent
+// packed elements 2g and 2g+1 of the 16 elements the m-tile covers.
+template <int BITS>
+struct Expand {
+  // element 2g of m-tile `mt_in_word_group` sits at bit offset (16*i + 2g)*BITS of its group
+  static __device__ __forceinline__ int bit_off(int i, int g) { return (i * 16 + 2 * g) * BITS; }
+};
+
+__device__ __forceinline__ uint32_t prmt_sel(int byte) {
+  return (uint32_t)(byte | (byte << 4) | ((4 + byte) << 8) | ((4 + byte) << 12));
+}
+
+// =================================================================================================
+// K1: scores
+// =================================================================================================
+template <int BITS>
+__global__ void __launch_bounds__(THREADS)
+k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ CUtensorMap tm_ks,
+          const __grid_constant__ CUtensorMap tm_kmn, Dims dm, const __half* __restrict__ q,
+          const __half* __restrict__ k_fp, __half* __restrict__ scores, float2* __restrict__ tile_mm,
+          int* __restrict__ status) {
+  constexpr int STAGES = k1_stages(BITS);
+  constexpr int STAGE_BYTES = k1_stage_bytes(BITS);
+  constexpr int CODE_BYTES = BITS * 16384;
+  constexpr int GU = 4 / BITS;             // groups per 16-byte chunk of a channel row
+  constexpr int UNITS = 8 / GU;            // chunks per warp (8 groups per warp)
+  constexpr uint32_t FIELD = (1u << BITS) - 1u;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(16) float qf_s[kMaxRep * kHeadDim];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int n_pairs = dm.batch * dm.hkv;
+  const int n_items = n_pairs * dm.n_ktiles;
+  const float inv_sqrt_d = 0.08838834764831845f;
+  const __half2 inv_sqrt_d2 = __float2half2_rn(inv_sqrt_d);
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  auto issue = [&](int k) {
+    const int it = blockIdx.x + k * gridDim.x;
+    if (it >= n_items) return;
+    const int s = k % STAGES;
+    const int pair = it / dm.n_ktiles, tile = it % dm.n_ktiles;
+    unsigned char* base = smem + s * STAGE_BYTES;
+    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+#pragma unroll
+    for (int bx = 0; bx < BITS; ++bx)
+      tma_load_2d(base + bx * 16384, &tm_code, (tile * TILE_G * BITS) + bx * 32, pair * kHeadDim, &full_bar[s]);
+    tma_load_2d(base + CODE_BYTES, &tm_ks, tile * TILE_G, pair * kHeadDim, &full_bar[s]);
+    tma_load_2d(base + CODE_BYTES + 8192, &tm_kmn, tile * TILE_G, pair * kHeadDim, &full_bar[s]);
+  };
+  if (tid == 0) {
+    fence_proxy_async_smem();
+    for (int k = 0; k < STAGES - 1; ++k) issue(k);
+  }
+
+  // lane constants: selectors / masks / accumulator scales for the two m-tiles of a group
+  uint32_t sel[2], m0[2], m1[2];
+  int word_in_group[2];
+  float sc0[2], sc1[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int off = Expand<BITS>::bit_off(i, g);
+    word_in_group[i] = off / 32;
+    const int byte = (off % 32) / 8, sh = off % 8;
+    sel[i] = prmt_sel(byte);
+    m0[i] = (FIELD << sh) * 0x00010001u;
+    m1[i] = (FIELD << (sh + BITS)) * 0x00010001u;
+    sc0[i] = exp2f((float)(24 - sh));
+    sc1[i] = exp2f((float)(24 - sh - BITS));
+  }
+
+  int cur_pair = -1;
+  uint32_t qA[8], qB[8];
+  bool failed = false;
+
+  for (int k = 0;; ++k) {
+    const int it = blockIdx.x + k * gridDim.x;
+    if (it >= n_items) break;
+    const int s = k % STAGES;
+    const int pair = it / dm.n_ktiles, tile = it % dm.n_ktiles;
+    if (tid == 0) {
+      fence_proxy_async_smem();
+      issue(k + STAGES - 1);
+    }
+    if (pair != cur_pair) {   // query fragments of this KV head's query heads (B operand, n = g)
+      cur_pair = pair;
+      const int b = pair / dm.hkv, hk = pair % dm.hkv;
+      const __half* qrow = q + ((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + g) * kHeadDim;
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
+        qA[kt] = g < dm.n_rep ? *reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c) : 0u;
+        qB[kt] = g < dm.n_rep ? *reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c + 8) : 0u;
+      }
+    }
+    if (!mbar_wait_bounded(&full_bar[s], (uint32_t)((k / STAGES) & 1), WAIT_TRIES)) {
+      atomicExch(status, CQ_ERR_TIMEOUT);
+      failed = true;
+      break;
+    }
+    const uint32_t code_base = smem_u32(smem + s * STAGE_BYTES);
+    const uint32_t ks_base = code_base + CODE_BYTES, kmn_base = ks_base + 8192;
+    const int live_groups = min(TILE_G, dm.n_groups - tile * TILE_G);
+
+    if (warp * 8 < live_groups) {
+      // ---- scale fragments: ksA/ksB[kt] = (ks[16kt+2c][G], ks[16kt+2c+1][G]) / (+8), G = 8*warp+g
+      uint32_t ksA[8], ksB[8];
+      float cb[4] = {0.f, 0.f, 0.f, 0.f};   // bias[G = 8*warp+g][heads 2c, 2c+1]
+      {
+        const int mat = lane >> 3, r = lane & 7;
+#pragma unroll
+        for (int kp = 0; kp < 4; ++kp) {
+          const int d = 16 * (2 * kp + (mat >> 1)) + 8 * (mat & 1) + r;
+          const uint32_t off = (uint32_t)(d * 64 + ((warp ^ ((d >> 1) & 3)) << 4));
+          ldmatrix_x4_trans(ks_base + off, ksA[2 * kp], ksB[2 * kp], ksA[2 * kp + 1], ksB[2 * kp + 1]);
+          uint32_t z0, z1, z2, z3;
+          ldmatrix_x4_trans(kmn_base + off, z0, z1, z2, z3);
+          mma_f16(cb, z0, 0u, z1, 0u, qA[2 * kp], qB[2 * kp]);
+          mma_f16(cb, z2, 0u, z3, 0u, qA[2 * kp + 1], qB[2 * kp + 1]);
+        }
+      }
+      const int b = pair / dm.hkv, hk = pair % dm.hkv;
+      const int64_t row_a = ((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + 2 * c) * dm.pitch;
+      const int64_t row_b = row_a + dm.pitch;
+      __half2 mnA = __float2half2_rn(65504.f), mxA = __float2half2_rn(-65504.f), mnB = mnA, mxB = mxA;
+
+#pragma unroll 1
+      for (int u = 0; u < UNITS; ++u) {
+        const int cidx = 2 * warp * BITS + u;                 // 16-byte chunk of the channel row
+        const uint32_t box_off = (uint32_t)(cidx >> 3) * 16384u;
+        const int ch = cidx & 7;
+        float acc[GU][2][4];
+#pragma unroll
+        for (int a = 0; a < GU; ++a)
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[a][i][e] = 0.f;
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) {
+          uint32_t W[4][4];
+#pragma unroll
+          for (int rr = 0; rr < 4; ++rr) {
+            const int d = 16 * kt + 2 * c + (rr & 1) + 8 * (rr >> 1);
+            const uint4 v = lds128(code_base + box_off + (uint32_t)(d * 128 + ((ch ^ (d & 7)) << 4)));
+            W[rr][0] = v.x; W[rr][1] = v.y; W[rr][2] = v.z; W[rr][3] = v.w;
+          }
+#pragma unroll
+          for (int a = 0; a < GU; ++a) {
+            const int gi = u * GU + a;                        // group within the warp's 8
+            const uint32_t ksa = __shfl_sync(0xffffffffu, ksA[kt], 4 * gi + c);
+            const uint32_t ksb = __shfl_sync(0xffffffffu, ksB[kt], 4 * gi + c);
+            const uint32_t b0 = hmul2_u32(qA[kt], ksa), b1 = hmul2_u32(qB[kt], ksb);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              uint32_t w0, w1, w8, w9;
+              if (BITS == 4) {   // the lane's element pair sits in word 2i or 2i+1 of the group
+                const bool hi = word_in_group[i] & 1;
+                w0 = hi ? W[0][2 * i + 1] : W[0][2 * i];
+                w1 = hi ? W[1][2 * i + 1] : W[1][2 * i];
+                w8 = hi ? W[2][2 * i + 1] : W[2][2 * i];
+                w9 = hi ? W[3][2 * i + 1] : W[3][2 * i];
+              } else {
+                const int wi = a * BITS + (BITS == 2 ? i : 0);
+                w0 = W[0][wi]; w1 = W[1][wi]; w8 = W[2][wi]; w9 = W[3][wi];
+              }
+              const uint32_t x01 = prmt(w0, w1, sel[i]), x89 = prmt(w8, w9, sel[i]);
+              mma_f16(acc[a][i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], b0, b1);
+            }
+          }
+        }
+        // ---- epilogue: rows g / g+8 are tokens 2g / 2g+1 of each 16-token m-tile
+#pragma unroll
+        for (int a = 0; a < GU; ++a) {
+          const int gi = u * GU + a;
+          const float bias0 = __shfl_sync(0xffffffffu, cb[0], 4 * gi + c);
+          const float bias1 = __shfl_sync(0xffffffffu, cb[1], 4 * gi + c);
+          const int tok0 = ((tile * TILE_G + warp * 8 + gi) * 32) + 2 * g;
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const __half2 ra = __floats2half2_rn(fmaf(acc[a][i][0], sc0[i], bias0), fmaf(acc[a][i][2], sc1[i], bias0));
+            const __half2 rb = __floats2half2_rn(fmaf(acc[a][i][1], sc0[i], bias1), fmaf(acc[a][i][3], sc1[i], bias1));
+            const __half2 sa = __hmul2(ra, inv_sqrt_d2), sb = __hmul2(rb, inv_sqrt_d2);
+            if (2 * c < dm.n_rep) {
+              *reinterpret_cast<__half2*>(scores + row_a + tok0 + 16 * i) = sa;
+              mnA = __hmin2(mnA, sa); mxA = __hmax2(mxA, sa);
+            }
+            if (2 * c + 1 < dm.n_rep) {
+              *reinterpret_cast<__half2*>(scores + row_b + tok0 + 16 * i) = sb;
+              mnB = __hmin2(mnB, sb); mxB = __hmax2(mxB, sb);
+            }
+          }
+        }
+      }
+      // ---- per-warp min/max of this tile, per head
+      float lo_a = fminf(__low2float(mnA), __high2float(mnA)), hi_a = fmaxf(__low2float(mxA), __high2float(mxA));
+      float lo_b = fminf(__low2float(mnB), __high2float(mnB)), hi_b = fmaxf(__low2float(mxB), __high2float(mxB));
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        lo_a = fminf(lo_a, __shfl_xor_sync(0xffffffffu, lo_a, o));
+        hi_a = fmaxf(hi_a, __shfl_xor_sync(0xffffffffu, hi_a, o));
+        lo_b = fminf(lo_b, __shfl_xor_sync(0xffffffffu, lo_b, o));
+        hi_b = fmaxf(hi_b, __shfl_xor_sync(0xffffffffu, hi_b, o));
+      }
+      if (g == 0) {
+        const int64_t r0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + 2 * c;
+        if (2 * c < dm.n_rep) tile_mm[r0 * dm.n_mm + tile * 4 + warp] = make_float2(lo_a, hi_a);
+        if (2 * c + 1 < dm.n_rep) tile_mm[(r0 + 1) * dm.n_mm + tile * 4 + warp] = make_float2(lo_b, hi_b);
+      }
+    } else if (lane < 2 * kMaxRep) {
+      // dead part of a ragged last tile: neutral min/max entries
+      const int b = pair / dm.hkv, hk = pair % dm.hkv;
+      if (lane < dm.n_rep)
+        tile_mm[((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + lane) * dm.n_mm + tile * 4 + warp] =
+            make_float2(INFINITY, -INFINITY);
+    }
+    __syncthreads();
+  }
+  if (failed) return;
+
+  // ---- full-precision tokens: one warp per token, lane owns 4 channels ---------------------------
+  const int n_fp_tiles = (dm.t_fp + 63) / 64;
+  for (int it = blockIdx.x; it < n_pairs * n_fp_tiles; it += gridDim.x) {
+    const int pair = it / n_fp_tiles, ft = it % n_fp_tiles;
+    const int b = pair / dm.hkv, hk = pair % dm.hkv;
+    __syncthreads();
+    for (int i = tid; i < dm.n_rep * kHeadDim; i += THREADS)
+      qf_s[i] = __half2float(q[((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep) * kHeadDim + i]);
+    __syncthreads();
+    const __half* kf = k_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h;
+    for (int i = warp; i < 64; i += THREADS / 32) {
+      const int t = ft * 64 + i;
+      if (t >= dm.t_fp) break;
+      const uint2 raw = __ldg(reinterpret_cast<const uint2*>(kf + (int64_t)t * kHeadDim) + lane);
+      const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+      const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+      for (int h = 0; h < dm.n_rep; ++h) {
+        const float4 qv = *reinterpret_cast<const float4*>(&qf_s[h * kHeadDim + lane * 4]);
+        float dot = qv.x * k01.x + qv.y * k01.y + qv.z * k23.x + qv.w * k23.y;
+        dot = warp_sum(dot);
+        if (lane == 0) {
+          const float sc = __fdiv_rn(__half2float(__float2half_rn(dot)), 11.313708498984761f);
+          scores[((int64_t)b * dm.hq + hk * dm.n_rep + h) * dm.pitch + dm.t_vis + t] = __float2half_rn(sc);
+        }
+      }
+    }
+  }
+}
+
+// =================================================================================================
+// K2: attn.V partials
+// =================================================================================================
+struct CalibH {   // per head, as fp16 pairs for half2 arithmetic
+  __half2 mn, rdenom, range;
+};
+
+template <int BITS>
+__global__ void __launch_bounds__(THREADS)
+k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__ tile_mm,
+          const int32_t* __restrict__ v_code, const __half* __restrict__ v_scale,
+          const __half* __restrict__ v_mn, const __half* __restrict__ v_fp,
+          float* __restrict__ partial, float2* __restrict__ ml, int* __restrict__ status) {
+  constexpr int STAGES = k2_stages(BITS);
+  constexpr int STAGE_BYTES = k2_stage_bytes(BITS);
+  constexpr int CODE_BYTES = VT_TOK * 16 * BITS;
+  constexpr int TOK_BYTES = 16 * BITS;      // code bytes per token
+  constexpr int WPT = 4 * BITS;             // code words per token
+  constexpr uint32_t FIELD = (1u << BITS) - 1u;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  // dynamic smem: [stages][STAGE_BYTES] | p_s [kMaxRep][CHUNK_TOK] half | red_s [4][kMaxRep][136] float
+  __half* p_s = reinterpret_cast<__half*>(smem + STAGES * STAGE_BYTES);
+  float* red_s = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + kMaxRep * CHUNK_TOK * 2);
+  constexpr int RED_STRIDE = 136;           // 128 channels + 4 group biases + 1 sum + pad
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ float m_s[kMaxRep];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int n_pairs = dm.batch * dm.hkv;
+  const int n_items = n_pairs * dm.n_chunks;
+  const int n_vtiles = dm.t_vis / VT_TOK;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  // producer state (thread 0): next live tile to issue
+  int p_k = 0, p_ti = 0, prod = 0;
+  auto issue_next = [&]() -> bool {
+    for (;;) {
+      const int it = blockIdx.x + p_k * gridDim.x;
+      if (it >= n_items) return false;
+      const int pair = it / dm.n_chunks, chunk = it % dm.n_chunks;
+      const int vt = chunk * (CHUNK_TOK / VT_TOK) + p_ti;
+      if (p_ti >= CHUNK_TOK / VT_TOK || vt >= n_vtiles) { ++p_k; p_ti = 0; continue; }
+      const int s = prod % STAGES;
+      unsigned char* base = smem + s * STAGE_BYTES;
+      const int64_t tok = (int64_t)pair * dm.t_vis + (int64_t)vt * VT_TOK;
+      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      bulk_load_1d(base, v_code + tok * WPT, CODE_BYTES, &full_bar[s]);
+      bulk_load_1d(base + CODE_BYTES, v_scale + tok * 4, VT_TOK * 8, &full_bar[s]);
+      bulk_load_1d(base + CODE_BYTES + VT_TOK * 8, v_mn + tok * 4, VT_TOK * 8, &full_bar[s]);
+      ++prod; ++p_ti;
+      return true;
+    }
+  };
+  if (tid == 0) {
+    fence_proxy_async_smem();
+    for (int i = 0; i < STAGES - 1; ++i) issue_next();
+  }
+
+  // lane constants for expanding channel pairs (2g, 2g+1) of m-tile j; pattern repeats with j%2
+  // for BITS==1 (two m-tiles per word) and is j-independent otherwise.
+  uint32_t sel[2], m0[2], m1[2];
+  float sc0[2], sc1[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int off = (i * 16 + 2 * g) * BITS;
+    const int byte = (off % 32) / 8, sh = off % 8;
+    sel[i] = prmt_sel(byte);
+    m0[i] = (FIELD << sh) * 0x00010001u;
+    m1[i] = (FIELD << (sh + BITS)) * 0x00010001u;
+    sc0[i] = exp2f((float)(24 - sh));
+    sc1[i] = exp2f((float)(24 - sh - BITS));
+  }
+
+  int cons = 0;
+  bool failed = false;
+  for (int k = 0; !failed; ++k) {
+    const int it = blockIdx.x + k * gridDim.x;
+    if (it >= n_items) break;
+    const int pair = it / dm.n_chunks, chunk = it % dm.n_chunks;
+    const int b = pair / dm.hkv, hk = pair % dm.hkv;
+    const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
+    const int tok_base = chunk * CHUNK_TOK;
+    const int n_tok = min(CHUNK_TOK, dm.t_vis - tok_base);
+
+    // ---- probabilities of the chunk: warp w serves heads w, w+4 --------------------------------
+    for (int h = warp; h < dm.n_rep; h += 4) {
+      CalibH cal;
+      if (dm.calibrate) {
+        float lo = INFINITY, hi = -INFINITY;
+        for (int i = lane; i < dm.n_mm; i += 32) {
+          const float2 v = tile_mm[(row0 + h) * dm.n_mm + i];
+          lo = fminf(lo, v.x);
+          hi = fmaxf(hi, v.y);
+        }
+        lo = warp_min(lo);
+        hi = warp_max(hi);
+        const float denom = rnd<__half>(rnd<__half>(hi - lo) + 1e-8f);
+        const float range = rnd<__half>(rnd<__half>(hi + (-3.f)) - lo);
+        cal.mn = __float2half2_rn(lo);
+        cal.rdenom = __float2half2_rn(1.f / denom);
+        cal.range = __float2half2_rn(range);
+      }
+      const __half* srow = scores + (row0 + h) * dm.pitch + tok_base;
+      __half2 x[4][4];
+      __half2 mx2 = __float2half2_rn(-65504.f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = (j * 32 + lane) * 8;
+        uint4 raw = make_uint4(0xfbfffbffu, 0xfbfffbffu, 0xfbfffbffu, 0xfbfffbffu);   // -65504
+        if (t < n_tok) raw = *reinterpret_cast<const uint4*>(srow + t);
+        const __half2* r2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __half2 v = r2[e];
+          if (dm.calibrate && t < n_tok) {
+            v = __hmul2(__hsub2(v, cal.mn), cal.rdenom);
+            v = __hadd2(__hmul2(v, cal.range), cal.mn);
+          }
+          x[j][e] = v;
+          mx2 = __hmax2(mx2, v);
+        }
+      }
+      const float m = warp_max(fmaxf(__low2float(mx2), __high2float(mx2)));
+      if (lane == 0) m_s[h] = m;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = (j * 32 + lane) * 8;
+        uint4 out;
+        __half2* o2 = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(x[j][e]);
+          o2[e] = t < n_tok ? __floats2half2_rn(exp2f((f.x - m) * LOG2E), exp2f((f.y - m) * LOG2E))
+                            : __float2half2_rn(0.f);
+        }
+        *reinterpret_cast<uint4*>(p_s + h * CHUNK_TOK + t) = out;
+      }
+    }
+    __syncthreads();
+
+    float acc[8][4];
+    float cb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+
+    for (int ti = 0; ti < CHUNK_TOK / VT_TOK; ++ti) {
+      const int vt = chunk * (CHUNK_TOK / VT_TOK) + ti;
+      if (vt >= n_vtiles) break;
+      if (tid == 0) {
+        fence_proxy_async_smem();
+        while (prod < cons + STAGES) if (!issue_next()) break;
+      }
+      const int s = cons % STAGES;
+      if (!mbar_wait_bounded(&full_bar[s], (uint32_t)((cons / STAGES) & 1), WAIT_TRIES)) {
+        atomicExch(status, CQ_ERR_TIMEOUT);
+        failed = true;
+        break;
+      }
+      ++cons;
+      const uint32_t code_b = smem_u32(smem + s * STAGE_BYTES);
+      const uint32_t vs_b = code_b + CODE_BYTES, vmn_b = vs_b + VT_TOK * 8;
+      const uint32_t p_b = smem_u32(p_s) + (uint32_t)((g < dm.n_rep ? g : 0) * CHUNK_TOK + ti * VT_TOK) * 2u;
+
+#pragma unroll 1
+      for (int kq = 0; kq < 4; ++kq) {
+        const int t0 = warp * 64 + kq * 16 + 2 * c;       // token (in tile) of the lane's first k pair
+        uint32_t pp0 = lds32(p_b + (uint32_t)t0 * 2u), pp1 = lds32(p_b + (uint32_t)(t0 + 8) * 2u);
+        if (g >= dm.n_rep) { pp0 = 0u; pp1 = 0u; }
+        // scales of tokens (t0, t0+1) and (t0+8, t0+9): 4 halves per token
+        const uint4 s0 = lds128(vs_b + (uint32_t)t0 * 8u), s1 = lds128(vs_b + (uint32_t)(t0 + 8) * 8u);
+        uint32_t bA[4], bB[4];
+        bA[0] = hmul2_u32(pp0, prmt(s0.x, s0.z, 0x5410)); bA[1] = hmul2_u32(pp0, prmt(s0.x, s0.z, 0x7632));
+        bA[2] = hmul2_u32(pp0, prmt(s0.y, s0.w, 0x5410)); bA[3] = hmul2_u32(pp0, prmt(s0.y, s0.w, 0x7632));
+        bB[0] = hmul2_u32(pp1, prmt(s1.x, s1.z, 0x5410)); bB[1] = hmul2_u32(pp1, prmt(s1.x, s1.z, 0x7632));
+        bB[2] = hmul2_u32(pp1, prmt(s1.y, s1.w, 0x5410)); bB[3] = hmul2_u32(pp1, prmt(s1.y, s1.w, 0x7632));
+        // minima + row sum: A = p (rows = heads), B column n = g: n<4 -> vmn[.][n], n==4 -> 1
+        {
+          const uint4 z0 = lds128(vmn_b + (uint32_t)t0 * 8u), z1 = lds128(vmn_b + (uint32_t)(t0 + 8) * 8u);
+          const uint32_t lo0 = (g & 2) ? z0.y : z0.x, hi0 = (g & 2) ? z0.w : z0.z;
+          const uint32_t lo1 = (g & 2) ? z1.y : z1.x, hi1 = (g & 2) ? z1.w : z1.z;
+          const uint32_t psel = (g & 1) ? 0x7632u : 0x5410u;
+          uint32_t zb0 = prmt(lo0, hi0, psel), zb1 = prmt(lo1, hi1, psel);
+          if (g == 4) { zb0 = 0x3c003c00u; zb1 = 0x3c003c00u; }
+          if (g > 4) { zb0 = 0u; zb1 = 0u; }
+          mma_f16(cb, pp0, 0u, pp1, 0u, zb0, zb1);
+        }
+        // code words of the lane's four tokens
+        const uint32_t tb = code_b + (uint32_t)t0 * TOK_BYTES;
+#pragma unroll
+        for (int part = 0; part < BITS; ++part) {      // 16 bytes of every token row at a time
+          const uint4 wa = lds128(tb + part * 16), wb = lds128(tb + TOK_BYTES + part * 16);
+          const uint4 wc = lds128(tb + 8 * TOK_BYTES + part * 16), wd = lds128(tb + 9 * TOK_BYTES + part * 16);
+          const uint32_t Wa[4] = {wa.x, wa.y, wa.z, wa.w}, Wb[4] = {wb.x, wb.y, wb.z, wb.w};
+          const uint32_t Wc[4] = {wc.x, wc.y, wc.z, wc.w}, Wd[4] = {wd.x, wd.y, wd.z, wd.w};
+          // m-tiles covered by these 4 words: 128/BITS channels = 8/BITS m-tiles
+#pragma unroll
+          for (int jj = 0; jj < 8 / BITS; ++jj) {
+            const int j = part * (8 / BITS) + jj;          // m-tile = channels 16j .. 16j+15
+            const int gq = j >> 1;                         // 32-channel group -> scale
+            int wi, i;
+            if (BITS == 1) { wi = jj >> 1; i = jj & 1; }
+            else if (BITS == 2) { wi = jj; i = 0; }
+            else { wi = 2 * jj + (g >> 2); i = 0; }
+            uint32_t a, bw, cw, dw;
+            if (BITS == 4) {
+              const bool hi = g >> 2;
+              a = hi ? Wa[2 * jj + 1] : Wa[2 * jj]; bw = hi ? Wb[2 * jj + 1] : Wb[2 * jj];
+              cw = hi ? Wc[2 * jj + 1] : Wc[2 * jj]; dw = hi ? Wd[2 * jj + 1] : Wd[2 * jj];
+              (void)wi;
+            } else {
+              a = Wa[wi]; bw = Wb[wi]; cw = Wc[wi]; dw = Wd[wi];
+            }
+            const uint32_t x01 = prmt(a, bw, sel[i]), x89 = prmt(cw, dw, sel[i]);
+            mma_f16(acc[j], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bA[gq], bB[gq]);
+          }
+        }
+      }
+      __syncthreads();
+    }
+    if (failed) break;
+
+    // ---- reduce the four warps, write the partial of this chunk --------------------------------
+    {
+      float* mine = red_s + warp * kMaxRep * RED_STRIDE;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = (BITS == 1) ? (j & 1) : 0;
+        const int ch = 16 * j + 2 * g;
+        if (2 * c < dm.n_rep) {
+          mine[(2 * c) * RED_STRIDE + ch] = acc[j][0] * sc0[i];
+          mine[(2 * c) * RED_STRIDE + ch + 1] = acc[j][2] * sc1[i];
+        }
+        if (2 * c + 1 < dm.n_rep) {
+          mine[(2 * c + 1) * RED_STRIDE + ch] = acc[j][1] * sc0[i];
+          mine[(2 * c + 1) * RED_STRIDE + ch + 1] = acc[j][3] * sc1[i];
+        }
+      }
+      if (g < dm.n_rep && c < 3) {      // bias columns 0..3 (c = 0,1) and the row sum (c = 2, col 4)
+        mine[g * RED_STRIDE + 128 + 2 * c] = cb[0];
+        if (c < 2) mine[g * RED_STRIDE + 128 + 2 * c + 1] = cb[1];
+      }
+    }
+    __syncthreads();
+    for (int h = 0; h < dm.n_rep; ++h) {
+      float o = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float* r = red_s + (w * kMaxRep + h) * RED_STRIDE;
+        o += r[tid] + r[128 + (tid >> 5)];
+        l += r[132];
+      }
+      partial[((row0 + h) * dm.n_slots + chunk) * kHeadDim + tid] = o;
+      if (tid == 0) ml[(row0 + h) * dm.n_slots + chunk] = make_float2(m_s[h], l);
+    }
+    __syncthreads();
+  }
+  if (failed) return;
+
+  // ---- full-precision tokens: chunks of 128, thread = channel -----------------------------------
+  float* pf_s = red_s;                      // [kMaxRep][128] probabilities
+  for (int it = blockIdx.x; it < n_pairs * dm.n_fp_chunks; it += gridDim.x) {
+    const int pair = it / dm.n_fp_chunks, fc = it % dm.n_fp_chunks;
+    const int b = pair / dm.hkv, hk = pair % dm.hkv;
+    const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
+    const int t0 = fc * 128, nt = min(128, dm.t_fp - t0);
+    __syncthreads();
+    for (int h = warp; h < dm.n_rep; h += 4) {
+      const __half* srow = scores + (row0 + h) * dm.pitch + dm.t_vis + t0;
+      float xv[4], m = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = j * 32 + lane;
+        xv[j] = t < nt ? __half2float(srow[t]) : -INFINITY;
+        m = fmaxf(m, xv[j]);
+      }
+      m = warp_max(m);
+      float l = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = j * 32 + lane;
+        const float p = t < nt ? __half2float(__float2half_rn(exp2f((xv[j] - m) * LOG2E))) : 0.f;
+        pf_s[h * 128 + t] = p;
+        l += p;
+      }
+      l = warp_sum(l);
+      if (lane == 0) ml[(row0 + h) * dm.n_slots + dm.n_chunks + fc] = make_float2(m, l);
+    }
+    __syncthreads();
+    float accf[kMaxRep];
+#pragma unroll
+    for (int h = 0; h < kMaxRep; ++h) accf[h] = 0.f;
+    const __half* vf = v_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h +
+                       (int64_t)t0 * kHeadDim + tid;
+    for (int t = 0; t < nt; ++t) {
+      const float v = __half2float(__ldg(vf + (int64_t)t * kHeadDim));
+#pragma unroll
+      for (int h = 0; h < kMaxRep; ++h)
+        if (h < dm.n_rep) accf[h] = fmaf(pf_s[h * 128 + t], v, accf[h]);
+    }
+#pragma unroll
+    for (int h = 0; h < kMaxRep; ++h)
+      if (h < dm.n_rep) partial[((row0 + h) * dm.n_slots + dm.n_chunks + fc) * kHeadDim + tid] = accf[h];
+  }
+}
+
+// =================================================================================================
+// K3: combine
+// =================================================================================================
+__global__ void __launch_bounds__(kHeadDim)
+k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict__ ml,
+           __half* __restrict__ out) {
+  const int64_t row = blockIdx.x;
+  const float2* r = ml + row * dm.n_slots;
+  float M = -INFINITY;
+  for (int i = 0; i < dm.n_slots; ++i) M = fmaxf(M, r[i].x);
+  float L = 0.f, o = 0.f;
+  const float* p = partial + row * dm.n_slots * kHeadDim + threadIdx.x;
+  for (int i = 0; i < dm.n_slots; ++i) {
+    const float w = exp2f((r[i].x - M) * LOG2E);
+    L = fmaf(r[i].y, w, L);
+    o = fmaf(p[(int64_t)i * kHeadDim], w, o);
+  }
+  out[row * kHeadDim + threadIdx.x] = __float2half_rn(o / L);
+}
+
+// =================================================================================================
+// host side
+// =================================================================================================
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// rows x cols matrix (cols contiguous), box = 32 columns x 128 rows.
+static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes,
+                     uint64_t cols, uint64_t rows, CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {32, 128};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct Layout {
+  size_t status_off, scores_off, mm_off, ml_off, partial_off, total;
+};
+
+static Dims make_dims(const cq_decode_args* a) {
+  Dims d;
+  d.batch = a->batch; d.hq = a->n_q_heads; d.hkv = a->n_kv_heads; d.n_rep = d.hq / d.hkv;
+  d.t_vis = a->t_vis; d.t_fp = a->t_fp; d.calibrate = a->calibrate ? 1 : 0;
+  d.n_groups = d.t_vis / 32;
+  d.n_ktiles = (d.n_groups + TILE_G - 1) / TILE_G;
+  d.n_chunks = (d.t_vis + CHUNK_TOK - 1) / CHUNK_TOK;
+  d.n_fp_chunks = (d.t_fp + 127) / 128;
+  d.n_slots = d.n_chunks + d.n_fp_chunks;
+  d.pitch = (d.t_vis + d.t_fp + 7) / 8 * 8;
+  d.n_mm = d.n_ktiles * 4;
+  d.fp_stride_b = a->fp_stride_b; d.fp_stride_h = a->fp_stride_h;
+  return d;
+}
+
+static Layout make_layout(const Dims& d) {
+  Layout l;
+  const size_t rows = (size_t)d.batch * d.hq;
+  l.status_off = 0;
+  l.scores_off = 256;
+  l.mm_off = l.scores_off + align_up(rows * (size_t)d.pitch * 2, 256);
+  l.ml_off = l.mm_off + align_up(rows * (size_t)d.n_mm * sizeof(float2), 256);
+  l.partial_off = l.ml_off + align_up(rows * (size_t)d.n_slots * sizeof(float2), 256);
+  l.total = l.partial_off + rows * (size_t)d.n_slots * kHeadDim * sizeof(float);
+  return l;
+}
+
+static int sm_count() {
+  static int n = []() {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+    return v;
+  }();
+  return n;
+}
+
+template <int BITS>
+static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st) {
+  int* status = reinterpret_cast<int*>(ws + l.status_off);
+  __half* scores = reinterpret_cast<__half*>(ws + l.scores_off);
+  float2* mm = reinterpret_cast<float2*>(ws + l.mm_off);
+  float2* ml = reinterpret_cast<float2*>(ws + l.ml_off);
+  float* partial = reinterpret_cast<float*>(ws + l.partial_off);
+  const int n_pairs = d.batch * d.hkv;
+
+  auto k1 = k1_scores<BITS>;
+  auto k2 = k2_attn_v<BITS>;
+  const int smem1 = k1_stages(BITS) * k1_stage_bytes(BITS) + 1024;
+  const int smem2 = k2_stages(BITS) * k2_stage_bytes(BITS) + kMaxRep * CHUNK_TOK * 2 + 4 * kMaxRep * 136 * 4 + 1024;
+  static bool configured_dev[64] = {};   // per template instance and device
+  static int occ1_dev[64], occ2_dev[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CQ_ERR_LAUNCH;
+  bool& configured = configured_dev[dev];
+  int& occ1 = occ1_dev[dev];
+  int& occ2 = occ2_dev[dev];
+  if (!configured) {
+    if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1) != cudaSuccess) return CQ_ERR_LAUNCH;
+    if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return CQ_ERR_LAUNCH;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ1, k1, THREADS, smem1) != cudaSuccess || occ1 < 1) return CQ_ERR_LAUNCH;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ2, k2, THREADS, smem2) != cudaSuccess || occ2 < 1) return CQ_ERR_LAUNCH;
+    configured = true;
+  }
+  if (d.t_vis > 0) {
+    CUtensorMap tm_code, tm_ks, tm_kmn;
+    const uint64_t rows = (uint64_t)n_pairs * kHeadDim;
+    if (!make_map(&tm_code, a->k_code, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)d.n_groups * BITS, rows,
+                  CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&tm_ks, a->k_scale, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)d.n_groups, rows,
+                  CU_TENSOR_MAP_SWIZZLE_64B) ||
+        !make_map(&tm_kmn, a->k_mn, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)d.n_groups, rows,
+                  CU_TENSOR_MAP_SWIZZLE_64B))
+      return CQ_ERR_LAUNCH;
+    const int items1 = n_pairs * d.n_ktiles;
+    const int grid1 = max(1, min(items1 + n_pairs * ((d.t_fp + 63) / 64), sm_count() * occ1));
+    k1<<<grid1, THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const __half*>(a->q),
+                                      static_cast<const __half*>(a->k_fp), scores, mm, status);
+    int rc = check_launch();
+    if (rc != CQ_OK) return rc;
+  }
+  const int items2 = n_pairs * (d.n_chunks + d.n_fp_chunks);
+  const int grid2 = max(1, min(items2, sm_count() * occ2));
+  k2<<<grid2, THREADS, smem2, st>>>(d, scores, mm, a->v_code, static_cast<const __half*>(a->v_scale),
+                                    static_cast<const __half*>(a->v_mn), static_cast<const __half*>(a->v_fp),
+                                    partial, ml, status);
+  int rc = check_launch();
+  if (rc != CQ_OK) return rc;
+  k3_combine<<<d.batch * d.hq, kHeadDim, 0, st>>>(d, partial, ml, static_cast<__half*>(a->out));
+  return check_launch();
+}
+
+}  // namespace mma
+
+bool mma_path_eligible(const cq_decode_args* a) {
+  // CQ_DECODE_GENERAL=1 forces the general kernels (A/B comparison of the two paths).
+  static const bool disabled = []() { const char* e = getenv("CQ_DECODE_GENERAL"); return e && e[0] == '1'; }();
+  if (disabled) return false;
+  if (a->dtype != CQ_DTYPE_F16 || a->mask != nullptr) return false;
+  if (a->t_vis <= 0 || a->t_vis % 256 != 0) return false;
+  if (a->bits != 1 && a->bits != 2 && a->bits != 4) return false;
+  const void* ptrs[] = {a->q, a->k_code, a->k_scale, a->k_mn, a->v_code, a->v_scale, a->v_mn};
+  for (const void* p : ptrs)
+    if (!aligned16(p)) return false;
+  if (a->t_fp > 0 && (!aligned16(a->k_fp) || !aligned16(a->v_fp))) return false;
+  return mma::encode_fn() != nullptr;
+}
+
+size_t mma_path_workspace_bytes(const cq_decode_args* a) {
+  return mma::make_layout(mma::make_dims(a)).total;
+}
+
+int mma_path_run(const cq_decode_args* a, void* workspace, cudaStream_t st) {
+  const mma::Dims d = mma::make_dims(a);
+  const mma::Layout l = mma::make_layout(d);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  switch (a->bits) {
+    case 1: return mma::run<1>(a, d, l, ws, st);
+    case 2: return mma::run<2>(a, d, l, ws, st);
+    default: return mma::run<4>(a, d, l, ws, st);
+  }
+}
+
+}  // namespace cq

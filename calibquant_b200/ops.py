@@ -41,13 +41,25 @@ _workspaces = {}
 
 
 def _workspace(nbytes: int, device) -> torch.Tensor:
-    """Grow-only scratch buffer per (device, stream)."""
+    """Grow-only scratch buffer per (device, stream), zeroed when created: its first word is
+    the sticky device status the decode kernels set when a bounded wait runs out."""
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=device)
+        buf = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
+
+
+def device_status(device=None) -> int:
+    """Sticky status word of the current stream's decode workspace (0 = no device-side wait has
+    timed out since the workspace was created).  Synchronises the stream."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None:
+        return 0
+    return int(buf[:4].view(torch.int32).item())
 
 
 def pack_last_dim(data: torch.Tensor, group_size: int, bits: int):

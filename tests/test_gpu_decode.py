@@ -87,6 +87,16 @@ def test_small_batched(ops, bits, dtype):
     assert rel_l2(out, ref) <= tol, rel_l2(out, ref)
 
 
+@pytest.mark.parametrize("bits", [1, 2, 4])
+@pytest.mark.parametrize("t_vis,t_txt,n_rep", [(256, 0, 4), (1024, 5, 4), (1280, 90, 6), (2304, 200, 8)])
+def test_tensor_core_path_shapes(ops, bits, t_vis, t_txt, n_rep):
+    """Shapes the TMA + MMA fast path takes (fp16, visual span a multiple of 256): single tile,
+    exactly one chunk, ragged last tile/chunk, 4/6/8 query heads per KV head."""
+    out, ref = _run_case(ops, 2, 2 * n_rep, 2, t_vis, t_txt, bits, torch.float16, seed=40 + bits + t_vis)
+    assert rel_l2(out, ref) <= TOL_ATTN, rel_l2(out, ref)
+    assert ops.device_status() == 0
+
+
 def test_n_rep_6(ops):
     """48 q / 8 KV heads (the 20B backbone's grouping)."""
     out, ref = _run_case(ops, 2, 12, 2, 256, 40, 1, torch.float16, seed=9)
