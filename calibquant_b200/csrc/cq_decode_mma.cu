@@ -42,13 +42,13 @@ using namespace ptx;
 constexpr int THREADS = 128;
 constexpr int TILE_G = 32;             // 32-token groups per K tile (1024 tokens)
 constexpr int CHUNK_TOK = 1024;        // tokens per attn.V work item
-constexpr int VT_TOK = 256;            // tokens per V tile
+constexpr int VT_TOK = 512;            // tokens per V tile
 constexpr uint32_t WAIT_TRIES = 1u << 22;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __host__ __device__ constexpr int k1_stages(int bits) { return bits == 1 ? 3 : 2; }
 __host__ __device__ constexpr int k1_stage_bytes(int bits) { return bits * 16384 + 2 * 8192; }
-__host__ __device__ constexpr int k2_stages(int) { return 4; }
+__host__ __device__ constexpr int k2_stages(int bits) { return bits == 4 ? 2 : 3; }
 __host__ __device__ constexpr int k2_stage_bytes(int bits) { return VT_TOK * 16 * bits + 2 * VT_TOK * 8; }
 
 struct Dims {
@@ -342,7 +342,8 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   // dynamic smem: [stages][STAGE_BYTES] | p_s [kMaxRep][CHUNK_TOK] half | red_s [4][kMaxRep][136] float
   __half* p_s = reinterpret_cast<__half*>(smem + STAGES * STAGE_BYTES);
-  float* red_s = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + kMaxRep * CHUNK_TOK * 2);
+  // the cross-warp reduction buffer [4][kMaxRep][136] float reuses the probability buffer
+  float* red_s = reinterpret_cast<float*>(p_s);
   constexpr int RED_STRIDE = 136;           // 128 channels + 4 group biases + 1 sum + pad
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ float m_s[kMaxRep];
@@ -350,7 +351,7 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int n_pairs = dm.batch * dm.hkv;
   const int n_items = n_pairs * dm.n_chunks;
-  const int n_vtiles = dm.t_vis / VT_TOK;
+  const int n_vtiles = (dm.t_vis + VT_TOK - 1) / VT_TOK;
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
@@ -370,10 +371,11 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
       const int s = prod % STAGES;
       unsigned char* base = smem + s * STAGE_BYTES;
       const int64_t tok = (int64_t)pair * dm.t_vis + (int64_t)vt * VT_TOK;
-      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-      bulk_load_1d(base, v_code + tok * WPT, CODE_BYTES, &full_bar[s]);
-      bulk_load_1d(base + CODE_BYTES, v_scale + tok * 4, VT_TOK * 8, &full_bar[s]);
-      bulk_load_1d(base + CODE_BYTES + VT_TOK * 8, v_mn + tok * 4, VT_TOK * 8, &full_bar[s]);
+      const int nt = min(VT_TOK, dm.t_vis - vt * VT_TOK);      // 512, or 256 for a ragged last tile
+      mbar_expect_tx(&full_bar[s], (uint32_t)(nt * (TOK_BYTES + 16)));
+      bulk_load_1d(base, v_code + tok * WPT, (uint32_t)(nt * TOK_BYTES), &full_bar[s]);
+      bulk_load_1d(base + CODE_BYTES, v_scale + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
+      bulk_load_1d(base + CODE_BYTES + VT_TOK * 8, v_mn + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
       ++prod; ++p_ti;
       return true;
     }
@@ -490,9 +492,11 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
       const uint32_t vs_b = code_b + CODE_BYTES, vmn_b = vs_b + VT_TOK * 8;
       const uint32_t p_b = smem_u32(p_s) + (uint32_t)((g < dm.n_rep ? g : 0) * CHUNK_TOK + ti * VT_TOK) * 2u;
 
+      const int nt_tile = min(VT_TOK, dm.t_vis - vt * VT_TOK);
 #pragma unroll 1
-      for (int kq = 0; kq < 4; ++kq) {
-        const int t0 = warp * 64 + kq * 16 + 2 * c;       // token (in tile) of the lane's first k pair
+      for (int kq = 0; kq < VT_TOK / 64; ++kq) {
+        if (warp * (VT_TOK / 4) + kq * 16 >= nt_tile) break;
+        const int t0 = warp * (VT_TOK / 4) + kq * 16 + 2 * c;   // token (in tile) of the lane's first k pair
         uint32_t pp0 = lds32(p_b + (uint32_t)t0 * 2u), pp1 = lds32(p_b + (uint32_t)(t0 + 8) * 2u);
         if (g >= dm.n_rep) { pp0 = 0u; pp1 = 0u; }
         // scales of tokens (t0, t0+1) and (t0+8, t0+9): 4 halves per token
@@ -738,7 +742,7 @@ static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned
   auto k1 = k1_scores<BITS>;
   auto k2 = k2_attn_v<BITS>;
   const int smem1 = k1_stages(BITS) * k1_stage_bytes(BITS) + 1024;
-  const int smem2 = k2_stages(BITS) * k2_stage_bytes(BITS) + kMaxRep * CHUNK_TOK * 2 + 4 * kMaxRep * 136 * 4 + 1024;
+  const int smem2 = k2_stages(BITS) * k2_stage_bytes(BITS) + 4 * kMaxRep * 136 * 4 + 1024;
   static bool configured_dev[64] = {};   // per template instance and device
   static int occ1_dev[64], occ2_dev[64];
   int dev = 0;
