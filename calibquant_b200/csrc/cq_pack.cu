@@ -16,11 +16,22 @@ __device__ __forceinline__ void group_params(float mn, float mx, int levels, flo
   scale = rnd<T>(__fdiv_rn(r, (float)levels));
 }
 
+// Quotient d/scale for the code decision.  `rcp` is the correctly rounded 1/scale (computed once
+// per group); one residual correction makes q faithful to well under one fp32 ulp.  That is
+// enough for bit-exact codes: d and scale carry at most 11 significant bits, so the exact
+// quotient is never closer than two fp32 ulps to any value at which rint(clamp(fp16(q))) changes
+// (those break points are odd 12-bit multiples of a half fp16 ulp), hence q, the IEEE quotient and
+// the exact quotient always fall on the same side of every break point.
+__device__ __forceinline__ float quotient(float d, float scale, float rcp) {
+  const float q = d * rcp;
+  return fmaf(fmaf(-scale, q, d), rcp, q);
+}
+
 template <typename T>
-__device__ __forceinline__ unsigned quantize_one(float x, float mn, float scale, int levels) {
+__device__ __forceinline__ unsigned quantize_one(float x, float mn, float scale, float rcp, int levels) {
   float d = rnd<T>(x - mn);
-  float y = rnd<T>(__fdiv_rn(d, scale));
-  y = fminf(fmaxf(y, 0.f), (float)levels);
+  float y = rnd<T>(quotient(d, scale, rcp));
+  y = fminf(fmaxf(y, 0.f), (float)levels);   // fmaxf drops the NaN of inf*0 (infinite scale) to 0
   return (unsigned)__float2int_rn(y);
 }
 
@@ -59,8 +70,9 @@ pack_last_dim_kernel(const T* __restrict__ data, int64_t n_chunks, int32_t* __re
   group_params<T>(mn, mx, LEVELS, scale);
   unsigned local = 0;
   if (mx != mn) {
+    const float rcp = __frcp_rn(scale);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) local |= quantize_one<T>(x[i], mn, scale, LEVELS) << (i * BITS);
+    for (int i = 0; i < 8; ++i) local |= quantize_one<T>(x[i], mn, scale, rcp, LEVELS) << (i * BITS);
   }
   // BITS*8 bits per thread; 32/(BITS*8) threads make one word.
   constexpr int THREADS_PER_WORD = 4 / BITS;   // 4, 2, 1
@@ -134,13 +146,14 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
     group_params<T>(mn, mx, LEVELS, scale);
     const int64_t row = (int64_t)bh * kHeadDim + cp * 2 + c;
     const bool constant = (mx == mn);
+    const float rcp = __frcp_rn(scale);
 #pragma unroll
     for (int w = 0; w < WORDS_PER_GROUP; ++w) {
       unsigned word = 0;
       if (!constant) {
 #pragma unroll
         for (int i = 0; i < FPI; ++i)
-          word |= quantize_one<T>(x[w * FPI + i], mn, scale, LEVELS) << (i * BITS);
+          word |= quantize_one<T>(x[w * FPI + i], mn, scale, rcp, LEVELS) << (i * BITS);
       }
       code[row * (n_groups * WORDS_PER_GROUP) + G * WORDS_PER_GROUP + w] = (int32_t)word;
     }

@@ -116,3 +116,28 @@ def test_full_size_properties(ops, bits):
     b = ops.pack_last_dim(sub.transpose(2, 3).contiguous(), 32, bits)
     for u, w in zip(a, b):
         assert bits_equal(u, w)
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4])
+def test_rounding_break_points(ops, bits):
+    """Adversarial groups: for every fp16 mantissa of the group range (three binades) the
+    elements are the fp16 neighbours of each decision threshold (k + 0.5) * scale, i.e. exactly the
+    inputs where an inexact quotient would flip a code."""
+    levels = 2 ** bits - 1
+    mant = torch.arange(1024, dtype=torch.float32)
+    groups = []
+    for exp in (-3, 0, 5):
+        rng = ((1 + mant / 1024) * 2.0 ** exp).half()                 # group max (min is 0)
+        scale = (rng / levels).float()                                 # what the kernel will derive
+        for k in range(levels):
+            thr = ((k + 0.5) * scale).half()
+            bits16 = thr.view(torch.int16).to(torch.int32)
+            cand = torch.stack([(bits16 + o).to(torch.int16).view(torch.float16) for o in range(-15, 15)], dim=1)
+            cand = torch.minimum(cand, rng[:, None])                   # stay inside [0, max]
+            cand = torch.maximum(cand, torch.zeros_like(cand))
+            g = torch.cat([torch.zeros(1024, 1, dtype=torch.float16), rng[:, None], cand], dim=1)
+            groups.append(g)                                           # [1024, 32]
+    x = torch.cat(groups, dim=0).reshape(1, 1, -1, 32).contiguous()
+    _check(ops.pack_last_dim(x.cuda(), 32, bits), gf.quantize_and_pack_last_dim(x, 32, bits))
+    xb = x.to(torch.bfloat16)
+    _check(ops.pack_last_dim(xb.cuda(), 32, bits), gf.quantize_and_pack_last_dim(xb, 32, bits))
