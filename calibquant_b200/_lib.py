@@ -57,6 +57,9 @@ SIGNATURES = {
     "cq_qbmm_static_capacity_bytes": (_sz, []),
     "cq_qbmm_static": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _i64, _i64,
                                   _c.c_int, _c.c_int, _c.c_int, _vp]),
+    "cq_prefill_attn": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                   _c.POINTER(_i64), _c.POINTER(_i64), _c.POINTER(_i64), _c.POINTER(_i64),
+                                   _c.c_int, _vp]),
     "cq_decode_attn_workspace_bytes": (_sz, [_c.POINTER(DecodeArgs)]),
     "cq_decode_attn": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _sz, _vp]),
 }

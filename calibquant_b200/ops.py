@@ -194,3 +194,27 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
         rc = lib().cq_decode_attn(ctypes.byref(a), _ptr(ws), ws.numel(), _stream())
     check(rc, "cq_decode_attn")
     return out.reshape(shape)
+
+
+def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out=None) -> torch.Tensor:
+    """Causal attention over unquantized K/V in the flash_attn layout.
+
+    q [B,T,Hq,D], k/v [B,T,Hkv,D] (any batch/token/head strides that are multiples of 8 elements,
+    channels contiguous) -> o [B,T,Hq,D] in q.dtype.
+    """
+    _need_cuda(q, k, v)
+    B, T, Hq, D = q.shape
+    Hkv = k.shape[2]
+
+    def ok(t):
+        return t.stride(3) == 1 and all(s % 8 == 0 for s in t.stride()[:3]) and t.data_ptr() % 16 == 0
+
+    q, k, v = (t if ok(t) else t.contiguous() for t in (q, k, v))
+    if out is None:
+        out = torch.empty((B, T, Hq, D), dtype=q.dtype, device=q.device)
+    arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    with torch.cuda.device(q.device):
+        rc = lib().cq_prefill_attn(_ptr(q), _ptr(k), _ptr(v), _ptr(out), B, T, Hq, Hkv, D,
+                                   arr(q), arr(k), arr(v), arr(out), _dtype_enum(q), _stream())
+    check(rc, "cq_prefill_attn")
+    return out

@@ -156,6 +156,21 @@ size_t cq_decode_attn_workspace_bytes(const cq_decode_args* args);
 int cq_decode_attn(const cq_decode_args* args, void* workspace, size_t workspace_bytes,
                    void* stream);
 
+/*
+ * Dense causal prefill attention over unquantized K/V with GQA head sharing.
+ * Replaces the flash_attn calls of the reference prefill: patch_internvl.py:464-468
+ * (self._flash_attention_forward in 1024-query chunks against the growing prefix) and :606-609
+ * (transformers' _flash_attention_forward); chunking is not needed, the kernel is causal over
+ * the whole sequence and needs no workspace.
+ *   q, out : element (b,t,h,d) at base + b*strides[0] + t*strides[1] + h*strides[2] + d
+ *   k, v   : same addressing with n_kv_heads heads; strides in elements, multiples of 8
+ *   o = softmax(q k^T / sqrt(head_dim) + causal mask) v, fp32 accumulation, head_dim == 128.
+ */
+int cq_prefill_attn(const void* q, const void* k, const void* v, void* out, int batch, int t_len,
+                    int n_q_heads, int n_kv_heads, int head_dim, const int64_t* q_strides,
+                    const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
+                    int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
