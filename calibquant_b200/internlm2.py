@@ -1,0 +1,197 @@
+"""HF-free InternLM2 backbone (the language model of InternVL2.5) for running the patched
+attention forward without downloading anything.
+
+Only what the quantized-KV attention path touches is modelled faithfully: the fused ``wqkv``
+projection with its per-KV-head ``(n_rep q heads, k, v)`` output layout, rotary embeddings with
+``rotary_emb(x, seq_len) -> (cos, sin)``, the attribute names the patched forward reads
+(``num_heads, num_key_value_groups, head_dim, hidden_size, wo, is_causal, config``) and the
+decoder-layer call signature.  Everything around it (RMSNorm, SwiGLU, embeddings, greedy loop) is
+plain PyTorch: the reference leaves those to the third-party model code as well.
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import torch
+from torch import nn
+
+
+@dataclass
+class InternLM2Config:
+    hidden_size: int = 4096
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 8
+    intermediate_size: int = 14336
+    num_hidden_layers: int = 32
+    vocab_size: int = 92544
+    rope_theta: float = 1e6
+    rms_norm_eps: float = 1e-5
+    max_position_embeddings: int = 32768
+
+    @property
+    def head_dim(self):
+        return self.hidden_size // self.num_attention_heads
+
+
+INTERNLM2_5_7B = InternLM2Config()
+INTERNLM2_20B = InternLM2Config(hidden_size=6144, num_attention_heads=48, num_key_value_heads=8,
+                                intermediate_size=16384, num_hidden_layers=48)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim, eps):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.eps = eps
+
+    def forward(self, x):
+        v = x.float()
+        v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)
+        return self.weight * v.to(x.dtype)
+
+
+class RotaryEmbedding(nn.Module):
+    """cos/sin tables [seq_len, head_dim] in the dtype of ``x`` (non-interleaved halves)."""
+
+    def __init__(self, dim, base):
+        super().__init__()
+        self.dim, self.base = dim, base
+        self._cache = {}
+
+    def forward(self, x, seq_len):
+        key = (x.device, x.dtype)
+        cached = self._cache.get(key)
+        if cached is None or cached[0].shape[0] < seq_len:
+            n = max(seq_len, 4096)
+            inv = 1.0 / (self.base ** (torch.arange(0, self.dim, 2, device=x.device, dtype=torch.float32) / self.dim))
+            t = torch.arange(n, device=x.device, dtype=torch.float32)
+            emb = torch.cat([torch.outer(t, inv)] * 2, dim=-1)
+            cached = (emb.cos().to(x.dtype), emb.sin().to(x.dtype))
+            self._cache[key] = cached
+        return cached[0][:seq_len], cached[1][:seq_len]
+
+
+class InternLM2Attention(nn.Module):
+    def __init__(self, config: InternLM2Config):
+        super().__init__()
+        self.config = config
+        self.hidden_size = config.hidden_size
+        self.num_heads = config.num_attention_heads
+        self.head_dim = config.head_dim
+        self.num_key_value_heads = config.num_key_value_heads
+        self.num_key_value_groups = self.num_heads // self.num_key_value_heads
+        self.is_causal = True
+        self.wqkv = nn.Linear(self.hidden_size, (self.num_heads + 2 * self.num_key_value_heads) * self.head_dim,
+                              bias=False)
+        self.wo = nn.Linear(self.num_heads * self.head_dim, self.hidden_size, bias=False)
+        self.rotary_emb = RotaryEmbedding(self.head_dim, config.rope_theta)
+
+    def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None,
+                output_attentions=False, use_cache=False, **kwargs):
+        raise RuntimeError("InternLM2Attention.forward is provided by calibquant_b200.patch_internvl.patch_model")
+
+
+class InternLM2MLP(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.w1 = nn.Linear(config.hidden_size, config.intermediate_size, bias=False)
+        self.w3 = nn.Linear(config.hidden_size, config.intermediate_size, bias=False)
+        self.w2 = nn.Linear(config.intermediate_size, config.hidden_size, bias=False)
+
+    def forward(self, x):
+        return self.w2(nn.functional.silu(self.w1(x)) * self.w3(x))
+
+
+class InternLM2DecoderLayer(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.attention = InternLM2Attention(config)
+        self.feed_forward = InternLM2MLP(config)
+        self.attention_norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+        self.ffn_norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+
+    def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None,
+                use_cache=True):
+        h, _, present = self.attention(self.attention_norm(hidden_states), attention_mask=attention_mask,
+                                       position_ids=position_ids, past_key_value=past_key_value,
+                                       output_attentions=False, use_cache=use_cache)
+        hidden_states = hidden_states + h
+        hidden_states = hidden_states + self.feed_forward(self.ffn_norm(hidden_states))
+        return hidden_states, present
+
+
+class InternLM2Model(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.tok_embeddings = nn.Embedding(config.vocab_size, config.hidden_size)
+        self.layers = nn.ModuleList([InternLM2DecoderLayer(config) for _ in range(config.num_hidden_layers)])
+        self.norm = RMSNorm(config.hidden_size, config.rms_norm_eps)
+
+
+class InternLM2ForCausalLM(nn.Module):
+    """``language_model`` of the chat model: ``.model.layers[i].attention`` as in HF."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.model = InternLM2Model(config)
+        self.output = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+
+    def get_input_embeddings(self):
+        return self.model.tok_embeddings
+
+    @torch.no_grad()
+    def forward_step(self, inputs_embeds, position_ids, past_key_values):
+        h = inputs_embeds
+        presents = []
+        for i, layer in enumerate(self.model.layers):
+            h, present = layer(h, position_ids=position_ids,
+                               past_key_value=None if past_key_values is None else past_key_values[i])
+            presents.append(present)
+        h = self.model.norm(h[:, -1:])
+        return self.output(h), presents
+
+    @torch.no_grad()
+    def generate(self, inputs_embeds, max_new_tokens, **_):
+        """Greedy decoding from embeddings: one prefill pass, then one token per step."""
+        B, T, _ = inputs_embeds.shape
+        pos = torch.arange(T, device=inputs_embeds.device).unsqueeze(0).expand(B, T)
+        logits, past = self.forward_step(inputs_embeds, pos, None)
+        tokens = []
+        for step in range(max_new_tokens):
+            nxt = logits[:, -1].argmax(-1)
+            tokens.append(nxt)
+            if step == max_new_tokens - 1:
+                break
+            emb = self.model.tok_embeddings(nxt).unsqueeze(1)
+            pos = torch.full((B, 1), T + step, device=emb.device, dtype=torch.long)
+            logits, past = self.forward_step(emb, pos, past)
+        return torch.stack(tokens, dim=1)
+
+
+class ChatModelShell(nn.Module):
+    """Minimal stand-in for InternVLChatModel: holds ``language_model`` and ``config.llm_config``
+    so that ``patch_model`` can be applied exactly as to the real model."""
+
+    def __init__(self, config: InternLM2Config):
+        super().__init__()
+        self.language_model = InternLM2ForCausalLM(config)
+        self.config = type("Cfg", (), {})()
+        self.config.llm_config = self.language_model.model.layers[0].attention.config
+        self.img_context_token_id = None
+
+    def generate(self, inputs_embeds, image_token_num, max_new_tokens):
+        os.environ["IMAGE_TOKEN_NUM"] = str(int(image_token_num))
+        return self.language_model.generate(inputs_embeds, max_new_tokens)
+
+
+def init_weights_(module: nn.Module, seed: int, std: float = 0.02):
+    """Seeded N(0, std) init of every matrix (norm weights stay 1), as the synthetic benchmarks use."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    with torch.no_grad():
+        for p in module.parameters():
+            if p.dim() >= 2:
+                p.copy_((torch.randn(p.shape, generator=g, dtype=torch.float32) * std).to(p.dtype))

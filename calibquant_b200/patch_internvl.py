@@ -1,0 +1,306 @@
+"""Drop-in for the reference module ``patch_internvl.py``: the model patch and the two patched
+InternLM2 attention forwards, running on the calibquant_b200 CUDA kernels.
+
+Kept from the reference (names, arguments, return values):
+``patch_model(model, quant_method, **kwargs)`` (``patch_internvl.py:645-660``),
+``ATTN_FORWARD_FUNCTIONS`` with keys ``"calibquant"`` and ``"qjl"`` (``:639-642``),
+``custom_generate`` (``:35-93``), ``repeat_kv`` (``:97-106``), ``rotate_half`` /
+``apply_rotary_pos_emb`` (``:110-138``), the module globals ``BITS_KV, SCALE_K, SCALE_V, LOW_BITS,
+SPROMPT_LEN, CHUNK_SIZE`` (``:20-31``) and the ``IMAGE_TOKEN_NUM`` environment side channel
+(``:78, :189``).
+
+What changes underneath:
+* the visual span of the KV cache is held in the group format (K per channel, V per token,
+  32-element groups, ``BITS_KV`` bits) written by one pack kernel each;
+* a decode step is ONE call (``ops.decode_attention``) covering scores with post-scaling, logit
+  calibration, softmax, packed attn.V and the fp16 system/text segments -- no ``repeat_kv`` copies,
+  no transposes, no per-step ``torch.cat`` of the text cache (it lives in a pre-allocated buffer);
+* prefill attention is ``ops.prefill_attention`` (causal over the whole sequence, no chunk loop).
+"""
+
+from __future__ import annotations
+
+import math
+import os
+import warnings
+from typing import Optional, Tuple
+
+import torch
+
+from . import ops
+from .qjl.matmul import cuda_quantized_bmm_dynamic
+from .qjl.new_pack import triton_quantize_and_pack_along_last_dim
+from .qjl.qjl_utils import QJLKeyQuantizer, repeat_kv_quant
+
+# global hyperparameters for quantization (same names and defaults as the reference)
+BITS_KV = 1
+
+if BITS_KV == 1:
+    SCALE_V = 0.3
+    SCALE_K = 0.5
+else:
+    SCALE_V = 1
+    SCALE_K = 1
+
+LOW_BITS = True
+SPROMPT_LEN = 41
+CHUNK_SIZE = 1024      # kept for compatibility; the prefill kernel needs no chunking
+GROUP_SIZE = 32
+TEXT_CAPACITY_STEP = 256   # growth step of the pre-allocated system+text cache
+
+
+@torch.no_grad()
+def custom_generate(self, pixel_values=None, input_ids=None, attention_mask=None, visual_features=None,
+                    generation_config=None, output_hidden_states=None, **generate_kwargs):
+    """``InternVLChatModel.generate`` replacement (``patch_internvl.py:35-93``): embeds the prompt,
+    scatters the ViT features over the image-context tokens, publishes ``IMAGE_TOKEN_NUM`` and
+    calls the language model's ``generate`` with ``inputs_embeds``."""
+    assert self.img_context_token_id is not None
+    if pixel_values is not None:
+        if visual_features is not None:
+            vit_embeds = visual_features
+        else:
+            chunks = [self.extract_feature(pixel_values[i:i + 10]) for i in range(0, pixel_values.size(0), 10)]
+            vit_embeds = torch.cat(chunks, dim=0)
+        input_embeds = self.language_model.get_input_embeddings()(input_ids)
+        B, N, C = input_embeds.shape
+        input_embeds = input_embeds.reshape(B * N, C)
+        selected = input_ids.reshape(B * N) == self.img_context_token_id
+        assert selected.sum() != 0
+        input_embeds[selected] = vit_embeds.reshape(-1, C).to(input_embeds.device)
+        os.environ["IMAGE_TOKEN_NUM"] = str(int(vit_embeds.shape[0] * vit_embeds.shape[1] / B))
+        input_embeds = input_embeds.reshape(B, N, C)
+    else:
+        input_embeds = self.language_model.get_input_embeddings()(input_ids)
+    return self.language_model.generate(inputs_embeds=input_embeds, attention_mask=attention_mask,
+                                        generation_config=generation_config,
+                                        output_hidden_states=output_hidden_states, use_cache=True,
+                                        **generate_kwargs)
+
+
+def repeat_kv(hidden_states: torch.Tensor, n_rep: int) -> torch.Tensor:
+    """[B,Hkv,S,D] -> [B,Hkv*n_rep,S,D]; kept for callers, the kernels never need it."""
+    batch, num_key_value_heads, slen, head_dim = hidden_states.shape
+    if n_rep == 1:
+        return hidden_states
+    hidden_states = hidden_states[:, :, None, :, :].expand(batch, num_key_value_heads, n_rep, slen, head_dim)
+    return hidden_states.reshape(batch, num_key_value_heads * n_rep, slen, head_dim)
+
+
+def rotate_half(x):
+    half = x.shape[-1] // 2
+    return torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+
+
+def apply_rotary_pos_emb(q, k, cos, sin, position_ids, unsqueeze_dim=1):
+    """Non-interleaved RoPE on q [B,Hq,q,D] and k [B,Hkv,q,D]; cos/sin are [seq, D] tables."""
+    cos = cos[position_ids].unsqueeze(unsqueeze_dim)
+    sin = sin[position_ids].unsqueeze(unsqueeze_dim)
+    # same two rounded steps as the reference: copy.mul_(cos) then addcmul_(rotate_half(x), sin)
+    return torch.addcmul(q * cos, rotate_half(q), sin), torch.addcmul(k * cos, rotate_half(k), sin)
+
+
+class _dummy_class_for_accessing_shape:
+    def __init__(self, kv_seq_len):
+        self.shape = (-1, -1, kv_seq_len, -1)
+
+
+class _TextCache:
+    """System + text K/V of one layer in pre-allocated [B,Hkv,capacity,D] buffers.  ``views()``
+    returns ``[B,Hkv,length,D]`` slices (token rows contiguous), so appending a token is one small
+    copy instead of the reference's ``torch.cat`` of the whole cache (``patch_internvl.py:265-266``)."""
+
+    def __init__(self, k, v):
+        B, H, T, D = k.shape
+        cap = T + TEXT_CAPACITY_STEP
+        self.k = torch.empty((B, H, cap, D), dtype=k.dtype, device=k.device)
+        self.v = torch.empty_like(self.k)
+        self.k[:, :, :T] = k
+        self.v[:, :, :T] = v
+        self.length = T
+
+    def append(self, k, v):
+        n = k.shape[2]
+        if self.length + n > self.k.shape[2]:
+            grow = max(TEXT_CAPACITY_STEP, n)
+            pad = torch.empty((*self.k.shape[:2], grow, self.k.shape[3]), dtype=self.k.dtype, device=self.k.device)
+            self.k = torch.cat([self.k, pad], dim=2)
+            self.v = torch.cat([self.v, pad.clone()], dim=2)
+        self.k[:, :, self.length:self.length + n] = k
+        self.v[:, :, self.length:self.length + n] = v
+        self.length += n
+
+    def views(self):
+        return self.k[:, :, :self.length], self.v[:, :, :self.length]
+
+
+def _split_qkv(self, hidden_states):
+    """``wqkv`` output -> q [B,q,Hq,D], k [B,q,Hkv,D], v [B,q,Hkv,D] as strided views (no copies):
+    per KV head the projection emits n_rep query heads, then k, then v (``patch_internvl.py:219-234``)."""
+    bsz, q_len, _ = hidden_states.size()
+    qkv = self.wqkv(hidden_states).view(bsz, q_len, -1, 2 + self.num_key_value_groups, self.head_dim)
+    q = qkv[..., : self.num_key_value_groups, :].reshape(bsz, q_len, -1, self.head_dim)
+    return q, qkv[..., -2, :], qkv[..., -1, :]
+
+
+def _image_token_num():
+    return int(os.environ.get("IMAGE_TOKEN_NUM"))
+
+
+def _pop_padding_mask(kwargs, attention_mask):
+    if "padding_mask" in kwargs:
+        warnings.warn("Passing `padding_mask` is deprecated and will be removed in v4.37. "
+                      "Please make sure use `attention_mask` instead.`")
+        attention_mask = kwargs.pop("padding_mask")
+    return attention_mask
+
+
+def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
+                                 attention_mask: Optional[torch.LongTensor] = None,
+                                 position_ids: Optional[torch.LongTensor] = None,
+                                 past_key_value: Optional[Tuple[torch.Tensor]] = None,
+                                 output_attentions: bool = False, use_cache: bool = False, **kwargs):
+    """Patched ``InternLM2FlashAttention2.forward`` (``patch_internvl.py:141-484``).
+
+    Prefill (q_len > 1): RoPE, quantize the visual span ``[SPROMPT_LEN, SPROMPT_LEN+IMAGE_TOKEN_NUM)``
+    of K (per channel) and V (per token) at ``BITS_KV`` bits, keep system+text K/V in fp, run causal
+    attention over the unquantized K/V.  Decode (q_len == 1): one fused attention call over
+    [system | quantized visual | text] with logit calibration when ``BITS_KV <= 2``.
+    Returns ``(attn_output, None, past_key_value)``; ``past_key_value`` is the legacy
+    ``(K_fp, V_fp)`` tuple of system+text tokens and the quantized state lives on the module, as in
+    the reference.
+    """
+    self.sprompt_len = SPROMPT_LEN
+    self.image_token_num = _image_token_num()
+    self.normalize = BITS_KV <= 2
+    attention_mask = _pop_padding_mask(kwargs, attention_mask)
+    bsz, q_len, _ = hidden_states.size()
+
+    q, k, v = _split_qkv(self, hidden_states)
+    q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)          # [B,H,q,D] views
+    kv_seq_len = q_len
+    if past_key_value is not None:
+        kv_seq_len += past_key_value[0].shape[-2] + (self.image_token_num if LOW_BITS else 0)
+    cos, sin = self.rotary_emb(v, seq_len=kv_seq_len)
+    q, k = apply_rotary_pos_emb(q, k, cos, sin, position_ids)
+
+    if q_len > 1:
+        if past_key_value is not None:
+            raise NotImplementedError("chunked prefill on top of an existing cache is not supported")
+        s0, s1 = self.sprompt_len, self.sprompt_len + self.image_token_num
+        if LOW_BITS:
+            if self.image_token_num % GROUP_SIZE:
+                raise ValueError(f"IMAGE_TOKEN_NUM must be a multiple of {GROUP_SIZE}, got {self.image_token_num}")
+            self.k_pack = ops.pack_k_per_channel(k[:, :, s0:s1], GROUP_SIZE, BITS_KV)
+            self.v_pack = ops.pack_last_dim(v[:, :, s0:s1].contiguous(), GROUP_SIZE, BITS_KV)
+            self._text_cache = _TextCache(torch.cat([k[:, :, :s0], k[:, :, s1:]], dim=2),
+                                          torch.cat([v[:, :, :s0], v[:, :, s1:]], dim=2))
+        else:
+            self.k_pack = self.v_pack = None
+            self._text_cache = _TextCache(k, v)
+        past_key_value = self._text_cache.views() if use_cache else None
+        attn = ops.prefill_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+        attn_output = self.wo(attn.reshape(bsz, q_len, self.hidden_size))
+        return attn_output, None, past_key_value
+
+    # ---- decode step -------------------------------------------------------------------------
+    self._text_cache.append(k, v)
+    k_fp, v_fp = self._text_cache.views()
+    past_key_value = (k_fp, v_fp) if use_cache else None
+    if attention_mask is not None and attention_mask.size() != (bsz, 1, q_len, kv_seq_len):
+        raise ValueError(f"Attention mask should be of size {(bsz, 1, q_len, kv_seq_len)}, "
+                         f"but is {attention_mask.size()}")
+    t_sys = self.sprompt_len if LOW_BITS else 0
+    attn = ops.decode_attention(q, self.k_pack, self.v_pack, k_fp, v_fp, t_sys, BITS_KV,
+                                group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
+                                mask=attention_mask)                             # [B,Hq,1,D]
+    if attn.size() != (bsz, self.num_heads, q_len, self.head_dim):
+        raise ValueError(f"`attn_output` should be of size {(bsz, self.num_heads, q_len, self.head_dim)}, "
+                         f"but is {attn.size()}")
+    attn_output = self.wo(attn.transpose(1, 2).reshape(bsz, q_len, self.hidden_size))
+    return attn_output, None, past_key_value
+
+
+def forward_internlm2_qjl(self, hidden_states: torch.Tensor,
+                          attention_mask: Optional[torch.LongTensor] = None,
+                          position_ids: Optional[torch.LongTensor] = None,
+                          past_key_value: Optional[Tuple[torch.Tensor]] = None,
+                          output_attentions: bool = False, use_cache: bool = False, **kwargs):
+    """Patched forward with the reference's ``qjl`` structure (``patch_internvl.py:492-636``): the
+    state travels in the 9-tuple ``(shape, kv_quant, K_sys, K_txt, V_code, V_scale, V_mn, V_sys,
+    V_txt)``; values use ``triton_quantize_and_pack_along_last_dim`` + ``cuda_quantized_bmm_dynamic``
+    and keys a ``QJLKeyQuantizer``-shaped object (here backed by per-channel group quantization
+    instead of a JL sketch).  No logit calibration, as in the reference's qjl forward.
+    """
+    self.sprompt_len = SPROMPT_LEN
+    self.image_token_num = _image_token_num()
+    attention_mask = _pop_padding_mask(kwargs, attention_mask)
+    bsz, q_len, _ = hidden_states.size()
+    cfg = self.config
+    q, k, v = _split_qkv(self, hidden_states)
+    q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    kv_seq_len = q_len + (past_key_value[0].shape[-2] if past_key_value is not None else 0)
+    cos, sin = self.rotary_emb(v, seq_len=kv_seq_len)
+    q, k = apply_rotary_pos_emb(q, k, cos, sin, position_ids)
+    n_rep = self.num_key_value_groups
+
+    if past_key_value is not None:
+        (_, kv_quant, k_sys, k_txt, v_code, v_scale, v_mn, v_sys, v_txt) = past_key_value
+        k_txt = torch.cat([k_txt, k], dim=2)
+        v_txt = torch.cat([v_txt, v], dim=2)
+        att_sys = q @ repeat_kv(k_sys, n_rep).transpose(2, 3)
+        att_txt = q @ repeat_kv(k_txt, n_rep).transpose(2, 3)
+        att = torch.cat((att_sys, kv_quant.attention_score(q), att_txt), dim=-1) / self.head_dim ** 0.5
+        if attention_mask is not None:
+            if attention_mask.size() != (bsz, 1, q_len, kv_seq_len):
+                raise ValueError(f"Attention mask should be of size {(bsz, 1, q_len, kv_seq_len)}, "
+                                 f"but is {attention_mask.size()}")
+            att = torch.max(att + attention_mask, torch.tensor(torch.finfo(att.dtype).min, device=att.device))
+        att = torch.softmax(att, dim=-1, dtype=torch.float32).to(q.dtype)
+        s0, s1 = self.sprompt_len, self.sprompt_len + self.image_token_num
+        out = cuda_quantized_bmm_dynamic(cfg.group_size, att[:, :, :, s0:s1].contiguous(),
+                                         v_code, v_scale, v_mn, cfg.v_bits)
+        out = out + (att[..., s1:] @ repeat_kv(v_txt, n_rep) + att[..., :s0] @ repeat_kv(v_sys, n_rep))
+        attn_output = out.transpose(1, 2)
+    else:
+        attn_output = ops.prefill_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+        sizes = [self.sprompt_len, self.image_token_num, q_len - self.sprompt_len - self.image_token_num]
+        k_sys, k_vis, k_txt = k.split(sizes, dim=-2)
+        v_sys, v_vis, v_txt = v.split(sizes, dim=-2)
+        kv_quant = QJLKeyQuantizer(getattr(cfg, "qjl", None), cfg.outlier_count_general, cfg.buffer_size,
+                                   cfg.group_size, cfg.k_bits)
+        kv_quant.build_sketch(k_vis)
+        if v.shape[-2] <= cfg.buffer_size:
+            raise NotImplementedError("value_states.shape[-2] <= self.config.buffer_size")
+        v_code, v_scale, v_mn = triton_quantize_and_pack_along_last_dim(v_vis.contiguous(), cfg.group_size,
+                                                                        cfg.v_bits)
+        k_sys, k_txt, v_sys, v_txt = (t.contiguous() for t in (k_sys, k_txt, v_sys, v_txt))
+    past_key_value = (_dummy_class_for_accessing_shape(kv_seq_len), kv_quant, k_sys, k_txt,
+                      v_code, v_scale, v_mn, v_sys, v_txt) if use_cache else None
+    attn_output = self.wo(attn_output.reshape(bsz, q_len, self.hidden_size))
+    return attn_output, None, past_key_value
+
+
+ATTN_FORWARD_FUNCTIONS = {
+    "calibquant": forward_internlm2_calibquant,
+    "qjl": forward_internlm2_qjl,
+}
+
+
+def patch_model(model, quant_method="calibquant", **kwargs):
+    """Swap the chat model's ``generate`` and the attention class's ``forward`` in place, exactly
+    as ``patch_internvl.py:645-660``; the ``qjl`` settings land on ``model.config.llm_config``."""
+    print("Patching InternVLChatModel.generate function ...")
+    if hasattr(model, "extract_feature"):
+        model.__class__.generate = custom_generate
+    print(f"Patching InternLM2FlashAttention2.forward function ... {quant_method}")
+    model.language_model.model.layers[0].attention.__class__.forward = ATTN_FORWARD_FUNCTIONS[quant_method]
+    if quant_method == "qjl":
+        cfg = model.config.llm_config
+        cfg.k_bits = kwargs.get("k_bits", 2)
+        cfg.v_bits = kwargs.get("v_bits", 2)
+        cfg.group_size = kwargs.get("group_size", 32)
+        cfg.buffer_size = kwargs.get("buffer_size", 128)
+        cfg.outlier_count_general = kwargs.get("outlier_count_general", 32)
+        cfg.qjl = None      # the JL sketch of the reference's baseline is not part of this path
+    return model

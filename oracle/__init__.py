@@ -22,4 +22,4 @@ on CPU and are "parity unpinned" by the reference itself:
   library, ``patch_internvl.py:464-468``); it is plain fp32 softmax attention.
 """
 
-from . import generator, group_format, calibquant_format, prefill  # noqa: F401
+from . import generator, group_format, calibquant_format, prefill, forward  # noqa: F401
