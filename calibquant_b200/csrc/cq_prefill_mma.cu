@@ -240,6 +240,33 @@ int launch(const Args& a, cudaStream_t st) {
 }  // namespace prefill
 }  // namespace cq
 
+namespace cq {
+bool prefill_tc_eligible(const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os);
+int prefill_tc_run(const void* q, const void* k, const void* v, void* out, int batch, int t_len, int hq, int hkv,
+                   const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, int is_bf16,
+                   int* status, cudaStream_t st);
+
+// Sticky status of the tcgen05 prefill kernel (it has no workspace to report into).
+static __device__ int g_prefill_status;
+static int* prefill_status_ptr() {
+  static int* cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_prefill_status) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<int*>(p);
+  }
+  return cached[dev];
+}
+}  // namespace cq
+
+extern "C" int cq_prefill_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, cq::g_prefill_status, sizeof(int)) != cudaSuccess) return CQ_ERR_LAUNCH;
+  return v;
+}
+
 extern "C" int cq_prefill_attn(const void* q, const void* k, const void* v, void* out, int batch, int t_len,
                                int n_q_heads, int n_kv_heads, int head_dim, const int64_t* q_strides,
                                const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
@@ -257,6 +284,13 @@ extern "C" int cq_prefill_attn(const void* q, const void* k, const void* v, void
   for (const int64_t* s : strides)
     for (int i = 0; i < 3; ++i)
       if (s[i] % 8) return CQ_ERR_BAD_ARG;
+  if (cq::prefill_tc_eligible(q_strides, k_strides, v_strides, o_strides)) {
+    int* status = cq::prefill_status_ptr();
+    if (status)
+      return cq::prefill_tc_run(q, k, v, out, batch, t_len, n_q_heads, n_kv_heads, q_strides, k_strides,
+                                v_strides, o_strides, dtype == CQ_DTYPE_BF16, status,
+                                static_cast<cudaStream_t>(stream));
+  }
   cq::prefill::Args a;
   a.q = q; a.k = k; a.v = v; a.out = out;
   a.batch = batch; a.t_len = t_len; a.hq = n_q_heads; a.hkv = n_kv_heads;

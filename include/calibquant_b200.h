@@ -171,6 +171,13 @@ int cq_prefill_attn(const void* q, const void* k, const void* v, void* out, int 
                     const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
                     int dtype, void* stream);
 
+/*
+ * Sticky device status of the prefill kernel (no reference counterpart: the reference checks no
+ * CUDA errors).  0, or CQ_ERR_TIMEOUT if one of its bounded barrier waits ever ran out on the
+ * current device.  Synchronises the device.
+ */
+int cq_prefill_status(void);
+
 #ifdef __cplusplus
 }
 #endif

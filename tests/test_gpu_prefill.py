@@ -68,3 +68,25 @@ def test_large_property(ops):
     ref = oracle_prefill.causal_attention(q[:, :, :4], k[:, :, :1], v[:, :, :1])
     assert rel_l2(out[:, :, :4], ref) <= 1e-2
     assert torch.isfinite(out.float()).all()
+
+
+def test_status_word_clean_and_general_kernel_agrees(ops):
+    """No bounded wait of the tensor-core kernel may have timed out during this module, and the
+    warp-MMA kernel (selected with CQ_PREFILL_GENERAL=1, read once per process) must agree."""
+    import os
+    import subprocess
+    import sys
+    from calibquant_b200 import _lib
+    assert _lib.lib().cq_prefill_status() == 0
+    code = (
+        "import torch, sys; sys.path.insert(0, '.'); sys.path.insert(0, 'tests')\n"
+        "from calibquant_b200 import ops; from oracle import prefill as op; from gpu_util import rel_l2\n"
+        "g = torch.Generator().manual_seed(3)\n"
+        "q = torch.randn(1, 333, 8, 128, generator=g).half(); k = torch.randn(1, 333, 2, 128, generator=g).half()\n"
+        "v = torch.randn(1, 333, 2, 128, generator=g).half()\n"
+        "o = ops.prefill_attention(q.cuda(), k.cuda(), v.cuda())\n"
+        "assert rel_l2(o, op.causal_attention(q, k, v)) <= 5e-3\n"
+    )
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CQ_PREFILL_GENERAL="1")
+    subprocess.run([sys.executable, "-c", code], cwd=root, env=env, check=True, timeout=300)
