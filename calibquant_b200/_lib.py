@@ -61,6 +61,16 @@ SIGNATURES = {
                                    _c.POINTER(_i64), _c.POINTER(_i64), _c.POINTER(_i64), _c.POINTER(_i64),
                                    _c.c_int, _vp]),
     "cq_prefill_status": (_c.c_int, []),
+    "cq_calib_minmax": (_c.c_int, [_vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_i64), _c.c_int,
+                                   _c.c_float, _c.c_int, _vp, _vp, _vp]),
+    "cq_calib_quantize": (_c.c_int, [_vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.POINTER(_i64), _c.c_int,
+                                     _c.c_int, _vp, _vp, _c.c_int, _vp, _vp, _vp]),
+    "cq_calib_encode_i64": (_c.c_int, [_vp, _i64, _c.c_int, _vp, _vp]),
+    "cq_lut_scores": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                 _c.c_int, _c.c_int, _vp]),
+    "cq_lut_out_workspace_bytes": (_sz, [_c.c_int, _c.c_int, _c.c_int]),
+    "cq_lut_out": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                              _c.c_int, _c.c_int, _vp, _sz, _vp]),
     "cq_decode_attn_workspace_bytes": (_sz, [_c.POINTER(DecodeArgs)]),
     "cq_decode_attn": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _sz, _vp]),
 }

@@ -1,0 +1,163 @@
+"""Drop-in for the reference module ``calibquant.py`` (the CalibQuant uint8 format).
+
+Same names, arguments and results as the reference: ``quant`` (``calibquant.py:24-42``), ``encode``
+(``:114-137``), ``fused_kernel`` (``:104-111``) and ``fused_kernel_wv`` (``:269-276``), plus the module
+constants ``BITS_KV, SCALE_K, SCALE_V, DATA_TYPE``.  The work is done by CUDA kernels of
+``libcalibquant_b200.so`` instead of eager torch / torch.compile / Triton; inputs must be CUDA tensors.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import ops
+from ._lib import check, lib
+from .ops import _dtype_enum, _need_cuda, _ptr, _stream, _workspace
+
+DATA_TYPE = torch.float16
+BITS_KV = 1
+
+if BITS_KV == 1:
+    SCALE_V = 0.3
+    SCALE_K = 0.5
+else:
+    SCALE_V = 1
+    SCALE_K = 1
+
+
+def _strides3(t):
+    return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _prep(x):
+    if x.stride(3) != 1 or any(s % 8 for s in x.stride()[:3]) or x.data_ptr() % 16:
+        x = x.contiguous()
+    return x
+
+
+def quant_params(x: torch.Tensor, bits: int, scale=1):
+    """Per-channel (over tokens, dim 1) scale and zero point of ``quant``: both [B,1,H,D]."""
+    _need_cuda(x)
+    x = _prep(x)
+    B, T, H, D = x.shape
+    s = torch.empty((B, 1, H, D), dtype=x.dtype, device=x.device)
+    zp = torch.empty_like(s)
+    with torch.cuda.device(x.device):
+        rc = lib().cq_calib_minmax(_ptr(x), B, T, H, D, _strides3(x), bits, float(scale), _dtype_enum(x),
+                                   _ptr(s), _ptr(zp), _stream())
+    check(rc, "cq_calib_minmax")
+    return s, zp
+
+
+def quant(x, bits, per_channel=False, scale=1, post_scale=False):
+    """``quant(x [B,T,H,D], bits, per_channel=True, scale=clip, post_scale)`` ->
+    ``(x_q or dequantized x, scale, zero_point)``.  Only ``per_channel=True`` is implemented (the only
+    mode the reference's attention forward uses, ``patch_internvl.py:292,297``)."""
+    if not per_channel:
+        raise NotImplementedError("only per_channel=True (min/max over tokens per channel) is implemented")
+    _need_cuda(x)
+    x = _prep(x)
+    B, T, H, D = x.shape
+    s, zp = quant_params(x, bits, scale)
+    out = torch.empty((B, T, H, D), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib().cq_calib_quantize(_ptr(x), B, T, H, D, _strides3(x), bits, _dtype_enum(x), _ptr(s), _ptr(zp),
+                                     0 if post_scale else 1, _ptr(out), None, _stream())
+    check(rc, "cq_calib_quantize")
+    return out, s, zp
+
+
+def quant_encode(x, bits, scale=1):
+    """Fused ``quant`` + ``encode``: x [B,T,H,D] -> (enc uint8 [B,H,T,D*bits/8], scale, zero_point)
+    without materialising the codes (replaces ``patch_internvl.py:292-339`` per tensor)."""
+    _need_cuda(x)
+    x = _prep(x)
+    B, T, H, D = x.shape
+    s, zp = quant_params(x, bits, scale)
+    enc = torch.empty((B, H, T, D * bits // 8), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib().cq_calib_quantize(_ptr(x), B, T, H, D, _strides3(x), bits, _dtype_enum(x), _ptr(s), _ptr(zp),
+                                     0, None, _ptr(enc), _stream())
+    check(rc, "cq_calib_quantize")
+    return enc, s, zp
+
+
+def encode(X: torch.Tensor, bits=BITS_KV, datum_per_elem=int(8 / BITS_KV)):
+    """Integer codes [B,H,T,D] -> uint8 [B,H,T,D/datum_per_elem], most significant field first."""
+    _need_cuda(X)
+    assert datum_per_elem * bits == 8
+    codes = X.to(torch.int64).contiguous()
+    out = torch.empty((*X.shape[:-1], X.shape[-1] // datum_per_elem), dtype=torch.uint8, device=X.device)
+    with torch.cuda.device(X.device):
+        rc = lib().cq_calib_encode_i64(_ptr(codes), codes.numel(), bits, _ptr(out), _stream())
+    check(rc, "cq_calib_encode_i64")
+    return out
+
+
+def fused_kernel(unique_values, weights, features_enc, BITS=BITS_KV, DATUM_PER_ELM=int(8 / BITS_KV)):
+    """scores[b,h,0,t] = sum_d weights[b,h,0,d] * unique_values[code[b,h',t,d]] -> fp16 [B,Hq,1,T].
+    ``features_enc`` may carry Hq heads (as the reference passes it) or the KV-head count."""
+    _need_cuda(unique_values, weights, features_enc)
+    B, Hq = weights.shape[0], weights.shape[1]
+    He, T = features_enc.shape[1], features_enc.shape[2]
+    w = weights.reshape(B, Hq, -1).contiguous()
+    lut = unique_values.to(w.dtype).contiguous()
+    enc = features_enc.contiguous()
+    out = torch.empty((B, Hq, 1, T), dtype=torch.float16, device=w.device)
+    with torch.cuda.device(w.device):
+        rc = lib().cq_lut_scores(_ptr(lut), _ptr(w), _ptr(enc), _ptr(out), B, Hq, He, T, w.shape[-1], BITS,
+                                 _dtype_enum(w), _stream())
+    check(rc, "cq_lut_scores")
+    return out
+
+
+def fused_kernel_wv(unique_values, weights, features_enc, BITS=BITS_KV, DATUM_PER_ELM=int(8 / BITS_KV)):
+    """out[b,h,0,n] = sum_t weights[b,h,0,t] * unique_values[code[b,h',t,n]] -> fp16 [B,Hq,1,D]."""
+    _need_cuda(unique_values, weights, features_enc)
+    B, Hq = weights.shape[0], weights.shape[1]
+    He, T = features_enc.shape[1], features_enc.shape[2]
+    D = features_enc.shape[3] * DATUM_PER_ELM
+    w = weights.reshape(B, Hq, -1).contiguous()
+    lut = unique_values.to(w.dtype).contiguous()
+    enc = features_enc.contiguous()
+    out = torch.empty((B, Hq, 1, D), dtype=torch.float16, device=w.device)
+    nbytes = lib().cq_lut_out_workspace_bytes(B, Hq, T)
+    ws = _workspace(nbytes + 256, w.device)
+    with torch.cuda.device(w.device):
+        rc = lib().cq_lut_out(_ptr(lut), _ptr(w), _ptr(enc), _ptr(out), B, Hq, He, T, D, BITS, _dtype_enum(w),
+                              ctypes.c_void_p(ws.data_ptr() + 256), nbytes, _stream())
+    check(rc, "cq_lut_out")
+    return out
+
+
+def decode_attention(q, state, k_fp, v_fp, bits, sys_len, normalize=None):
+    """Decode step of the reference's calibquant forward (``patch_internvl.py:356-436``) on the
+    uint8 format: post-scaling (scale folded into the query, zero point into a scalar bias), logit
+    calibration, fp32 softmax, LUT products, fp16 system/text segments.  ``state`` holds ``enc_k, enc_v``
+    [B,Hkv,T,D*bits/8] and ``scale_key, zero_point_key, scale_value, zero_point_value`` [B,Hq,1,D].
+    Returns [B,Hq,1,D] in bfloat16 as the reference does."""
+    import math
+    from .patch_internvl import repeat_kv
+    n_rep = q.shape[1] // k_fp.shape[1]
+    normalize = (bits <= 2) if normalize is None else normalize
+    sd = math.sqrt(q.shape[-1])
+    lut = torch.arange(2 ** bits, dtype=q.dtype, device=q.device)
+    k, v = repeat_kv(k_fp, n_rep), repeat_kv(v_fp, n_rep)
+    sk, zk, sv, zv = state["scale_key"], state["zero_point_key"], state["scale_value"], state["zero_point_value"]
+    s_sys = torch.matmul(q, k[:, :, :sys_len].transpose(2, 3)) / sd
+    s_txt = torch.matmul(q, k[:, :, sys_len:].transpose(2, 3)) / sd
+    bias_k = torch.sum(sk * zk * q, dim=-1, keepdim=True) / sd
+    s_vis = fused_kernel(lut, q * sk, state["enc_k"], bits, 8 // bits) / sd - bias_k
+    if normalize:
+        cur_max = s_vis.amax(dim=(2, 3), keepdim=True)
+        cur_min = s_vis.amin(dim=(2, 3), keepdim=True)
+        s_vis = (s_vis - cur_min) / (cur_max - cur_min + 1e-8) * ((cur_max + (-3)) - cur_min) + cur_min
+    t_vis = s_vis.shape[-1]
+    att = torch.softmax(torch.cat([s_sys, s_vis, s_txt], dim=-1), dim=-1, dtype=torch.float32).to(q.dtype)
+    a_vis = att[..., sys_len:sys_len + t_vis]
+    o_vis = fused_kernel_wv(lut.half(), a_vis.half().contiguous(), state["enc_v"], bits, 8 // bits) * sv
+    o_vis = o_vis - sv * zv * torch.sum(a_vis, dim=-1, keepdim=True)
+    o = o_vis + torch.matmul(att[..., :sys_len], v[:, :, :sys_len]) + torch.matmul(att[..., sys_len + t_vis:], v[:, :, sys_len:])
+    return o.to(torch.bfloat16)

@@ -124,16 +124,17 @@ def qbmm(group_size: int, fA: torch.Tensor, qB: torch.Tensor, scales: torch.Tens
     scales, zeros = scales.contiguous(), zeros.contiguous()
     out = torch.empty((B, Hq, 1, N), dtype=fA.dtype, device=fA.device)
     nbytes = lib().cq_qbmm_workspace_bytes(B, Hq, K, N)
-    ws = _workspace(nbytes, fA.device)
+    ws = _workspace(nbytes + 256, fA.device)      # the first 256 bytes stay the decode status word
     with torch.cuda.device(fA.device):
         rc = lib().cq_qbmm(_ptr(fA), _ptr(qB), _ptr(scales), _ptr(zeros), _ptr(out), B, Hq, Hkv,
-                           K, N, group_size, bits, _dtype_enum(fA), _ptr(ws), ws.numel(), _stream())
+                           K, N, group_size, bits, _dtype_enum(fA), ctypes.c_void_p(ws.data_ptr() + 256),
+                           nbytes, _stream())
     check(rc, "cq_qbmm")
     return out
 
 
 def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
-                     calibrate=None, mask=None, out=None, t_fp=None):
+                     calibrate=None, mask=None, out=None, t_fp=None, _stages=0):
     """One decode step over [sys | visual (quantized) | text].
 
     q [B,Hq,1,D] or [B,Hq,D]; k_pack/v_pack = (code, scale, mn) in the group format (K per
@@ -152,6 +153,7 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
     a.batch, a.n_q_heads, a.n_kv_heads, a.head_dim = B, Hq, Hkv, D
     a.bits, a.group_size, a.dtype = bits, group_size, _dtype_enum(q)
     a.calibrate = int(bits <= 2 if calibrate is None else calibrate)
+    a.reserved = _stages      # profiling aid, see the header; 0 = the whole step
     a.q = q2.data_ptr()
     keep = [q2]
     if k_pack is not None and k_pack[0].numel() > 0:

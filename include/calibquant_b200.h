@@ -135,7 +135,8 @@ typedef struct cq_decode_args {
                         /* used to index `mask` in the original key order               */
   int32_t bits, group_size, dtype;
   int32_t calibrate;    /* 1: remap visual logits (patch_internvl.py:376-385)           */
-  int32_t reserved;
+  int32_t reserved;     /* 0.  Profiling aid of the tensor-core path: bit 0/1/2 = run only the    */
+                        /* scores / attn.V / combine launch on buffers a full call has filled    */
   /* operands (device pointers) */
   const void* q;                 /* [B,Hq,D]                                            */
   const int32_t* k_code;         /* [B,Hkv,D,t_vis*bits/32]                             */
@@ -170,6 +171,47 @@ int cq_prefill_attn(const void* q, const void* k, const void* v, void* out, int 
                     int n_q_heads, int n_kv_heads, int head_dim, const int64_t* q_strides,
                     const int64_t* k_strides, const int64_t* v_strides, const int64_t* o_strides,
                     int dtype, void* stream);
+
+/*
+ * ---- CalibQuant uint8 format (whole visual span = one quantization group per channel) -----------
+ *
+ * cq_calib_minmax: scale and zero point of calibquant.py:24-42 `quant(x, bits, per_channel=True,
+ * scale=clip)` (the min/max/scale/zero_point lines :27-33).
+ *   x : element (b,t,h,d) at x + b*strides[0] + t*strides[1] + h*strides[2] + d   (head_dim 128)
+ *   scale, zero_point : [B,H,D] in the data dtype (the reference's [B,1,H,D])
+ */
+int cq_calib_minmax(const void* x, int batch, int t_len, int heads, int head_dim, const int64_t* strides,
+                    int bits, float clip, int dtype, void* scale, void* zero_point, void* stream);
+
+/*
+ * cq_calib_quantize: the quantize / dequantize lines of calibquant.py:35-41 and, fused, the byte
+ * packing of calibquant.py:114-137 `encode` (most significant field first).
+ *   xq_out  (optional) : [B,T,H,D] contiguous, the codes as numbers of the data dtype
+ *                        (dequantize == 0, the reference's post_scale=True) or scale*(code - zp)
+ *   enc_out (optional) : uint8 [B,H,T,D*bits/8]
+ */
+int cq_calib_quantize(const void* x, int batch, int t_len, int heads, int head_dim, const int64_t* strides,
+                      int bits, int dtype, const void* scale, const void* zero_point, int dequantize,
+                      void* xq_out, uint8_t* enc_out, void* stream);
+
+/* calibquant.py:114-137 `encode` on int64 codes (any leading shape, last dim a multiple of 8/bits). */
+int cq_calib_encode_i64(const int64_t* codes, int64_t n_codes, int bits, uint8_t* out, void* stream);
+
+/*
+ * cq_lut_scores replaces calibquant.py:54-111 `fused_kernel` (Triton LUT vec-mat, transposed):
+ *   out[b,h,t] = sum_d weights[b,h,d] * lut[code[b,he,t,d]],  he = h / (n_q_heads/n_enc_heads)
+ *   weights [B,Hq,D]; enc uint8 [B,Henc,T,D*bits/8] (Henc = Hq as the reference passes it, or the KV
+ *   head count); lut 2^bits values in the data dtype; out [B,Hq,T] always fp16 (calibquant.py:109).
+ * cq_lut_out replaces calibquant.py:192-276 `fused_kernel_wv`:
+ *   out[b,h,d] = sum_t weights[b,h,t] * lut[code[b,he,t,d]],  weights [B,Hq,T], out [B,Hq,D] fp16;
+ *   workspace: cq_lut_out_workspace_bytes(...) bytes of fp32 partial sums.
+ */
+int cq_lut_scores(const void* lut, const void* weights, const uint8_t* enc, void* out, int batch,
+                  int n_q_heads, int n_enc_heads, int t_len, int head_dim, int bits, int dtype, void* stream);
+size_t cq_lut_out_workspace_bytes(int batch, int n_q_heads, int t_len);
+int cq_lut_out(const void* lut, const void* weights, const uint8_t* enc, void* out, int batch, int n_q_heads,
+               int n_enc_heads, int t_len, int head_dim, int bits, int dtype, void* workspace,
+               size_t workspace_bytes, void* stream);
 
 /*
  * Sticky device status of the prefill kernel (no reference counterpart: the reference checks no
