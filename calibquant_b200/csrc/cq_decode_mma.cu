@@ -639,21 +639,34 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
 // =================================================================================================
 // K3: combine
 // =================================================================================================
-__global__ void __launch_bounds__(kHeadDim)
+constexpr int K3_LANES = 4;    // slot-parallel groups of 128 channel threads
+__global__ void __launch_bounds__(kHeadDim * K3_LANES)
 k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict__ ml,
            __half* __restrict__ out) {
+  __shared__ float o_s[K3_LANES][kHeadDim];
+  __shared__ float l_s[K3_LANES];
   const int64_t row = blockIdx.x;
+  const int d = threadIdx.x & (kHeadDim - 1), sl = threadIdx.x >> 7;
   const float2* r = ml + row * dm.n_slots;
   float M = -INFINITY;
-  for (int i = 0; i < dm.n_slots; ++i) M = fmaxf(M, r[i].x);
+  for (int i = 0; i < dm.n_slots; ++i) M = fmaxf(M, __ldg(&r[i]).x);
   float L = 0.f, o = 0.f;
-  const float* p = partial + row * dm.n_slots * kHeadDim + threadIdx.x;
-  for (int i = 0; i < dm.n_slots; ++i) {
-    const float w = exp2f((r[i].x - M) * LOG2E);
-    L = fmaf(r[i].y, w, L);
-    o = fmaf(p[(int64_t)i * kHeadDim], w, o);
+  const float* p = partial + row * dm.n_slots * kHeadDim + d;
+#pragma unroll 4
+  for (int i = sl; i < dm.n_slots; i += K3_LANES) {
+    const float2 mlv = __ldg(&r[i]);
+    const float w = exp2f((mlv.x - M) * LOG2E);
+    L = fmaf(mlv.y, w, L);
+    o = fmaf(__ldg(p + (int64_t)i * kHeadDim), w, o);
   }
-  out[row * kHeadDim + threadIdx.x] = __float2half_rn(o / L);
+  o_s[sl][d] = o;
+  if (d == 0) l_s[sl] = L;
+  __syncthreads();
+  if (sl == 0) {
+#pragma unroll
+    for (int j = 1; j < K3_LANES; ++j) { o += o_s[j][d]; L += l_s[j]; }
+    out[row * kHeadDim + d] = __float2half_rn(o / L);
+  }
 }
 
 // =================================================================================================
@@ -787,7 +800,7 @@ static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned
     if (rc != CQ_OK) return rc;
   }
   if (stages & 4) {
-    k3_combine<<<d.batch * d.hq, kHeadDim, 0, st>>>(d, partial, ml, static_cast<__half*>(a->out));
+    k3_combine<<<d.batch * d.hq, kHeadDim * K3_LANES, 0, st>>>(d, partial, ml, static_cast<__half*>(a->out));
     return check_launch();
   }
   return CQ_OK;
