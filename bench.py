@@ -314,8 +314,68 @@ def run_reference(args, rank, world):
     }
 
 
+def run_model(args, rank, world, device):
+    """End-to-end decode throughput of an InternLM2-architecture backbone with the quantized-KV
+    attention path: random-init bf16 weights, prefill of 41 system + 3328 (6656) visual + text
+    embeddings, then greedy decode steps.  N > 1: attention sharded by KV head with one all-gather
+    of head outputs per layer (everything else replicated); tok/s = batch * steps / decode time."""
+    from calibquant_b200 import patch_internvl as pi
+    from calibquant_b200.internlm2 import INTERNLM2_5_7B, INTERNLM2_20B, ChatModelShell
+    big = args.workload == "model20b"
+    cfg = INTERNLM2_20B if big else INTERNLM2_5_7B
+    batch = args.batch if args.batch != 8 else (64 if big else 16)
+    t_vis, t_txt = (6656, 128 - 41) if big else (3328, 64 - 41)
+    torch.manual_seed(1234)
+    with torch.device(device):
+        shell = ChatModelShell(cfg).to(torch.bfloat16)
+    for prm in shell.parameters():
+        if prm.dim() >= 2:
+            torch.nn.init.normal_(prm, std=0.02)
+    pi.patch_model(shell, "calibquant")
+    pi.BITS_KV = args.bits
+    if world > 1:
+        for layer in shell.language_model.model.layers:
+            pi.shard_attention_(layer.attention, rank, world)
+    lm = shell.language_model
+    T = 41 + t_vis + t_txt
+    emb = torch.randn(batch, T, cfg.hidden_size, device=device, dtype=torch.bfloat16) * 0.02
+    os.environ["IMAGE_TOKEN_NUM"] = str(t_vis)
+    pos = torch.arange(T, device=device).unsqueeze(0).expand(batch, T)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    torch.cuda.synchronize()
+    ev[0].record()
+    with torch.no_grad():
+        logits, past = lm.forward_step(emb, pos, None)
+        ev[1].record()
+        steps = args.steps
+        for step in range(steps):
+            nxt = logits[:, -1].argmax(-1)
+            e = lm.model.tok_embeddings(nxt).unsqueeze(1)
+            p1 = torch.full((batch, 1), T + step, device=device, dtype=torch.long)
+            logits, past = lm.forward_step(e, p1, past)
+    ev[2].record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], device=device, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    prefill_ms, decode_ms = t.tolist()
+    tok_s = batch * steps / (decode_ms * 1e-3)
+    return {
+        "metric": "decode_tok_per_s", "value": round(tok_s, 1), "unit": "tok/s", "n_gpus": world,
+        "steps": steps, "warmup": 0, "ms_per_step": round(decode_ms / steps, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{'InternLM2-20B' if big else 'InternLM2.5-7B'} architecture, random-init bf16, "
+                               f"batch {batch}, prefill 41+{t_vis}+{t_txt} tokens, {steps} greedy steps, "
+                               f"{args.bits}-bit KV (group 32)",
+                   "parallelism": "single GPU" if world == 1 else f"attention sharded by KV head x{world}, "
+                                  "NCCL all-gather of head outputs per layer, rest replicated",
+                   "prefill_ms": round(prefill_ms, 1), "eager": "no CUDA graph"},
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="attn", choices=["attn", "model7b", "model20b"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
@@ -346,7 +406,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=device)
     try:
-        line = run_ours(args, rank, world, device)
+        line = run_ours(args, rank, world, device) if args.workload == "attn" else run_model(args, rank, world, device)
         if rank == 0:
             print(json.dumps(line), flush=True)
     finally:

@@ -25,10 +25,12 @@
 //                 write (max, sum, acc[128]) partials
 //   K3 combine  : merge the chunk partials (online-softmax rescale), round to the output dtype
 //
-// Eligibility (otherwise cq_decode_attn uses the general kernels): fp16, t_vis % 256 == 0,
+// Eligibility (otherwise cq_decode_attn uses the general kernels): t_vis % 256 == 0,
 // no additive mask, 16-byte aligned operands.
 #include <cuda.h>
 #include <stdlib.h>
+
+#include <type_traits>
 
 #include "cq_common.cuh"
 #include "cq_ptx.cuh"
@@ -76,15 +78,47 @@ __device__ __forceinline__ uint32_t prmt_sel(int byte) {
   return (uint32_t)(byte | (byte << 4) | ((4 + byte) << 8) | ((4 + byte) << 12));
 }
 
+// ---- data-dtype helpers.  The MMA operands are always fp16: bf16 scales, minima and queries fit
+// ---- fp16 exactly (8 significant bits) within its range, so they are converted on the way in,
+// ---- while every value the reference rounds to the data dtype is rounded to T here too.
+template <typename T> struct D16;
+template <> struct D16<__half> {
+  using T2 = __half2;
+  static __device__ __forceinline__ uint32_t to_h2(uint32_t v) { return v; }
+  static __device__ __forceinline__ T2 round2(float a, float b) { return __floats2half2_rn(a, b); }
+  static __device__ __forceinline__ T2 bcast(float a) { return __float2half2_rn(a); }
+  static __device__ __forceinline__ float2 to_f2(T2 v) { return __half22float2(v); }
+  static __device__ __forceinline__ float big() { return 65504.f; }
+  // rnd(x * c): fp16(c) is within 2^-12 of c, a packed multiply is accurate enough
+  static __device__ __forceinline__ T2 scale2(T2 x, float c) { return __hmul2(x, __float2half2_rn(c)); }
+};
+template <> struct D16<__nv_bfloat16> {
+  using T2 = __nv_bfloat162;
+  static __device__ __forceinline__ uint32_t to_h2(uint32_t v) {
+    const __half2 h = __floats2half2_rn(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ T2 round2(float a, float b) { return __floats2bfloat162_rn(a, b); }
+  static __device__ __forceinline__ T2 bcast(float a) { return __float2bfloat162_rn(a); }
+  static __device__ __forceinline__ float2 to_f2(T2 v) { return __bfloat1622float2(v); }
+  static __device__ __forceinline__ float big() { return 3.0e38f; }
+  // bf16(c) would be off by up to 2^-9 (a systematic error on every logit): multiply in fp32
+  static __device__ __forceinline__ T2 scale2(T2 x, float c) {
+    const float2 f = __bfloat1622float2(x);
+    return __floats2bfloat162_rn(f.x * c, f.y * c);
+  }
+};
+
 // =================================================================================================
 // K1: scores
 // =================================================================================================
-template <int BITS>
+template <typename T, int BITS>
 __global__ void __launch_bounds__(THREADS)
 k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ CUtensorMap tm_ks,
-          const __grid_constant__ CUtensorMap tm_kmn, Dims dm, const __half* __restrict__ q,
-          const __half* __restrict__ k_fp, __half* __restrict__ scores, float2* __restrict__ tile_mm,
+          const __grid_constant__ CUtensorMap tm_kmn, Dims dm, const T* __restrict__ q,
+          const T* __restrict__ k_fp, T* __restrict__ scores, float2* __restrict__ tile_mm,
           int* __restrict__ status) {
+  using T2 = typename D16<T>::T2;
   constexpr int STAGES = k1_stages(BITS);
   constexpr int STAGE_BYTES = k1_stage_bytes(BITS);
   constexpr int CODE_BYTES = BITS * 16384;
@@ -100,7 +134,6 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   const int n_pairs = dm.batch * dm.hkv;
   const int n_items = n_pairs * dm.n_ktiles;
   const float inv_sqrt_d = 0.08838834764831845f;
-  const __half2 inv_sqrt_d2 = __float2half2_rn(inv_sqrt_d);
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
@@ -158,11 +191,11 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
     if (pair != cur_pair) {   // query fragments of this KV head's query heads (B operand, n = g)
       cur_pair = pair;
       const int b = pair / dm.hkv, hk = pair % dm.hkv;
-      const __half* qrow = q + ((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + g) * kHeadDim;
+      const T* qrow = q + ((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + g) * kHeadDim;
 #pragma unroll
       for (int kt = 0; kt < 8; ++kt) {
-        qA[kt] = g < dm.n_rep ? *reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c) : 0u;
-        qB[kt] = g < dm.n_rep ? *reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c + 8) : 0u;
+        qA[kt] = g < dm.n_rep ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c)) : 0u;
+        qB[kt] = g < dm.n_rep ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c + 8)) : 0u;
       }
     }
     if (!mbar_wait_bounded(&full_bar[s], (uint32_t)((k / STAGES) & 1), WAIT_TRIES)) {
@@ -187,6 +220,9 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
           ldmatrix_x4_trans(ks_base + off, ksA[2 * kp], ksB[2 * kp], ksA[2 * kp + 1], ksB[2 * kp + 1]);
           uint32_t z0, z1, z2, z3;
           ldmatrix_x4_trans(kmn_base + off, z0, z1, z2, z3);
+          ksA[2 * kp] = D16<T>::to_h2(ksA[2 * kp]); ksB[2 * kp] = D16<T>::to_h2(ksB[2 * kp]);
+          ksA[2 * kp + 1] = D16<T>::to_h2(ksA[2 * kp + 1]); ksB[2 * kp + 1] = D16<T>::to_h2(ksB[2 * kp + 1]);
+          z0 = D16<T>::to_h2(z0); z1 = D16<T>::to_h2(z1); z2 = D16<T>::to_h2(z2); z3 = D16<T>::to_h2(z3);
           mma_f16(cb, z0, 0u, z1, 0u, qA[2 * kp], qB[2 * kp]);
           mma_f16(cb, z2, 0u, z3, 0u, qA[2 * kp + 1], qB[2 * kp + 1]);
         }
@@ -194,7 +230,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
       const int b = pair / dm.hkv, hk = pair % dm.hkv;
       const int64_t row_a = ((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + 2 * c) * dm.pitch;
       const int64_t row_b = row_a + dm.pitch;
-      __half2 mnA = __float2half2_rn(65504.f), mxA = __float2half2_rn(-65504.f), mnB = mnA, mxB = mxA;
+      T2 mnA = D16<T>::bcast(D16<T>::big()), mxA = D16<T>::bcast(-D16<T>::big()), mnB = mnA, mxB = mxA;
 
 #pragma unroll 1
       for (int u = 0; u < UNITS; ++u) {
@@ -250,23 +286,24 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
           const int tok0 = ((tile * TILE_G + warp * 8 + gi) * 32) + 2 * g;
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
-            const __half2 ra = __floats2half2_rn(fmaf(acc[a][i][0], sc0[i], bias0), fmaf(acc[a][i][2], sc1[i], bias0));
-            const __half2 rb = __floats2half2_rn(fmaf(acc[a][i][1], sc0[i], bias1), fmaf(acc[a][i][3], sc1[i], bias1));
-            const __half2 sa = __hmul2(ra, inv_sqrt_d2), sb = __hmul2(rb, inv_sqrt_d2);
+            const T2 ra = D16<T>::round2(fmaf(acc[a][i][0], sc0[i], bias0), fmaf(acc[a][i][2], sc1[i], bias0));
+            const T2 rb = D16<T>::round2(fmaf(acc[a][i][1], sc0[i], bias1), fmaf(acc[a][i][3], sc1[i], bias1));
+            const T2 sa = D16<T>::scale2(ra, inv_sqrt_d), sb = D16<T>::scale2(rb, inv_sqrt_d);
             if (2 * c < dm.n_rep) {
-              *reinterpret_cast<__half2*>(scores + row_a + tok0 + 16 * i) = sa;
+              *reinterpret_cast<T2*>(scores + row_a + tok0 + 16 * i) = sa;
               mnA = __hmin2(mnA, sa); mxA = __hmax2(mxA, sa);
             }
             if (2 * c + 1 < dm.n_rep) {
-              *reinterpret_cast<__half2*>(scores + row_b + tok0 + 16 * i) = sb;
+              *reinterpret_cast<T2*>(scores + row_b + tok0 + 16 * i) = sb;
               mnB = __hmin2(mnB, sb); mxB = __hmax2(mxB, sb);
             }
           }
         }
       }
       // ---- per-warp min/max of this tile, per head
-      float lo_a = fminf(__low2float(mnA), __high2float(mnA)), hi_a = fmaxf(__low2float(mxA), __high2float(mxA));
-      float lo_b = fminf(__low2float(mnB), __high2float(mnB)), hi_b = fmaxf(__low2float(mxB), __high2float(mxB));
+      const float2 fmnA = D16<T>::to_f2(mnA), fmxA = D16<T>::to_f2(mxA), fmnB = D16<T>::to_f2(mnB), fmxB = D16<T>::to_f2(mxB);
+      float lo_a = fminf(fmnA.x, fmnA.y), hi_a = fmaxf(fmxA.x, fmxA.y);
+      float lo_b = fminf(fmnB.x, fmnB.y), hi_b = fmaxf(fmxB.x, fmxB.y);
 #pragma unroll
       for (int o = 4; o < 32; o <<= 1) {
         lo_a = fminf(lo_a, __shfl_xor_sync(0xffffffffu, lo_a, o));
@@ -297,22 +334,22 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
     const int b = pair / dm.hkv, hk = pair % dm.hkv;
     __syncthreads();
     for (int i = tid; i < dm.n_rep * kHeadDim; i += THREADS)
-      qf_s[i] = __half2float(q[((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep) * kHeadDim + i]);
+      qf_s[i] = Elem<T>::to_f(q[((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep) * kHeadDim + i]);
     __syncthreads();
-    const __half* kf = k_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h;
+    const T* kf = k_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h;
     for (int i = warp; i < 64; i += THREADS / 32) {
       const int t = ft * 64 + i;
       if (t >= dm.t_fp) break;
       const uint2 raw = __ldg(reinterpret_cast<const uint2*>(kf + (int64_t)t * kHeadDim) + lane);
-      const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-      const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+      const float2 k01 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw.x));
+      const float2 k23 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw.y));
       for (int h = 0; h < dm.n_rep; ++h) {
         const float4 qv = *reinterpret_cast<const float4*>(&qf_s[h * kHeadDim + lane * 4]);
         float dot = qv.x * k01.x + qv.y * k01.y + qv.z * k23.x + qv.w * k23.y;
         dot = warp_sum(dot);
         if (lane == 0) {
-          const float sc = __fdiv_rn(__half2float(__float2half_rn(dot)), 11.313708498984761f);
-          scores[((int64_t)b * dm.hq + hk * dm.n_rep + h) * dm.pitch + dm.t_vis + t] = __float2half_rn(sc);
+          const float sc = __fdiv_rn(rnd<T>(dot), 11.313708498984761f);
+          scores[((int64_t)b * dm.hq + hk * dm.n_rep + h) * dm.pitch + dm.t_vis + t] = Elem<T>::from_f(sc);
         }
       }
     }
@@ -322,16 +359,18 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
 // =================================================================================================
 // K2: attn.V partials
 // =================================================================================================
-struct CalibH {   // per head, as fp16 pairs for half2 arithmetic
-  __half2 mn, rdenom, range;
+template <typename T>
+struct CalibH {   // per head, as 16-bit pairs for packed arithmetic in the data dtype
+  typename D16<T>::T2 mn, rdenom, rdenom_lo, range;
 };
 
-template <int BITS>
+template <typename T, int BITS>
 __global__ void __launch_bounds__(THREADS)
-k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__ tile_mm,
-          const int32_t* __restrict__ v_code, const __half* __restrict__ v_scale,
-          const __half* __restrict__ v_mn, const __half* __restrict__ v_fp,
+k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile_mm,
+          const int32_t* __restrict__ v_code, const T* __restrict__ v_scale,
+          const T* __restrict__ v_mn, const T* __restrict__ v_fp,
           float* __restrict__ partial, float2* __restrict__ ml, int* __restrict__ status) {
+  using T2 = typename D16<T>::T2;
   constexpr int STAGES = k2_stages(BITS);
   constexpr int STAGE_BYTES = k2_stage_bytes(BITS);
   constexpr int CODE_BYTES = VT_TOK * 16 * BITS;
@@ -413,7 +452,7 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
 
     // ---- probabilities of the chunk: warp w serves heads w, w+4 --------------------------------
     for (int h = warp; h < dm.n_rep; h += 4) {
-      CalibH cal;
+      CalibH<T> cal;
       if (dm.calibrate) {
         float lo = INFINITY, hi = -INFINITY;
         for (int i = lane; i < dm.n_mm; i += 32) {
@@ -423,33 +462,38 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
         }
         lo = warp_min(lo);
         hi = warp_max(hi);
-        const float denom = rnd<__half>(rnd<__half>(hi - lo) + 1e-8f);
-        const float range = rnd<__half>(rnd<__half>(hi + (-3.f)) - lo);
-        cal.mn = __float2half2_rn(lo);
-        cal.rdenom = __float2half2_rn(1.f / denom);
-        cal.range = __float2half2_rn(range);
+        const float denom = rnd<T>(rnd<T>(hi - lo) + 1e-8f);
+        const float range = rnd<T>(rnd<T>(hi + (-3.f)) - lo);
+        cal.mn = D16<T>::bcast(lo);
+        cal.rdenom = D16<T>::bcast(1.f / denom);
+        cal.rdenom_lo = D16<T>::bcast(1.f / denom - rnd<T>(1.f / denom));   // two-term reciprocal
+        cal.range = D16<T>::bcast(range);
       }
-      const __half* srow = scores + (row0 + h) * dm.pitch + tok_base;
-      __half2 x[4][4];
-      __half2 mx2 = __float2half2_rn(-65504.f);
+      const T* srow = scores + (row0 + h) * dm.pitch + tok_base;
+      T2 x[4][4];
+      T2 mx2 = D16<T>::bcast(-D16<T>::big());
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int t = (j * 32 + lane) * 8;
-        uint4 raw = make_uint4(0xfbfffbffu, 0xfbfffbffu, 0xfbfffbffu, 0xfbfffbffu);   // -65504
+        const T2 neg_big = D16<T>::bcast(-D16<T>::big());
+        const uint32_t nb = *reinterpret_cast<const uint32_t*>(&neg_big);
+        uint4 raw = make_uint4(nb, nb, nb, nb);
         if (t < n_tok) raw = *reinterpret_cast<const uint4*>(srow + t);
-        const __half2* r2 = reinterpret_cast<const __half2*>(&raw);
+        const T2* r2 = reinterpret_cast<const T2*>(&raw);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          __half2 v = r2[e];
+          T2 v = r2[e];
           if (dm.calibrate && t < n_tok) {
-            v = __hmul2(__hsub2(v, cal.mn), cal.rdenom);
+            v = __hsub2(v, cal.mn);
+            v = __hfma2(v, cal.rdenom, __hmul2(v, cal.rdenom_lo));   // ~ rnd(v / denom)
             v = __hadd2(__hmul2(v, cal.range), cal.mn);
           }
           x[j][e] = v;
           mx2 = __hmax2(mx2, v);
         }
       }
-      const float m = warp_max(fmaxf(__low2float(mx2), __high2float(mx2)));
+      const float2 fmx2 = D16<T>::to_f2(mx2);
+      const float m = warp_max(fmaxf(fmx2.x, fmx2.y));
       if (lane == 0) m_s[h] = m;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -458,8 +502,9 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
         __half2* o2 = reinterpret_cast<__half2*>(&out);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float2 f = __half22float2(x[j][e]);
-          o2[e] = t < n_tok ? __floats2half2_rn(exp2f((f.x - m) * LOG2E), exp2f((f.y - m) * LOG2E))
+          const float2 f = D16<T>::to_f2(x[j][e]);
+          // the reference rounds the probabilities to the data dtype; they are then exact in fp16
+          o2[e] = t < n_tok ? __floats2half2_rn(rnd<T>(exp2f((f.x - m) * LOG2E)), rnd<T>(exp2f((f.y - m) * LOG2E)))
                             : __float2half2_rn(0.f);
         }
         *reinterpret_cast<uint4*>(p_s + h * CHUNK_TOK + t) = out;
@@ -493,6 +538,21 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
       const uint32_t p_b = smem_u32(p_s) + (uint32_t)((g < dm.n_rep ? g : 0) * CHUNK_TOK + ti * VT_TOK) * 2u;
 
       const int nt_tile = min(VT_TOK, dm.t_vis - vt * VT_TOK);
+      if (!std::is_same<T, __half>::value) {
+        // scales and minima of this warp's 128 tokens: bf16 -> fp16 in place (2 x 1 KB per array)
+#pragma unroll
+        for (int arr = 0; arr < 2; ++arr) {
+          const uint32_t base = (arr == 0 ? vs_b : vmn_b) + (uint32_t)(warp * (VT_TOK / 4)) * 8u;
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const uint32_t addr = base + (uint32_t)(i * 32 + lane) * 16u;
+            uint4 v = lds128(addr);
+            v.x = D16<T>::to_h2(v.x); v.y = D16<T>::to_h2(v.y); v.z = D16<T>::to_h2(v.z); v.w = D16<T>::to_h2(v.w);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+          }
+        }
+        __syncwarp();
+      }
 #pragma unroll 1
       for (int kq = 0; kq < VT_TOK / 64; ++kq) {
         if (warp * (VT_TOK / 4) + kq * 16 >= nt_tile) break;
@@ -598,12 +658,12 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
     const int t0 = fc * 128, nt = min(128, dm.t_fp - t0);
     __syncthreads();
     for (int h = warp; h < dm.n_rep; h += 4) {
-      const __half* srow = scores + (row0 + h) * dm.pitch + dm.t_vis + t0;
+      const T* srow = scores + (row0 + h) * dm.pitch + dm.t_vis + t0;
       float xv[4], m = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int t = j * 32 + lane;
-        xv[j] = t < nt ? __half2float(srow[t]) : -INFINITY;
+        xv[j] = t < nt ? Elem<T>::to_f(srow[t]) : -INFINITY;
         m = fmaxf(m, xv[j]);
       }
       m = warp_max(m);
@@ -611,7 +671,7 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int t = j * 32 + lane;
-        const float p = t < nt ? __half2float(__float2half_rn(exp2f((xv[j] - m) * LOG2E))) : 0.f;
+        const float p = t < nt ? rnd<T>(exp2f((xv[j] - m) * LOG2E)) : 0.f;
         pf_s[h * 128 + t] = p;
         l += p;
       }
@@ -622,10 +682,10 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
     float accf[kMaxRep];
 #pragma unroll
     for (int h = 0; h < kMaxRep; ++h) accf[h] = 0.f;
-    const __half* vf = v_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h +
+    const T* vf = v_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h +
                        (int64_t)t0 * kHeadDim + tid;
     for (int t = 0; t < nt; ++t) {
-      const float v = __half2float(__ldg(vf + (int64_t)t * kHeadDim));
+      const float v = Elem<T>::to_f(__ldg(vf + (int64_t)t * kHeadDim));
 #pragma unroll
       for (int h = 0; h < kMaxRep; ++h)
         if (h < dm.n_rep) accf[h] = fmaf(pf_s[h * 128 + t], v, accf[h]);
@@ -640,9 +700,10 @@ k2_attn_v(Dims dm, const __half* __restrict__ scores, const float2* __restrict__
 // K3: combine
 // =================================================================================================
 constexpr int K3_LANES = 4;    // slot-parallel groups of 128 channel threads
+template <typename T>
 __global__ void __launch_bounds__(kHeadDim * K3_LANES)
 k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict__ ml,
-           __half* __restrict__ out) {
+           T* __restrict__ out) {
   __shared__ float o_s[K3_LANES][kHeadDim];
   __shared__ float l_s[K3_LANES];
   const int64_t row = blockIdx.x;
@@ -665,7 +726,7 @@ k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict_
   if (sl == 0) {
 #pragma unroll
     for (int j = 1; j < K3_LANES; ++j) { o += o_s[j][d]; L += l_s[j]; }
-    out[row * kHeadDim + d] = __float2half_rn(o / L);
+    out[row * kHeadDim + d] = Elem<T>::from_f(o / L);
   }
 }
 
@@ -743,17 +804,17 @@ static int sm_count() {
   return n;
 }
 
-template <int BITS>
+template <typename T, int BITS>
 static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st) {
   int* status = reinterpret_cast<int*>(ws + l.status_off);
-  __half* scores = reinterpret_cast<__half*>(ws + l.scores_off);
+  T* scores = reinterpret_cast<T*>(ws + l.scores_off);
   float2* mm = reinterpret_cast<float2*>(ws + l.mm_off);
   float2* ml = reinterpret_cast<float2*>(ws + l.ml_off);
   float* partial = reinterpret_cast<float*>(ws + l.partial_off);
   const int n_pairs = d.batch * d.hkv;
 
-  auto k1 = k1_scores<BITS>;
-  auto k2 = k2_attn_v<BITS>;
+  auto k1 = k1_scores<T, BITS>;
+  auto k2 = k2_attn_v<T, BITS>;
   const int smem1 = k1_stages(BITS) * k1_stage_bytes(BITS) + 1024;
   const int smem2 = k2_stages(BITS) * k2_stage_bytes(BITS) + 4 * kMaxRep * 136 * 4 + 1024;
   static bool configured_dev[64] = {};   // per template instance and device
@@ -785,22 +846,22 @@ static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned
       return CQ_ERR_LAUNCH;
     const int items1 = n_pairs * d.n_ktiles;
     const int grid1 = max(1, min(items1 + n_pairs * ((d.t_fp + 63) / 64), sm_count() * occ1));
-    k1<<<grid1, THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const __half*>(a->q),
-                                      static_cast<const __half*>(a->k_fp), scores, mm, status);
+    k1<<<grid1, THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(a->q),
+                                      static_cast<const T*>(a->k_fp), scores, mm, status);
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
   }
   if (stages & 2) {
     const int items2 = n_pairs * (d.n_chunks + d.n_fp_chunks);
     const int grid2 = max(1, min(items2, sm_count() * occ2));
-    k2<<<grid2, THREADS, smem2, st>>>(d, scores, mm, a->v_code, static_cast<const __half*>(a->v_scale),
-                                      static_cast<const __half*>(a->v_mn), static_cast<const __half*>(a->v_fp),
+    k2<<<grid2, THREADS, smem2, st>>>(d, scores, mm, a->v_code, static_cast<const T*>(a->v_scale),
+                                      static_cast<const T*>(a->v_mn), static_cast<const T*>(a->v_fp),
                                       partial, ml, status);
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
   }
   if (stages & 4) {
-    k3_combine<<<d.batch * d.hq, kHeadDim * K3_LANES, 0, st>>>(d, partial, ml, static_cast<__half*>(a->out));
+    k3_combine<T><<<d.batch * d.hq, kHeadDim * K3_LANES, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
     return check_launch();
   }
   return CQ_OK;
@@ -812,7 +873,7 @@ bool mma_path_eligible(const cq_decode_args* a) {
   // CQ_DECODE_GENERAL=1 forces the general kernels (A/B comparison of the two paths).
   static const bool disabled = []() { const char* e = getenv("CQ_DECODE_GENERAL"); return e && e[0] == '1'; }();
   if (disabled) return false;
-  if (a->dtype != CQ_DTYPE_F16 || a->mask != nullptr) return false;
+  if (a->mask != nullptr) return false;
   if (a->t_vis <= 0 || a->t_vis % 256 != 0) return false;
   if (a->bits != 1 && a->bits != 2 && a->bits != 4) return false;
   const void* ptrs[] = {a->q, a->k_code, a->k_scale, a->k_mn, a->v_code, a->v_scale, a->v_mn};
@@ -830,10 +891,17 @@ int mma_path_run(const cq_decode_args* a, void* workspace, cudaStream_t st) {
   const mma::Dims d = mma::make_dims(a);
   const mma::Layout l = mma::make_layout(d);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
+  if (a->dtype == CQ_DTYPE_F16) {
+    switch (a->bits) {
+      case 1: return mma::run<__half, 1>(a, d, l, ws, st);
+      case 2: return mma::run<__half, 2>(a, d, l, ws, st);
+      default: return mma::run<__half, 4>(a, d, l, ws, st);
+    }
+  }
   switch (a->bits) {
-    case 1: return mma::run<1>(a, d, l, ws, st);
-    case 2: return mma::run<2>(a, d, l, ws, st);
-    default: return mma::run<4>(a, d, l, ws, st);
+    case 1: return mma::run<__nv_bfloat16, 1>(a, d, l, ws, st);
+    case 2: return mma::run<__nv_bfloat16, 2>(a, d, l, ws, st);
+    default: return mma::run<__nv_bfloat16, 4>(a, d, l, ws, st);
   }
 }
 

@@ -143,6 +143,38 @@ def _split_qkv(self, hidden_states):
     return q, qkv[..., -2, :], qkv[..., -1, :]
 
 
+def _shard_world(self):
+    shard = getattr(self, "_shard", None)
+    return shard[1] if shard else 1
+
+
+def _gather_heads(self, x):
+    """x [B,q,Hq_local*D] -> [B,q,Hq*D].  Identity unless ``shard_attention_`` split this layer by KV
+    head across ranks; then the single collective of the layer: an all-gather of the head outputs."""
+    shard = getattr(self, "_shard", None)
+    if not shard:
+        return x
+    from . import sharding
+    return sharding.all_gather_last_dim(x, shard[2])
+
+
+def shard_attention_(attn, rank: int, world: int, group=None):
+    """Keep only this rank's KV heads in ``attn.wqkv`` (their rows are contiguous, see
+    ``sharding.wqkv_rows``); the patched forward then packs, caches and attends over the local heads
+    and all-gathers the head outputs before the (replicated) ``wo``."""
+    from . import sharding
+    if world == 1:
+        return attn
+    r0, r1 = sharding.wqkv_rows(rank, world, attn.num_key_value_heads, attn.num_key_value_groups, attn.head_dim)
+    local = torch.nn.Linear(attn.wqkv.in_features, r1 - r0, bias=False, device=attn.wqkv.weight.device,
+                            dtype=attn.wqkv.weight.dtype)
+    with torch.no_grad():
+        local.weight.copy_(attn.wqkv.weight[r0:r1])
+    attn.wqkv = local
+    attn._shard = (rank, world, group)
+    return attn
+
+
 def _image_token_num():
     return int(os.environ.get("IMAGE_TOKEN_NUM"))
 
@@ -200,6 +232,7 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
             self._text_cache = _TextCache(k, v)
         past_key_value = self._text_cache.views() if use_cache else None
         attn = ops.prefill_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+        attn = _gather_heads(self, attn.reshape(bsz, q_len, -1))
         attn_output = self.wo(attn.reshape(bsz, q_len, self.hidden_size))
         return attn_output, None, past_key_value
 
@@ -214,10 +247,12 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
     attn = ops.decode_attention(q, self.k_pack, self.v_pack, k_fp, v_fp, t_sys, BITS_KV,
                                 group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
                                 mask=attention_mask)                             # [B,Hq,1,D]
-    if attn.size() != (bsz, self.num_heads, q_len, self.head_dim):
-        raise ValueError(f"`attn_output` should be of size {(bsz, self.num_heads, q_len, self.head_dim)}, "
+    local_heads = self.num_heads // _shard_world(self)
+    if attn.size() != (bsz, local_heads, q_len, self.head_dim):
+        raise ValueError(f"`attn_output` should be of size {(bsz, local_heads, q_len, self.head_dim)}, "
                          f"but is {attn.size()}")
-    attn_output = self.wo(attn.transpose(1, 2).reshape(bsz, q_len, self.hidden_size))
+    attn = _gather_heads(self, attn.transpose(1, 2).reshape(bsz, q_len, -1))
+    attn_output = self.wo(attn.reshape(bsz, q_len, self.hidden_size))
     return attn_output, None, past_key_value
 
 

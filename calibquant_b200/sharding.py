@@ -61,6 +61,18 @@ def all_gather_heads(o_local: torch.Tensor, group=None) -> torch.Tensor:
     return gathered.view(world, B, h, D).permute(1, 0, 2, 3).reshape(B, world * h, D)
 
 
+def all_gather_last_dim(x: torch.Tensor, group=None) -> torch.Tensor:
+    """x [..., n] on every rank -> [..., world*n], rank r's slice at ``[r*n, (r+1)*n)``."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        return x
+    lead, n = x.shape[:-1], x.shape[-1]
+    flat = x.reshape(-1, n).contiguous()
+    gathered = torch.empty((world * flat.shape[0], n), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(gathered, flat, group=group)
+    return gathered.view(world, flat.shape[0], n).permute(1, 0, 2).reshape(*lead, world * n)
+
+
 class HeadShardedAttention:
     """Decode attention over this rank's KV heads followed by the all-gather of head outputs.
 

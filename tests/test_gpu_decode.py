@@ -97,6 +97,20 @@ def test_tensor_core_path_shapes(ops, bits, t_vis, t_txt, n_rep):
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("bits", [1, 2, 4])
+@pytest.mark.parametrize("t_vis,t_txt,n_rep", [(512, 3, 4), (1280, 90, 6)])
+def test_tensor_core_path_bf16(ops, bits, t_vis, t_txt, n_rep):
+    """bf16 caches on the fast path: scales, minima and queries are converted to fp16 MMA operands,
+    logits and probabilities are rounded to bf16 where the reference rounds them.  Tolerance 4e-2:
+    raw scores near |300| have a bf16 spacing of 2 (0.18 after the 1/sqrt(D) scale), so the 2^-12
+    relative rounding of the fp16 operand q*ks moves a few percent of the logits to the neighbouring
+    bf16 value; the general kernels (fp32 dequantisation) stay within 2e-2 on the same inputs."""
+    out, ref = _run_case(ops, 2, 2 * n_rep, 2, t_vis, t_txt, bits, torch.bfloat16, seed=70 + bits + t_vis)
+    assert out.dtype == torch.bfloat16
+    assert rel_l2(out, ref) <= 4e-2, rel_l2(out, ref)
+    assert ops.device_status() == 0
+
+
 def test_n_rep_6(ops):
     """48 q / 8 KV heads (the 20B backbone's grouping)."""
     out, ref = _run_case(ops, 2, 12, 2, 256, 40, 1, torch.float16, seed=9)
