@@ -44,6 +44,7 @@ using namespace ptx;
 constexpr int THREADS = 128;
 constexpr int TILE_G = 32;             // 32-token groups per K tile (1024 tokens)
 constexpr int CHUNK_TOK = 1024;        // tokens per attn.V work item
+constexpr int P_PITCH = CHUNK_TOK + 8;  // probability row pitch (halves): +16 B keeps the heads on different banks
 constexpr int VT_TOK = 512;            // tokens per V tile
 constexpr uint32_t WAIT_TRIES = 1u << 22;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -507,7 +508,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
           o2[e] = t < n_tok ? __floats2half2_rn(rnd<T>(exp2f((f.x - m) * LOG2E)), rnd<T>(exp2f((f.y - m) * LOG2E)))
                             : __float2half2_rn(0.f);
         }
-        *reinterpret_cast<uint4*>(p_s + h * CHUNK_TOK + t) = out;
+        *reinterpret_cast<uint4*>(p_s + h * P_PITCH + t) = out;
       }
     }
     __syncthreads();
@@ -535,7 +536,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
       ++cons;
       const uint32_t code_b = smem_u32(smem + s * STAGE_BYTES);
       const uint32_t vs_b = code_b + CODE_BYTES, vmn_b = vs_b + VT_TOK * 8;
-      const uint32_t p_b = smem_u32(p_s) + (uint32_t)((g < dm.n_rep ? g : 0) * CHUNK_TOK + ti * VT_TOK) * 2u;
+      const uint32_t p_b = smem_u32(p_s) + (uint32_t)((g < dm.n_rep ? g : 0) * P_PITCH + ti * VT_TOK) * 2u;
 
       const int nt_tile = min(VT_TOK, dm.t_vis - vt * VT_TOK);
       if (!std::is_same<T, __half>::value) {
