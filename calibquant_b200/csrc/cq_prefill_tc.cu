@@ -1,13 +1,15 @@
 // Dense causal prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
 //
-// One CTA = 128 queries of one (batch, query head).  Warp 4 (one elected lane) is the producer and
+// One CTA = 128 queries of one (batch, query head).  Warp 8 (one elected lane) is the producer and
 // the MMA issuer: it streams 128-key K/V tiles through a two-stage shared-memory ring with tiled
 // TMA loads and issues
-//     S  = Q K^T      tcgen05.mma kind::f16, A = Q (K-major), B = K (K-major), D in TMEM cols [0,128)
+//     S  = Q K^T      tcgen05.mma kind::f16, A = Q (K-major), B = K (K-major), D in TMEM columns
+//                     [0,128) / [128,256) alternately, so S(j+1) is computed while tile j is in softmax
 //     PV = P V        A = P (K-major, written by the softmax warps), B = V (MN-major), D in TMEM
-//                     cols [128,256)
-// Warps 0-3 own one query row per thread: they read S from TMEM (tcgen05.ld), apply scale, causal
-// mask and the online softmax, write P (16-bit) into the swizzled A-operand layout, and fold each
+//                     columns [256,384)
+// Warps 0-7 are the softmax warps: thread = (query row, 64-column half).  They read S from TMEM
+// (tcgen05.ld), apply scale, causal mask and the online softmax (the row maximum of the two halves
+// meets in shared memory), write P (16-bit) into the swizzled A-operand layout, and fold each
 // tile's PV into fp32 accumulators held in registers (o = o*alpha + pv), so TMEM is never written
 // by threads.  All operand tiles use the 128-byte swizzle: a [128 rows x 64 elements] TMA box lands
 // directly in the canonical UMMA layout (8-row atoms of 1024 bytes).
@@ -29,9 +31,9 @@ constexpr int BM = 128, BN = 128;
 constexpr int PANEL_BYTES = 128 * 128;          // [128 rows][64 x 16-bit]
 constexpr int TILE_BYTES = 2 * PANEL_BYTES;     // [128 rows][128 x 16-bit]
 constexpr int SMEM_BYTES = TILE_BYTES * 6 + 1024;   // Q, K x2, V x2, P (+ alignment slack)
-constexpr int THREADS = 160;
+constexpr int SOFTMAX_THREADS = 256, MMA_WARP = 8, THREADS = SOFTMAX_THREADS + 32;
 constexpr uint32_t WAIT_TRIES = 1u << 22;
-constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t TMEM_COLS = 512;          // S x2 (double-buffered) + PV; allocations are powers of two
 
 struct Params {
   void* out;
@@ -95,6 +97,12 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   return d;
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
   if (is_bf16) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
@@ -113,9 +121,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   unsigned char* k_s = q_s + TILE_BYTES;        // 2 stages
   unsigned char* v_s = k_s + 2 * TILE_BYTES;    // 2 stages
   unsigned char* p_s = v_s + 2 * TILE_BYTES;
-  __shared__ __align__(8) uint64_t bar_q, bar_kv_full[2], bar_kv_free[2], bar_s, bar_p, bar_pv;
+  __shared__ __align__(8) uint64_t bar_q, bar_kv_full[2], bar_kv_free[2], bar_s[2], bar_p, bar_pv;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int fail_s;
+  __shared__ float half_max_s[2][BM];           // per-row maximum of each 64-column half
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qt = gridDim.x - 1 - blockIdx.x;
@@ -126,21 +134,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   if (tid == 0) {
     mbar_init(&bar_q, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&bar_kv_full[s], 1); mbar_init(&bar_kv_free[s], 1); }
-    mbar_init(&bar_s, 1);
-    mbar_init(&bar_p, 128);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar_kv_full[s], 1);
+      mbar_init(&bar_kv_free[s], 1);
+      mbar_init(&bar_s[s], 1);
+    }
+    mbar_init(&bar_p, SOFTMAX_THREADS);
     mbar_init(&bar_pv, 1);
-    fail_s = 0;
     mbar_fence_init();
   }
-  if (warp == 4) tmem_alloc(&tmem_base_s, TMEM_COLS);
+  if (warp == MMA_WARP) tmem_alloc(&tmem_base_s, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tmem_S = tmem, tmem_PV = tmem + 128;
+  const uint32_t tmem_PV = tmem + 256;          // S buffers at columns [0,128) and [128,256)
 
-  if (warp == 4) {
+  if (warp == MMA_WARP) {
     // ================= producer + MMA issuer (one lane) =================
     if (lane == 0) {
       auto load_kv = [&](int j) {
@@ -151,72 +161,82 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tma_load_4d(v_s + s * TILE_BYTES, &tm_v, 0, hk, j * BN, b, &bar_kv_full[s]);
         tma_load_4d(v_s + s * TILE_BYTES + PANEL_BYTES, &tm_v, 64, hk, j * BN, b, &bar_kv_full[s]);
       };
+      const uint32_t qa = smem_u32(q_s), pa = smem_u32(p_s);
+      auto issue_s = [&](int j) -> bool {       // S(j) = Q K(j)^T into S buffer j&1
+        const int s = j & 1;
+        if (!mbar_wait_bounded(&bar_kv_full[s], (uint32_t)((j >> 1) & 1), WAIT_TRIES)) return false;
+        tc_fence_after();
+        const uint32_t ka = smem_u32(k_s + s * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {        // 16 channels per step; panel = ks/4, 32 B per step
+          const uint32_t off = (uint32_t)((ks >> 2) * PANEL_BYTES + (ks & 3) * 32);
+          umma(tmem + (uint32_t)s * 128u, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024),
+               p.idesc_s, ks > 0);
+        }
+        umma_commit(&bar_s[s]);
+        return true;
+      };
       mbar_expect_tx(&bar_q, TILE_BYTES);
       tma_load_4d(q_s, &tm_q, 0, h, q0, b, &bar_q);
       tma_load_4d(q_s + PANEL_BYTES, &tm_q, 64, h, q0, b, &bar_q);
       load_kv(0);
-      if (n_tiles > 1) load_kv(1);   // tile j+1 is loaded during iteration j from j = 1 on
+      if (n_tiles > 1) load_kv(1);
       bool ok = mbar_wait_bounded(&bar_q, 0, WAIT_TRIES);
-      const uint32_t qa = smem_u32(q_s), pa = smem_u32(p_s);
+      ok = ok && issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
-        const uint32_t ka = smem_u32(k_s + s * TILE_BYTES), va = smem_u32(v_s + s * TILE_BYTES);
-        ok = mbar_wait_bounded(&bar_kv_full[s], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
-        if (!ok) break;
-        tc_fence_after();
-        // S = Q K^T : 8 k-steps of 16 channels; channel panel = ks/4, 32 bytes per step inside it
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (uint32_t)((ks >> 2) * PANEL_BYTES + (ks & 3) * 32);
-          umma(tmem_S, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), p.idesc_s, ks > 0);
-        }
-        umma_commit(&bar_s);
-        // refill the other stage (tile j-1's) while S(j) runs: its MMAs were committed last iteration
-        if (j >= 1 && j + 1 < n_tiles) {
-          ok = mbar_wait_bounded(&bar_kv_free[s ^ 1], (uint32_t)(((j - 1) >> 1) & 1), WAIT_TRIES);
+        // S(j+1) goes to the other S buffer as soon as its K tile is there: the softmax warps
+        // released that buffer when they signalled P(j-1), which was waited for last iteration
+        if (j + 1 < n_tiles) {
+          ok = issue_s(j + 1);
           if (!ok) break;
-          load_kv(j + 1);
         }
-        // PV = P V once the softmax warps have written P
         ok = mbar_wait_bounded(&bar_p, (uint32_t)(j & 1), WAIT_TRIES);
         if (!ok) break;
         tc_fence_after();
+        const uint32_t va = smem_u32(v_s + s * TILE_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {       // 16 keys per step
+        for (int ks = 0; ks < 8; ++ks) {        // PV(j): 16 keys per step
           const uint64_t ad = smem_desc(pa + (uint32_t)((ks >> 2) * PANEL_BYTES + (ks & 3) * 32), 16, 1024);
           const uint64_t bd = smem_desc(va + (uint32_t)(ks * 2048), PANEL_BYTES, 1024);
           umma(tmem_PV, ad, bd, p.idesc_pv, ks > 0);
         }
         umma_commit(&bar_pv);
         umma_commit(&bar_kv_free[s]);
+        if (j + 2 < n_tiles) {                  // refill this stage once its MMAs have drained
+          ok = mbar_wait_bounded(&bar_kv_free[s], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
+          if (!ok) break;
+          load_kv(j + 2);
+        }
       }
-      if (!ok) {
-        atomicExch(p.status, CQ_ERR_TIMEOUT);
-        atomicExch(&fail_s, 1);
-      }
+      if (!ok) atomicExch(p.status, CQ_ERR_TIMEOUT);
     }
     __syncwarp();
   } else {
-    // ================= softmax + accumulation: one query row per thread =================
-    const int row = q0 + tid;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-    float o[128];
+    // ===== softmax + accumulation: thread = (query row, 64-column half); 8 warps =====
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r_in = quarter * 32 + lane;               // row inside the tile = TMEM lane
+    const int row = q0 + r_in;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const uint32_t col0 = (uint32_t)half * 64u;
+    float o[64];
 #pragma unroll
-    for (int i = 0; i < 128; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;               // l_run: sum over this thread's columns only
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int key0 = j * BN;
-      const bool need_mask = (key0 + BN - 1 > q0) || (key0 + BN > p.t_len);
-      ok = mbar_wait_bounded(&bar_s, (uint32_t)(j & 1), WAIT_TRIES);
+      const int key0 = j * BN + (int)col0;
+      const bool need_mask = (j * BN + BN - 1 > q0) || (j * BN + BN > p.t_len);
+      const uint32_t tS = tmem + (uint32_t)(j & 1) * 128u + lane_off + col0;
+      ok = mbar_wait_bounded(&bar_s[j & 1], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
       if (!ok) break;
       tc_fence_after();
-      // pass 1: row maximum
+      // pass 1: maximum of this half of the row, exchanged with the other half through smem
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t r[32];
-        tmem_ld32(tmem_S + lane_off + cc * 32, r);
+        tmem_ld32(tS + cc * 32, r);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float v = __uint_as_float(r[i]);
@@ -227,21 +247,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           mx = fmaxf(mx, v);
         }
       }
+      half_max_s[half][r_in] = mx;
+      asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
+      mx = fmaxf(mx, half_max_s[half ^ 1][r_in]);
       const float m_new = fmaxf(m_run, mx * p.scale_log2);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = exp2f(m_run - m_use);
       m_run = m_new;
-      // pass 2: probabilities -> shared memory (A operand layout), row sum
+      // pass 2: probabilities of this half -> its 64-key panel of P (A-operand layout), row sum
       float rs = 0.f;
+      unsigned char* prow = p_s + half * PANEL_BYTES + r_in * 128;
 #pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t r[32];
-        tmem_ld32(tmem_S + lane_off + cc * 32, r);
+        tmem_ld32(tS + cc * 32, r);
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float v0 = __uint_as_float(r[i]), v1 = __uint_as_float(r[i + 1]);
-          float p0 = exp2f(fmaf(v0, p.scale_log2, -m_use)), p1 = exp2f(fmaf(v1, p.scale_log2, -m_use));
+          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_use));
+          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_use));
           if (need_mask) {
             const int key = key0 + cc * 32 + i;
             if (key > row || key >= p.t_len) p0 = 0.f;
@@ -250,11 +274,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           rs += p0 + p1;
           w[i >> 1] = pack16(p0, p1, p.is_bf16);
         }
-        // 32 keys = 4 chunks of 16 bytes in panel cc/2, chunk index (cc%2)*4 + q, XOR row%8
-        unsigned char* prow = p_s + (cc >> 1) * PANEL_BYTES + tid * 128;
 #pragma unroll
         for (int qd = 0; qd < 4; ++qd) {
-          const int chunk = ((cc & 1) * 4 + qd) ^ (tid & 7);
+          const int chunk = (cc * 4 + qd) ^ (r_in & 7);
           *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(w[4 * qd], w[4 * qd + 1], w[4 * qd + 2], w[4 * qd + 3]);
         }
       }
@@ -262,27 +284,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       fence_proxy_async_smem();        // P (generic-proxy writes) must be visible to the MMA (async proxy)
       tc_fence_before();
       mbar_arrive(&bar_p);
-      // fold PV of this tile into the register accumulators
+      // fold this thread's 64 output columns of PV(j) into the register accumulators
       ok = mbar_wait_bounded(&bar_pv, (uint32_t)(j & 1), WAIT_TRIES);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
+      for (int cc = 0; cc < 2; ++cc) {
         uint32_t r[32];
-        tmem_ld32(tmem_PV + lane_off + cc * 32, r);
+        tmem_ld32(tmem_PV + lane_off + col0 + cc * 32, r);
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[cc * 32 + i] = fmaf(o[cc * 32 + i], alpha, __uint_as_float(r[i]));
       }
       tc_fence_before();
     }
+    // the row sum is split over the two halves
+    half_max_s[half][r_in] = l_run;
+    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
+    const float l_tot = l_run + half_max_s[half ^ 1][r_in];
     if (!ok) {
       atomicExch(p.status, CQ_ERR_TIMEOUT);
     } else if (row < p.t_len) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
       unsigned char* dst = reinterpret_cast<unsigned char*>(p.out) +
-                           2 * ((int64_t)b * p.o_sb + (int64_t)row * p.o_st + (int64_t)h * p.o_sh);
+                           2 * ((int64_t)b * p.o_sb + (int64_t)row * p.o_st + (int64_t)h * p.o_sh) + col0 * 2;
 #pragma unroll
-      for (int i = 0; i < 128; i += 8) {
+      for (int i = 0; i < 64; i += 8) {
         uint4 w;
         w.x = pack16(o[i] * inv, o[i + 1] * inv, p.is_bf16);
         w.y = pack16(o[i + 2] * inv, o[i + 3] * inv, p.is_bf16);
@@ -294,7 +320,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, TMEM_COLS);
+  if (warp == MMA_WARP) tmem_dealloc(tmem, TMEM_COLS);
 }
 
 // ---- host ---------------------------------------------------------------------------------------
