@@ -35,33 +35,86 @@ __device__ __forceinline__ unsigned quantize_one(float x, float mn, float scale,
   return (unsigned)__float2int_rn(y);
 }
 
+// ---- 1- and 2-bit codes without a division ------------------------------------------------------
+// rint(clamp(rnd(d/scale))) >= k+1 exactly when the real quotient d/scale lies above the break
+// point c_k (see quotient()): c_0 = 1/2 + u/4, c_1 = 3/2 - u/2, c_2 = 5/2 + u, u = 2^-p the unit
+// of the data type in [1,2) (p = 10 for fp16, 7 for bf16).  c_k has at most p+3 significant bits and
+// scale at most p+1, so c_k*scale is exact in fp32 (2p+4 <= 24 bits), and d, being a number of the
+// data type, exceeds it exactly when it exceeds the largest data-type number below it.  So
+//     code = sum_k [ d > floor_T(c_k * scale) ]
+// with one packed 16-bit compare per threshold and two elements.
+template <typename T> struct Pk;
+template <> struct Pk<__half> {
+  using T2 = __half2;
+  static constexpr float U = 0.0009765625f;    // 2^-10
+  static __device__ __forceinline__ T2 floor2(float v) { const __half h = __float2half_rz(v); return __halves2half2(h, h); }
+  static __device__ __forceinline__ T2 pair(float a, float b) { return __halves2half2(__float2half_rz(a), __float2half_rz(b)); }
+  static __device__ __forceinline__ T2 bcast(float v) { return __float2half2_rn(v); }
+  static __device__ __forceinline__ T2 pair_rn(float a, float b) { return __floats2half2_rn(a, b); }
+  static __device__ __forceinline__ T2 magic() { return __float2half2_rn(1024.f); }
+};
+template <> struct Pk<__nv_bfloat16> {
+  using T2 = __nv_bfloat162;
+  static constexpr float U = 0.0078125f;       // 2^-7
+  static __device__ __forceinline__ T2 floor2(float v) { const __nv_bfloat16 h = __float2bfloat16_rz(v); return __halves2bfloat162(h, h); }
+  static __device__ __forceinline__ T2 pair(float a, float b) { return __halves2bfloat162(__float2bfloat16_rz(a), __float2bfloat16_rz(b)); }
+  static __device__ __forceinline__ T2 bcast(float v) { return __float2bfloat162_rn(v); }
+  static __device__ __forceinline__ T2 pair_rn(float a, float b) { return __floats2bfloat162_rn(a, b); }
+  static __device__ __forceinline__ T2 magic() { return __float2bfloat162_rn(128.f); }
+};
+
+template <typename T> __device__ __forceinline__ float break_point(int k) {
+  return k == 0 ? 0.5f + 0.25f * Pk<T>::U : (k == 1 ? 1.5f - 0.5f * Pk<T>::U : 2.5f + Pk<T>::U);
+}
+
+// codes of two elements (low half -> bits [0,BITS), high half -> bits [16,16+BITS)) of d2 = x - mn
+template <typename T, int BITS>
+__device__ __forceinline__ unsigned codes2(typename Pk<T>::T2 d2, const typename Pk<T>::T2 (&thr)[3]) {
+  if (BITS == 1) return __hgt2_mask(d2, thr[0]) & 0x00010001u;
+  typename Pk<T>::T2 c = __hadd2(__hadd2(__hgt2(d2, thr[0]), __hgt2(d2, thr[1])), __hgt2(d2, thr[2]));
+  c = __hadd2(c, Pk<T>::magic());          // 0..3 as integers in the low mantissa bits
+  return *reinterpret_cast<unsigned*>(&c) & 0x00030003u;
+}
+
 // ---- rows of L contiguous elements; a thread owns 8 consecutive elements (one 128-bit load),
 // ---- four neighbouring lanes own one group of 32.
+constexpr int PACK_CHUNKS_PER_THREAD = 4;   // independent 128-bit loads in flight per thread
+
+template <typename T, int BITS>
+__device__ __forceinline__ void pack_chunk(const uint4& raw, int64_t chunk, bool live,
+                                           int32_t* __restrict__ code, T* __restrict__ scale_out,
+                                           T* __restrict__ mn_out);
+
 template <typename T, int BITS>
 __global__ void __launch_bounds__(256)
 pack_last_dim_kernel(const T* __restrict__ data, int64_t n_chunks, int32_t* __restrict__ code,
                      T* __restrict__ scale_out, T* __restrict__ mn_out) {
+  uint4 raw[PACK_CHUNKS_PER_THREAD];
+  int64_t chunk[PACK_CHUNKS_PER_THREAD];
+#pragma unroll
+  for (int k = 0; k < PACK_CHUNKS_PER_THREAD; ++k) {
+    chunk[k] = ((int64_t)blockIdx.x * PACK_CHUNKS_PER_THREAD + k) * blockDim.x + threadIdx.x;
+    raw[k] = make_uint4(0, 0, 0, 0);
+    if (chunk[k] < n_chunks) raw[k] = __ldg(reinterpret_cast<const uint4*>(data) + chunk[k]);
+  }
+#pragma unroll
+  for (int k = 0; k < PACK_CHUNKS_PER_THREAD; ++k)
+    pack_chunk<T, BITS>(raw[k], chunk[k], chunk[k] < n_chunks, code, scale_out, mn_out);
+}
+
+template <typename T, int BITS>
+__device__ __forceinline__ void pack_chunk(const uint4& raw, int64_t chunk, bool live,
+                                           int32_t* __restrict__ code, T* __restrict__ scale_out,
+                                           T* __restrict__ mn_out) {
+  // n_chunks is a multiple of 4, so the four lanes of a group are live or dead together
+  using T2 = typename Pk<T>::T2;
   constexpr int LEVELS = (1 << BITS) - 1;
-  const int64_t chunk = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const bool live = chunk < n_chunks;   // n_chunks is a multiple of 4, so quads are uniform
-  uint4 raw = make_uint4(0, 0, 0, 0);
-  if (live) raw = __ldg(reinterpret_cast<const uint4*>(data) + chunk);
-  float x[8];
-  {
-    const typename Elem<T>::T2* p = reinterpret_cast<const typename Elem<T>::T2*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 f = Elem<T>::to_f2(p[i]);
-      x[2 * i] = f.x;
-      x[2 * i + 1] = f.y;
-    }
-  }
-  float mn = x[0], mx = x[0];
-#pragma unroll
-  for (int i = 1; i < 8; ++i) {
-    mn = fminf(mn, x[i]);
-    mx = fmaxf(mx, x[i]);
-  }
+  const T2* xv = reinterpret_cast<const T2*>(&raw);
+  // min / max of the 8 elements in packed 16-bit arithmetic (exact), then across the quad
+  T2 mn2 = __hmin2(__hmin2(xv[0], xv[1]), __hmin2(xv[2], xv[3]));
+  T2 mx2 = __hmax2(__hmax2(xv[0], xv[1]), __hmax2(xv[2], xv[3]));
+  const float2 fmn = Elem<T>::to_f2(mn2), fmx = Elem<T>::to_f2(mx2);
+  float mn = fminf(fmn.x, fmn.y), mx = fmaxf(fmx.x, fmx.y);
   mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 1));
   mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
   mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 2));
@@ -70,9 +123,25 @@ pack_last_dim_kernel(const T* __restrict__ data, int64_t n_chunks, int32_t* __re
   group_params<T>(mn, mx, LEVELS, scale);
   unsigned local = 0;
   if (mx != mn) {
-    const float rcp = __frcp_rn(scale);
+    if (BITS <= 2) {
+      T2 thr[3];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) local |= quantize_one<T>(x[i], mn, scale, rcp, LEVELS) << (i * BITS);
+      for (int k = 0; k < 3; ++k) thr[k] = Pk<T>::floor2(break_point<T>(k) * scale);
+      const T2 mnb = Pk<T>::bcast(mn);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const unsigned c = codes2<T, BITS>(__hsub2(xv[i], mnb), thr);   // x - mn: one rounding, as the reference
+        local |= ((c & 0xffffu) | (c >> (16 - BITS))) << (2 * i * BITS);
+      }
+    } else {
+      const float rcp = __frcp_rn(scale);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = Elem<T>::to_f2(xv[i]);
+        local |= quantize_one<T>(f.x, mn, scale, rcp, LEVELS) << (2 * i * BITS);
+        local |= quantize_one<T>(f.y, mn, scale, rcp, LEVELS) << ((2 * i + 1) * BITS);
+      }
+    }
   }
   // BITS*8 bits per thread; 32/(BITS*8) threads make one word.
   constexpr int THREADS_PER_WORD = 4 / BITS;   // 4, 2, 1
@@ -92,7 +161,8 @@ pack_last_dim_kernel(const T* __restrict__ data, int64_t n_chunks, int32_t* __re
 }
 
 // ---- K per channel, transpose fused: a CTA stages 128 tokens x 128 channels in shared memory
-// ---- with coalesced 128-bit loads, then each thread walks 32 tokens of two adjacent channels.
+// ---- with coalesced 128-bit loads, then each thread walks 32 tokens of two adjacent channels
+// ---- (one packed 16-bit pair per token).
 constexpr int KT_TOKENS = 128;
 
 template <typename T, int BITS>
@@ -101,6 +171,7 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
                           int64_t stride_b, int64_t stride_h, int64_t stride_t,
                           int32_t* __restrict__ code, T* __restrict__ scale_out,
                           T* __restrict__ mn_out) {
+  using T2 = typename Pk<T>::T2;
   constexpr int LEVELS = (1 << BITS) - 1;
   constexpr int FPI = 32 / BITS;
   constexpr int WORDS_PER_GROUP = BITS;  // 32 tokens * BITS / 32
@@ -124,41 +195,56 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
   const int gq = threadIdx.x / 64;        // group (of 32 tokens) inside the tile
   const int cp = threadIdx.x % 64;        // channel pair
   if (gq * 32 >= n_tok) return;
-  float xa[32], xb[32];
+  T2 xv[32];
 #pragma unroll
-  for (int t = 0; t < 32; ++t) {
-    float2 f = Elem<T>::to_f2(*reinterpret_cast<const typename Elem<T>::T2*>(&tile[gq * 32 + t][cp * 2]));
-    xa[t] = f.x;
-    xb[t] = f.y;
+  for (int t = 0; t < 32; ++t) xv[t] = *reinterpret_cast<const T2*>(&tile[gq * 32 + t][cp * 2]);
+  T2 mn2 = xv[0], mx2 = xv[0];
+#pragma unroll
+  for (int t = 1; t < 32; ++t) {
+    mn2 = __hmin2(mn2, xv[t]);
+    mx2 = __hmax2(mx2, xv[t]);
+  }
+  const float2 fmn = Elem<T>::to_f2(mn2), fmx = Elem<T>::to_f2(mx2);
+  float scale[2];
+  group_params<T>(fmn.x, fmx.x, LEVELS, scale[0]);
+  group_params<T>(fmn.y, fmx.y, LEVELS, scale[1]);
+  const bool constant[2] = {fmx.x == fmn.x, fmx.y == fmn.y};
+  unsigned words[2][WORDS_PER_GROUP];
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+#pragma unroll
+    for (int w = 0; w < WORDS_PER_GROUP; ++w) words[c][w] = 0u;
+
+  if (BITS <= 2) {
+    T2 thr[3];
+#pragma unroll
+    for (int kk = 0; kk < 3; ++kk) thr[kk] = Pk<T>::pair(break_point<T>(kk) * scale[0], break_point<T>(kk) * scale[1]);
+#pragma unroll
+    for (int t = 0; t < 32; ++t) {
+      const unsigned c = codes2<T, BITS>(__hsub2(xv[t], mn2), thr);
+      words[0][t / FPI] |= (c & 0xffffu) << ((t % FPI) * BITS);
+      words[1][t / FPI] |= (c >> 16) << ((t % FPI) * BITS);
+    }
+  } else {
+    const float mnf[2] = {fmn.x, fmn.y};
+    const float rcp[2] = {__frcp_rn(scale[0]), __frcp_rn(scale[1])};
+#pragma unroll
+    for (int t = 0; t < 32; ++t) {
+      const float2 f = Elem<T>::to_f2(xv[t]);
+      words[0][t / FPI] |= quantize_one<T>(f.x, mnf[0], scale[0], rcp[0], LEVELS) << ((t % FPI) * BITS);
+      words[1][t / FPI] |= quantize_one<T>(f.y, mnf[1], scale[1], rcp[1], LEVELS) << ((t % FPI) * BITS);
+    }
   }
   const int64_t G = t0 / 32 + gq;
   const int64_t n_groups = T_len / 32;
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
-    float* x = c == 0 ? xa : xb;
-    float mn = x[0], mx = x[0];
-#pragma unroll
-    for (int t = 1; t < 32; ++t) {
-      mn = fminf(mn, x[t]);
-      mx = fmaxf(mx, x[t]);
-    }
-    float scale;
-    group_params<T>(mn, mx, LEVELS, scale);
     const int64_t row = (int64_t)bh * kHeadDim + cp * 2 + c;
-    const bool constant = (mx == mn);
-    const float rcp = __frcp_rn(scale);
 #pragma unroll
-    for (int w = 0; w < WORDS_PER_GROUP; ++w) {
-      unsigned word = 0;
-      if (!constant) {
-#pragma unroll
-        for (int i = 0; i < FPI; ++i)
-          word |= quantize_one<T>(x[w * FPI + i], mn, scale, rcp, LEVELS) << (i * BITS);
-      }
-      code[row * (n_groups * WORDS_PER_GROUP) + G * WORDS_PER_GROUP + w] = (int32_t)word;
-    }
-    scale_out[row * n_groups + G] = Elem<T>::from_f(scale);
-    mn_out[row * n_groups + G] = Elem<T>::from_f(mn);
+    for (int w = 0; w < WORDS_PER_GROUP; ++w)
+      code[row * (n_groups * WORDS_PER_GROUP) + G * WORDS_PER_GROUP + w] = (int32_t)(constant[c] ? 0u : words[c][w]);
+    scale_out[row * n_groups + G] = Elem<T>::from_f(scale[c]);
+    mn_out[row * n_groups + G] = c == 0 ? Elem<T>::from_f(fmn.x) : Elem<T>::from_f(fmn.y);
   }
 }
 
@@ -166,7 +252,8 @@ template <typename T>
 int launch_pack_last_dim(const void* data, int64_t rows, int64_t L, int bits, int32_t* code,
                          void* scale, void* mn, cudaStream_t st) {
   const int64_t n_chunks = rows * L / 8;
-  const int64_t blocks = (n_chunks + 255) / 256;
+  const int64_t per_block = 256 * PACK_CHUNKS_PER_THREAD;
+  const int64_t blocks = (n_chunks + per_block - 1) / per_block;
   if (blocks > 0x7fffffffLL) return CQ_ERR_UNSUPPORTED;
   const T* d = static_cast<const T*>(data);
   T* s = static_cast<T*>(scale);
