@@ -160,10 +160,13 @@ __device__ __forceinline__ void pack_chunk(const uint4& raw, int64_t chunk, bool
   }
 }
 
-// ---- K per channel, transpose fused: a CTA stages 128 tokens x 128 channels in shared memory
-// ---- with coalesced 128-bit loads, then each thread walks 32 tokens of two adjacent channels
-// ---- (one packed 16-bit pair per token).
+// ---- K per channel, transpose fused.  A CTA walks a span of 512 tokens (256 at 4 bits) of one
+// ---- (batch, head) in sub-tiles of 128 tokens x 128 channels: coalesced 128-bit loads into shared
+// ---- memory, then each thread reduces 32 tokens of two adjacent channels (one packed 16-bit pair
+// ---- per token).  Words, scales and minima of the span collect in shared memory and leave with
+// ---- the lanes running along each channel's row, so a store instruction covers whole sectors.
 constexpr int KT_TOKENS = 128;
+__host__ __device__ constexpr int kt_span(int bits) { return bits == 4 ? 256 : 512; }
 
 template <typename T, int BITS>
 __global__ void __launch_bounds__(256)
@@ -174,77 +177,116 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
   using T2 = typename Pk<T>::T2;
   constexpr int LEVELS = (1 << BITS) - 1;
   constexpr int FPI = 32 / BITS;
-  constexpr int WORDS_PER_GROUP = BITS;  // 32 tokens * BITS / 32
-  __shared__ __align__(16) T tile[KT_TOKENS][kHeadDim];
+  constexpr int WORDS_PER_GROUP = BITS;      // 32 tokens * BITS / 32
+  constexpr int SPAN = kt_span(BITS);
+  constexpr int SPAN_GROUPS = SPAN / 32;
+  constexpr int WPR = SPAN_GROUPS * BITS;    // code words per channel row per span
+  constexpr int CP = WPR + 1, SP = SPAN_GROUPS + 2;    // padded row pitches: rows on different banks
+  extern __shared__ __align__(16) unsigned char pack_smem[];
+  T (*tile)[kHeadDim] = reinterpret_cast<T (*)[kHeadDim]>(pack_smem);
+  unsigned (*code_s)[CP] = reinterpret_cast<unsigned (*)[CP]>(pack_smem + KT_TOKENS * kHeadDim * sizeof(T));
+  T (*scale_s)[SP] = reinterpret_cast<T (*)[SP]>(pack_smem + KT_TOKENS * kHeadDim * sizeof(T) + kHeadDim * CP * 4);
+  T (*mn_s)[SP] = scale_s + kHeadDim;
 
   const int bh = blockIdx.y;
   const int b = bh / heads, h = bh % heads;
-  const int64_t t0 = (int64_t)blockIdx.x * KT_TOKENS;
+  const int64_t span0 = (int64_t)blockIdx.x * SPAN;
   const T* src = k + b * stride_b + h * stride_h;
-  const int n_tok = (int)min((int64_t)KT_TOKENS, T_len - t0);   // multiple of 32
+  const int span_tok = (int)min((int64_t)SPAN, T_len - span0);   // multiple of 32
+  const int gq = threadIdx.x / 64;        // group (of 32 tokens) inside the sub-tile
+  const int cp = threadIdx.x % 64;        // channel pair
 
-  for (int i = threadIdx.x; i < KT_TOKENS * (kHeadDim / 8); i += blockDim.x) {
-    const int row = i / (kHeadDim / 8), col = i % (kHeadDim / 8);
-    if (row < n_tok) {
-      uint4 v = __ldg(reinterpret_cast<const uint4*>(src + (t0 + row) * stride_t) + col);
-      *reinterpret_cast<uint4*>(&tile[row][col * 8]) = v;
+  for (int sub = 0; sub * KT_TOKENS < span_tok; ++sub) {
+    const int64_t t0 = span0 + sub * KT_TOKENS;
+    const int n_tok = min(KT_TOKENS, span_tok - sub * KT_TOKENS);
+    __syncthreads();                       // previous sub-tile fully consumed
+    {
+      // 2048 16-byte pieces, 8 per thread: all loads are issued before the first store
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * 256;
+        const int row = i / (kHeadDim / 8), col = i % (kHeadDim / 8);
+        v[j] = make_uint4(0, 0, 0, 0);
+        if (row < n_tok) v[j] = __ldg(reinterpret_cast<const uint4*>(src + (t0 + row) * stride_t) + col);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * 256;
+        *reinterpret_cast<uint4*>(&tile[i / (kHeadDim / 8)][(i % (kHeadDim / 8)) * 8]) = v[j];
+      }
+    }
+    __syncthreads();
+    if (gq * 32 >= n_tok) continue;
+
+    T2 xv[32];
+#pragma unroll
+    for (int t = 0; t < 32; ++t) xv[t] = *reinterpret_cast<const T2*>(&tile[gq * 32 + t][cp * 2]);
+    T2 mn2 = xv[0], mx2 = xv[0];
+#pragma unroll
+    for (int t = 1; t < 32; ++t) {
+      mn2 = __hmin2(mn2, xv[t]);
+      mx2 = __hmax2(mx2, xv[t]);
+    }
+    const float2 fmn = Elem<T>::to_f2(mn2), fmx = Elem<T>::to_f2(mx2);
+    float scale[2];
+    group_params<T>(fmn.x, fmx.x, LEVELS, scale[0]);
+    group_params<T>(fmn.y, fmx.y, LEVELS, scale[1]);
+    const bool constant[2] = {fmx.x == fmn.x, fmx.y == fmn.y};
+    unsigned words[2][WORDS_PER_GROUP];
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int w = 0; w < WORDS_PER_GROUP; ++w) words[c][w] = 0u;
+
+    if (BITS <= 2) {
+      T2 thr[3];
+#pragma unroll
+      for (int kk = 0; kk < 3; ++kk)
+        thr[kk] = Pk<T>::pair(break_point<T>(kk) * scale[0], break_point<T>(kk) * scale[1]);
+#pragma unroll
+      for (int t = 0; t < 32; ++t) {
+        const unsigned c = codes2<T, BITS>(__hsub2(xv[t], mn2), thr);
+        words[0][t / FPI] |= (c & 0xffffu) << ((t % FPI) * BITS);
+        words[1][t / FPI] |= (c >> 16) << ((t % FPI) * BITS);
+      }
+    } else {
+      const float mnf[2] = {fmn.x, fmn.y};
+      const float rcp[2] = {__frcp_rn(scale[0]), __frcp_rn(scale[1])};
+#pragma unroll
+      for (int t = 0; t < 32; ++t) {
+        const float2 f = Elem<T>::to_f2(xv[t]);
+        words[0][t / FPI] |= quantize_one<T>(f.x, mnf[0], scale[0], rcp[0], LEVELS) << ((t % FPI) * BITS);
+        words[1][t / FPI] |= quantize_one<T>(f.y, mnf[1], scale[1], rcp[1], LEVELS) << ((t % FPI) * BITS);
+      }
+    }
+    const int gs = sub * (KT_TOKENS / 32) + gq;            // group inside the span
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+      for (int w = 0; w < WORDS_PER_GROUP; ++w)
+        code_s[cp * 2 + c][gs * WORDS_PER_GROUP + w] = constant[c] ? 0u : words[c][w];
+      scale_s[cp * 2 + c][gs] = Elem<T>::from_f(scale[c]);
+      mn_s[cp * 2 + c][gs] = Elem<T>::from_f(c == 0 ? fmn.x : fmn.y);
     }
   }
   __syncthreads();
 
-  const int gq = threadIdx.x / 64;        // group (of 32 tokens) inside the tile
-  const int cp = threadIdx.x % 64;        // channel pair
-  if (gq * 32 >= n_tok) return;
-  T2 xv[32];
-#pragma unroll
-  for (int t = 0; t < 32; ++t) xv[t] = *reinterpret_cast<const T2*>(&tile[gq * 32 + t][cp * 2]);
-  T2 mn2 = xv[0], mx2 = xv[0];
-#pragma unroll
-  for (int t = 1; t < 32; ++t) {
-    mn2 = __hmin2(mn2, xv[t]);
-    mx2 = __hmax2(mx2, xv[t]);
-  }
-  const float2 fmn = Elem<T>::to_f2(mn2), fmx = Elem<T>::to_f2(mx2);
-  float scale[2];
-  group_params<T>(fmn.x, fmx.x, LEVELS, scale[0]);
-  group_params<T>(fmn.y, fmx.y, LEVELS, scale[1]);
-  const bool constant[2] = {fmx.x == fmn.x, fmx.y == fmn.y};
-  unsigned words[2][WORDS_PER_GROUP];
-#pragma unroll
-  for (int c = 0; c < 2; ++c)
-#pragma unroll
-    for (int w = 0; w < WORDS_PER_GROUP; ++w) words[c][w] = 0u;
-
-  if (BITS <= 2) {
-    T2 thr[3];
-#pragma unroll
-    for (int kk = 0; kk < 3; ++kk) thr[kk] = Pk<T>::pair(break_point<T>(kk) * scale[0], break_point<T>(kk) * scale[1]);
-#pragma unroll
-    for (int t = 0; t < 32; ++t) {
-      const unsigned c = codes2<T, BITS>(__hsub2(xv[t], mn2), thr);
-      words[0][t / FPI] |= (c & 0xffffu) << ((t % FPI) * BITS);
-      words[1][t / FPI] |= (c >> 16) << ((t % FPI) * BITS);
-    }
-  } else {
-    const float mnf[2] = {fmn.x, fmn.y};
-    const float rcp[2] = {__frcp_rn(scale[0]), __frcp_rn(scale[1])};
-#pragma unroll
-    for (int t = 0; t < 32; ++t) {
-      const float2 f = Elem<T>::to_f2(xv[t]);
-      words[0][t / FPI] |= quantize_one<T>(f.x, mnf[0], scale[0], rcp[0], LEVELS) << ((t % FPI) * BITS);
-      words[1][t / FPI] |= quantize_one<T>(f.y, mnf[1], scale[1], rcp[1], LEVELS) << ((t % FPI) * BITS);
-    }
-  }
-  const int64_t G = t0 / 32 + gq;
+  // ---- flush the span: lanes run along a channel's row
   const int64_t n_groups = T_len / 32;
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    const int64_t row = (int64_t)bh * kHeadDim + cp * 2 + c;
-#pragma unroll
-    for (int w = 0; w < WORDS_PER_GROUP; ++w)
-      code[row * (n_groups * WORDS_PER_GROUP) + G * WORDS_PER_GROUP + w] = (int32_t)(constant[c] ? 0u : words[c][w]);
-    scale_out[row * n_groups + G] = Elem<T>::from_f(scale[c]);
-    mn_out[row * n_groups + G] = c == 0 ? Elem<T>::from_f(fmn.x) : Elem<T>::from_f(fmn.y);
+  const int64_t g0 = span0 / 32;
+  const int live_groups = span_tok / 32, live_words = live_groups * WORDS_PER_GROUP;
+  const int64_t row0 = (int64_t)bh * kHeadDim;
+  for (int i = threadIdx.x; i < kHeadDim * WPR; i += 256) {
+    const int ch = i / WPR, w = i % WPR;
+    if (w < live_words) code[(row0 + ch) * (n_groups * WORDS_PER_GROUP) + g0 * WORDS_PER_GROUP + w] = (int32_t)code_s[ch][w];
+  }
+  for (int i = threadIdx.x; i < kHeadDim * SPAN_GROUPS; i += 256) {
+    const int ch = i / SPAN_GROUPS, gg = i % SPAN_GROUPS;
+    if (gg < live_groups) {
+      scale_out[(row0 + ch) * n_groups + g0 + gg] = scale_s[ch][gg];
+      mn_out[(row0 + ch) * n_groups + g0 + gg] = mn_s[ch][gg];
+    }
   }
 }
 
@@ -269,14 +311,25 @@ int launch_pack_last_dim(const void* data, int64_t rows, int64_t L, int bits, in
 template <typename T>
 int launch_pack_k(const void* k, int batch, int heads, int64_t T_len, int64_t sb, int64_t sh,
                   int64_t st_, int bits, int32_t* code, void* scale, void* mn, cudaStream_t st) {
-  dim3 grid((unsigned)((T_len + KT_TOKENS - 1) / KT_TOKENS), (unsigned)(batch * heads));
+  const int span = kt_span(bits);
+  dim3 grid((unsigned)((T_len + span - 1) / span), (unsigned)(batch * heads));
+  const int wpr = span / 32 * bits;
+  const size_t smem = (size_t)KT_TOKENS * kHeadDim * 2 + (size_t)kHeadDim * (wpr + 1) * 4 +
+                      2 * (size_t)kHeadDim * (span / 32 + 2) * 2;
+  cudaError_t e;
+  switch (bits) {
+    case 1: e = cudaFuncSetAttribute(pack_k_per_channel_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); break;
+    case 2: e = cudaFuncSetAttribute(pack_k_per_channel_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); break;
+    default: e = cudaFuncSetAttribute(pack_k_per_channel_kernel<T, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); break;
+  }
+  if (e != cudaSuccess) return CQ_ERR_LAUNCH;
   const T* d = static_cast<const T*>(k);
   T* s = static_cast<T*>(scale);
   T* m = static_cast<T*>(mn);
   switch (bits) {
-    case 1: pack_k_per_channel_kernel<T, 1><<<grid, 256, 0, st>>>(d, heads, T_len, sb, sh, st_, code, s, m); break;
-    case 2: pack_k_per_channel_kernel<T, 2><<<grid, 256, 0, st>>>(d, heads, T_len, sb, sh, st_, code, s, m); break;
-    default: pack_k_per_channel_kernel<T, 4><<<grid, 256, 0, st>>>(d, heads, T_len, sb, sh, st_, code, s, m); break;
+    case 1: pack_k_per_channel_kernel<T, 1><<<grid, 256, smem, st>>>(d, heads, T_len, sb, sh, st_, code, s, m); break;
+    case 2: pack_k_per_channel_kernel<T, 2><<<grid, 256, smem, st>>>(d, heads, T_len, sb, sh, st_, code, s, m); break;
+    default: pack_k_per_channel_kernel<T, 4><<<grid, 256, smem, st>>>(d, heads, T_len, sb, sh, st_, code, s, m); break;
   }
   return check_launch();
 }
