@@ -126,6 +126,31 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+def time_pack(batch, t_vis, bits, device, reps=5):
+    """Quantize+pack throughput (K per channel with the transpose fused, V per token) on fp16 tensors
+    of the workload's shape; two source tensors alternate so that each pass streams from HBM."""
+    from calibquant_b200 import ops
+    g = torch.Generator(device=device).manual_seed(7)
+    src = [torch.randn(batch, HKV, t_vis, D, generator=g, device=device).half() for _ in range(2)]
+    n = batch * HKV * t_vis * D
+    nbytes = n * (2 + bits / 8 + 4 / GROUP)
+    out = {}
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for name, fn in (("k_per_channel", ops.pack_k_per_channel), ("v_per_token", ops.pack_last_dim)):
+        for i in range(2):
+            fn(src[i % 2], GROUP, bits)
+        torch.cuda.synchronize()
+        ev0.record()
+        for i in range(reps):
+            fn(src[i % 2], GROUP, bits)
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1) / reps
+        out[name] = {"ms": round(ms, 4), "GBps": round(nbytes / ms / 1e6, 1)}
+    out["bytes_per_element"] = 2 + bits / 8 + 4 / GROUP
+    return out
+
+
 def build_caches(batch, t_vis, t_fp, bits, n_caches, device, seed):
     """Synthetic caches with the reference generator's value distribution (K ~ N(0,1) times a
     per-channel lognormal factor, V ~ N(0,1)), generated and packed on the device."""
@@ -217,6 +242,7 @@ def run_ours(args, rank, world, device):
         t = torch.tensor([ms, ms_e2e], device=device, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms, ms_e2e = t.tolist()
+    pack = time_pack(batch, t_vis, bits, device) if rank == 0 else None
     per_step_ms = ms / args.steps
     gbs = world * step_bytes / (per_step_ms * 1e-3) / 1e9
     gbs_e2e = world * step_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
@@ -255,6 +281,7 @@ def run_ours(args, rank, world, device):
                 "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": o_host.numel() * 2,
                 "ms_per_step": round(ms_e2e / args.steps, 5)},
         "gpu_launches": launches_per_step * args.steps,
+        "pack": pack,
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
