@@ -375,11 +375,18 @@ def run_model(args, rank, world, device):
         logits, past = lm.forward_step(emb, pos, None)
         ev[1].record()
         steps = args.steps
-        for step in range(steps):
-            nxt = logits[:, -1].argmax(-1)
-            e = lm.model.tok_embeddings(nxt).unsqueeze(1)
-            p1 = torch.full((batch, 1), T + step, device=device, dtype=torch.long)
-            logits, past = lm.forward_step(e, p1, past)
+        if args.eager:
+            for step in range(steps):
+                nxt = logits[:, -1].argmax(-1)
+                e = lm.model.tok_embeddings(nxt).unsqueeze(1)
+                p1 = torch.full((batch, 1), T + step, device=device, dtype=torch.long)
+                logits, past = lm.forward_step(e, p1, past)
+        else:
+            from calibquant_b200.internlm2 import GraphedDecoder
+            dec = GraphedDecoder(lm, past, logits[:, -1].argmax(-1), T, steps)   # capture: not timed
+            torch.cuda.synchronize()
+            ev[1].record()
+            dec.run(steps)
     ev[2].record()
     torch.cuda.synchronize()
     t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], device=device, dtype=torch.float64)
@@ -396,7 +403,8 @@ def run_model(args, rank, world, device):
                                f"{args.bits}-bit KV (group 32)",
                    "parallelism": "single GPU" if world == 1 else f"attention sharded by KV head x{world}, "
                                   "NCCL all-gather of head outputs per layer, rest replicated",
-                   "prefill_ms": round(prefill_ms, 1), "eager": "no CUDA graph"},
+                   "prefill_ms": round(prefill_ms, 1) if args.eager else None,
+                   "decode_loop": "eager launches" if args.eager else "one CUDA graph replayed per token"},
     }
 
 
@@ -412,6 +420,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--fp-tokens", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="model workloads: no CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 

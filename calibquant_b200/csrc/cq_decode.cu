@@ -451,6 +451,7 @@ extern "C" int cq_decode_attn(const cq_decode_args* args, void* workspace, size_
       return CQ_ERR_WORKSPACE;
     return cq::mma_path_run(args, workspace, st);
   }
+  if (args->t_fp_dev) return CQ_ERR_UNSUPPORTED;   // device-side token count: tensor-core path only
   const cq::DecodeDims dm = cq::make_dims(args);
   const cq::WsLayout w = cq::make_layout(dm);
   if (!workspace || workspace_bytes < w.total || !cq::aligned16(workspace)) return CQ_ERR_WORKSPACE;

@@ -64,7 +64,14 @@ struct Dims {
   int pitch;           // score row pitch in elements (multiple of 8)
   int n_mm;            // min/max entries per row: n_ktiles * 4
   int64_t fp_stride_b, fp_stride_h;
+  const int32_t* t_fp_dev;   // optional: live number of fp tokens on the device (t_fp is then the capacity)
 };
+
+// Number of full-precision tokens this launch works on: the by-value extent, or, when the caller keeps
+// the count on the device (a decode step replayed from a CUDA graph), that count clamped to it.
+__device__ __forceinline__ int live_t_fp(const Dims& dm) {
+  return dm.t_fp_dev ? min(__ldg(dm.t_fp_dev), dm.t_fp) : dm.t_fp;
+}
 
 // ---- per-lane constants for expanding packed codes into MMA A operands -------------------------
 // A lane (g = lane/4) owns rows g and g+8 of a 16-row m-tile; they are mapped to the adjacent
@@ -329,7 +336,8 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   if (failed) return;
 
   // ---- full-precision tokens: one warp per token, lane owns 4 channels ---------------------------
-  const int n_fp_tiles = (dm.t_fp + 63) / 64;
+  const int t_fp = live_t_fp(dm);
+  const int n_fp_tiles = (t_fp + 63) / 64;
   for (int it = blockIdx.x; it < n_pairs * n_fp_tiles; it += gridDim.x) {
     const int pair = it / n_fp_tiles, ft = it % n_fp_tiles;
     const int b = pair / dm.hkv, hk = pair % dm.hkv;
@@ -340,7 +348,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
     const T* kf = k_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h;
     for (int i = warp; i < 64; i += THREADS / 32) {
       const int t = ft * 64 + i;
-      if (t >= dm.t_fp) break;
+      if (t >= t_fp) break;
       const uint2 raw = __ldg(reinterpret_cast<const uint2*>(kf + (int64_t)t * kHeadDim) + lane);
       const float2 k01 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw.x));
       const float2 k23 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw.y));
@@ -652,11 +660,13 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
 
   // ---- full-precision tokens: chunks of 128, thread = channel -----------------------------------
   float* pf_s = red_s;                      // [kMaxRep][128] probabilities
-  for (int it = blockIdx.x; it < n_pairs * dm.n_fp_chunks; it += gridDim.x) {
-    const int pair = it / dm.n_fp_chunks, fc = it % dm.n_fp_chunks;
+  const int t_fp = live_t_fp(dm);
+  const int n_fp_chunks = (t_fp + 127) / 128;
+  for (int it = blockIdx.x; it < n_pairs * n_fp_chunks; it += gridDim.x) {
+    const int pair = it / n_fp_chunks, fc = it % n_fp_chunks;
     const int b = pair / dm.hkv, hk = pair % dm.hkv;
     const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
-    const int t0 = fc * 128, nt = min(128, dm.t_fp - t0);
+    const int t0 = fc * 128, nt = min(128, t_fp - t0);
     __syncthreads();
     for (int h = warp; h < dm.n_rep; h += 4) {
       const T* srow = scores + (row0 + h) * dm.pitch + dm.t_vis + t0;
@@ -710,12 +720,13 @@ k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict_
   const int64_t row = blockIdx.x;
   const int d = threadIdx.x & (kHeadDim - 1), sl = threadIdx.x >> 7;
   const float2* r = ml + row * dm.n_slots;
+  const int n_live = dm.n_chunks + (live_t_fp(dm) + 127) / 128;   // visual chunks, then fp chunks
   float M = -INFINITY;
-  for (int i = 0; i < dm.n_slots; ++i) M = fmaxf(M, __ldg(&r[i]).x);
+  for (int i = 0; i < n_live; ++i) M = fmaxf(M, __ldg(&r[i]).x);
   float L = 0.f, o = 0.f;
   const float* p = partial + row * dm.n_slots * kHeadDim + d;
 #pragma unroll 4
-  for (int i = sl; i < dm.n_slots; i += K3_LANES) {
+  for (int i = sl; i < n_live; i += K3_LANES) {
     const float2 mlv = __ldg(&r[i]);
     const float w = exp2f((mlv.x - M) * LOG2E);
     L = fmaf(mlv.y, w, L);
@@ -780,6 +791,7 @@ static Dims make_dims(const cq_decode_args* a) {
   d.pitch = (d.t_vis + d.t_fp + 7) / 8 * 8;
   d.n_mm = d.n_ktiles * 4;
   d.fp_stride_b = a->fp_stride_b; d.fp_stride_h = a->fp_stride_h;
+  d.t_fp_dev = a->t_fp_dev;
   return d;
 }
 

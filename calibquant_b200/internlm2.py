@@ -172,6 +172,67 @@ class InternLM2ForCausalLM(nn.Module):
         return torch.stack(tokens, dim=1)
 
 
+class GraphedDecoder:
+    """Greedy decoding with the whole step (embedding, all layers, logits, argmax, cache append,
+    position and length counters) captured once in a CUDA graph and replayed per token.  Everything
+    that changes from step to step lives on the device: the token, the position, and each layer's
+    text-cache length, which the attention kernels read through ``t_fp_dev``."""
+
+    def __init__(self, lm: "InternLM2ForCausalLM", past, first_token, start_pos: int, max_new_tokens: int):
+        self.lm, self.past = lm, past
+        B = first_token.shape[0]
+        dev = first_token.device
+        self.caches = [layer.attention._text_cache for layer in lm.model.layers]
+        for layer, tc in zip(lm.model.layers, self.caches):
+            tc.enable_static(tc.length + max_new_tokens + 2)
+            layer.attention._static_decode = True
+            layer.attention._static_rope_len = start_pos + max_new_tokens + 2
+        self.tok = first_token.clone()
+        self.pos = torch.full((B, 1), start_pos, device=dev, dtype=torch.long)
+        self.out = torch.zeros((max_new_tokens + 2, B), device=dev, dtype=torch.long)
+        self.step_idx = torch.zeros(1, device=dev, dtype=torch.long)
+        state0 = (self.tok.clone(), [tc.length for tc in self.caches])
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                       # warm-up outside capture, then roll back
+            for _ in range(2):
+                self._step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self._reset(state0, start_pos)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._step()
+        self._reset(state0, start_pos)
+
+    def _reset(self, state0, start_pos):
+        self.tok.copy_(state0[0])
+        self.pos.fill_(start_pos)
+        self.step_idx.zero_()
+        for tc, n in zip(self.caches, state0[1]):
+            tc.set_static_length(n)
+
+    @torch.no_grad()
+    def _step(self):
+        emb = self.lm.model.tok_embeddings(self.tok).unsqueeze(1)
+        logits, _ = self.lm.forward_step(emb, self.pos, self.past)
+        self.tok.copy_(logits[:, -1].argmax(-1))
+        self.out.index_copy_(0, self.step_idx, self.tok.unsqueeze(0))
+        self.pos += 1
+        self.step_idx += 1
+
+    def run(self, n_steps: int):
+        """Replay ``n_steps`` decode steps; returns the generated tokens [B, n_steps]."""
+        for _ in range(n_steps):
+            self.graph.replay()
+        return self.out[:n_steps].t()
+
+    def close(self):
+        for layer, tc in zip(self.lm.model.layers, self.caches):
+            layer.attention._static_decode = False
+            tc.length = int(tc.len_dev.item())
+
+
 class ChatModelShell(nn.Module):
     """Minimal stand-in for InternVLChatModel: holds ``language_model`` and ``config.llm_config``
     so that ``patch_model`` can be applied exactly as to the real model."""

@@ -134,7 +134,7 @@ def qbmm(group_size: int, fA: torch.Tensor, qB: torch.Tensor, scales: torch.Tens
 
 
 def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
-                     calibrate=None, mask=None, out=None, t_fp=None, _stages=0):
+                     calibrate=None, mask=None, out=None, t_fp=None, _stages=0, t_fp_dev=None):
     """One decode step over [sys | visual (quantized) | text].
 
     q [B,Hq,1,D] or [B,Hq,D]; k_pack/v_pack = (code, scale, mn) in the group format (K per
@@ -177,6 +177,10 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
     else:
         a.t_fp = 0
     a.t_sys = min(t_sys, a.t_fp)
+    if t_fp_dev is not None:      # int32 device scalar: live token count, a.t_fp is the capacity
+        assert t_fp_dev.dtype == torch.int32 and t_fp_dev.is_cuda
+        keep.append(t_fp_dev)
+        a.t_fp_dev = t_fp_dev.data_ptr()
     if mask is not None:
         mask = mask.reshape(B, -1)
         if mask.dtype != q.dtype or mask.stride(1) != 1:

@@ -133,6 +133,27 @@ class _TextCache:
     def views(self):
         return self.k[:, :, :self.length], self.v[:, :, :self.length]
 
+    # ---- static mode: the token count lives on the device, so that one captured CUDA graph can
+    # ---- append a token and attend over the live part at every decode step
+    def enable_static(self, capacity):
+        if capacity > self.k.shape[2]:
+            pad = torch.empty((*self.k.shape[:2], capacity - self.k.shape[2], self.k.shape[3]),
+                              dtype=self.k.dtype, device=self.k.device)
+            self.k = torch.cat([self.k, pad], dim=2)
+            self.v = torch.cat([self.v, pad.clone()], dim=2)
+        self.len_dev = torch.tensor([self.length], dtype=torch.int32, device=self.k.device)
+        self.idx_dev = torch.tensor([self.length], dtype=torch.int64, device=self.k.device)
+
+    def set_static_length(self, length):
+        self.len_dev.fill_(length)
+        self.idx_dev.fill_(length)
+
+    def append_static(self, k, v):
+        self.k.index_copy_(2, self.idx_dev, k)
+        self.v.index_copy_(2, self.idx_dev, v)
+        self.len_dev += 1
+        self.idx_dev += 1
+
 
 def _split_qkv(self, hidden_states):
     """``wqkv`` output -> q [B,q,Hq,D], k [B,q,Hkv,D], v [B,q,Hkv,D] as strided views (no copies):
@@ -213,7 +234,8 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
     kv_seq_len = q_len
     if past_key_value is not None:
         kv_seq_len += past_key_value[0].shape[-2] + (self.image_token_num if LOW_BITS else 0)
-    cos, sin = self.rotary_emb(v, seq_len=kv_seq_len)
+    static_decode = q_len == 1 and getattr(self, "_static_decode", False)
+    cos, sin = self.rotary_emb(v, seq_len=self._static_rope_len if static_decode else kv_seq_len)
     q, k = apply_rotary_pos_emb(q, k, cos, sin, position_ids)
 
     if q_len > 1:
@@ -237,6 +259,15 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
         return attn_output, None, past_key_value
 
     # ---- decode step -------------------------------------------------------------------------
+    if static_decode:
+        # graph-replayable step: append at the device-side position, attend over the live count
+        tc = self._text_cache
+        tc.append_static(k, v)
+        attn = ops.decode_attention(q, self.k_pack, self.v_pack, tc.k, tc.v, self.sprompt_len if LOW_BITS else 0,
+                                    BITS_KV, group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
+                                    t_fp_dev=tc.len_dev)
+        attn = _gather_heads(self, attn.transpose(1, 2).reshape(bsz, q_len, -1))
+        return self.wo(attn.reshape(bsz, q_len, self.hidden_size)), None, past_key_value
     self._text_cache.append(k, v)
     k_fp, v_fp = self._text_cache.views()
     past_key_value = (k_fp, v_fp) if use_cache else None

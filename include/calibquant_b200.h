@@ -151,6 +151,10 @@ typedef struct cq_decode_args {
   const void* mask;              /* optional additive mask [B, t_fp + t_vis] in `dtype`, */
   int64_t mask_stride_b;         /* key order [sys | visual | text]; NULL = none         */
   void* out;                     /* [B,Hq,D] in `dtype`                                 */
+  const int32_t* t_fp_dev;       /* optional device counter of live fp tokens: when set, t_fp is  */
+                                 /* the capacity of k_fp/v_fp and min(*t_fp_dev, t_fp) tokens are  */
+                                 /* attended; lets one captured CUDA graph serve every decode step */
+                                 /* (tensor-core path only, otherwise CQ_ERR_UNSUPPORTED)          */
 } cq_decode_args;
 
 size_t cq_decode_attn_workspace_bytes(const cq_decode_args* args);

@@ -124,3 +124,31 @@ def test_tiny_model_generates_and_is_deterministic():
     a = shell.generate(emb, image_token_num=64, max_new_tokens=5)
     b = shell.generate(emb, image_token_num=64, max_new_tokens=5)
     assert a.shape == (2, 5) and torch.equal(a, b)
+
+
+def test_graph_replayed_decode_matches_eager():
+    """The decode step captured in a CUDA graph (device-side token, position and cache-length
+    counters) must generate exactly the tokens of the eager loop."""
+    from calibquant_b200 import patch_internvl as pi
+    from calibquant_b200.internlm2 import ChatModelShell, GraphedDecoder, InternLM2Config, init_weights_
+    cfg = InternLM2Config(hidden_size=512, num_attention_heads=4, num_key_value_heads=1,
+                          intermediate_size=1024, num_hidden_layers=2, vocab_size=128)
+    shell = ChatModelShell(cfg).half()
+    init_weights_(shell, 7, std=0.05)
+    pi.patch_model(shell, "calibquant")
+    shell.cuda()
+    lm = shell.language_model
+    g = torch.Generator().manual_seed(2)
+    T, t_vis, n_new = 41 + 256 + 10, 256, 6
+    emb = (torch.randn(2, T, 512, generator=g) * 0.3).half().cuda()
+    eager = shell.generate(emb, image_token_num=t_vis, max_new_tokens=n_new)
+    os.environ["IMAGE_TOKEN_NUM"] = str(t_vis)
+    pos = torch.arange(T, device="cuda").unsqueeze(0).expand(2, T)
+    with torch.no_grad():
+        logits, past = lm.forward_step(emb, pos, None)
+    first = logits[:, -1].argmax(-1)
+    dec = GraphedDecoder(lm, past, first, T, n_new)
+    toks = dec.run(n_new - 1)
+    dec.close()
+    assert torch.equal(first, eager[:, 0])
+    assert torch.equal(toks, eager[:, 1:])
