@@ -121,7 +121,7 @@ template <> struct D16<__nv_bfloat16> {
 // K1: scores
 // =================================================================================================
 template <typename T, int BITS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ CUtensorMap tm_ks,
           const __grid_constant__ CUtensorMap tm_kmn, Dims dm, const T* __restrict__ q,
           const T* __restrict__ k_fp, T* __restrict__ scores, float2* __restrict__ tile_mm,
@@ -374,7 +374,7 @@ struct CalibH {   // per head, as 16-bit pairs for packed arithmetic in the data
 };
 
 template <typename T, int BITS>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 3)
 k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile_mm,
           const int32_t* __restrict__ v_code, const T* __restrict__ v_scale,
           const T* __restrict__ v_mn, const T* __restrict__ v_fp,
@@ -547,8 +547,11 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
       const uint32_t p_b = smem_u32(p_s) + (uint32_t)((g < dm.n_rep ? g : 0) * P_PITCH + ti * VT_TOK) * 2u;
 
       const int nt_tile = min(VT_TOK, dm.t_vis - vt * VT_TOK);
-      if (!std::is_same<T, __half>::value) {
-        // scales and minima of this warp's 128 tokens: bf16 -> fp16 in place (2 x 1 KB per array)
+      {
+        // Scales and minima of this warp's 128 tokens, re-laid out in place (2 x 1 KB): each 16-byte
+        // unit holds two tokens x four channel groups; it becomes four (token, token+1) pairs, one
+        // per group, which is the MMA B-fragment order, so the main loop needs no permutes.  bf16
+        // values are converted to fp16 on the way.
 #pragma unroll
         for (int arr = 0; arr < 2; ++arr) {
           const uint32_t base = (arr == 0 ? vs_b : vmn_b) + (uint32_t)(warp * (VT_TOK / 4)) * 8u;
@@ -557,31 +560,28 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
             const uint32_t addr = base + (uint32_t)(i * 32 + lane) * 16u;
             uint4 v = lds128(addr);
             v.x = D16<T>::to_h2(v.x); v.y = D16<T>::to_h2(v.y); v.z = D16<T>::to_h2(v.z); v.w = D16<T>::to_h2(v.w);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            const uint32_t o0 = prmt(v.x, v.z, 0x5410), o1 = prmt(v.x, v.z, 0x7632);
+            const uint32_t o2 = prmt(v.y, v.w, 0x5410), o3 = prmt(v.y, v.w, 0x7632);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
           }
         }
         __syncwarp();
       }
+      const uint32_t zoff = (uint32_t)(g < 4 ? g : 0) * 4u;   // this lane's column of the minima MMA
 #pragma unroll 1
       for (int kq = 0; kq < VT_TOK / 64; ++kq) {
         if (warp * (VT_TOK / 4) + kq * 16 >= nt_tile) break;
         const int t0 = warp * (VT_TOK / 4) + kq * 16 + 2 * c;   // token (in tile) of the lane's first k pair
         uint32_t pp0 = lds32(p_b + (uint32_t)t0 * 2u), pp1 = lds32(p_b + (uint32_t)(t0 + 8) * 2u);
         if (g >= dm.n_rep) { pp0 = 0u; pp1 = 0u; }
-        // scales of tokens (t0, t0+1) and (t0+8, t0+9): 4 halves per token
+        // scale pairs of tokens (t0, t0+1) and (t0+8, t0+9), one register per channel group
         const uint4 s0 = lds128(vs_b + (uint32_t)t0 * 8u), s1 = lds128(vs_b + (uint32_t)(t0 + 8) * 8u);
         uint32_t bA[4], bB[4];
-        bA[0] = hmul2_u32(pp0, prmt(s0.x, s0.z, 0x5410)); bA[1] = hmul2_u32(pp0, prmt(s0.x, s0.z, 0x7632));
-        bA[2] = hmul2_u32(pp0, prmt(s0.y, s0.w, 0x5410)); bA[3] = hmul2_u32(pp0, prmt(s0.y, s0.w, 0x7632));
-        bB[0] = hmul2_u32(pp1, prmt(s1.x, s1.z, 0x5410)); bB[1] = hmul2_u32(pp1, prmt(s1.x, s1.z, 0x7632));
-        bB[2] = hmul2_u32(pp1, prmt(s1.y, s1.w, 0x5410)); bB[3] = hmul2_u32(pp1, prmt(s1.y, s1.w, 0x7632));
+        bA[0] = hmul2_u32(pp0, s0.x); bA[1] = hmul2_u32(pp0, s0.y); bA[2] = hmul2_u32(pp0, s0.z); bA[3] = hmul2_u32(pp0, s0.w);
+        bB[0] = hmul2_u32(pp1, s1.x); bB[1] = hmul2_u32(pp1, s1.y); bB[2] = hmul2_u32(pp1, s1.z); bB[3] = hmul2_u32(pp1, s1.w);
         // minima + row sum: A = p (rows = heads), B column n = g: n<4 -> vmn[.][n], n==4 -> 1
         {
-          const uint4 z0 = lds128(vmn_b + (uint32_t)t0 * 8u), z1 = lds128(vmn_b + (uint32_t)(t0 + 8) * 8u);
-          const uint32_t lo0 = (g & 2) ? z0.y : z0.x, hi0 = (g & 2) ? z0.w : z0.z;
-          const uint32_t lo1 = (g & 2) ? z1.y : z1.x, hi1 = (g & 2) ? z1.w : z1.z;
-          const uint32_t psel = (g & 1) ? 0x7632u : 0x5410u;
-          uint32_t zb0 = prmt(lo0, hi0, psel), zb1 = prmt(lo1, hi1, psel);
+          uint32_t zb0 = lds32(vmn_b + (uint32_t)t0 * 8u + zoff), zb1 = lds32(vmn_b + (uint32_t)(t0 + 8) * 8u + zoff);
           if (g == 4) { zb0 = 0x3c003c00u; zb1 = 0x3c003c00u; }
           if (g > 4) { zb0 = 0u; zb1 = 0u; }
           mma_f16(cb, pp0, 0u, pp1, 0u, zb0, zb1);
