@@ -42,6 +42,9 @@ namespace mma {
 using namespace ptx;
 
 constexpr int THREADS = 128;
+constexpr int K1_WARPS = 4;            // warps of a score CTA; each owns 32 / K1_WARPS groups of a K tile
+constexpr int K1_THREADS = K1_WARPS * 32;
+constexpr int K1_GPW = 32 / K1_WARPS;
 constexpr int TILE_G = 32;             // 32-token groups per K tile (1024 tokens)
 constexpr int CHUNK_TOK = 1024;        // tokens per attn.V work item
 constexpr int P_PITCH = CHUNK_TOK + 8;  // probability row pitch (halves): +16 B keeps the heads on different banks
@@ -62,7 +65,7 @@ struct Dims {
   int n_fp_chunks;     // ceil(t_fp / 128)
   int n_slots;         // n_chunks + n_fp_chunks
   int pitch;           // score row pitch in elements (multiple of 8)
-  int n_mm;            // min/max entries per row: n_ktiles * 4
+  int n_mm;            // min/max entries per row: n_ktiles * K1_WARPS
   int64_t fp_stride_b, fp_stride_h;
   const int32_t* t_fp_dev;   // optional: live number of fp tokens on the device (t_fp is then the capacity)
 };
@@ -74,12 +77,16 @@ __device__ __forceinline__ int live_t_fp(const Dims& dm) {
 }
 
 // ---- per-lane constants for expanding packed codes into MMA A operands -------------------------
-// A lane (g = lane/4) owns rows g and g+8 of a 16-row m-tile; they are mapped to the adjacent
-// packed elements 2g and 2g+1 of the 16 elements the m-tile covers.
+// A lane (g = lane/4) owns rows g and g+8 of a 16-row m-tile; they are mapped to two adjacent
+// packed elements e, e+1 of the 32-element group the m-tile belongs to (m-tile i = 0, 1 of the group).
+// Which element a row stands for is free, as long as the epilogue agrees:
+//   2 and 4 bits: e = 16 i + 2g, so m-tile i is word-aligned in the group;
+//   1 bit:        e = 4g + 2i, so both m-tiles take their bits from the same byte of the same word
+//                 and share one byte permute.
 template <int BITS>
 struct Expand {
-  // element 2g of m-tile `mt_in_word_group` sits at bit offset (16*i + 2g)*BITS of its group
-  static __device__ __forceinline__ int bit_off(int i, int g) { return (i * 16 + 2 * g) * BITS; }
+  static __device__ __forceinline__ int elem(int i, int g) { return BITS == 1 ? 4 * g + 2 * i : 16 * i + 2 * g; }
+  static __device__ __forceinline__ int bit_off(int i, int g) { return elem(i, g) * BITS; }
 };
 
 __device__ __forceinline__ uint32_t prmt_sel(int byte) {
@@ -121,7 +128,7 @@ template <> struct D16<__nv_bfloat16> {
 // K1: scores
 // =================================================================================================
 template <typename T, int BITS>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(K1_THREADS, 2)
 k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ CUtensorMap tm_ks,
           const __grid_constant__ CUtensorMap tm_kmn, Dims dm, const T* __restrict__ q,
           const T* __restrict__ k_fp, T* __restrict__ scores, float2* __restrict__ tile_mm,
@@ -131,7 +138,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   constexpr int STAGE_BYTES = k1_stage_bytes(BITS);
   constexpr int CODE_BYTES = BITS * 16384;
   constexpr int GU = 4 / BITS;             // groups per 16-byte chunk of a channel row
-  constexpr int UNITS = 8 / GU;            // chunks per warp (8 groups per warp)
+  constexpr int UNITS = K1_GPW / GU;       // chunks per warp
   constexpr uint32_t FIELD = (1u << BITS) - 1u;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -215,8 +222,9 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
     const uint32_t ks_base = code_base + CODE_BYTES, kmn_base = ks_base + 8192;
     const int live_groups = min(TILE_G, dm.n_groups - tile * TILE_G);
 
-    if (warp * 8 < live_groups) {
-      // ---- scale fragments: ksA/ksB[kt] = (ks[16kt+2c][G], ks[16kt+2c+1][G]) / (+8), G = 8*warp+g
+    if (warp * K1_GPW < live_groups) {
+      // ---- scale fragments: ksA/ksB[kt] = (ks[16kt+2c][G], ks[16kt+2c+1][G]) / (+8), G = 8*col8+g
+      const int col8 = (warp * K1_GPW) >> 3, g_in_col = (warp * K1_GPW) & 7;
       uint32_t ksA[8], ksB[8];
       float cb[4] = {0.f, 0.f, 0.f, 0.f};   // bias[G = 8*warp+g][heads 2c, 2c+1]
       {
@@ -224,7 +232,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
 #pragma unroll
         for (int kp = 0; kp < 4; ++kp) {
           const int d = 16 * (2 * kp + (mat >> 1)) + 8 * (mat & 1) + r;
-          const uint32_t off = (uint32_t)(d * 64 + ((warp ^ ((d >> 1) & 3)) << 4));
+          const uint32_t off = (uint32_t)(d * 64 + ((col8 ^ ((d >> 1) & 3)) << 4));
           ldmatrix_x4_trans(ks_base + off, ksA[2 * kp], ksB[2 * kp], ksA[2 * kp + 1], ksB[2 * kp + 1]);
           uint32_t z0, z1, z2, z3;
           ldmatrix_x4_trans(kmn_base + off, z0, z1, z2, z3);
@@ -242,7 +250,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
 
 #pragma unroll 1
       for (int u = 0; u < UNITS; ++u) {
-        const int cidx = 2 * warp * BITS + u;                 // 16-byte chunk of the channel row
+        const int cidx = warp * UNITS + u;                    // 16-byte chunk of the channel row
         const uint32_t box_off = (uint32_t)(cidx >> 3) * 16384u;
         const int ch = cidx & 7;
         float acc[GU][2][4];
@@ -263,46 +271,54 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
           }
 #pragma unroll
           for (int a = 0; a < GU; ++a) {
-            const int gi = u * GU + a;                        // group within the warp's 8
+            const int gi = g_in_col + u * GU + a;             // group within the 8 of the scale fragment
             const uint32_t ksa = __shfl_sync(0xffffffffu, ksA[kt], 4 * gi + c);
             const uint32_t ksb = __shfl_sync(0xffffffffu, ksB[kt], 4 * gi + c);
             const uint32_t b0 = hmul2_u32(qA[kt], ksa), b1 = hmul2_u32(qB[kt], ksb);
+            if (BITS == 1) {   // one byte of the group's word feeds both m-tiles
+              const uint32_t x01 = prmt(W[0][a], W[1][a], sel[0]), x89 = prmt(W[2][a], W[3][a], sel[0]);
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              uint32_t w0, w1, w8, w9;
-              if (BITS == 4) {   // the lane's element pair sits in word 2i or 2i+1 of the group
-                const bool hi = word_in_group[i] & 1;
-                w0 = hi ? W[0][2 * i + 1] : W[0][2 * i];
-                w1 = hi ? W[1][2 * i + 1] : W[1][2 * i];
-                w8 = hi ? W[2][2 * i + 1] : W[2][2 * i];
-                w9 = hi ? W[3][2 * i + 1] : W[3][2 * i];
-              } else {
-                const int wi = a * BITS + (BITS == 2 ? i : 0);
-                w0 = W[0][wi]; w1 = W[1][wi]; w8 = W[2][wi]; w9 = W[3][wi];
+              for (int i = 0; i < 2; ++i)
+                mma_f16(acc[a][i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], b0, b1);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                uint32_t w0, w1, w8, w9;
+                if (BITS == 4) {   // the lane's element pair sits in word 2i or 2i+1 of the group
+                  const bool hi = word_in_group[i] & 1;
+                  w0 = hi ? W[0][2 * i + 1] : W[0][2 * i];
+                  w1 = hi ? W[1][2 * i + 1] : W[1][2 * i];
+                  w8 = hi ? W[2][2 * i + 1] : W[2][2 * i];
+                  w9 = hi ? W[3][2 * i + 1] : W[3][2 * i];
+                } else {
+                  const int wi = a * BITS + i;
+                  w0 = W[0][wi]; w1 = W[1][wi]; w8 = W[2][wi]; w9 = W[3][wi];
+                }
+                const uint32_t x01 = prmt(w0, w1, sel[i]), x89 = prmt(w8, w9, sel[i]);
+                mma_f16(acc[a][i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], b0, b1);
               }
-              const uint32_t x01 = prmt(w0, w1, sel[i]), x89 = prmt(w8, w9, sel[i]);
-              mma_f16(acc[a][i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], b0, b1);
             }
           }
         }
-        // ---- epilogue: rows g / g+8 are tokens 2g / 2g+1 of each 16-token m-tile
+        // ---- epilogue: rows g / g+8 are the adjacent tokens Expand::elem(i, g), +1 of the group
 #pragma unroll
         for (int a = 0; a < GU; ++a) {
-          const int gi = u * GU + a;
+          const int gi = g_in_col + u * GU + a;
           const float bias0 = __shfl_sync(0xffffffffu, cb[0], 4 * gi + c);
           const float bias1 = __shfl_sync(0xffffffffu, cb[1], 4 * gi + c);
-          const int tok0 = ((tile * TILE_G + warp * 8 + gi) * 32) + 2 * g;
+          const int tokg = (tile * TILE_G + col8 * 8 + gi) * 32;
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
+            const int tok = tokg + Expand<BITS>::elem(i, g);      // rows g, g+8 = tokens tok, tok+1
             const T2 ra = D16<T>::round2(fmaf(acc[a][i][0], sc0[i], bias0), fmaf(acc[a][i][2], sc1[i], bias0));
             const T2 rb = D16<T>::round2(fmaf(acc[a][i][1], sc0[i], bias1), fmaf(acc[a][i][3], sc1[i], bias1));
             const T2 sa = D16<T>::scale2(ra, inv_sqrt_d), sb = D16<T>::scale2(rb, inv_sqrt_d);
             if (2 * c < dm.n_rep) {
-              *reinterpret_cast<T2*>(scores + row_a + tok0 + 16 * i) = sa;
+              *reinterpret_cast<T2*>(scores + row_a + tok) = sa;
               mnA = __hmin2(mnA, sa); mxA = __hmax2(mxA, sa);
             }
             if (2 * c + 1 < dm.n_rep) {
-              *reinterpret_cast<T2*>(scores + row_b + tok0 + 16 * i) = sb;
+              *reinterpret_cast<T2*>(scores + row_b + tok) = sb;
               mnB = __hmin2(mnB, sb); mxB = __hmax2(mxB, sb);
             }
           }
@@ -321,14 +337,14 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
       }
       if (g == 0) {
         const int64_t r0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + 2 * c;
-        if (2 * c < dm.n_rep) tile_mm[r0 * dm.n_mm + tile * 4 + warp] = make_float2(lo_a, hi_a);
-        if (2 * c + 1 < dm.n_rep) tile_mm[(r0 + 1) * dm.n_mm + tile * 4 + warp] = make_float2(lo_b, hi_b);
+        if (2 * c < dm.n_rep) tile_mm[r0 * dm.n_mm + tile * K1_WARPS + warp] = make_float2(lo_a, hi_a);
+        if (2 * c + 1 < dm.n_rep) tile_mm[(r0 + 1) * dm.n_mm + tile * K1_WARPS + warp] = make_float2(lo_b, hi_b);
       }
     } else if (lane < 2 * kMaxRep) {
       // dead part of a ragged last tile: neutral min/max entries
       const int b = pair / dm.hkv, hk = pair % dm.hkv;
       if (lane < dm.n_rep)
-        tile_mm[((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + lane) * dm.n_mm + tile * 4 + warp] =
+        tile_mm[((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + lane) * dm.n_mm + tile * K1_WARPS + warp] =
             make_float2(INFINITY, -INFINITY);
     }
     __syncthreads();
@@ -342,11 +358,11 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
     const int pair = it / n_fp_tiles, ft = it % n_fp_tiles;
     const int b = pair / dm.hkv, hk = pair % dm.hkv;
     __syncthreads();
-    for (int i = tid; i < dm.n_rep * kHeadDim; i += THREADS)
+    for (int i = tid; i < dm.n_rep * kHeadDim; i += K1_THREADS)
       qf_s[i] = Elem<T>::to_f(q[((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep) * kHeadDim + i]);
     __syncthreads();
     const T* kf = k_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h;
-    for (int i = warp; i < 64; i += THREADS / 32) {
+    for (int i = warp; i < 64; i += K1_WARPS) {
       const int t = ft * 64 + i;
       if (t >= t_fp) break;
       const uint2 raw = __ldg(reinterpret_cast<const uint2*>(kf + (int64_t)t * kHeadDim) + lane);
@@ -433,13 +449,14 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
     for (int i = 0; i < STAGES - 1; ++i) issue_next();
   }
 
-  // lane constants for expanding channel pairs (2g, 2g+1) of m-tile j; pattern repeats with j%2
-  // for BITS==1 (two m-tiles per word) and is j-independent otherwise.
+  // lane constants for expanding the channel pair that rows g, g+8 of m-tile j stand for
+  // (Expand::elem): at 1 bit two m-tiles share a word and the pattern repeats with j % 2, otherwise
+  // it does not depend on j.
   uint32_t sel[2], m0[2], m1[2];
   float sc0[2], sc1[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    const int off = (i * 16 + 2 * g) * BITS;
+    const int off = Expand<BITS>::bit_off(i, g);
     const int byte = (off % 32) / 8, sh = off % 8;
     sel[i] = prmt_sel(byte);
     m0[i] = (FIELD << sh) * 0x00010001u;
@@ -595,14 +612,20 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
           const uint32_t Wa[4] = {wa.x, wa.y, wa.z, wa.w}, Wb[4] = {wb.x, wb.y, wb.z, wb.w};
           const uint32_t Wc[4] = {wc.x, wc.y, wc.z, wc.w}, Wd[4] = {wd.x, wd.y, wd.z, wd.w};
           // m-tiles covered by these 4 words: 128/BITS channels = 8/BITS m-tiles
+          if (BITS == 1) {      // word m = channels 32m .. 32m+31 = m-tiles 2m, 2m+1, one byte permute for both
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+              const uint32_t x01 = prmt(Wa[m], Wb[m], sel[0]), x89 = prmt(Wc[m], Wd[m], sel[0]);
+#pragma unroll
+              for (int i = 0; i < 2; ++i)
+                mma_f16(acc[2 * m + i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bA[m], bB[m]);
+            }
+          } else
 #pragma unroll
           for (int jj = 0; jj < 8 / BITS; ++jj) {
             const int j = part * (8 / BITS) + jj;          // m-tile = channels 16j .. 16j+15
             const int gq = j >> 1;                         // 32-channel group -> scale
-            int wi, i;
-            if (BITS == 1) { wi = jj >> 1; i = jj & 1; }
-            else if (BITS == 2) { wi = jj; i = 0; }
-            else { wi = 2 * jj + (g >> 2); i = 0; }
+            const int wi = BITS == 2 ? jj : 2 * jj + (g >> 2), i = 0;
             uint32_t a, bw, cw, dw;
             if (BITS == 4) {
               const bool hi = g >> 2;
@@ -627,7 +650,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int i = (BITS == 1) ? (j & 1) : 0;
-        const int ch = 16 * j + 2 * g;
+        const int ch = BITS == 1 ? 32 * (j >> 1) + Expand<1>::elem(i, g) : 16 * j + 2 * g;
         if (2 * c < dm.n_rep) {
           mine[(2 * c) * RED_STRIDE + ch] = acc[j][0] * sc0[i];
           mine[(2 * c) * RED_STRIDE + ch + 1] = acc[j][2] * sc1[i];
@@ -789,7 +812,7 @@ static Dims make_dims(const cq_decode_args* a) {
   d.n_fp_chunks = (d.t_fp + 127) / 128;
   d.n_slots = d.n_chunks + d.n_fp_chunks;
   d.pitch = (d.t_vis + d.t_fp + 7) / 8 * 8;
-  d.n_mm = d.n_ktiles * 4;
+  d.n_mm = d.n_ktiles * K1_WARPS;
   d.fp_stride_b = a->fp_stride_b; d.fp_stride_h = a->fp_stride_h;
   d.t_fp_dev = a->t_fp_dev;
   return d;
@@ -840,7 +863,7 @@ static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned
   if (!configured) {
     if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1) != cudaSuccess) return CQ_ERR_LAUNCH;
     if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return CQ_ERR_LAUNCH;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ1, k1, THREADS, smem1) != cudaSuccess || occ1 < 1) return CQ_ERR_LAUNCH;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ1, k1, K1_THREADS, smem1) != cudaSuccess || occ1 < 1) return CQ_ERR_LAUNCH;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ2, k2, THREADS, smem2) != cudaSuccess || occ2 < 1) return CQ_ERR_LAUNCH;
     configured = true;
   }
@@ -859,7 +882,7 @@ static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned
       return CQ_ERR_LAUNCH;
     const int items1 = n_pairs * d.n_ktiles;
     const int grid1 = max(1, min(items1 + n_pairs * ((d.t_fp + 63) / 64), sm_count() * occ1));
-    k1<<<grid1, THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(a->q),
+    k1<<<grid1, K1_THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(a->q),
                                       static_cast<const T*>(a->k_fp), scores, mm, status);
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
