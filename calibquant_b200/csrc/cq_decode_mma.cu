@@ -156,9 +156,13 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   }
   __syncthreads();
 
+  // every CTA takes a contiguous range of (KV head, tile) items: the query fragments are reloaded
+  // only when the KV head changes, and neighbouring CTAs stream neighbouring tiles
+  const int it_first = (int)(((int64_t)blockIdx.x * n_items) / gridDim.x);
+  const int it_end = (int)(((int64_t)(blockIdx.x + 1) * n_items) / gridDim.x);
   auto issue = [&](int k) {
-    const int it = blockIdx.x + k * gridDim.x;
-    if (it >= n_items) return;
+    const int it = it_first + k;
+    if (it >= it_end) return;
     const int s = k % STAGES;
     const int pair = it / dm.n_ktiles, tile = it % dm.n_ktiles;
     unsigned char* base = smem + s * STAGE_BYTES;
@@ -195,8 +199,8 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   bool failed = false;
 
   for (int k = 0;; ++k) {
-    const int it = blockIdx.x + k * gridDim.x;
-    if (it >= n_items) break;
+    const int it = it_first + k;
+    if (it >= it_end) break;
     const int s = k % STAGES;
     const int pair = it / dm.n_ktiles, tile = it % dm.n_ktiles;
     if (tid == 0) {
@@ -585,7 +589,8 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         __syncwarp();
       }
       const uint32_t zoff = (uint32_t)(g < 4 ? g : 0) * 4u;   // this lane's column of the minima MMA
-#pragma unroll 1
+      const uint32_t z_and = g < 4 ? 0xffffffffu : 0u, z_or = g == 4 ? 0x3c003c00u : 0u;   // column 4 = ones
+#pragma unroll
       for (int kq = 0; kq < VT_TOK / 64; ++kq) {
         if (warp * (VT_TOK / 4) + kq * 16 >= nt_tile) break;
         const int t0 = warp * (VT_TOK / 4) + kq * 16 + 2 * c;   // token (in tile) of the lane's first k pair
@@ -598,9 +603,8 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         bB[0] = hmul2_u32(pp1, s1.x); bB[1] = hmul2_u32(pp1, s1.y); bB[2] = hmul2_u32(pp1, s1.z); bB[3] = hmul2_u32(pp1, s1.w);
         // minima + row sum: A = p (rows = heads), B column n = g: n<4 -> vmn[.][n], n==4 -> 1
         {
-          uint32_t zb0 = lds32(vmn_b + (uint32_t)t0 * 8u + zoff), zb1 = lds32(vmn_b + (uint32_t)(t0 + 8) * 8u + zoff);
-          if (g == 4) { zb0 = 0x3c003c00u; zb1 = 0x3c003c00u; }
-          if (g > 4) { zb0 = 0u; zb1 = 0u; }
+          const uint32_t zb0 = (lds32(vmn_b + (uint32_t)t0 * 8u + zoff) & z_and) | z_or;
+          const uint32_t zb1 = (lds32(vmn_b + (uint32_t)(t0 + 8) * 8u + zoff) & z_and) | z_or;
           mma_f16(cb, pp0, 0u, pp1, 0u, zb0, zb1);
         }
         // code words of the lane's four tokens
