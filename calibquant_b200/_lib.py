@@ -72,6 +72,10 @@ SIGNATURES = {
     "cq_lut_out_workspace_bytes": (_sz, [_c.c_int, _c.c_int, _c.c_int]),
     "cq_lut_out": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                               _c.c_int, _c.c_int, _vp, _sz, _vp]),
+    "cq_rope_split_append": (_c.c_int, [_vp, _i64, _vp, _vp, _c.c_int, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                        _vp, _vp, _vp, _i64, _i64, _c.c_int, _c.c_int, _vp, _c.c_int, _vp]),
+    "cq_add_rmsnorm": (_c.c_int, [_vp, _vp, _vp, _vp, _i64, _c.c_int, _c.c_float, _c.c_int, _vp]),
+    "cq_swiglu": (_c.c_int, [_vp, _vp, _vp, _i64, _c.c_int, _vp]),
     "cq_decode_attn_workspace_bytes": (_sz, [_c.POINTER(DecodeArgs)]),
     "cq_decode_attn": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _sz, _vp]),
 }

@@ -1,0 +1,211 @@
+// Small fused kernels around the attention call of one decode step: the QKV split + rotary
+// embedding + cache append that precedes it, and the two elementwise blocks of the decoder layer
+// (residual add + RMSNorm, SwiGLU gate).  Each replaces a chain of 4-10 elementwise torch kernels
+// whose launch gaps dominate a batch-16 decode step; all are memory-trivial (KBs per launch).
+// Every value torch would round to the tensor dtype between two ops is rounded here as well.
+#include "cq_common.cuh"
+
+namespace cq {
+namespace step {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_VEC = 8;          // elements per 16-byte access
+constexpr int NORM_MAXV = 8;         // vectors per thread held in registers -> hidden <= 16384
+
+template <typename T>
+__global__ void __launch_bounds__(NORM_THREADS)
+add_rmsnorm_kernel(const T* __restrict__ delta, T* __restrict__ residual, const T* __restrict__ weight,
+                   T* __restrict__ out, int hidden, float eps) {
+  const int64_t row = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int n_vec = hidden / NORM_VEC;
+  T* res = residual + row * hidden;
+  const T* dl = delta ? delta + row * hidden : nullptr;
+  float v[NORM_MAXV][NORM_VEC];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NORM_MAXV; ++k) {
+    const int iv = tid + k * NORM_THREADS;
+    if (iv < n_vec) {
+      uint4 raw = *reinterpret_cast<const uint4*>(res + iv * NORM_VEC);
+      const T* r = reinterpret_cast<const T*>(&raw);
+      if (dl) {
+        const uint4 draw = *reinterpret_cast<const uint4*>(dl + iv * NORM_VEC);
+        const T* d = reinterpret_cast<const T*>(&draw);
+        uint4 sum;
+        T* s = reinterpret_cast<T*>(&sum);
+#pragma unroll
+        for (int e = 0; e < NORM_VEC; ++e) {
+          s[e] = Elem<T>::from_f(Elem<T>::to_f(r[e]) + Elem<T>::to_f(d[e]));   // hidden = hidden + delta
+          v[k][e] = Elem<T>::to_f(s[e]);
+        }
+        *reinterpret_cast<uint4*>(res + iv * NORM_VEC) = sum;
+      } else {
+#pragma unroll
+        for (int e = 0; e < NORM_VEC; ++e) v[k][e] = Elem<T>::to_f(r[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < NORM_VEC; ++e) ss = fmaf(v[k][e], v[k][e], ss);
+    }
+  }
+  __shared__ float part[NORM_THREADS / 32];
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) part[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < NORM_THREADS / 32; ++w) tot += part[w];
+  const float inv = rsqrtf(tot / (float)hidden + eps);
+  if (!out) return;
+  T* o = out + row * hidden;
+#pragma unroll
+  for (int k = 0; k < NORM_MAXV; ++k) {
+    const int iv = tid + k * NORM_THREADS;
+    if (iv < n_vec) {
+      const uint4 wraw = *reinterpret_cast<const uint4*>(weight + iv * NORM_VEC);
+      const T* w = reinterpret_cast<const T*>(&wraw);
+      uint4 res4;
+      T* r = reinterpret_cast<T*>(&res4);
+#pragma unroll
+      for (int e = 0; e < NORM_VEC; ++e)   // weight * (x_fp32 * rsqrt(var + eps)).to(dtype)
+        r[e] = Elem<T>::from_f(Elem<T>::to_f(w[e]) * rnd<T>(v[k][e] * inv));
+      *reinterpret_cast<uint4*>(o + iv * NORM_VEC) = res4;
+    }
+  }
+}
+
+// One block of 64 threads per (batch row, head of the projection output); thread d owns the
+// rotary pair (d, d + 64).
+template <typename T>
+__global__ void __launch_bounds__(64)
+rope_split_append_kernel(const T* __restrict__ qkv, int64_t qkv_stride_b, const T* __restrict__ cos_t,
+                         const T* __restrict__ sin_t, const int64_t* __restrict__ position_ids, int n_kv_heads,
+                         int n_rep, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                         int64_t cache_stride_b, int64_t cache_stride_h, int capacity, int append_index,
+                         const int32_t* __restrict__ t_fp_dev, int rope_len) {
+  const int per_kv = n_rep + 2;
+  const int b = blockIdx.x / (n_kv_heads * per_kv);
+  const int rem = blockIdx.x % (n_kv_heads * per_kv);
+  const int hk = rem / per_kv, slot = rem % per_kv;     // slot < n_rep: query head; n_rep: key; n_rep+1: value
+  const int d = threadIdx.x;
+  const T* src = qkv + b * qkv_stride_b + (int64_t)(hk * per_kv + slot) * kHeadDim;
+  const int idx = t_fp_dev ? __ldg(t_fp_dev) - 1 : append_index;   // the live count includes this token
+  T* dst;
+  if (slot < n_rep) {
+    dst = q_out + ((int64_t)b * n_kv_heads * n_rep + (int64_t)hk * n_rep + slot) * kHeadDim;
+  } else {
+    if (idx < 0 || idx >= capacity) return;             // a full cache drops the token instead of writing outside
+    dst = (slot == n_rep ? k_cache : v_cache) + b * cache_stride_b + hk * cache_stride_h + (int64_t)idx * kHeadDim;
+  }
+  const float x0 = Elem<T>::to_f(src[d]), x1 = Elem<T>::to_f(src[d + 64]);
+  if (slot == n_rep + 1) {                               // values are not rotated
+    dst[d] = src[d];
+    dst[d + 64] = src[d + 64];
+    return;
+  }
+  int64_t pos = position_ids[b];
+  pos = pos < 0 ? 0 : (pos >= rope_len ? rope_len - 1 : pos);
+  const T* cr = cos_t + pos * kHeadDim;
+  const T* sr = sin_t + pos * kHeadDim;
+  // x*cos rounded, then + rotate_half(x)*sin with one more rounding (the product of two 16-bit
+  // floats is exact in fp32)
+  const float a0 = rnd<T>(x0 * Elem<T>::to_f(cr[d])), a1 = rnd<T>(x1 * Elem<T>::to_f(cr[d + 64]));
+  dst[d] = Elem<T>::from_f(__fadd_rn(a0, __fmul_rn(-x1, Elem<T>::to_f(sr[d]))));
+  dst[d + 64] = Elem<T>::from_f(__fadd_rn(a1, __fmul_rn(x0, Elem<T>::to_f(sr[d + 64]))));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out, int64_t n_vec) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n_vec; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 graw = reinterpret_cast<const uint4*>(gate)[i], uraw = reinterpret_cast<const uint4*>(up)[i];
+    const T* g = reinterpret_cast<const T*>(&graw);
+    const T* u = reinterpret_cast<const T*>(&uraw);
+    uint4 res;
+    T* r = reinterpret_cast<T*>(&res);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float x = Elem<T>::to_f(g[e]);
+      const float s = rnd<T>(x / (1.f + expf(-x)));      // silu(gate) as its own rounded tensor
+      r[e] = Elem<T>::from_f(s * Elem<T>::to_f(u[e]));
+    }
+    reinterpret_cast<uint4*>(out)[i] = res;
+  }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace step
+}  // namespace cq
+
+using namespace cq;
+
+extern "C" int cq_add_rmsnorm(const void* delta, void* residual, const void* weight, void* out, int64_t rows,
+                              int hidden, float eps, int dtype, void* stream) {
+  if (rows == 0) return CQ_OK;
+  if (!residual || rows < 0 || hidden <= 0 || (out && !weight)) return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (hidden % step::NORM_VEC || hidden > step::NORM_THREADS * step::NORM_VEC * step::NORM_MAXV) return CQ_ERR_UNSUPPORTED;
+  if (!step::aligned16(residual) || !step::aligned16(delta) || !step::aligned16(weight) || !step::aligned16(out))
+    return CQ_ERR_BAD_ARG;
+  if (rows > 0x7fffffff) return CQ_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CQ_DTYPE_F16)
+    step::add_rmsnorm_kernel<__half><<<(unsigned)rows, step::NORM_THREADS, 0, st>>>(
+        static_cast<const __half*>(delta), static_cast<__half*>(residual), static_cast<const __half*>(weight),
+        static_cast<__half*>(out), hidden, eps);
+  else
+    step::add_rmsnorm_kernel<__nv_bfloat16><<<(unsigned)rows, step::NORM_THREADS, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(delta), static_cast<__nv_bfloat16*>(residual),
+        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), hidden, eps);
+  return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
+}
+
+extern "C" int cq_rope_split_append(const void* qkv, int64_t qkv_stride_b, const void* cos_table,
+                                    const void* sin_table, int rope_len, const int64_t* position_ids, int batch,
+                                    int n_kv_heads, int n_rep, int head_dim, void* q_out, void* k_cache,
+                                    void* v_cache, int64_t cache_stride_b, int64_t cache_stride_h, int capacity,
+                                    int append_index, const int32_t* t_fp_dev, int dtype, void* stream) {
+  if (batch == 0) return CQ_OK;
+  if (!qkv || !cos_table || !sin_table || !position_ids || !q_out || !k_cache || !v_cache) return CQ_ERR_BAD_ARG;
+  if (batch < 0 || n_kv_heads <= 0 || n_rep <= 0 || rope_len <= 0 || capacity <= 0) return CQ_ERR_BAD_ARG;
+  if (!t_fp_dev && (append_index < 0 || append_index >= capacity)) return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (head_dim != kHeadDim) return CQ_ERR_UNSUPPORTED;
+  const int64_t blocks = (int64_t)batch * n_kv_heads * (n_rep + 2);
+  if (blocks > 0x7fffffff) return CQ_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CQ_DTYPE_F16)
+    step::rope_split_append_kernel<__half><<<(unsigned)blocks, 64, 0, st>>>(
+        static_cast<const __half*>(qkv), qkv_stride_b, static_cast<const __half*>(cos_table),
+        static_cast<const __half*>(sin_table), position_ids, n_kv_heads, n_rep, static_cast<__half*>(q_out),
+        static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), cache_stride_b, cache_stride_h, capacity,
+        append_index, t_fp_dev, rope_len);
+  else
+    step::rope_split_append_kernel<__nv_bfloat16><<<(unsigned)blocks, 64, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(qkv), qkv_stride_b, static_cast<const __nv_bfloat16*>(cos_table),
+        static_cast<const __nv_bfloat16*>(sin_table), position_ids, n_kv_heads, n_rep,
+        static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+        static_cast<__nv_bfloat16*>(v_cache), cache_stride_b, cache_stride_h, capacity, append_index, t_fp_dev,
+        rope_len);
+  return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
+}
+
+extern "C" int cq_swiglu(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream) {
+  if (n == 0) return CQ_OK;
+  if (!gate || !up || !out || n < 0) return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (n % 8) return CQ_ERR_UNSUPPORTED;
+  if (!step::aligned16(gate) || !step::aligned16(up) || !step::aligned16(out)) return CQ_ERR_BAD_ARG;
+  const int64_t n_vec = n / 8;
+  const unsigned grid = (unsigned)((n_vec + 255) / 256 < 148 * 8 ? (n_vec + 255) / 256 : 148 * 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CQ_DTYPE_F16)
+    step::swiglu_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(gate),
+                                                      static_cast<const __half*>(up), static_cast<__half*>(out), n_vec);
+  else
+    step::swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gate),
+                                                             static_cast<const __nv_bfloat16*>(up),
+                                                             static_cast<__nv_bfloat16*>(out), n_vec);
+  return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
+}

@@ -155,6 +155,25 @@ class InternLM2ForCausalLM(nn.Module):
         return self.output(h), presents
 
     @torch.no_grad()
+    def forward_step_fused(self, inputs_embeds, position_ids, past_key_values):
+        """Decode step (one token per row) with the elementwise blocks of every layer fused: residual
+        add + RMSNorm in one launch, SwiGLU gate in one launch.  Same arithmetic and rounding points
+        as ``forward_step``; the attention modules are called as usual."""
+        from . import ops
+        eps = self.config.rms_norm_eps
+        h = inputs_embeds.contiguous().clone()      # running residual stream, updated in place
+        delta = None
+        for i, layer in enumerate(self.model.layers):
+            x = ops.add_rmsnorm(h, delta, layer.attention_norm.weight, eps)
+            a, _, _ = layer.attention(x, position_ids=position_ids, past_key_value=past_key_values[i],
+                                      output_attentions=False, use_cache=True)
+            x = ops.add_rmsnorm(h, a.contiguous(), layer.ffn_norm.weight, eps)
+            ff = layer.feed_forward
+            delta = ff.w2(ops.swiglu(ff.w1(x), ff.w3(x)))
+        x = ops.add_rmsnorm(h, delta, self.model.norm.weight, eps)
+        return self.output(x[:, -1:])
+
+    @torch.no_grad()
     def generate(self, inputs_embeds, max_new_tokens, **_):
         """Greedy decoding from embeddings: one prefill pass, then one token per step."""
         B, T, _ = inputs_embeds.shape
@@ -178,20 +197,23 @@ class GraphedDecoder:
     that changes from step to step lives on the device: the token, the position, and each layer's
     text-cache length, which the attention kernels read through ``t_fp_dev``."""
 
-    def __init__(self, lm: "InternLM2ForCausalLM", past, first_token, start_pos: int, max_new_tokens: int):
-        self.lm, self.past = lm, past
+    def __init__(self, lm: "InternLM2ForCausalLM", past, first_token, start_pos: int, max_new_tokens: int,
+                 fused: bool = True):
+        self.lm, self.past, self.fused = lm, past, fused
         B = first_token.shape[0]
         dev = first_token.device
         self.caches = [layer.attention._text_cache for layer in lm.model.layers]
+        self.len_dev = torch.tensor([self.caches[0].length], dtype=torch.int32, device=dev)
         for layer, tc in zip(lm.model.layers, self.caches):
-            tc.enable_static(tc.length + max_new_tokens + 2)
+            assert tc.length == self.caches[0].length
+            tc.enable_static(tc.length + max_new_tokens + 2, self.len_dev)
             layer.attention._static_decode = True
             layer.attention._static_rope_len = start_pos + max_new_tokens + 2
         self.tok = first_token.clone()
         self.pos = torch.full((B, 1), start_pos, device=dev, dtype=torch.long)
         self.out = torch.zeros((max_new_tokens + 2, B), device=dev, dtype=torch.long)
         self.step_idx = torch.zeros(1, device=dev, dtype=torch.long)
-        state0 = (self.tok.clone(), [tc.length for tc in self.caches])
+        state0 = (self.tok.clone(), self.caches[0].length)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):                       # warm-up outside capture, then roll back
@@ -209,13 +231,16 @@ class GraphedDecoder:
         self.tok.copy_(state0[0])
         self.pos.fill_(start_pos)
         self.step_idx.zero_()
-        for tc, n in zip(self.caches, state0[1]):
-            tc.set_static_length(n)
+        self.len_dev.fill_(state0[1])
 
     @torch.no_grad()
     def _step(self):
         emb = self.lm.model.tok_embeddings(self.tok).unsqueeze(1)
-        logits, _ = self.lm.forward_step(emb, self.pos, self.past)
+        self.len_dev += 1                 # the caches now count the token this step appends
+        if self.fused:
+            logits = self.lm.forward_step_fused(emb, self.pos, self.past)
+        else:
+            logits, _ = self.lm.forward_step(emb, self.pos, self.past)
         self.tok.copy_(logits[:, -1].argmax(-1))
         self.out.index_copy_(0, self.step_idx, self.tok.unsqueeze(0))
         self.pos += 1
@@ -230,7 +255,7 @@ class GraphedDecoder:
     def close(self):
         for layer, tc in zip(self.lm.model.layers, self.caches):
             layer.attention._static_decode = False
-            tc.length = int(tc.len_dev.item())
+            tc.length = int(self.len_dev.item())
 
 
 class ChatModelShell(nn.Module):

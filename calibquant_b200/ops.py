@@ -224,3 +224,85 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out=Non
                                    arr(q), arr(k), arr(v), arr(out), _dtype_enum(q), _stream())
     check(rc, "cq_prefill_attn")
     return out
+
+
+def rope_split_append(qkv, cos, sin, position_ids, n_kv_heads, n_rep, k_cache, v_cache,
+                      append_index=None, t_fp_dev=None):
+    """One decode token per batch row: split the ``wqkv`` output ``qkv`` [B,1,Hkv*(n_rep+2)*D]
+    (per KV head: n_rep query heads, key, value), rotate queries and key with the ``cos``/``sin``
+    tables [S,D] at ``position_ids`` [B,1], and write the rotated key and the value into the fp caches
+    ``k_cache``/``v_cache`` [B,Hkv,capacity,D] at token ``append_index`` -- or at ``t_fp_dev - 1`` when
+    the live token count is the int32 device scalar ``t_fp_dev`` (which then already counts the new
+    token).  Returns the rotated queries [B,Hq,1,D]."""
+    _need_cuda(qkv, cos, sin, position_ids, k_cache, v_cache)
+    B = qkv.shape[0]
+    D = cos.shape[-1]
+    qkv2 = qkv.reshape(B, -1)
+    if qkv2.stride(1) != 1:
+        qkv2 = qkv2.contiguous()
+    if qkv2.shape[1] != n_kv_heads * (n_rep + 2) * D:
+        raise ValueError(f"qkv rows must hold {n_kv_heads * (n_rep + 2) * D} elements, got {qkv2.shape[1]}")
+    if cos.dtype != qkv.dtype or sin.dtype != qkv.dtype or k_cache.dtype != qkv.dtype:
+        raise TypeError("qkv, rotary tables and caches must share one dtype")
+    cos, sin = cos.contiguous(), sin.contiguous()
+    pos = position_ids.reshape(-1)
+    if pos.dtype != torch.int64 or pos.numel() != B:
+        raise ValueError("position_ids must be int64 with one position per batch row")
+    pos = pos.contiguous()
+    for t in (k_cache, v_cache):
+        if t.stride(3) != 1 or t.stride(2) != D:
+            raise ValueError("cache token rows must be contiguous ([.., T, D] with stride D)")
+    if k_cache.stride() != v_cache.stride():
+        raise ValueError("k_cache and v_cache must share strides")
+    if (append_index is None) == (t_fp_dev is None):
+        raise ValueError("give exactly one of append_index and t_fp_dev")
+    if t_fp_dev is not None:
+        assert t_fp_dev.dtype == torch.int32 and t_fp_dev.is_cuda
+    q_out = torch.empty((B, n_kv_heads * n_rep, 1, D), dtype=qkv.dtype, device=qkv.device)
+    with torch.cuda.device(qkv.device):
+        rc = lib().cq_rope_split_append(_ptr(qkv2), qkv2.stride(0), _ptr(cos), _ptr(sin), cos.shape[0], _ptr(pos),
+                                        B, n_kv_heads, n_rep, D, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+                                        k_cache.stride(0), k_cache.stride(1), k_cache.shape[2],
+                                        0 if append_index is None else int(append_index), _ptr(t_fp_dev),
+                                        _dtype_enum(qkv), _stream())
+    check(rc, "cq_rope_split_append")
+    return q_out
+
+
+def add_rmsnorm(residual, delta, weight, eps, out=None, normalize=True):
+    """``residual += delta`` in place (skipped when ``delta`` is None), then RMSNorm of the rows of
+    ``residual`` [..., hidden] scaled by ``weight``.  Returns the normalised tensor (None when
+    ``normalize`` is False: the bare residual add)."""
+    _need_cuda(residual, delta, weight)
+    hidden = residual.shape[-1]
+    if not residual.is_contiguous() or (delta is not None and not delta.is_contiguous()):
+        raise ValueError("residual and delta must be contiguous")
+    if delta is not None and (delta.shape != residual.shape or delta.dtype != residual.dtype):
+        raise ValueError("delta must match residual in shape and dtype")
+    if normalize:
+        if weight.dtype != residual.dtype or weight.numel() != hidden:
+            raise ValueError("weight must hold `hidden` values of the data dtype")
+        weight = weight.contiguous()
+        if out is None:
+            out = torch.empty_like(residual)
+    rows = residual.numel() // hidden if hidden else 0
+    with torch.cuda.device(residual.device):
+        rc = lib().cq_add_rmsnorm(_ptr(delta), _ptr(residual), _ptr(weight) if normalize else None,
+                                  _ptr(out) if normalize else None, rows, hidden, float(eps),
+                                  _dtype_enum(residual), _stream())
+    check(rc, "cq_add_rmsnorm")
+    return out if normalize else None
+
+
+def swiglu(gate, up, out=None):
+    """``silu(gate) * up`` with torch's two roundings (the activation, then the product)."""
+    _need_cuda(gate, up)
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("gate and up must match in shape and dtype")
+    gate, up = gate.contiguous(), up.contiguous()
+    if out is None:
+        out = torch.empty_like(gate)
+    with torch.cuda.device(gate.device):
+        rc = lib().cq_swiglu(_ptr(gate), _ptr(up), _ptr(out), gate.numel(), _dtype_enum(gate), _stream())
+    check(rc, "cq_swiglu")
+    return out

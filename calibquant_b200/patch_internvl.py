@@ -135,24 +135,17 @@ class _TextCache:
 
     # ---- static mode: the token count lives on the device, so that one captured CUDA graph can
     # ---- append a token and attend over the live part at every decode step
-    def enable_static(self, capacity):
+    def enable_static(self, capacity, len_dev=None):
+        """``len_dev``: int32 device scalar holding the live token count.  Layers of one model hold
+        equally many tokens, so their caches may share one counter; whoever owns it adds one per
+        decode step *before* the layers run (the count then includes the token being appended)."""
         if capacity > self.k.shape[2]:
             pad = torch.empty((*self.k.shape[:2], capacity - self.k.shape[2], self.k.shape[3]),
                               dtype=self.k.dtype, device=self.k.device)
             self.k = torch.cat([self.k, pad], dim=2)
             self.v = torch.cat([self.v, pad.clone()], dim=2)
-        self.len_dev = torch.tensor([self.length], dtype=torch.int32, device=self.k.device)
-        self.idx_dev = torch.tensor([self.length], dtype=torch.int64, device=self.k.device)
-
-    def set_static_length(self, length):
-        self.len_dev.fill_(length)
-        self.idx_dev.fill_(length)
-
-    def append_static(self, k, v):
-        self.k.index_copy_(2, self.idx_dev, k)
-        self.v.index_copy_(2, self.idx_dev, v)
-        self.len_dev += 1
-        self.idx_dev += 1
+        self.len_dev = len_dev if len_dev is not None else \
+            torch.tensor([self.length], dtype=torch.int32, device=self.k.device)
 
 
 def _split_qkv(self, hidden_states):
@@ -229,13 +222,29 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
     attention_mask = _pop_padding_mask(kwargs, attention_mask)
     bsz, q_len, _ = hidden_states.size()
 
+    if q_len == 1 and getattr(self, "_static_decode", False):
+        # graph-replayable step: everything that changes between steps is read from device memory.
+        # One launch splits the projection, rotates q and k and appends k, v at the device-side
+        # token count (already advanced by the owner of the counter), one call attends over the
+        # live part of the cache.
+        tc = self._text_cache
+        cos, sin = self.rotary_emb(hidden_states, seq_len=self._static_rope_len)
+        n_rep = self.num_key_value_groups
+        q = ops.rope_split_append(self.wqkv(hidden_states), cos, sin, position_ids,
+                                  self.wqkv.out_features // ((n_rep + 2) * self.head_dim), n_rep,
+                                  tc.k, tc.v, t_fp_dev=tc.len_dev)
+        attn = ops.decode_attention(q, self.k_pack, self.v_pack, tc.k, tc.v, self.sprompt_len if LOW_BITS else 0,
+                                    BITS_KV, group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
+                                    t_fp_dev=tc.len_dev)
+        attn = _gather_heads(self, attn.transpose(1, 2).reshape(bsz, q_len, -1))
+        return self.wo(attn.reshape(bsz, q_len, self.hidden_size)), None, past_key_value
+
     q, k, v = _split_qkv(self, hidden_states)
     q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)          # [B,H,q,D] views
     kv_seq_len = q_len
     if past_key_value is not None:
         kv_seq_len += past_key_value[0].shape[-2] + (self.image_token_num if LOW_BITS else 0)
-    static_decode = q_len == 1 and getattr(self, "_static_decode", False)
-    cos, sin = self.rotary_emb(v, seq_len=self._static_rope_len if static_decode else kv_seq_len)
+    cos, sin = self.rotary_emb(v, seq_len=kv_seq_len)
     q, k = apply_rotary_pos_emb(q, k, cos, sin, position_ids)
 
     if q_len > 1:
@@ -259,15 +268,6 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
         return attn_output, None, past_key_value
 
     # ---- decode step -------------------------------------------------------------------------
-    if static_decode:
-        # graph-replayable step: append at the device-side position, attend over the live count
-        tc = self._text_cache
-        tc.append_static(k, v)
-        attn = ops.decode_attention(q, self.k_pack, self.v_pack, tc.k, tc.v, self.sprompt_len if LOW_BITS else 0,
-                                    BITS_KV, group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
-                                    t_fp_dev=tc.len_dev)
-        attn = _gather_heads(self, attn.transpose(1, 2).reshape(bsz, q_len, -1))
-        return self.wo(attn.reshape(bsz, q_len, self.hidden_size)), None, past_key_value
     self._text_cache.append(k, v)
     k_fp, v_fp = self._text_cache.views()
     past_key_value = (k_fp, v_fp) if use_cache else None

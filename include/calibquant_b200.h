@@ -218,6 +218,41 @@ int cq_lut_out(const void* lut, const void* weights, const uint8_t* enc, void* o
                size_t workspace_bytes, void* stream);
 
 /*
+ * ---- decode-step glue around the attention call ---------------------------------------------------
+ *
+ * cq_rope_split_append replaces, for one decode token per batch row, the QKV split, rotary embedding
+ * and cache append of the patched forward (patch_internvl.py:214-260 split + `apply_rotary_pos_emb`,
+ * :265-266 `torch.cat` of the new key/value onto the fp cache) with one launch.
+ *   qkv          : wqkv output, row b at qkv + b*qkv_stride_b, laid out [n_kv_heads][n_rep q heads, k, v][128]
+ *   cos/sin      : rotary tables [rope_len,128] in the data dtype (what `rotary_emb(x, seq_len)` returns)
+ *   position_ids : int64 [batch] on the device; clamped to [0, rope_len)
+ *   q_out        : [batch, n_kv_heads*n_rep, 128] rotated queries
+ *   k_cache/v_cache : fp caches, token t of (b,h) at base + b*cache_stride_b + h*cache_stride_h + t*128;
+ *                  the rotated key and the value are written at token index `append_index`, or, when
+ *                  t_fp_dev is set, at *t_fp_dev - 1 (the device-side live count already includes the
+ *                  new token, so the same pointer can be handed to cq_decode_attn afterwards).  An
+ *                  index outside [0, capacity) writes nothing.
+ *   Rounding as torch: x*cos rounded to the data dtype, then + rotate_half(x)*sin rounded once more.
+ *
+ * cq_add_rmsnorm and cq_swiglu have no counterpart in the reference repository: they fuse the
+ * elementwise blocks of the InternLM2 decoder layer that the reference leaves to the third-party
+ * model code (residual add + RMSNorm; silu(w1 x) * w3 x), so that a decode step is a dozen launches
+ * per layer.
+ *   cq_add_rmsnorm: if delta != NULL, residual += delta (rounded to the data dtype, in place); then,
+ *     if out != NULL, out = weight * (r_fp32 * rsqrt(mean(r_fp32^2) + eps)).to(dtype) per row of
+ *     `hidden` elements (hidden % 8 == 0, hidden <= 16384; rows contiguous).
+ *   cq_swiglu: out = (silu(gate).to(dtype) * up).to(dtype) over n elements (n % 8 == 0).
+ */
+int cq_rope_split_append(const void* qkv, int64_t qkv_stride_b, const void* cos_table, const void* sin_table,
+                         int rope_len, const int64_t* position_ids, int batch, int n_kv_heads, int n_rep,
+                         int head_dim, void* q_out, void* k_cache, void* v_cache, int64_t cache_stride_b,
+                         int64_t cache_stride_h, int capacity, int append_index, const int32_t* t_fp_dev,
+                         int dtype, void* stream);
+int cq_add_rmsnorm(const void* delta, void* residual, const void* weight, void* out, int64_t rows, int hidden,
+                   float eps, int dtype, void* stream);
+int cq_swiglu(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream);
+
+/*
  * Sticky device status of the prefill kernel (no reference counterpart: the reference checks no
  * CUDA errors).  0, or CQ_ERR_TIMEOUT if one of its bounded barrier waits ever ran out on the
  * current device.  Synchronises the device.
