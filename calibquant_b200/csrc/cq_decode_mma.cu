@@ -143,7 +143,6 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t full_bar[STAGES];
-  __shared__ __align__(16) float qf_s[kMaxRep * kHeadDim];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int n_pairs = dm.batch * dm.hkv;
@@ -355,32 +354,42 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   }
   if (failed) return;
 
-  // ---- full-precision tokens: one warp per token, lane owns 4 channels ---------------------------
+  // ---- full-precision tokens: one 16-token m-tile per warp, K rows straight from global memory
+  // as A fragments (all loads of a tile are independent), query heads as B; MMA in the data dtype.
   const int t_fp = live_t_fp(dm);
-  const int n_fp_tiles = (t_fp + 63) / 64;
-  for (int it = blockIdx.x; it < n_pairs * n_fp_tiles; it += gridDim.x) {
-    const int pair = it / n_fp_tiles, ft = it % n_fp_tiles;
+  const int n_fp_tiles = (t_fp + 15) / 16;
+  for (int it = blockIdx.x * K1_WARPS + warp; it < n_pairs * n_fp_tiles; it += gridDim.x * K1_WARPS) {
+    const int pair = it / n_fp_tiles, t0 = (it % n_fp_tiles) * 16;
     const int b = pair / dm.hkv, hk = pair % dm.hkv;
-    __syncthreads();
-    for (int i = tid; i < dm.n_rep * kHeadDim; i += K1_THREADS)
-      qf_s[i] = Elem<T>::to_f(q[((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep) * kHeadDim + i]);
-    __syncthreads();
-    const T* kf = k_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h;
-    for (int i = warp; i < 64; i += K1_WARPS) {
-      const int t = ft * 64 + i;
-      if (t >= t_fp) break;
-      const uint2 raw = __ldg(reinterpret_cast<const uint2*>(kf + (int64_t)t * kHeadDim) + lane);
-      const float2 k01 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw.x));
-      const float2 k23 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw.y));
-      for (int h = 0; h < dm.n_rep; ++h) {
-        const float4 qv = *reinterpret_cast<const float4*>(&qf_s[h * kHeadDim + lane * 4]);
-        float dot = qv.x * k01.x + qv.y * k01.y + qv.z * k23.x + qv.w * k23.y;
-        dot = warp_sum(dot);
-        if (lane == 0) {
-          const float sc = __fdiv_rn(rnd<T>(dot), 11.313708498984761f);
-          scores[((int64_t)b * dm.hq + hk * dm.n_rep + h) * dm.pitch + dm.t_vis + t] = Elem<T>::from_f(sc);
-        }
-      }
+    const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
+    const T* qrow = q + (row0 + (g < dm.n_rep ? g : 0)) * kHeadDim + 2 * c;
+    const T* kf = k_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h + 2 * c;
+    const T* k_lo = kf + (int64_t)min(t0 + g, t_fp - 1) * kHeadDim;        // rows past the end repeat the last
+    const T* k_hi = kf + (int64_t)min(t0 + g + 8, t_fp - 1) * kHeadDim;    // token; their scores are not stored
+    uint32_t a[8][4], bq[8][2];
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt) {
+      a[kt][0] = __ldg(reinterpret_cast<const uint32_t*>(k_lo + kt * 16));
+      a[kt][1] = __ldg(reinterpret_cast<const uint32_t*>(k_hi + kt * 16));
+      a[kt][2] = __ldg(reinterpret_cast<const uint32_t*>(k_lo + kt * 16 + 8));
+      a[kt][3] = __ldg(reinterpret_cast<const uint32_t*>(k_hi + kt * 16 + 8));
+      bq[kt][0] = g < dm.n_rep ? __ldg(reinterpret_cast<const uint32_t*>(qrow + kt * 16)) : 0u;
+      bq[kt][1] = g < dm.n_rep ? __ldg(reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 8)) : 0u;
+    }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value)
+        mma_bf16(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], bq[kt][0], bq[kt][1]);
+      else
+        mma_f16(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], bq[kt][0], bq[kt][1]);
+    }
+    // acc[0..1] = (token t0+g, heads 2c, 2c+1), acc[2..3] = (token t0+g+8, same heads)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int h = 2 * c + (e & 1), t = t0 + g + 8 * (e >> 1);
+      if (h < dm.n_rep && t < t_fp)
+        scores[(row0 + h) * dm.pitch + dm.t_vis + t] = Elem<T>::from_f(__fdiv_rn(rnd<T>(acc[e]), 11.313708498984761f));
     }
   }
 }
