@@ -46,22 +46,24 @@ constexpr int K1_WARPS = 4;            // warps of a score CTA; each owns 32 / K
 constexpr int K1_THREADS = K1_WARPS * 32;
 constexpr int K1_GPW = 32 / K1_WARPS;
 constexpr int TILE_G = 32;             // 32-token groups per K tile (1024 tokens)
-constexpr int CHUNK_TOK = 1024;        // tokens per attn.V work item
-constexpr int P_PITCH = CHUNK_TOK + 8;  // probability row pitch (halves): +16 B keeps the heads on different banks
-constexpr int VT_TOK = 512;            // tokens per V tile
+// attn.V work items: CT tokens per item, streamed as tiles of VT tokens.  Two shapes are compiled: the
+// large one for long contexts, the small one when the large one would leave CTAs without work.
+constexpr int CT_LARGE = 1024, VT_LARGE = 512, CT_SMALL = 256, VT_SMALL = 256;
+constexpr int K2_RESIDENT = 444;       // attn.V CTAs resident on the device (3 per SM), for the choice below
 constexpr uint32_t WAIT_TRIES = 1u << 22;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __host__ __device__ constexpr int k1_stages(int bits) { return bits == 1 ? 3 : 2; }
 __host__ __device__ constexpr int k1_stage_bytes(int bits) { return bits * 16384 + 2 * 8192; }
 __host__ __device__ constexpr int k2_stages(int bits) { return bits == 4 ? 2 : 3; }
-__host__ __device__ constexpr int k2_stage_bytes(int bits) { return VT_TOK * 16 * bits + 2 * VT_TOK * 8; }
+__host__ __device__ constexpr int k2_stage_bytes(int bits, int vt) { return vt * 16 * bits + 2 * vt * 8; }
 
 struct Dims {
   int batch, hq, hkv, n_rep, t_vis, t_fp, calibrate;
   int n_groups;        // t_vis / 32
   int n_ktiles;        // ceil(n_groups / 32)
-  int n_chunks;        // ceil(t_vis / 1024)
+  int chunk_tok;       // tokens per attn.V work item: CT_LARGE or CT_SMALL
+  int n_chunks;        // ceil(t_vis / chunk_tok)
   int n_fp_chunks;     // ceil(t_fp / 128)
   int n_slots;         // n_chunks + n_fp_chunks
   int pitch;           // score row pitch in elements (multiple of 8)
@@ -402,15 +404,16 @@ struct CalibH {   // per head, as 16-bit pairs for packed arithmetic in the data
   typename D16<T>::T2 mn, rdenom, rdenom_lo, range;
 };
 
-template <typename T, int BITS>
-__global__ void __launch_bounds__(THREADS, 3)
+template <typename T, int BITS, int CHUNK_TOK, int VT_TOK>
+__global__ void __launch_bounds__(THREADS, CHUNK_TOK == CT_SMALL ? 4 : 3)
 k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile_mm,
           const int32_t* __restrict__ v_code, const T* __restrict__ v_scale,
           const T* __restrict__ v_mn, const T* __restrict__ v_fp,
           float* __restrict__ partial, float2* __restrict__ ml, int* __restrict__ status) {
   using T2 = typename D16<T>::T2;
   constexpr int STAGES = k2_stages(BITS);
-  constexpr int STAGE_BYTES = k2_stage_bytes(BITS);
+  constexpr int STAGE_BYTES = k2_stage_bytes(BITS, VT_TOK);
+  constexpr int P_PITCH = CHUNK_TOK + 8;    // probability row pitch (halves): +16 B keeps the heads on different banks
   constexpr int CODE_BYTES = VT_TOK * 16 * BITS;
   constexpr int TOK_BYTES = 16 * BITS;      // code bytes per token
   constexpr int WPT = 4 * BITS;             // code words per token
@@ -436,19 +439,23 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
   }
   __syncthreads();
 
+  // every CTA takes a contiguous range of (KV head, chunk) items, so that the calibration constants
+  // of a head are computed once per run of chunks
+  const int it_first = (int)(((int64_t)blockIdx.x * n_items) / gridDim.x);
+  const int it_end = (int)(((int64_t)(blockIdx.x + 1) * n_items) / gridDim.x);
   // producer state (thread 0): next live tile to issue
   int p_k = 0, p_ti = 0, prod = 0;
   auto issue_next = [&]() -> bool {
     for (;;) {
-      const int it = blockIdx.x + p_k * gridDim.x;
-      if (it >= n_items) return false;
+      const int it = it_first + p_k;
+      if (it >= it_end) return false;
       const int pair = it / dm.n_chunks, chunk = it % dm.n_chunks;
       const int vt = chunk * (CHUNK_TOK / VT_TOK) + p_ti;
       if (p_ti >= CHUNK_TOK / VT_TOK || vt >= n_vtiles) { ++p_k; p_ti = 0; continue; }
       const int s = prod % STAGES;
       unsigned char* base = smem + s * STAGE_BYTES;
       const int64_t tok = (int64_t)pair * dm.t_vis + (int64_t)vt * VT_TOK;
-      const int nt = min(VT_TOK, dm.t_vis - vt * VT_TOK);      // 512, or 256 for a ragged last tile
+      const int nt = min(VT_TOK, dm.t_vis - vt * VT_TOK);      // a ragged last tile holds 256 tokens
       mbar_expect_tx(&full_bar[s], (uint32_t)(nt * (TOK_BYTES + 16)));
       bulk_load_1d(base, v_code + tok * WPT, (uint32_t)(nt * TOK_BYTES), &full_bar[s]);
       bulk_load_1d(base + CODE_BYTES, v_scale + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
@@ -478,21 +485,46 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
     sc1[i] = exp2f((float)(24 - sh - BITS));
   }
 
-  int cons = 0;
+  int cons = 0, cal_pair = -1;
+  CalibH<T> cal_h[2];      // calibration constants of the warp's heads (warp, warp + 4) for cal_pair
   bool failed = false;
+
+  // Logits of one item for head warp + 4*hh, 8 per lane per 256 tokens.  With one-vector items (the
+  // small shape) the next item's logits are fetched while the current item is being multiplied.
+  constexpr int NV = CHUNK_TOK / 256;
+  constexpr bool PREFETCH = NV == 1;
+  const T2 neg_big2 = D16<T>::bcast(-D16<T>::big());
+  const uint32_t nb = *reinterpret_cast<const uint32_t*>(&neg_big2);
+  // (pr, ck) = (KV head, chunk) of the item; score rows of a KV head's query heads are consecutive:
+  // row = pr * n_rep + head
+  auto fetch = [&](int pr, int ck, int hh, int j) -> uint4 {
+    const int64_t row = (int64_t)pr * dm.n_rep + warp + 4 * hh;
+    const int t = (j * 32 + lane) * 8;
+    if (t >= min(CHUNK_TOK, dm.t_vis - ck * CHUNK_TOK)) return make_uint4(nb, nb, nb, nb);
+    return *reinterpret_cast<const uint4*>(scores + row * dm.pitch + ck * CHUNK_TOK + t);
+  };
+  uint4 pre[2] = {make_uint4(nb, nb, nb, nb), make_uint4(nb, nb, nb, nb)};
+  int pair = it_first / dm.n_chunks, chunk = it_first % dm.n_chunks;   // advanced item by item below
+  if (PREFETCH && it_first < it_end) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh)
+      if (warp + 4 * hh < dm.n_rep) pre[hh] = fetch(pair, chunk, hh, 0);
+  }
   for (int k = 0; !failed; ++k) {
-    const int it = blockIdx.x + k * gridDim.x;
-    if (it >= n_items) break;
-    const int pair = it / dm.n_chunks, chunk = it % dm.n_chunks;
-    const int b = pair / dm.hkv, hk = pair % dm.hkv;
-    const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
+    const int it = it_first + k;
+    if (it >= it_end) break;
+    if (k > 0 && ++chunk == dm.n_chunks) { chunk = 0; ++pair; }
+    const int64_t row0 = (int64_t)pair * dm.n_rep;        // = b * hq + hk * n_rep
     const int tok_base = chunk * CHUNK_TOK;
     const int n_tok = min(CHUNK_TOK, dm.t_vis - tok_base);
 
     // ---- probabilities of the chunk: warp w serves heads w, w+4 --------------------------------
-    for (int h = warp; h < dm.n_rep; h += 4) {
-      CalibH<T> cal;
-      if (dm.calibrate) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int h = warp + 4 * hh;
+      if (h >= dm.n_rep) break;
+      CalibH<T>& cal = cal_h[hh];
+      if (dm.calibrate && pair != cal_pair) {
         float lo = INFINITY, hi = -INFINITY;
         for (int i = lane; i < dm.n_mm; i += 32) {
           const float2 v = tile_mm[(row0 + h) * dm.n_mm + i];
@@ -508,16 +540,21 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         cal.rdenom_lo = D16<T>::bcast(1.f / denom - rnd<T>(1.f / denom));   // two-term reciprocal
         cal.range = D16<T>::bcast(range);
       }
-      const T* srow = scores + (row0 + h) * dm.pitch + tok_base;
-      T2 x[4][4];
-      T2 mx2 = D16<T>::bcast(-D16<T>::big());
+      T2 x[NV][4];
+      T2 mx2 = neg_big2;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < NV; ++j) {
         const int t = (j * 32 + lane) * 8;
-        const T2 neg_big = D16<T>::bcast(-D16<T>::big());
-        const uint32_t nb = *reinterpret_cast<const uint32_t*>(&neg_big);
-        uint4 raw = make_uint4(nb, nb, nb, nb);
-        if (t < n_tok) raw = *reinterpret_cast<const uint4*>(srow + t);
+        uint4 raw;
+        if (PREFETCH) {
+          raw = pre[hh];
+          if (it + 1 < it_end) {
+            const bool wrap = chunk + 1 == dm.n_chunks;
+            pre[hh] = fetch(wrap ? pair + 1 : pair, wrap ? 0 : chunk + 1, hh, 0);
+          }
+        } else {
+          raw = fetch(pair, chunk, hh, j);
+        }
         const T2* r2 = reinterpret_cast<const T2*>(&raw);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -535,7 +572,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
       const float m = warp_max(fmaxf(fmx2.x, fmx2.y));
       if (lane == 0) m_s[h] = m;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < CHUNK_TOK / 256; ++j) {
         const int t = (j * 32 + lane) * 8;
         uint4 out;
         __half2* o2 = reinterpret_cast<__half2*>(&out);
@@ -549,6 +586,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         *reinterpret_cast<uint4*>(p_s + h * P_PITCH + t) = out;
       }
     }
+    cal_pair = pair;
     __syncthreads();
 
     float acc[8][4];
@@ -578,7 +616,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
 
       const int nt_tile = min(VT_TOK, dm.t_vis - vt * VT_TOK);
       {
-        // Scales and minima of this warp's 128 tokens, re-laid out in place (2 x 1 KB): each 16-byte
+        // Scales and minima of this warp's quarter of the tile, re-laid out in place: each 16-byte
         // unit holds two tokens x four channel groups; it becomes four (token, token+1) pairs, one
         // per group, which is the MMA B-fragment order, so the main loop needs no permutes.  bf16
         // values are converted to fp16 on the way.
@@ -586,7 +624,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         for (int arr = 0; arr < 2; ++arr) {
           const uint32_t base = (arr == 0 ? vs_b : vmn_b) + (uint32_t)(warp * (VT_TOK / 4)) * 8u;
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
+          for (int i = 0; i < VT_TOK / 256; ++i) {
             const uint32_t addr = base + (uint32_t)(i * 32 + lane) * 16u;
             uint4 v = lds128(addr);
             v.x = D16<T>::to_h2(v.x); v.y = D16<T>::to_h2(v.y); v.z = D16<T>::to_h2(v.z); v.w = D16<T>::to_h2(v.w);
@@ -694,7 +732,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
   }
   if (failed) return;
 
-  // ---- full-precision tokens: chunks of 128, thread = channel -----------------------------------
+  // ---- full-precision tokens: chunks of 128 ------------------------------------------------------
   float* pf_s = red_s;                      // [kMaxRep][128] probabilities
   const int t_fp = live_t_fp(dm);
   const int n_fp_chunks = (t_fp + 127) / 128;
@@ -726,20 +764,51 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
       if (lane == 0) ml[(row0 + h) * dm.n_slots + dm.n_chunks + fc] = make_float2(m, l);
     }
     __syncthreads();
-    float accf[kMaxRep];
-#pragma unroll
-    for (int h = 0; h < kMaxRep; ++h) accf[h] = 0.f;
-    const T* vf = v_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h +
-                       (int64_t)t0 * kHeadDim + tid;
-    for (int t = 0; t < nt; ++t) {
-      const float v = Elem<T>::to_f(__ldg(vf + (int64_t)t * kHeadDim));
-#pragma unroll
-      for (int h = 0; h < kMaxRep; ++h)
-        if (h < dm.n_rep) accf[h] = fmaf(pf_s[h * 128 + t], v, accf[h]);
-    }
+    // warp w takes tokens w, w+4, ...; a lane owns 4 channels; 8 token rows are in flight per batch
+    float accf[kMaxRep][4];
 #pragma unroll
     for (int h = 0; h < kMaxRep; ++h)
-      if (h < dm.n_rep) partial[((row0 + h) * dm.n_slots + dm.n_chunks + fc) * kHeadDim + tid] = accf[h];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) accf[h][e] = 0.f;
+    const T* vf = v_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h +
+                       (int64_t)t0 * kHeadDim + lane * 4;
+    for (int tb = warp; tb < nt; tb += 32) {
+      uint2 raw[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int t = tb + 4 * u;
+        raw[u] = t < nt ? __ldg(reinterpret_cast<const uint2*>(vf + (int64_t)t * kHeadDim)) : make_uint2(0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int t = tb + 4 * u;
+        if (t < nt) {
+          const float2 v01 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw[u].x));
+          const float2 v23 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw[u].y));
+#pragma unroll
+          for (int h = 0; h < kMaxRep; ++h)
+            if (h < dm.n_rep) {
+              const float p = pf_s[h * 128 + t];
+              accf[h][0] = fmaf(p, v01.x, accf[h][0]); accf[h][1] = fmaf(p, v01.y, accf[h][1]);
+              accf[h][2] = fmaf(p, v23.x, accf[h][2]); accf[h][3] = fmaf(p, v23.y, accf[h][3]);
+            }
+        }
+      }
+    }
+    // the stage buffers are idle by now (every tile issued has been consumed): [4][kMaxRep][128] floats
+    float* xs = reinterpret_cast<float*>(smem);
+#pragma unroll
+    for (int h = 0; h < kMaxRep; ++h)
+      if (h < dm.n_rep)
+        *reinterpret_cast<float4*>(xs + (warp * kMaxRep + h) * kHeadDim + lane * 4) =
+            make_float4(accf[h][0], accf[h][1], accf[h][2], accf[h][3]);
+    __syncthreads();
+    for (int h = 0; h < dm.n_rep; ++h) {
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) o += xs[(w * kMaxRep + h) * kHeadDim + tid];
+      partial[((row0 + h) * dm.n_slots + dm.n_chunks + fc) * kHeadDim + tid] = o;
+    }
   }
 }
 
@@ -821,7 +890,9 @@ static Dims make_dims(const cq_decode_args* a) {
   d.t_vis = a->t_vis; d.t_fp = a->t_fp; d.calibrate = a->calibrate ? 1 : 0;
   d.n_groups = d.t_vis / 32;
   d.n_ktiles = (d.n_groups + TILE_G - 1) / TILE_G;
-  d.n_chunks = (d.t_vis + CHUNK_TOK - 1) / CHUNK_TOK;
+  // the large items only when they fill the resident CTAs about three times over
+  d.chunk_tok = (int64_t)d.batch * d.hkv * ((d.t_vis + CT_LARGE - 1) / CT_LARGE) >= 3 * K2_RESIDENT ? CT_LARGE : CT_SMALL;
+  d.n_chunks = (d.t_vis + d.chunk_tok - 1) / d.chunk_tok;
   d.n_fp_chunks = (d.t_fp + 127) / 128;
   d.n_slots = d.n_chunks + d.n_fp_chunks;
   d.pitch = (d.t_vis + d.t_fp + 7) / 8 * 8;
@@ -853,8 +924,8 @@ static int sm_count() {
   return n;
 }
 
-template <typename T, int BITS>
-static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st) {
+template <typename T, int BITS, int CT, int VT>
+static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st) {
   int* status = reinterpret_cast<int*>(ws + l.status_off);
   T* scores = reinterpret_cast<T*>(ws + l.scores_off);
   float2* mm = reinterpret_cast<float2*>(ws + l.mm_off);
@@ -863,9 +934,10 @@ static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned
   const int n_pairs = d.batch * d.hkv;
 
   auto k1 = k1_scores<T, BITS>;
-  auto k2 = k2_attn_v<T, BITS>;
+  auto k2 = k2_attn_v<T, BITS, CT, VT>;
   const int smem1 = k1_stages(BITS) * k1_stage_bytes(BITS) + 1024;
-  const int smem2 = k2_stages(BITS) * k2_stage_bytes(BITS) + 4 * kMaxRep * 136 * 4 + 1024;
+  constexpr int p_bytes = kMaxRep * (CT + 8) * 2, red_bytes = 4 * kMaxRep * 136 * 4;
+  const int smem2 = k2_stages(BITS) * k2_stage_bytes(BITS, VT) + (p_bytes > red_bytes ? p_bytes : red_bytes) + 1024;
   static bool configured_dev[64] = {};   // per template instance and device
   static int occ1_dev[64], occ2_dev[64];
   int dev = 0;
@@ -914,6 +986,12 @@ static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned
     return check_launch();
   }
   return CQ_OK;
+}
+
+template <typename T, int BITS>
+static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st) {
+  return d.chunk_tok == CT_LARGE ? run_shape<T, BITS, CT_LARGE, VT_LARGE>(a, d, l, ws, st)
+                                 : run_shape<T, BITS, CT_SMALL, VT_SMALL>(a, d, l, ws, st);
 }
 
 }  // namespace mma
