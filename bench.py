@@ -42,8 +42,8 @@ L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (kernel, bits, context, batch) -> bytes
 NCU_TRAFFIC = {
-    ("k2_attn_v", 1, 32768, 8): 87_874_816,
-    ("k1_scores", 1, 32768, 8): 69_842_432,
+    ("k2_attn_v", 1, 32768, 8): 87_182_336,
+    ("k1_scores", 1, 32768, 8): 70_405_888,
 }
 
 
@@ -408,9 +408,81 @@ def run_model(args, rank, world, device):
     }
 
 
+def run_pack(args, rank, world, device):
+    """Quantize+pack of the visual span alone (the prefill-side kernel of the path): K per channel
+    and V per token of `batch` rows per GPU, fp16 in, codes + scales + minima out."""
+    peak, which = measured_peak()
+    res = time_pack(args.batch, args.context, args.bits, device, reps=max(args.steps, 1))
+    ms = res["k_per_channel"]["ms"] + res["v_per_token"]["ms"]
+    n = args.batch * HKV * args.context * D
+    nbytes = 2 * n * res["bytes_per_element"]
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms = float(t.item())
+    gbps = world * nbytes / ms / 1e6
+    worst = min(res["k_per_channel"]["GBps"], res["v_per_token"]["GBps"])
+    return {
+        "metric": f"pack_{args.bits}bit_GBps", "value": round(gbps, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": 2, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"quantize+pack K (per channel) and V (per token), batch {args.batch}/GPU, 8 KV heads, "
+                               f"{args.context} tokens, head_dim 128, {args.bits}-bit, group 32",
+                   "l2": "two source tensors of %.0f MB alternate" % (n * 2 / 1e6)},
+        "kernels": res,
+        "roofline": {"bound": "hbm", "kernel": "pack_k_per_channel_kernel / pack_last_dim_kernel",
+                     "achieved": worst, "peak": peak, "unit": "GB/s", "frac": round(worst / peak, 4),
+                     "peak_source": which, "traffic": None,
+                     "algorithmic_bytes_per_element": res["bytes_per_element"]},
+        "gpu_launches": 2 * max(args.steps, 1),
+    }
+
+
+def run_prefill(args, rank, world, device):
+    """Dense causal prefill attention alone (tcgen05 kernel) on the 7B prefill shape: batch rows per
+    GPU x 3392 tokens, 32 query / 8 KV heads, bf16."""
+    from calibquant_b200 import ops
+    B, T, HQ = (args.batch if args.batch != 8 else 16), 3392, 32
+    g = torch.Generator(device=device).manual_seed(3)
+    q = torch.randn(B, T, HQ, D, generator=g, device=device).to(torch.bfloat16)
+    k = torch.randn(B, T, HKV, D, generator=g, device=device).to(torch.bfloat16)
+    v = torch.randn(B, T, HKV, D, generator=g, device=device).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    for _ in range(max(args.warmup, 3)):
+        ops.prefill_attention(q, k, v, out=out)
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        ops.prefill_attention(q, k, v, out=out)
+    ev1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=device, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms = float(t.item())
+    flops = 4.0 * B * HQ * T * T * D / 2
+    tf = world * flops / ms / 1e9
+    pk_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pk_path):
+        peak, which = float(json.load(open(pk_path))["bf16_tflops"]), "measured (cuBLAS bf16 burst)"
+    else:
+        peak, which = 1590.0, "fallback"
+    return {
+        "metric": "prefill_attn_TFLOPs", "value": round(tf, 1), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"causal prefill attention, batch {B}/GPU, {T} tokens, 32q/8kv heads, head_dim 128",
+                   "flops": "4*B*Hq*T^2*D/2 (causal half)", "l2": "q+k+v+out = %.0f MB per pass" % ((2 * q.numel() + 2 * k.numel()) * 2 / 1e6)},
+        "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": round(tf / world, 1), "peak": peak,
+                     "unit": "TFLOP/s", "frac": round(tf / world / peak, 4), "peak_source": which, "traffic": None},
+        "gpu_launches": args.steps,
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="attn", choices=["attn", "model7b", "model20b"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "model7b", "model20b", "pack", "prefill"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
@@ -442,7 +514,8 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=device)
     try:
-        line = run_ours(args, rank, world, device) if args.workload == "attn" else run_model(args, rank, world, device)
+        runner = {"attn": run_ours, "pack": run_pack, "prefill": run_prefill}.get(args.workload, run_model)
+        line = runner(args, rank, world, device)
         if rank == 0:
             print(json.dumps(line), flush=True)
     finally:
