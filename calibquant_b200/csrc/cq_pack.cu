@@ -128,10 +128,18 @@ __device__ __forceinline__ void pack_chunk(const uint4& raw, int64_t chunk, bool
 #pragma unroll
       for (int k = 0; k < 3; ++k) thr[k] = Pk<T>::floor2(break_point<T>(k) * scale);
       const T2 mnb = Pk<T>::bcast(mn);
+      if (BITS == 1) {
+        // all-ones compare masks, element 2i -> bit 2i, element 2i+1 -> bit 17+2i, folded at the end
+        unsigned r = 0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const unsigned c = codes2<T, BITS>(__hsub2(xv[i], mnb), thr);   // x - mn: one rounding, as the reference
-        local |= ((c & 0xffffu) | (c >> (16 - BITS))) << (2 * i * BITS);
+        for (int i = 0; i < 4; ++i) r |= __hgt2_mask(__hsub2(xv[i], mnb), thr[0]) & (0x00020001u << (2 * i));
+        local = (r | (r >> 16)) & 0xffu;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const unsigned c = codes2<T, BITS>(__hsub2(xv[i], mnb), thr);   // x - mn: one rounding, as the reference
+          local |= ((c & 0xffffu) | (c >> (16 - BITS))) << (2 * i * BITS);
+        }
       }
     } else {
       const float rcp = __frcp_rn(scale);
