@@ -3,16 +3,18 @@
 // One CTA = 128 queries of one (batch, query head).  Warp 8 (one elected lane) is the producer and
 // the MMA issuer: it streams 128-key K/V tiles through a two-stage shared-memory ring with tiled
 // TMA loads and issues
-//     S  = Q K^T      tcgen05.mma kind::f16, A = Q (K-major), B = K (K-major), D in TMEM columns
+//     S = Q K^T       tcgen05.mma kind::f16, A = Q (K-major), B = K (K-major), D in TMEM columns
 //                     [0,128) / [128,256) alternately, so S(j+1) is computed while tile j is in softmax
-//     PV = P V        A = P (K-major, written by the softmax warps), B = V (MN-major), D in TMEM
-//                     columns [256,384)
-// Warps 0-7 are the softmax warps: thread = (query row, 64-column half).  They read S from TMEM
+//     O += P V        A = P (K-major, written by the softmax warps into one of two shared-memory
+//                     buffers), B = V (MN-major), D accumulates in TMEM columns [256,384) over all tiles
+// Warps 0-7 are the softmax warps: thread = (query row, 64-column half).  They read S from TMEM once
 // (tcgen05.ld), apply scale, causal mask and the online softmax (the row maximum of the two halves
-// meets in shared memory), write P (16-bit) into the swizzled A-operand layout, and fold each
-// tile's PV into fp32 accumulators held in registers (o = o*alpha + pv), so TMEM is never written
-// by threads.  All operand tiles use the 128-byte swizzle: a [128 rows x 64 elements] TMA box lands
-// directly in the canonical UMMA layout (8-row atoms of 1024 bytes).
+// meets in shared memory) and write P (16-bit) into the swizzled A-operand layout.  The running
+// maximum is lazy: a row keeps its reference maximum until the true one exceeds it by more than 2^8,
+// and only then are that row's O columns in TMEM and its running sum rescaled (tcgen05.ld / st
+// between two PV products); probabilities therefore stay below 256 and O is read back once, at the
+// end.  All operand tiles use the 128-byte swizzle: a [128 rows x 64 elements] TMA box lands directly
+// in the canonical UMMA layout (8-row atoms of 1024 bytes).
 //
 // Every mbarrier wait is bounded; on a timeout the CTA records CQ_ERR_TIMEOUT in the status word,
 // stops issuing work, frees its TMEM and returns.
@@ -30,10 +32,11 @@ using namespace ptx;
 constexpr int BM = 128, BN = 128;
 constexpr int PANEL_BYTES = 128 * 128;          // [128 rows][64 x 16-bit]
 constexpr int TILE_BYTES = 2 * PANEL_BYTES;     // [128 rows][128 x 16-bit]
-constexpr int SMEM_BYTES = TILE_BYTES * 6 + 1024;   // Q, K x2, V x2, P (+ alignment slack)
+constexpr int SMEM_BYTES = TILE_BYTES * 7 + 1024;   // Q, K x2, V x2, P x2 (+ alignment slack)
 constexpr int SOFTMAX_THREADS = 256, MMA_WARP = 8, THREADS = SOFTMAX_THREADS + 32;
 constexpr uint32_t WAIT_TRIES = 1u << 22;
-constexpr uint32_t TMEM_COLS = 512;          // S x2 (double-buffered) + PV; allocations are powers of two
+constexpr uint32_t TMEM_COLS = 512;          // S x2 (double-buffered) + O; allocations are powers of two
+constexpr float RESCALE_LOG2 = 8.f;          // a row is rescaled when its maximum grew by more than 2^8
 
 struct Params {
   void* out;
@@ -76,6 +79,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, int c0, int c1, int c2, int c3, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
@@ -120,8 +145,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   unsigned char* q_s = smem;
   unsigned char* k_s = q_s + TILE_BYTES;        // 2 stages
   unsigned char* v_s = k_s + 2 * TILE_BYTES;    // 2 stages
-  unsigned char* p_s = v_s + 2 * TILE_BYTES;
-  __shared__ __align__(8) uint64_t bar_q, bar_kv_full[2], bar_kv_free[2], bar_s[2], bar_p, bar_pv;
+  unsigned char* p_s = v_s + 2 * TILE_BYTES;    // 2 buffers
+  __shared__ __align__(8) uint64_t bar_q, bar_kv_full[2], bar_kv_free[2], bar_s[2], bar_p[2], bar_pv[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ float half_max_s[2][BM];           // per-row maximum of each 64-column half
 
@@ -138,9 +163,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(&bar_kv_full[s], 1);
       mbar_init(&bar_kv_free[s], 1);
       mbar_init(&bar_s[s], 1);
+      mbar_init(&bar_p[s], SOFTMAX_THREADS);    // P buffer s written (tiles s, s+2, ...)
+      mbar_init(&bar_pv[s], 1);                 // the PV product that read P buffer s has completed
     }
-    mbar_init(&bar_p, SOFTMAX_THREADS);
-    mbar_init(&bar_pv, 1);
     mbar_fence_init();
   }
   if (warp == MMA_WARP) tmem_alloc(&tmem_base_s, TMEM_COLS);
@@ -148,7 +173,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tmem_PV = tmem + 256;          // S buffers at columns [0,128) and [128,256)
+  const uint32_t tmem_O = tmem + 256;           // S buffers at columns [0,128) and [128,256)
 
   if (warp == MMA_WARP) {
     // ================= producer + MMA issuer (one lane) =================
@@ -161,7 +186,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tma_load_4d(v_s + s * TILE_BYTES, &tm_v, 0, hk, j * BN, b, &bar_kv_full[s]);
         tma_load_4d(v_s + s * TILE_BYTES + PANEL_BYTES, &tm_v, 64, hk, j * BN, b, &bar_kv_full[s]);
       };
-      const uint32_t qa = smem_u32(q_s), pa = smem_u32(p_s);
+      const uint32_t qa = smem_u32(q_s);
       auto issue_s = [&](int j) -> bool {       // S(j) = Q K(j)^T into S buffer j&1
         const int s = j & 1;
         if (!mbar_wait_bounded(&bar_kv_full[s], (uint32_t)((j >> 1) & 1), WAIT_TRIES)) return false;
@@ -191,17 +216,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           ok = issue_s(j + 1);
           if (!ok) break;
         }
-        ok = mbar_wait_bounded(&bar_p, (uint32_t)(j & 1), WAIT_TRIES);
+        ok = mbar_wait_bounded(&bar_p[s], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t va = smem_u32(v_s + s * TILE_BYTES);
+        const uint32_t va = smem_u32(v_s + s * TILE_BYTES), pa = smem_u32(p_s + s * TILE_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {        // PV(j): 16 keys per step
+        for (int ks = 0; ks < 8; ++ks) {        // O += P(j) V(j): 16 keys per step
           const uint64_t ad = smem_desc(pa + (uint32_t)((ks >> 2) * PANEL_BYTES + (ks & 3) * 32), 16, 1024);
           const uint64_t bd = smem_desc(va + (uint32_t)(ks * 2048), PANEL_BYTES, 1024);
-          umma(tmem_PV, ad, bd, p.idesc_pv, ks > 0);
+          umma(tmem_O, ad, bd, p.idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(&bar_pv);
+        umma_commit(&bar_pv[s]);
         umma_commit(&bar_kv_free[s]);
         if (j + 2 < n_tiles) {                  // refill this stage once its MMAs have drained
           ok = mbar_wait_bounded(&bar_kv_free[s], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
@@ -213,64 +238,73 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
     __syncwarp();
   } else {
-    // ===== softmax + accumulation: thread = (query row, 64-column half); 8 warps =====
+    // ===== softmax: thread = (query row, 64-column half); 8 warps =====
     const int quarter = warp & 3, half = warp >> 2;
     const int r_in = quarter * 32 + lane;               // row inside the tile = TMEM lane
     const int row = q0 + r_in;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const uint32_t col0 = (uint32_t)half * 64u;
-    float o[64];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;               // l_run: sum over this thread's columns only
+    float m_ref = -INFINITY, l_run = 0.f;               // reference maximum (log2 units); sum over this thread's columns
+    // Once a bounded wait has run out, `ok` stays false and all later waits are skipped, but every
+    // thread still walks all tiles so that the named barrier below always sees its 256 arrivals.
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    for (int j = 0; j < n_tiles; ++j) {
       const int key0 = j * BN + (int)col0;
       const bool need_mask = (j * BN + BN - 1 > q0) || (j * BN + BN > p.t_len);
       const uint32_t tS = tmem + (uint32_t)(j & 1) * 128u + lane_off + col0;
-      ok = mbar_wait_bounded(&bar_s[j & 1], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
-      if (!ok) break;
+      if (ok) ok = mbar_wait_bounded(&bar_s[j & 1], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
       tc_fence_after();
-      // pass 1: maximum of this half of the row, exchanged with the other half through smem
+      uint32_t sv[2][32];                               // this thread's 64 logits, read once
+      tmem_ld32_nowait(tS, sv[0]);
+      tmem_ld32_nowait(tS + 32, sv[1]);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(tS + cc * 32, r);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc)
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
           if (need_mask) {
             const int key = key0 + cc * 32 + i;
-            if (key > row || key >= p.t_len) v = -INFINITY;
+            if (key > row || key >= p.t_len) sv[cc][i] = 0xff800000u;   // -inf
           }
-          mx = fmaxf(mx, v);
+          mx = fmaxf(mx, __uint_as_float(sv[cc][i]));
         }
-      }
       half_max_s[half][r_in] = mx;
       asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
       mx = fmaxf(mx, half_max_s[half ^ 1][r_in]);
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
-      m_run = m_new;
-      // pass 2: probabilities of this half -> its 64-key panel of P (A-operand layout), row sum
-      float rs = 0.f;
-      unsigned char* prow = p_s + half * PANEL_BYTES + r_in * 128;
+      const float m_true = fmaxf(m_ref, mx * p.scale_log2);
+      // both threads of a row see the same m_ref and m_true, hence take the same decision
+      const bool grow = m_true - m_ref > RESCALE_LOG2;  // also true for the first tile (m_ref = -inf)
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // O holds PV(0..j-1); the product that last wrote it read P buffer (j-1)&1
+        if (ok) ok = mbar_wait_bounded(&bar_pv[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), WAIT_TRIES);
+        tc_fence_after();
+        const float alpha = grow ? exp2f(m_ref - m_true) : 1.f;    // 0 when m_ref was -inf
 #pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t r[32];
+          tmem_ld32(tmem_O + lane_off + col0 + cc * 32, r);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(tmem_O + lane_off + col0 + cc * 32, r);
+        }
+        tmem_st_wait();
+        l_run *= alpha;
+      }
+      if (grow) m_ref = m_true;
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      // the P buffer of this tile was last read by PV(j-2)
+      if (j >= 2 && ok) ok = mbar_wait_bounded(&bar_pv[j & 1], (uint32_t)(((j - 2) >> 1) & 1), WAIT_TRIES);
+      float rs = 0.f;
+      unsigned char* prow = p_s + (j & 1) * TILE_BYTES + half * PANEL_BYTES + r_in * 128;
+#pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(tS + cc * 32, r);
         uint32_t w[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_use));
-          float p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_use));
-          if (need_mask) {
-            const int key = key0 + cc * 32 + i;
-            if (key > row || key >= p.t_len) p0 = 0.f;
-            if (key + 1 > row || key + 1 >= p.t_len) p1 = 0.f;
-          }
+          // masked logits are -inf: ex2 gives 0
+          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[cc][i]), p.scale_log2, -m_use));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[cc][i + 1]), p.scale_log2, -m_use));
           rs += p0 + p1;
           w[i >> 1] = pack16(p0, p1, p.is_bf16);
         }
@@ -280,41 +314,38 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(w[4 * qd], w[4 * qd + 1], w[4 * qd + 2], w[4 * qd + 3]);
         }
       }
-      l_run = l_run * alpha + rs;
+      l_run += rs;
       fence_proxy_async_smem();        // P (generic-proxy writes) must be visible to the MMA (async proxy)
       tc_fence_before();
-      mbar_arrive(&bar_p);
-      // fold this thread's 64 output columns of PV(j) into the register accumulators
-      ok = mbar_wait_bounded(&bar_pv, (uint32_t)(j & 1), WAIT_TRIES);
-      if (!ok) break;
-      tc_fence_after();
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(tmem_PV + lane_off + col0 + cc * 32, r);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[cc * 32 + i] = fmaf(o[cc * 32 + i], alpha, __uint_as_float(r[i]));
-      }
-      tc_fence_before();
+      mbar_arrive(&bar_p[j & 1]);
     }
     // the row sum is split over the two halves
     half_max_s[half][r_in] = l_run;
     asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
     const float l_tot = l_run + half_max_s[half ^ 1][r_in];
+    if (ok) ok = mbar_wait_bounded(&bar_pv[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), WAIT_TRIES);
     if (!ok) {
       atomicExch(p.status, CQ_ERR_TIMEOUT);
-    } else if (row < p.t_len) {
+    } else {
+      tc_fence_after();
       const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
       unsigned char* dst = reinterpret_cast<unsigned char*>(p.out) +
                            2 * ((int64_t)b * p.o_sb + (int64_t)row * p.o_st + (int64_t)h * p.o_sh) + col0 * 2;
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t r[32];
+        tmem_ld32(tmem_O + lane_off + col0 + cc * 32, r);     // warp-collective: rows past the end load too
+        if (row < p.t_len) {
 #pragma unroll
-      for (int i = 0; i < 64; i += 8) {
-        uint4 w;
-        w.x = pack16(o[i] * inv, o[i + 1] * inv, p.is_bf16);
-        w.y = pack16(o[i + 2] * inv, o[i + 3] * inv, p.is_bf16);
-        w.z = pack16(o[i + 4] * inv, o[i + 5] * inv, p.is_bf16);
-        w.w = pack16(o[i + 6] * inv, o[i + 7] * inv, p.is_bf16);
-        *reinterpret_cast<uint4*>(dst + i * 2) = w;
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv, p.is_bf16);
+            w.y = pack16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv, p.is_bf16);
+            w.z = pack16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv, p.is_bf16);
+            w.w = pack16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv, p.is_bf16);
+            *reinterpret_cast<uint4*>(dst + (cc * 32 + i) * 2) = w;
+          }
+        }
       }
     }
   }
