@@ -90,3 +90,21 @@ def test_status_word_clean_and_general_kernel_agrees(ops):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, CQ_PREFILL_GENERAL="1")
     subprocess.run([sys.executable, "-c", code], cwd=root, env=env, check=True, timeout=300)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 5e-3), (torch.bfloat16, 1e-2)])
+def test_growing_logits_force_row_rescales(ops, dtype, tol):
+    """Keys whose norm grows along the sequence make the row maximum jump by far more than 2^8
+    between key tiles, so the lazily rescaled accumulator path runs on most rows and tiles; a few
+    rows also see a *falling* maximum (stale reference kept)."""
+    B, T, Hq, Hkv = 1, 700, 4, 2
+    g = torch.Generator().manual_seed(21)
+    q = (torch.randn(B, T, Hq, 128, generator=g) * 3).to(dtype)
+    ramp = torch.linspace(0.2, 4.0, T).view(1, T, 1, 1)
+    ramp[:, 300:420] *= 0.1
+    k = (torch.randn(B, T, Hkv, 128, generator=g) * ramp).to(dtype)
+    v = torch.randn(B, T, Hkv, 128, generator=g).to(dtype)
+    ref = oracle_prefill.causal_attention(q, k, v)
+    out = ops.prefill_attention(q.cuda(), k.cuda(), v.cuda())
+    assert torch.isfinite(out.float()).all()
+    assert rel_l2(out, ref) <= tol, rel_l2(out, ref)
