@@ -1,23 +1,28 @@
 // Dense causal prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
 //
-// One CTA = 128 queries of one (batch, query head).  Warp 8 (one elected lane) is the producer and
-// the MMA issuer: it streams 128-key K/V tiles through a two-stage shared-memory ring with tiled
-// TMA loads and issues
-//     S = Q K^T       tcgen05.mma kind::f16, A = Q (K-major), B = K (K-major), D in TMEM columns
-//                     [0,128) / [128,256) alternately, so S(j+1) is computed while tile j is in softmax
-//     O += P V        A = P (K-major, written by the softmax warps into one of two shared-memory
-//                     buffers), B = V (MN-major), D accumulates in TMEM columns [256,384) over all tiles
-// Warps 0-7 are the softmax warps: thread = (query row, 64-column half).  They read S from TMEM once
-// (tcgen05.ld), apply scale, causal mask and the online softmax (the row maximum of the two halves
-// meets in shared memory) and write P (16-bit) into the swizzled A-operand layout.  The running
-// maximum is lazy: a row keeps its reference maximum until the true one exceeds it by more than 2^8,
-// and only then are that row's O columns in TMEM and its running sum rescaled (tcgen05.ld / st
-// between two PV products); probabilities therefore stay below 256 and O is read back once, at the
-// end.  All operand tiles use the 128-byte swizzle: a [128 rows x 64 elements] TMA box lands directly
-// in the canonical UMMA layout (8-row atoms of 1024 bytes).
+// One CTA = 256 queries of one (batch, query head), as two 128-row tiles A and B that share the
+// K/V stream.  Roles:
+//   warp 9 (one lane)  TMA producer: Q tiles once, then 128-key K/V tiles through a two-stage ring
+//   warp 8 (one lane)  MMA issuer:
+//        S_X = Q_X K^T   tcgen05.mma kind::f16, A = Q_X and B = K from shared memory (K-major), D in the
+//                        tile's 128 TMEM columns
+//        O_X += P_X V    A = P_X read from TENSOR MEMORY (16-bit pairs the softmax warps stored over the
+//                        first 64 columns of S_X), B = V from shared memory (MN-major), D accumulates in
+//                        the tile's O columns over all key tiles
+//   warps 0-3 / 4-7    softmax of tile A / B: thread = one query row (= TMEM lane).  It reads its 128
+//                        logits once (tcgen05.ld), applies scale, causal mask and the online softmax
+//                        with a lazy maximum, and stores P back to TMEM (tcgen05.st).  No shared memory,
+//                        no cross-thread exchange: the two tiles run out of phase, so one tile's
+//                        exponentials overlap the other tile's products on the tensor pipe.
+// Lazy maximum: a row keeps its reference maximum until the true one exceeds it by more than 2^8, and
+// only then are that row's O columns and running sum rescaled (tcgen05.ld / st between two PV
+// products); probabilities stay below 256 and O is read back once, at the end.
+// TMEM columns: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512).  Operand tiles in shared
+// memory use the 128-byte swizzle: a [128 rows x 64 elements] TMA box lands directly in the
+// canonical UMMA layout (8-row atoms of 1024 bytes).
 //
 // Every mbarrier wait is bounded; on a timeout the CTA records CQ_ERR_TIMEOUT in the status word,
-// stops issuing work, frees its TMEM and returns.
+// skips its remaining waits, frees its TMEM and returns.
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -32,10 +37,10 @@ using namespace ptx;
 constexpr int BM = 128, BN = 128;
 constexpr int PANEL_BYTES = 128 * 128;          // [128 rows][64 x 16-bit]
 constexpr int TILE_BYTES = 2 * PANEL_BYTES;     // [128 rows][128 x 16-bit]
-constexpr int SMEM_BYTES = TILE_BYTES * 7 + 1024;   // Q, K x2, V x2, P x2 (+ alignment slack)
-constexpr int SOFTMAX_THREADS = 256, MMA_WARP = 8, THREADS = SOFTMAX_THREADS + 32;
+constexpr int SMEM_BYTES = TILE_BYTES * 6 + 1024;   // Q x2, K x2, V x2 (+ alignment slack)
+constexpr int SOFTMAX_THREADS = 256, MMA_WARP = 8, TMA_WARP = 9, THREADS = SOFTMAX_THREADS + 64;
 constexpr uint32_t WAIT_TRIES = 1u << 22;
-constexpr uint32_t TMEM_COLS = 512;          // S x2 (double-buffered) + O; allocations are powers of two
+constexpr uint32_t TMEM_COLS = 512;
 constexpr float RESCALE_LOG2 = 8.f;          // a row is rescaled when its maximum grew by more than 2^8
 
 struct Params {
@@ -63,6 +68,14 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t b
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// the same product with the A operand in tensor memory (16-bit elements, two per 32-bit column)
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -128,8 +141,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-__device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
-  if (is_bf16) {
+template <bool IS_BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if (IS_BF16) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
   }
@@ -137,25 +151,30 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi, int is_bf16) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+template <bool IS_BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  unsigned char* q_s = smem;
-  unsigned char* k_s = q_s + TILE_BYTES;        // 2 stages
+  unsigned char* q_s = smem;                    // tiles A, B
+  unsigned char* k_s = q_s + 2 * TILE_BYTES;    // 2 stages
   unsigned char* v_s = k_s + 2 * TILE_BYTES;    // 2 stages
-  unsigned char* p_s = v_s + 2 * TILE_BYTES;    // 2 buffers
+  // per query tile X: bar_s (S_X ready), bar_p (P_X stored, 128 arrivals), bar_pv (O_X += P_X V done);
+  // each completes once per key tile of X
   __shared__ __align__(8) uint64_t bar_q, bar_kv_full[2], bar_kv_free[2], bar_s[2], bar_p[2], bar_pv[2];
   __shared__ uint32_t tmem_base_s;
-  __shared__ float half_max_s[2][BM];           // per-row maximum of each 64-column half
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int qt = gridDim.x - 1 - blockIdx.x;    // longest rows first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.hq / p.hkv);
-  const int q0 = qt * BM;
-  const int n_tiles = min((q0 + BM + BN - 1) / BN, (p.t_len + BN - 1) / BN);
+  const int q0 = qt * 2 * BM;
+  const int t_tiles = (p.t_len + BN - 1) / BN;
+  // key tiles of query tile X = 0 (A), 1 (B); B may lie wholly past the end
+  const int n_a = min((q0 + BM + BN - 1) / BN, t_tiles);
+  const int n_b = q0 + BM < p.t_len ? min((q0 + 2 * BM + BN - 1) / BN, t_tiles) : 0;
+  const int n_max = max(n_a, n_b);
 
   if (tid == 0) {
     mbar_init(&bar_q, 1);
@@ -163,8 +182,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(&bar_kv_full[s], 1);
       mbar_init(&bar_kv_free[s], 1);
       mbar_init(&bar_s[s], 1);
-      mbar_init(&bar_p[s], SOFTMAX_THREADS);    // P buffer s written (tiles s, s+2, ...)
-      mbar_init(&bar_pv[s], 1);                 // the PV product that read P buffer s has completed
+      mbar_init(&bar_p[s], SOFTMAX_THREADS / 2);
+      mbar_init(&bar_pv[s], 1);
     }
     mbar_fence_init();
   }
@@ -173,177 +192,180 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t tmem_O = tmem + 256;           // S buffers at columns [0,128) and [128,256)
 
-  if (warp == MMA_WARP) {
-    // ================= producer + MMA issuer (one lane) =================
+  if (warp == TMA_WARP) {
+    // ================= TMA producer (one lane) =================
     if (lane == 0) {
-      auto load_kv = [&](int j) {
+      mbar_expect_tx(&bar_q, 2 * TILE_BYTES);
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        tma_load_4d(q_s + x * TILE_BYTES, &tm_q, 0, h, q0 + x * BM, b, &bar_q);
+        tma_load_4d(q_s + x * TILE_BYTES + PANEL_BYTES, &tm_q, 64, h, q0 + x * BM, b, &bar_q);
+      }
+      bool ok = true;
+      for (int j = 0; j < n_max && ok; ++j) {
         const int s = j & 1;
+        if (j >= 2) ok = mbar_wait_bounded(&bar_kv_free[s], (uint32_t)(((j - 2) >> 1) & 1), WAIT_TRIES);
+        if (!ok) break;
         mbar_expect_tx(&bar_kv_full[s], 2 * TILE_BYTES);
         tma_load_4d(k_s + s * TILE_BYTES, &tm_k, 0, hk, j * BN, b, &bar_kv_full[s]);
         tma_load_4d(k_s + s * TILE_BYTES + PANEL_BYTES, &tm_k, 64, hk, j * BN, b, &bar_kv_full[s]);
         tma_load_4d(v_s + s * TILE_BYTES, &tm_v, 0, hk, j * BN, b, &bar_kv_full[s]);
         tma_load_4d(v_s + s * TILE_BYTES + PANEL_BYTES, &tm_v, 64, hk, j * BN, b, &bar_kv_full[s]);
-      };
-      const uint32_t qa = smem_u32(q_s);
-      auto issue_s = [&](int j) -> bool {       // S(j) = Q K(j)^T into S buffer j&1
-        const int s = j & 1;
-        if (!mbar_wait_bounded(&bar_kv_full[s], (uint32_t)((j >> 1) & 1), WAIT_TRIES)) return false;
-        tc_fence_after();
-        const uint32_t ka = smem_u32(k_s + s * TILE_BYTES);
+      }
+      if (!ok) atomicExch(p.status, CQ_ERR_TIMEOUT);
+    }
+    __syncwarp();
+  } else if (warp == MMA_WARP) {
+    // ================= MMA issuer (one lane) =================
+    if (lane == 0) {
+      auto issue_s = [&](int x, int j) {        // S_x(j) = Q_x K(j)^T; the K tile is known to be there
+        const uint32_t qa = smem_u32(q_s + x * TILE_BYTES), ka = smem_u32(k_s + (j & 1) * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {        // 16 channels per step; panel = ks/4, 32 B per step
           const uint32_t off = (uint32_t)((ks >> 2) * PANEL_BYTES + (ks & 3) * 32);
-          umma(tmem + (uint32_t)s * 128u, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024),
+          umma(tmem + (uint32_t)x * 128u, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024),
                p.idesc_s, ks > 0);
         }
-        umma_commit(&bar_s[s]);
-        return true;
+        umma_commit(&bar_s[x]);
       };
-      mbar_expect_tx(&bar_q, TILE_BYTES);
-      tma_load_4d(q_s, &tm_q, 0, h, q0, b, &bar_q);
-      tma_load_4d(q_s + PANEL_BYTES, &tm_q, 64, h, q0, b, &bar_q);
-      load_kv(0);
-      if (n_tiles > 1) load_kv(1);
       bool ok = mbar_wait_bounded(&bar_q, 0, WAIT_TRIES);
-      ok = ok && issue_s(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1;
-        // S(j+1) goes to the other S buffer as soon as its K tile is there: the softmax warps
-        // released that buffer when they signalled P(j-1), which was waited for last iteration
-        if (j + 1 < n_tiles) {
-          ok = issue_s(j + 1);
-          if (!ok) break;
-        }
-        ok = mbar_wait_bounded(&bar_p[s], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
-        if (!ok) break;
+      ok = ok && mbar_wait_bounded(&bar_kv_full[0], 0, WAIT_TRIES);
+      if (ok) {
         tc_fence_after();
-        const uint32_t va = smem_u32(v_s + s * TILE_BYTES), pa = smem_u32(p_s + s * TILE_BYTES);
+        issue_s(0, 0);
+        if (n_b > 0) issue_s(1, 0);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t va = smem_u32(v_s + s * TILE_BYTES);
+        bool next_k_ready = false;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {        // O += P(j) V(j): 16 keys per step
-          const uint64_t ad = smem_desc(pa + (uint32_t)((ks >> 2) * PANEL_BYTES + (ks & 3) * 32), 16, 1024);
-          const uint64_t bd = smem_desc(va + (uint32_t)(ks * 2048), PANEL_BYTES, 1024);
-          umma(tmem_O, ad, bd, p.idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        umma_commit(&bar_pv[s]);
-        umma_commit(&bar_kv_free[s]);
-        if (j + 2 < n_tiles) {                  // refill this stage once its MMAs have drained
-          ok = mbar_wait_bounded(&bar_kv_free[s], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
+        for (int x = 0; x < 2; ++x) {
+          if (j >= (x == 0 ? n_a : n_b)) continue;
+          ok = mbar_wait_bounded(&bar_p[x], (uint32_t)(j & 1), WAIT_TRIES);
           if (!ok) break;
-          load_kv(j + 2);
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {      // O_x += P_x(j) V(j): 16 keys = 8 TMEM columns per step
+            const uint64_t bd = smem_desc(va + (uint32_t)(ks * 2048), PANEL_BYTES, 1024);
+            umma_ts(tmem + 256u + (uint32_t)x * 128u, tmem + (uint32_t)x * 128u + (uint32_t)ks * 8u, bd, p.idesc_pv,
+                    (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(&bar_pv[x]);
+          // S_x(j+1) overwrites the columns P_x(j) lives in; the tensor pipe runs in issue order
+          if (j + 1 < (x == 0 ? n_a : n_b)) {
+            if (!next_k_ready) {
+              ok = mbar_wait_bounded(&bar_kv_full[s ^ 1], (uint32_t)(((j + 1) >> 1) & 1), WAIT_TRIES);
+              if (!ok) break;
+              tc_fence_after();
+              next_k_ready = true;
+            }
+            issue_s(x, j + 1);
+          }
         }
+        if (!ok) break;
+        umma_commit(&bar_kv_free[s]);             // K(j), V(j) are free once everything issued so far has drained
       }
       if (!ok) atomicExch(p.status, CQ_ERR_TIMEOUT);
     }
     __syncwarp();
   } else {
-    // ===== softmax: thread = (query row, 64-column half); 8 warps =====
-    const int quarter = warp & 3, half = warp >> 2;
+    // ===== softmax: warps 0-3 tile A, 4-7 tile B; thread = one query row =====
+    const int x = warp >> 2, quarter = warp & 3;
+    const int n_x = x == 0 ? n_a : n_b;
     const int r_in = quarter * 32 + lane;               // row inside the tile = TMEM lane
-    const int row = q0 + r_in;
+    const int qx0 = q0 + x * BM;
+    const int row = qx0 + r_in;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    const uint32_t col0 = (uint32_t)half * 64u;
-    float m_ref = -INFINITY, l_run = 0.f;               // reference maximum (log2 units); sum over this thread's columns
-    // Once a bounded wait has run out, `ok` stays false and all later waits are skipped, but every
-    // thread still walks all tiles so that the named barrier below always sees its 256 arrivals.
-    bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int key0 = j * BN + (int)col0;
-      const bool need_mask = (j * BN + BN - 1 > q0) || (j * BN + BN > p.t_len);
-      const uint32_t tS = tmem + (uint32_t)(j & 1) * 128u + lane_off + col0;
-      if (ok) ok = mbar_wait_bounded(&bar_s[j & 1], (uint32_t)((j >> 1) & 1), WAIT_TRIES);
+    const uint32_t tS = tmem + (uint32_t)x * 128u + lane_off;
+    const uint32_t tO = tmem + 256u + (uint32_t)x * 128u + lane_off;
+    float m_ref = -INFINITY, l_run = 0.f;               // reference maximum (log2 units), row sum
+    bool ok = true;                                     // stays false after a timeout; later waits are skipped
+    for (int j = 0; j < n_x; ++j) {
+      const int key0 = j * BN;
+      const bool need_mask = (key0 + BN - 1 > qx0) || (key0 + BN > p.t_len);
+      if (ok) ok = mbar_wait_bounded(&bar_s[x], (uint32_t)(j & 1), WAIT_TRIES);
       tc_fence_after();
-      uint32_t sv[2][32];                               // this thread's 64 logits, read once
-      tmem_ld32_nowait(tS, sv[0]);
-      tmem_ld32_nowait(tS + 32, sv[1]);
+      uint32_t sv[4][32];                               // this row's 128 logits, read once
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) tmem_ld32_nowait(tS + cc * 32, sv[cc]);
       tmem_ld_wait();
-      float mx = -INFINITY;
+      if (need_mask) {                                  // diagonal and last key tiles only
+        const int lim = min(row, p.t_len - 1) - key0;   // columns above lim are masked
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc)
+        for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (need_mask) {
-            const int key = key0 + cc * 32 + i;
-            if (key > row || key >= p.t_len) sv[cc][i] = 0xff800000u;   // -inf
-          }
-          mx = fmaxf(mx, __uint_as_float(sv[cc][i]));
-        }
-      half_max_s[half][r_in] = mx;
-      asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
-      mx = fmaxf(mx, half_max_s[half ^ 1][r_in]);
+          for (int i = 0; i < 32; ++i)
+            if (cc * 32 + i > lim) sv[cc][i] = 0xff800000u;   // -inf
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[cc][i]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_true = fmaxf(m_ref, mx * p.scale_log2);
-      // both threads of a row see the same m_ref and m_true, hence take the same decision
       const bool grow = m_true - m_ref > RESCALE_LOG2;  // also true for the first tile (m_ref = -inf)
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // O holds PV(0..j-1); the product that last wrote it read P buffer (j-1)&1
-        if (ok) ok = mbar_wait_bounded(&bar_pv[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), WAIT_TRIES);
+        // O_x holds the products of tiles 0..j-1; the last of them must have completed
+        if (ok) ok = mbar_wait_bounded(&bar_pv[x], (uint32_t)((j - 1) & 1), WAIT_TRIES);
         tc_fence_after();
-        const float alpha = grow ? exp2f(m_ref - m_true) : 1.f;    // 0 when m_ref was -inf
+        const float alpha = grow ? exp2f(m_ref - m_true) : 1.f;
 #pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
+        for (int cc = 0; cc < 4; ++cc) {
           uint32_t r[32];
-          tmem_ld32(tmem_O + lane_off + col0 + cc * 32, r);
+          tmem_ld32(tO + cc * 32, r);
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(tmem_O + lane_off + col0 + cc * 32, r);
+          tmem_st32(tO + cc * 32, r);
         }
-        tmem_st_wait();
         l_run *= alpha;
       }
       if (grow) m_ref = m_true;
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      // the P buffer of this tile was last read by PV(j-2)
-      if (j >= 2 && ok) ok = mbar_wait_bounded(&bar_pv[j & 1], (uint32_t)(((j - 2) >> 1) & 1), WAIT_TRIES);
-      float rs = 0.f;
-      unsigned char* prow = p_s + (j & 1) * TILE_BYTES + half * PANEL_BYTES + r_in * 128;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t w[16];
+      for (int cc = 0; cc < 4; cc += 2) {
+        uint32_t w[32];                                 // 64 probabilities as 16-bit pairs = 32 TMEM columns
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
+        for (int i = 0; i < 64; i += 2) {
           // masked logits are -inf: ex2 gives 0
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[cc][i]), p.scale_log2, -m_use));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[cc][i + 1]), p.scale_log2, -m_use));
-          rs += p0 + p1;
-          w[i >> 1] = pack16(p0, p1, p.is_bf16);
+          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[cc + (i >> 5)][i & 31]), p.scale_log2, -m_use));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[cc + (i >> 5)][(i & 31) + 1]), p.scale_log2, -m_use));
+          rs4[(i >> 1) & 3] += p0 + p1;
+          w[i >> 1] = pack16<IS_BF16>(p0, p1);
         }
-#pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
-          const int chunk = (cc * 4 + qd) ^ (r_in & 7);
-          *reinterpret_cast<uint4*>(prow + chunk * 16) = make_uint4(w[4 * qd], w[4 * qd + 1], w[4 * qd + 2], w[4 * qd + 3]);
-        }
+        tmem_st32(tS + (cc >> 1) * 32, w);              // over the first 64 columns of S_x
       }
-      l_run += rs;
-      fence_proxy_async_smem();        // P (generic-proxy writes) must be visible to the MMA (async proxy)
+      l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bar_p[j & 1]);
+      mbar_arrive(&bar_p[x]);
     }
-    // the row sum is split over the two halves
-    half_max_s[half][r_in] = l_run;
-    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
-    const float l_tot = l_run + half_max_s[half ^ 1][r_in];
-    if (ok) ok = mbar_wait_bounded(&bar_pv[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), WAIT_TRIES);
-    if (!ok) {
-      atomicExch(p.status, CQ_ERR_TIMEOUT);
-    } else {
-      tc_fence_after();
-      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-      unsigned char* dst = reinterpret_cast<unsigned char*>(p.out) +
-                           2 * ((int64_t)b * p.o_sb + (int64_t)row * p.o_st + (int64_t)h * p.o_sh) + col0 * 2;
+    if (n_x > 0) {
+      if (ok) ok = mbar_wait_bounded(&bar_pv[x], (uint32_t)((n_x - 1) & 1), WAIT_TRIES);
+      if (!ok) {
+        atomicExch(p.status, CQ_ERR_TIMEOUT);
+      } else {
+        tc_fence_after();
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        unsigned char* dst = reinterpret_cast<unsigned char*>(p.out) +
+                             2 * ((int64_t)b * p.o_sb + (int64_t)row * p.o_st + (int64_t)h * p.o_sh);
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(tmem_O + lane_off + col0 + cc * 32, r);     // warp-collective: rows past the end load too
-        if (row < p.t_len) {
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t r[32];
+          tmem_ld32(tO + cc * 32, r);                   // warp-collective: rows past the end load too
+          if (row < p.t_len) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv, p.is_bf16);
-            w.y = pack16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv, p.is_bf16);
-            w.z = pack16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv, p.is_bf16);
-            w.w = pack16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv, p.is_bf16);
-            *reinterpret_cast<uint4*>(dst + (cc * 32 + i) * 2) = w;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 w;
+              w.x = pack16<IS_BF16>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              w.y = pack16<IS_BF16>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              w.z = pack16<IS_BF16>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              w.w = pack16<IS_BF16>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + (cc * 32 + i) * 2) = w;
+            }
           }
         }
       }
@@ -422,7 +444,8 @@ int prefill_tc_run(const void* q, const void* k, const void* v, void* out, int b
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CQ_ERR_LAUNCH;
   if (!configured[dev]) {
-    if (cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return CQ_ERR_LAUNCH;
     configured[dev] = true;
   }
@@ -434,8 +457,9 @@ int prefill_tc_run(const void* q, const void* k, const void* v, void* out, int b
   p.idesc_pv = make_idesc(is_bf16, 1);
   p.is_bf16 = is_bf16;
   p.status = status;
-  dim3 grid((unsigned)((t_len + BM - 1) / BM), (unsigned)hq, (unsigned)batch);
-  prefill_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+  dim3 grid((unsigned)((t_len + 2 * BM - 1) / (2 * BM)), (unsigned)hq, (unsigned)batch);
+  if (is_bf16) prefill_tc_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+  else prefill_tc_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
   return check_launch();
 }
 
