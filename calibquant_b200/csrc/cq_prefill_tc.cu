@@ -40,6 +40,7 @@ constexpr int TILE_BYTES = 2 * PANEL_BYTES;     // [128 rows][128 x 16-bit]
 constexpr int SMEM_BYTES = TILE_BYTES * 6 + 1024;   // Q x2, K x2, V x2 (+ alignment slack)
 constexpr int SOFTMAX_THREADS = 256, MMA_WARP = 8, TMA_WARP = 9, THREADS = SOFTMAX_THREADS + 64;
 constexpr uint32_t WAIT_TRIES = 1u << 22;
+constexpr long long WAIT_CYCLES = 1ll << 30;     // ~0.5 s: bound of the waits on the S / P hand-offs
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float RESCALE_LOG2 = 8.f;          // a row is rescaled when its maximum grew by more than 2^8
 
@@ -141,6 +142,28 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// sm_100 arithmetic that halves the instruction count of the softmax: 3-input maximum, and fp32
+// operations on register pairs
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// (x0, x1) = (a0, a1) * (b, b) + (c, c)
+__device__ __forceinline__ void fma_pair(float& x0, float& x1, float a0, float a1, float b, float c) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(x0), "=f"(x1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+// (s0, s1) += (a0, a1)
+__device__ __forceinline__ void add_pair(float& s0, float& s1, float a0, float a1) {
+  asm("{\n\t.reg .b64 ra, rs;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rs, {%0, %1};\n\t"
+      "add.rn.f32x2 rs, rs, ra;\n\tmov.b64 {%0, %1}, rs;\n\t}"
+      : "+f"(s0), "+f"(s1) : "f"(a0), "f"(a1));
+}
+
 template <bool IS_BF16>
 __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   if (IS_BF16) {
@@ -219,13 +242,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   } else if (warp == MMA_WARP) {
     // ================= MMA issuer (one lane) =================
     if (lane == 0) {
+      // descriptors of the operand tiles; a k-step only moves the start address (14-bit field of
+      // 16-byte units in the low word, which cannot carry: shared memory ends below 256 KB)
+      const uint64_t qd[2] = {smem_desc(smem_u32(q_s), 16, 1024), smem_desc(smem_u32(q_s + TILE_BYTES), 16, 1024)};
+      const uint64_t kd[2] = {smem_desc(smem_u32(k_s), 16, 1024), smem_desc(smem_u32(k_s + TILE_BYTES), 16, 1024)};
+      const uint64_t vd[2] = {smem_desc(smem_u32(v_s), PANEL_BYTES, 1024),
+                              smem_desc(smem_u32(v_s + TILE_BYTES), PANEL_BYTES, 1024)};
       auto issue_s = [&](int x, int j) {        // S_x(j) = Q_x K(j)^T; the K tile is known to be there
-        const uint32_t qa = smem_u32(q_s + x * TILE_BYTES), ka = smem_u32(k_s + (j & 1) * TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {        // 16 channels per step; panel = ks/4, 32 B per step
-          const uint32_t off = (uint32_t)((ks >> 2) * PANEL_BYTES + (ks & 3) * 32);
-          umma(tmem + (uint32_t)x * 128u, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024),
-               p.idesc_s, ks > 0);
+          const uint64_t off = (uint64_t)(((ks >> 2) * PANEL_BYTES + (ks & 3) * 32) >> 4);
+          umma(tmem + (uint32_t)x * 128u, qd[x] + off, kd[j & 1] + off, p.idesc_s, ks > 0);
         }
         umma_commit(&bar_s[x]);
       };
@@ -238,20 +265,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       for (int j = 0; j < n_max && ok; ++j) {
         const int s = j & 1;
-        const uint32_t va = smem_u32(v_s + s * TILE_BYTES);
         bool next_k_ready = false;
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (j >= (x == 0 ? n_a : n_b)) continue;
-          ok = mbar_wait_bounded(&bar_p[x], (uint32_t)(j & 1), WAIT_TRIES);
+          ok = mbar_wait_cycles(&bar_p[x], (uint32_t)(j & 1), WAIT_CYCLES);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {      // O_x += P_x(j) V(j): 16 keys = 8 TMEM columns per step
-            const uint64_t bd = smem_desc(va + (uint32_t)(ks * 2048), PANEL_BYTES, 1024);
-            umma_ts(tmem + 256u + (uint32_t)x * 128u, tmem + (uint32_t)x * 128u + (uint32_t)ks * 8u, bd, p.idesc_pv,
-                    (j > 0 || ks > 0) ? 1u : 0u);
-          }
+          for (int ks = 0; ks < 8; ++ks)        // O_x += P_x(j) V(j): 16 keys = 8 TMEM columns per step
+            umma_ts(tmem + 256u + (uint32_t)x * 128u, tmem + (uint32_t)x * 128u + (uint32_t)ks * 8u,
+                    vd[s] + (uint64_t)(ks * 2048 >> 4), p.idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
           umma_commit(&bar_pv[x]);
           // S_x(j+1) overwrites the columns P_x(j) lives in; the tensor pipe runs in issue order
           if (j + 1 < (x == 0 ? n_a : n_b)) {
@@ -285,7 +309,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int j = 0; j < n_x; ++j) {
       const int key0 = j * BN;
       const bool need_mask = (key0 + BN - 1 > qx0) || (key0 + BN > p.t_len);
-      if (ok) ok = mbar_wait_bounded(&bar_s[x], (uint32_t)(j & 1), WAIT_TRIES);
+      if (ok) ok = mbar_wait_cycles(&bar_s[x], (uint32_t)(j & 1), WAIT_CYCLES);
       tc_fence_after();
       uint32_t sv[4][32];                               // this row's 128 logits, read once
 #pragma unroll
@@ -303,7 +327,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[cc][i]));
+        for (int i = 0; i < 32; i += 2)
+          mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1]));
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_true = fmaxf(m_ref, mx * p.scale_log2);
       const bool grow = m_true - m_ref > RESCALE_LOG2;  // also true for the first tile (m_ref = -inf)
@@ -331,9 +356,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int i = 0; i < 64; i += 2) {
           // masked logits are -inf: ex2 gives 0
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[cc + (i >> 5)][i & 31]), p.scale_log2, -m_use));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[cc + (i >> 5)][(i & 31) + 1]), p.scale_log2, -m_use));
-          rs4[(i >> 1) & 3] += p0 + p1;
+          float x0, x1;
+          fma_pair(x0, x1, __uint_as_float(sv[cc + (i >> 5)][i & 31]), __uint_as_float(sv[cc + (i >> 5)][(i & 31) + 1]),
+                   p.scale_log2, -m_use);
+          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+          add_pair(rs4[i & 2], rs4[(i & 2) + 1], p0, p1);
           w[i >> 1] = pack16<IS_BF16>(p0, p1);
         }
         tmem_st32(tS + (cc >> 1) * 32, w);              // over the first 64 columns of S_x

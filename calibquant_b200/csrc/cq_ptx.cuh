@@ -46,6 +46,18 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// Bounded wait for the hand-offs on a kernel's critical path: polls back to back (try_wait itself
+// suspends the thread for a hardware-defined interval, so this is not a hot spin) and gives up after
+// `max_cycles` of the SM clock.
+__device__ __forceinline__ bool mbar_wait_cycles(uint64_t* bar, uint32_t parity, long long max_cycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > max_cycles) return false;
+  }
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
