@@ -183,9 +183,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   unsigned char* q_s = smem;                    // tiles A, B
   unsigned char* k_s = q_s + 2 * TILE_BYTES;    // 2 stages
   unsigned char* v_s = k_s + 2 * TILE_BYTES;    // 2 stages
-  // per query tile X: bar_s (S_X ready), bar_p (P_X stored, 128 arrivals), bar_pv (O_X += P_X V done);
-  // each completes once per key tile of X
-  __shared__ __align__(8) uint64_t bar_q, bar_kv_full[2], bar_kv_free[2], bar_s[2], bar_p[2], bar_pv[2];
+  // per query tile X: bar_s (S_X ready), bar_p[X][half] (P_X of keys 0-63 / 64-127 stored, 128 arrivals
+  // each), bar_pv (O_X += P_X V done); each completes once per key tile of X
+  __shared__ __align__(8) uint64_t bar_q, bar_kv_full[2], bar_kv_free[2], bar_s[2], bar_p[2][2], bar_pv[2];
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -205,7 +205,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(&bar_kv_full[s], 1);
       mbar_init(&bar_kv_free[s], 1);
       mbar_init(&bar_s[s], 1);
-      mbar_init(&bar_p[s], SOFTMAX_THREADS / 2);
+      mbar_init(&bar_p[s][0], SOFTMAX_THREADS / 2);
+      mbar_init(&bar_p[s][1], SOFTMAX_THREADS / 2);
       mbar_init(&bar_pv[s], 1);
     }
     mbar_fence_init();
@@ -269,13 +270,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (j >= (x == 0 ? n_a : n_b)) continue;
-          ok = mbar_wait_cycles(&bar_p[x], (uint32_t)(j & 1), WAIT_CYCLES);
-          if (!ok) break;
-          tc_fence_after();
+          // O_x += P_x(j) V(j), 16 keys = 8 TMEM columns per step; the first four steps start as soon as
+          // the probabilities of keys 0-63 are stored, while the softmax warps work on keys 64-127
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)        // O_x += P_x(j) V(j): 16 keys = 8 TMEM columns per step
-            umma_ts(tmem + 256u + (uint32_t)x * 128u, tmem + (uint32_t)x * 128u + (uint32_t)ks * 8u,
-                    vd[s] + (uint64_t)(ks * 2048 >> 4), p.idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          for (int hf = 0; hf < 2; ++hf) {
+            ok = mbar_wait_cycles(&bar_p[x][hf], (uint32_t)(j & 1), WAIT_CYCLES);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 4 * hf; ks < 4 * hf + 4; ++ks)
+              umma_ts(tmem + 256u + (uint32_t)x * 128u, tmem + (uint32_t)x * 128u + (uint32_t)ks * 8u,
+                      vd[s] + (uint64_t)(ks * 2048 >> 4), p.idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          if (!ok) break;
           umma_commit(&bar_pv[x]);
           // S_x(j+1) overwrites the columns P_x(j) lives in; the tensor pipe runs in issue order
           if (j + 1 < (x == 0 ? n_a : n_b)) {
@@ -364,11 +371,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           w[i >> 1] = pack16<IS_BF16>(p0, p1);
         }
         tmem_st32(tS + (cc >> 1) * 32, w);              // over the first 64 columns of S_x
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&bar_p[x][cc >> 1]);
       }
       l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&bar_p[x]);
     }
     if (n_x > 0) {
       if (ok) ok = mbar_wait_bounded(&bar_pv[x], (uint32_t)((n_x - 1) & 1), WAIT_TRIES);
