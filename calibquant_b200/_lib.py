@@ -22,6 +22,7 @@ CQ_ERR_TOO_LARGE = -6
 
 CQ_DTYPE_F16 = 0
 CQ_DTYPE_BF16 = 1
+CQ_DTYPE_F32 = 2
 
 _c = ctypes
 _vp, _i32, _i64, _sz = _c.c_void_p, _c.c_int32, _c.c_int64, _c.c_size_t
@@ -76,6 +77,10 @@ SIGNATURES = {
                                         _vp, _vp, _vp, _i64, _i64, _c.c_int, _c.c_int, _vp, _c.c_int, _vp]),
     "cq_add_rmsnorm": (_c.c_int, [_vp, _vp, _vp, _vp, _i64, _c.c_int, _c.c_float, _c.c_int, _vp]),
     "cq_swiglu": (_c.c_int, [_vp, _vp, _vp, _i64, _c.c_int, _vp]),
+    "cq_qjl_quant": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _i64, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                _c.c_int, _vp, _vp, _vp, _vp]),
+    "cq_qjl_gqa_score": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
+                                    _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _vp, _vp]),
     "cq_decode_attn_workspace_bytes": (_sz, [_c.POINTER(DecodeArgs)]),
     "cq_decode_attn": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _sz, _vp]),
 }

@@ -1,0 +1,265 @@
+// QJL sign-sketch key quantizer and its GQA score estimator (the reference's `qjl` baseline method).
+//
+// quantize: keys come in groups of G tokens; per group a set of outlier channels is given.  For every
+// token the sign bits of  S k_inlier  and  S k_outlier  (S = sketch_dim x 128 projection, k split by
+// the outlier mask) are packed LSB-first, 8 per byte, plus the norm of the outlier part.
+// score:    for a query q and a key sketched that way
+//     score = sqrt(pi/2)/s * |k_in| * sum_p sgn_p * (qS - q_out S)_p  +  sqrt(pi/2)/s_o * |k_out| * sum_{p<s_o} sgn'_p * (q_out S)_p
+// with q_out = q restricted to the group's outlier channels and |k_in| = sqrt(|k|^2 - |k_out|^2).
+//
+// Both kernels are CUDA-core kernels: one CTA per (group, chunk of 32 tokens); thread = (token, block
+// of 32 projections).  The sign sums run over "bit set" terms only: sum_p sgn_p x_p = 2 sum_{bit_p} x_p - sum_p x_p.
+#include "cq_common.cuh"
+
+namespace cq {
+namespace qjl {
+
+constexpr int WARPS = 8, THREADS = WARPS * 32;
+constexpr int MAX_SKETCH = 256;       // projections per token handled by one CTA (32 per warp)
+constexpr int D_CHUNK = 16;           // channels of the projection staged per step
+
+template <typename TP> __device__ __forceinline__ float proj_f(TP v);
+template <> __device__ __forceinline__ float proj_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float proj_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float proj_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// keys [groups][G][128], outlier_idx [groups][oc], proj [sketch][128] -> key_quant [groups][G][sketch/8],
+// key_outlier_quant [groups][G][o_sketch/8], outlier_norm [groups][G]
+template <typename T, typename TP>
+__global__ void __launch_bounds__(THREADS)
+quant_kernel(const T* __restrict__ keys, const uint8_t* __restrict__ outlier_idx, const TP* __restrict__ proj,
+             uint8_t* __restrict__ key_quant, uint8_t* __restrict__ key_outlier_quant, T* __restrict__ outlier_norm,
+             int G, int sketch, int o_sketch, int oc) {
+  __shared__ float key_s[kHeadDim][33];            // [channel][token], padded
+  __shared__ float proj_s[D_CHUNK][MAX_SKETCH];    // [channel in chunk][projection]
+  __shared__ uint8_t mask_s[kHeadDim];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+  const int64_t grp = blockIdx.x;
+  const int tok0 = blockIdx.y * 32;
+  const int n_tok = min(32, G - tok0);
+  if (tid < kHeadDim) mask_s[tid] = 0;
+  __syncthreads();
+  if (tid < oc) mask_s[outlier_idx[grp * oc + tid] & (kHeadDim - 1)] = 1;
+  const T* kbase = keys + (grp * G + tok0) * kHeadDim;
+  for (int i = tid; i < 32 * kHeadDim; i += THREADS) {
+    const int t = i >> 7, d = i & (kHeadDim - 1);
+    key_s[d][t] = t < n_tok ? Elem<T>::to_f(kbase[t * kHeadDim + d]) : 0.f;
+  }
+  float acc_in[32], acc_out[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) { acc_in[j] = 0.f; acc_out[j] = 0.f; }
+  const int p0 = warp * 32;                         // this warp's projections
+  for (int d0 = 0; d0 < kHeadDim; d0 += D_CHUNK) {
+    __syncthreads();                                // previous chunk consumed (first pass: key_s, mask_s written)
+    for (int i = tid; i < sketch * D_CHUNK; i += THREADS) {
+      const int p = i / D_CHUNK, dd = i % D_CHUNK;
+      proj_s[dd][p] = proj_f<TP>(proj[(int64_t)p * kHeadDim + d0 + dd]);
+    }
+    __syncthreads();
+    if (p0 < sketch) {
+#pragma unroll 4
+      for (int dd = 0; dd < D_CHUNK; ++dd) {
+        const float kv = key_s[d0 + dd][lane];
+        const float4* pr = reinterpret_cast<const float4*>(&proj_s[dd][p0]);
+        if (mask_s[d0 + dd]) {                      // uniform over the CTA
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = pr[j];
+            acc_out[4 * j] = fmaf(v.x, kv, acc_out[4 * j]); acc_out[4 * j + 1] = fmaf(v.y, kv, acc_out[4 * j + 1]);
+            acc_out[4 * j + 2] = fmaf(v.z, kv, acc_out[4 * j + 2]); acc_out[4 * j + 3] = fmaf(v.w, kv, acc_out[4 * j + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = pr[j];
+            acc_in[4 * j] = fmaf(v.x, kv, acc_in[4 * j]); acc_in[4 * j + 1] = fmaf(v.y, kv, acc_in[4 * j + 1]);
+            acc_in[4 * j + 2] = fmaf(v.z, kv, acc_in[4 * j + 2]); acc_in[4 * j + 3] = fmaf(v.w, kv, acc_in[4 * j + 3]);
+          }
+        }
+      }
+    }
+  }
+  if (lane < n_tok && p0 < sketch) {
+    uint32_t w_in = 0, w_out = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      w_in |= (acc_in[j] > 0.f ? 1u : 0u) << j;
+      w_out |= (acc_out[j] > 0.f ? 1u : 0u) << j;
+    }
+    const int64_t tok = grp * G + tok0 + lane;
+    *reinterpret_cast<uint32_t*>(key_quant + tok * (sketch / 8) + p0 / 8) = w_in;
+    if (p0 < o_sketch) *reinterpret_cast<uint32_t*>(key_outlier_quant + tok * (o_sketch / 8) + p0 / 8) = w_out;
+  }
+  if (warp == 0 && lane < n_tok) {
+    float ss = 0.f;
+    for (int d = 0; d < kHeadDim; ++d)
+      if (mask_s[d]) ss = fmaf(key_s[d][lane], key_s[d][lane], ss);
+    outlier_norm[grp * G + tok0 + lane] = Elem<T>::from_f(sqrtf(ss));
+  }
+}
+
+// One CTA per (batch x KV head, group, chunk of 32 tokens).  R = query heads per KV head held per thread.
+template <typename T, typename TP, int R>
+__global__ void __launch_bounds__(THREADS)
+score_kernel(const uint8_t* __restrict__ key_quant, const uint8_t* __restrict__ key_outlier_quant,
+             const T* __restrict__ key_norm, const T* __restrict__ key_outlier_norm,
+             const uint8_t* __restrict__ outlier_idx, const float* __restrict__ query_sketch,
+             const T* __restrict__ query, const TP* __restrict__ proj_score, float* __restrict__ scores,
+             int n_groups, int G, int n_rep, int sketch, int o_sketch, int oc) {
+  __shared__ __align__(16) float qin_s[MAX_SKETCH][R];     // (q S - q_out S)_p per head
+  __shared__ __align__(16) float qout_s[MAX_SKETCH][R];    // (q_out S)_p per head
+  __shared__ float q_s[R][kHeadDim];
+  __shared__ float part_s[WARPS][32][2 * R];
+  __shared__ float tot_s[2][R];
+  __shared__ uint8_t otl_s[kHeadDim];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+  const int64_t kbh = blockIdx.x;                           // batch * n_kv_heads + kv head
+  const int n = blockIdx.y, tok0 = blockIdx.z * 32;
+  const int n_tok = min(32, G - tok0);
+  const int64_t qrow0 = kbh * n_rep;                        // first query head of this KV head
+  const int64_t grp = kbh * n_groups + n;
+  for (int i = tid; i < R * kHeadDim; i += THREADS) {
+    const int r = i >> 7, d = i & (kHeadDim - 1);
+    q_s[r][d] = r < n_rep ? Elem<T>::to_f(query[(qrow0 + r) * kHeadDim + d]) : 0.f;
+  }
+  if (tid < oc) otl_s[tid] = outlier_idx[grp * oc + tid] & (kHeadDim - 1);
+  if (tid < 2 * R) tot_s[tid / R][tid % R] = 0.f;
+  __syncthreads();
+  // sketches of the query's outlier part and of the rest, per projection; their totals per head
+  for (int p = tid; p < sketch; p += THREADS) {
+    float o[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) o[r] = 0.f;
+    for (int i = 0; i < oc; ++i) {
+      const int d = otl_s[i];
+      const float pv = proj_f<TP>(proj_score[(int64_t)d * sketch + p]);
+#pragma unroll
+      for (int r = 0; r < R; ++r) o[r] = fmaf(q_s[r][d], pv, o[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float qs = r < n_rep ? query_sketch[(qrow0 + r) * sketch + p] : 0.f;
+      qin_s[p][r] = qs - o[r];
+      qout_s[p][r] = o[r];
+    }
+  }
+  __syncthreads();
+  if (tid < 2 * R) {                                        // totals: 2R threads, serial over p (sketch <= 256)
+    const int which = tid / R, r = tid % R;
+    float t = 0.f;
+    const int lim = which == 0 ? sketch : o_sketch;
+    for (int p = 0; p < lim; ++p) t += which == 0 ? qin_s[p][r] : qout_s[p][r];
+    tot_s[which][r] = t;
+  }
+  // set-bit sums of this warp's 32 projections for token `lane`
+  float s_in[R], s_out[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) { s_in[r] = 0.f; s_out[r] = 0.f; }
+  const int p0 = warp * 32;
+  if (lane < n_tok && p0 < sketch) {
+    const int64_t tok = grp * G + tok0 + lane;
+    const uint32_t w_in = *reinterpret_cast<const uint32_t*>(key_quant + tok * (sketch / 8) + p0 / 8);
+    const uint32_t w_out = p0 < o_sketch ? *reinterpret_cast<const uint32_t*>(key_outlier_quant + tok * (o_sketch / 8) + p0 / 8) : 0u;
+#pragma unroll 8
+    for (int k = 0; k < 32; ++k) {
+      const bool b_in = (w_in >> k) & 1u, b_out = (w_out >> k) & 1u;
+#pragma unroll
+      for (int r4 = 0; r4 < R; r4 += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(&qin_s[p0 + k][r4]);
+        const float4 b = *reinterpret_cast<const float4*>(&qout_s[p0 + k][r4]);
+        if (b_in) { s_in[r4] += a.x; s_in[r4 + 1] += a.y; s_in[r4 + 2] += a.z; s_in[r4 + 3] += a.w; }
+        if (b_out) { s_out[r4] += b.x; s_out[r4 + 1] += b.y; s_out[r4 + 2] += b.z; s_out[r4 + 3] += b.w; }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) { part_s[warp][lane][r] = s_in[r]; part_s[warp][lane][R + r] = s_out[r]; }
+  __syncthreads();
+  for (int i = tid; i < 32 * R; i += THREADS) {
+    const int t = i / R, r = i % R;
+    if (t >= n_tok || r >= n_rep) continue;
+    float si = 0.f, so = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) { si += part_s[w][t][r]; so += part_s[w][t][R + r]; }
+    const float inner = 2.f * si - tot_s[0][r], outer = 2.f * so - tot_s[1][r];
+    const int64_t tok = grp * G + tok0 + t;
+    const float norm_o = Elem<T>::to_f(key_outlier_norm[tok]);
+    const float norm_k = Elem<T>::to_f(key_norm[tok]);
+    // |k_in|: the two norms are rounded separately, so the difference can dip below zero
+    const float norm_in = sqrtf(fmaxf(norm_k * norm_k - norm_o * norm_o, 0.f));
+    const float scl = 1.2533141373155001f / (float)sketch, scl_o = 1.2533141373155001f / (float)o_sketch;
+    scores[(qrow0 + r) * ((int64_t)n_groups * G) + (int64_t)n * G + tok0 + t] =
+        scl * norm_in * inner + scl_o * norm_o * outer;
+  }
+}
+
+static bool sizes_ok(int G, int sketch, int o_sketch, int oc) {
+  return G > 0 && sketch > 0 && sketch <= MAX_SKETCH && sketch % 32 == 0 && o_sketch > 0 && o_sketch <= sketch &&
+         o_sketch % 32 == 0 && oc >= 0 && oc <= kHeadDim;
+}
+
+}  // namespace qjl
+}  // namespace cq
+
+using namespace cq;
+
+extern "C" int cq_qjl_quant(const void* keys, const uint8_t* outlier_indices, const void* proj, int proj_dtype,
+                            int64_t n_groups_total, int group_size, int head_dim, int sketch_dim,
+                            int outlier_sketch_dim, int outlier_count, int dtype, uint8_t* key_quant,
+                            uint8_t* key_outlier_quant, void* outlier_norms, void* stream) {
+  if (n_groups_total == 0) return CQ_OK;
+  if (!keys || !outlier_indices || !proj || !key_quant || !key_outlier_quant || !outlier_norms || n_groups_total < 0)
+    return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (proj_dtype != CQ_DTYPE_F32 && proj_dtype != dtype) return CQ_ERR_BAD_ARG;
+  if (head_dim != kHeadDim || !qjl::sizes_ok(group_size, sketch_dim, outlier_sketch_dim, outlier_count))
+    return CQ_ERR_UNSUPPORTED;
+  if (n_groups_total > 0x7fffffff) return CQ_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid((unsigned)n_groups_total, (unsigned)((group_size + 31) / 32));
+#define CQ_QJL_QUANT(T, TP)                                                                                   \
+  qjl::quant_kernel<T, TP><<<grid, qjl::THREADS, 0, st>>>(static_cast<const T*>(keys), outlier_indices,       \
+      static_cast<const TP*>(proj), key_quant, key_outlier_quant, static_cast<T*>(outlier_norms), group_size,  \
+      sketch_dim, outlier_sketch_dim, outlier_count)
+  if (dtype == CQ_DTYPE_F16) {
+    if (proj_dtype == CQ_DTYPE_F32) CQ_QJL_QUANT(__half, float); else CQ_QJL_QUANT(__half, __half);
+  } else {
+    if (proj_dtype == CQ_DTYPE_F32) CQ_QJL_QUANT(__nv_bfloat16, float); else CQ_QJL_QUANT(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef CQ_QJL_QUANT
+  return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
+}
+
+extern "C" int cq_qjl_gqa_score(const uint8_t* key_quant, const uint8_t* key_outlier_quant, const void* key_norm,
+                                const void* key_outlier_norm, const uint8_t* outlier_indices,
+                                const float* query_sketch, const void* query, const void* proj_score,
+                                int proj_dtype, int batch, int n_kv_heads, int n_rep, int n_groups, int group_size,
+                                int head_dim, int sketch_dim, int outlier_sketch_dim, int outlier_count, int dtype,
+                                float* scores, void* stream) {
+  if (batch == 0 || n_groups == 0) return CQ_OK;
+  if (!key_quant || !key_outlier_quant || !key_norm || !key_outlier_norm || !outlier_indices || !query_sketch ||
+      !query || !proj_score || !scores)
+    return CQ_ERR_BAD_ARG;
+  if (batch < 0 || n_kv_heads <= 0 || n_rep <= 0 || n_groups < 0) return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (proj_dtype != CQ_DTYPE_F32 && proj_dtype != dtype) return CQ_ERR_BAD_ARG;
+  if (head_dim != kHeadDim || n_rep > kMaxRep || !qjl::sizes_ok(group_size, sketch_dim, outlier_sketch_dim, outlier_count))
+    return CQ_ERR_UNSUPPORTED;
+  if (n_groups > 65535) return CQ_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid((unsigned)(batch * n_kv_heads), (unsigned)n_groups, (unsigned)((group_size + 31) / 32));
+#define CQ_QJL_SCORE(T, TP, R)                                                                                 \
+  qjl::score_kernel<T, TP, R><<<grid, qjl::THREADS, 0, st>>>(key_quant, key_outlier_quant,                      \
+      static_cast<const T*>(key_norm), static_cast<const T*>(key_outlier_norm), outlier_indices, query_sketch,  \
+      static_cast<const T*>(query), static_cast<const TP*>(proj_score), scores, n_groups, group_size, n_rep,    \
+      sketch_dim, outlier_sketch_dim, outlier_count)
+#define CQ_QJL_SCORE_R(T, TP) do { if (n_rep <= 4) CQ_QJL_SCORE(T, TP, 4); else CQ_QJL_SCORE(T, TP, 8); } while (0)
+  if (dtype == CQ_DTYPE_F16) {
+    if (proj_dtype == CQ_DTYPE_F32) CQ_QJL_SCORE_R(__half, float); else CQ_QJL_SCORE_R(__half, __half);
+  } else {
+    if (proj_dtype == CQ_DTYPE_F32) CQ_QJL_SCORE_R(__nv_bfloat16, float); else CQ_QJL_SCORE_R(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef CQ_QJL_SCORE_R
+#undef CQ_QJL_SCORE
+  return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
+}

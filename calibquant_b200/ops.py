@@ -306,3 +306,62 @@ def swiglu(gate, up, out=None):
         rc = lib().cq_swiglu(_ptr(gate), _ptr(up), _ptr(out), gate.numel(), _dtype_enum(gate), _stream())
     check(rc, "cq_swiglu")
     return out
+
+
+def _proj_dtype_enum(proj, data):
+    if proj.dtype == torch.float32:
+        return _lib.CQ_DTYPE_F32
+    if proj.dtype == data.dtype:
+        return _dtype_enum(data)
+    raise TypeError("Unsupported data types for QJL: the projection must be float32 or match the keys")
+
+
+def qjl_quant(key_states, outlier_indices, rand_prj, outlier_sketch_dim):
+    """QJL sign sketch of grouped keys.  key_states [B,H,n,G,128]; outlier_indices uint8 [B,H,n,oc];
+    rand_prj [sketch_dim,128].  Returns (key_quant uint8 [B,H,n,G,sketch_dim/8], key_outlier_quant uint8
+    [B,H,n,G,outlier_sketch_dim/8], outlier_norms [B,H,n,G] in the key dtype)."""
+    _need_cuda(key_states, outlier_indices, rand_prj)
+    B, H, n, G, D = key_states.shape
+    dt = _dtype_enum(key_states)
+    pdt = _proj_dtype_enum(rand_prj, key_states)
+    if outlier_indices.dtype != torch.uint8 or outlier_indices.shape[:3] != (B, H, n):
+        raise ValueError("outlier_indices must be uint8 [B,H,n,outlier_count]")
+    key_states, outlier_indices, rand_prj = key_states.contiguous(), outlier_indices.contiguous(), rand_prj.contiguous()
+    s = rand_prj.shape[0]
+    kq = torch.empty((B, H, n, G, s // 8), dtype=torch.uint8, device=key_states.device)
+    koq = torch.empty((B, H, n, G, outlier_sketch_dim // 8), dtype=torch.uint8, device=key_states.device)
+    norms = torch.empty((B, H, n, G), dtype=key_states.dtype, device=key_states.device)
+    with torch.cuda.device(key_states.device):
+        rc = lib().cq_qjl_quant(_ptr(key_states), _ptr(outlier_indices), _ptr(rand_prj), pdt, B * H * n, G, D, s,
+                                outlier_sketch_dim, outlier_indices.shape[3], dt, _ptr(kq), _ptr(koq), _ptr(norms),
+                                _stream())
+    check(rc, "cq_qjl_quant")
+    return kq, koq, norms
+
+
+def qjl_gqa_score(key_quant, key_outlier_quant, key_norm, key_outlier_norm, outlier_indices, query_sketch,
+                  query_states, rand_prj):
+    """Score estimate of one query per head against QJL-sketched keys (GQA: the keys stay at KV-head
+    count).  query_states [B,Hq,1,128], query_sketch fp32 [B,Hq,1,sketch_dim], rand_prj [128,sketch_dim].
+    Returns fp32 [B,Hq,n*G,1] as the reference's kernel does."""
+    _need_cuda(key_quant, key_outlier_quant, key_norm, key_outlier_norm, outlier_indices, query_sketch,
+               query_states, rand_prj)
+    B, Hkv, n, G, hb = key_quant.shape
+    Hq, D = query_states.shape[1], query_states.shape[-1]
+    dt = _dtype_enum(query_states)
+    pdt = _proj_dtype_enum(rand_prj, query_states)
+    if query_sketch.dtype != torch.float32:
+        query_sketch = query_sketch.float()
+    if key_norm.dtype != query_states.dtype or key_outlier_norm.dtype != query_states.dtype:
+        raise TypeError("key norms must have the query dtype")
+    if Hq % Hkv:
+        raise ValueError("query heads must be a multiple of key heads")
+    tensors = [t.contiguous() for t in (key_quant, key_outlier_quant, key_norm, key_outlier_norm, outlier_indices,
+                                        query_sketch, query_states, rand_prj)]
+    scores = torch.empty((B, Hq, n * G, 1), dtype=torch.float32, device=query_states.device)
+    with torch.cuda.device(query_states.device):
+        rc = lib().cq_qjl_gqa_score(*[_ptr(t) for t in tensors], pdt, B, Hkv, Hq // Hkv, n, G, D, hb * 8,
+                                    key_outlier_quant.shape[-1] * 8, outlier_indices.shape[3], dt, _ptr(scores),
+                                    _stream())
+    check(rc, "cq_qjl_gqa_score")
+    return scores

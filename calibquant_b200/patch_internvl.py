@@ -295,8 +295,8 @@ def forward_internlm2_qjl(self, hidden_states: torch.Tensor,
     """Patched forward with the reference's ``qjl`` structure (``patch_internvl.py:492-636``): the
     state travels in the 9-tuple ``(shape, kv_quant, K_sys, K_txt, V_code, V_scale, V_mn, V_sys,
     V_txt)``; values use ``triton_quantize_and_pack_along_last_dim`` + ``cuda_quantized_bmm_dynamic``
-    and keys a ``QJLKeyQuantizer``-shaped object (here backed by per-channel group quantization
-    instead of a JL sketch).  No logit calibration, as in the reference's qjl forward.
+    and keys a ``QJLKeyQuantizer`` (the JL sign sketch ``config.qjl``, or per-channel group
+    quantization when that is None).  No logit calibration, as in the reference's qjl forward.
     """
     self.sprompt_len = SPROMPT_LEN
     self.image_token_num = _image_token_num()
@@ -333,8 +333,12 @@ def forward_internlm2_qjl(self, hidden_states: torch.Tensor,
         sizes = [self.sprompt_len, self.image_token_num, q_len - self.sprompt_len - self.image_token_num]
         k_sys, k_vis, k_txt = k.split(sizes, dim=-2)
         v_sys, v_vis, v_txt = v.split(sizes, dim=-2)
-        kv_quant = QJLKeyQuantizer(getattr(cfg, "qjl", None), cfg.outlier_count_general, cfg.buffer_size,
-                                   cfg.group_size, cfg.k_bits)
+        sketch = getattr(cfg, "qjl", None)
+        if sketch is not None and sketch.proj_dir_score.device != k.device:   # the model moved after patching
+            for name in ("proj_dir", "proj_dir_score", "proj_dir_quant"):
+                setattr(sketch, name, getattr(sketch, name).to(k.device))
+            sketch.device = k.device
+        kv_quant = QJLKeyQuantizer(sketch, cfg.outlier_count_general, cfg.buffer_size, cfg.group_size, cfg.k_bits)
         kv_quant.build_sketch(k_vis)
         if v.shape[-2] <= cfg.buffer_size:
             raise NotImplementedError("value_states.shape[-2] <= self.config.buffer_size")
@@ -368,5 +372,13 @@ def patch_model(model, quant_method="calibquant", **kwargs):
         cfg.group_size = kwargs.get("group_size", 32)
         cfg.buffer_size = kwargs.get("buffer_size", 128)
         cfg.outlier_count_general = kwargs.get("outlier_count_general", 32)
-        cfg.qjl = None      # the JL sketch of the reference's baseline is not part of this path
+        # key_format="qjl" (default, as the reference): Johnson-Lindenstrauss sign sketch of the keys;
+        # key_format="group": the same forward with keys in the per-channel group format
+        if kwargs.get("key_format", "qjl") == "qjl":
+            from .qjl.qjl_utils import QJLSketch
+            dev = next(model.parameters()).device
+            generator = torch.Generator(device=dev).manual_seed(kwargs.get("seed", 1234))
+            cfg.qjl = QJLSketch(dim=(128, cfg.k_bits * 128), dim_outlier=256, device=dev, rot=True, rng=generator)
+        else:
+            cfg.qjl = None
     return model

@@ -38,6 +38,7 @@ extern "C" {
 
 #define CQ_DTYPE_F16 0
 #define CQ_DTYPE_BF16 1
+#define CQ_DTYPE_F32 2             /* accepted only where an argument says so (QJL projections) */
 
 /* Library version (major*10000 + minor*100 + patch). */
 int cq_version(void);
@@ -251,6 +252,39 @@ int cq_rope_split_append(const void* qkv, int64_t qkv_stride_b, const void* cos_
 int cq_add_rmsnorm(const void* delta, void* residual, const void* weight, void* out, int64_t rows, int hidden,
                    float eps, int dtype, void* stream);
 int cq_swiglu(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream);
+
+/*
+ * ---- QJL sign-sketch key quantizer (the reference's `qjl` baseline method) ---------------------------
+ *
+ * cq_qjl_quant replaces qjl/qjl_kernel.py:8-28 `qjl_quant` -> `quantize_with_outliers_kernel`
+ * (qjl/csrc/qjl_quant_kernel.cu:53-168).
+ *   keys            : [n_groups_total][group_size][128] in `dtype` (the reference's [B,H,n,G,D])
+ *   outlier_indices : uint8 [n_groups_total][outlier_count], channels treated as outliers in that group
+ *   proj            : [sketch_dim][128] (QJLSketch.proj_dir_quant), `proj_dtype` = CQ_DTYPE_F32 or `dtype`
+ *   key_quant         uint8 [n_groups_total][group_size][sketch_dim/8]: bit p%8 of byte p/8 is
+ *                     [ sum_{d not outlier} proj[p][d]*k[d] > 0 ], fp32 sums in channel order
+ *   key_outlier_quant uint8 [...][outlier_sketch_dim/8]: same over the outlier channels, p < outlier_sketch_dim
+ *   outlier_norms     [n_groups_total][group_size] in `dtype`: 2-norm of the outlier channels
+ *   sketch_dim <= 256, sketch_dim and outlier_sketch_dim multiples of 32.
+ *
+ * cq_qjl_gqa_score replaces qjl/qjl_kernel.py:52-72 `qjl_gqa_score` -> `calc_gqa_score_kernel`
+ * (qjl/csrc/qjl_gqa_score_kernel.cu:40-180), for any n_rep <= 8 (the reference's shared arrays hold 4):
+ *   score[b,h,t] = sqrt(pi/2)/sketch_dim * |k_in| * sum_p sgn_p (qS - q_out S)_p
+ *                + sqrt(pi/2)/outlier_sketch_dim * |k_out| * sum_{p<o} sgn'_p (q_out S)_p
+ *   key_norm / key_outlier_norm [B,Hkv,n,G] in `dtype`; |k_in| = sqrt(max(|k|^2 - |k_out|^2, 0)) (the
+ *   reference takes the square root of the unclamped difference); query_sketch fp32 [B,Hq,sketch_dim] =
+ *   q @ proj_score; query [B,Hq,128]; proj_score [128][sketch_dim] (QJLSketch.proj_dir_score);
+ *   scores fp32 [B,Hq,n*G].
+ */
+int cq_qjl_quant(const void* keys, const uint8_t* outlier_indices, const void* proj, int proj_dtype,
+                 int64_t n_groups_total, int group_size, int head_dim, int sketch_dim, int outlier_sketch_dim,
+                 int outlier_count, int dtype, uint8_t* key_quant, uint8_t* key_outlier_quant,
+                 void* outlier_norms, void* stream);
+int cq_qjl_gqa_score(const uint8_t* key_quant, const uint8_t* key_outlier_quant, const void* key_norm,
+                     const void* key_outlier_norm, const uint8_t* outlier_indices, const float* query_sketch,
+                     const void* query, const void* proj_score, int proj_dtype, int batch, int n_kv_heads,
+                     int n_rep, int n_groups, int group_size, int head_dim, int sketch_dim,
+                     int outlier_sketch_dim, int outlier_count, int dtype, float* scores, void* stream);
 
 /*
  * Sticky device status of the prefill kernel (no reference counterpart: the reference checks no

@@ -65,7 +65,7 @@ def test_qjl_forward_structure_and_scores():
     agree with the oracle of the same arithmetic (2-bit keys and values, group 32)."""
     from calibquant_b200 import patch_internvl as pi
     shell = _layer(8, 2, seed=5)
-    pi.patch_model(shell, "qjl", k_bits=2, v_bits=2, buffer_size=128)
+    pi.patch_model(shell, "qjl", k_bits=2, v_bits=2, buffer_size=128, key_format="group")
     attn_cpu = shell.language_model.model.layers[0].attention
     oracle = AttentionOracle(attn_cpu.wqkv.weight.detach().clone(), attn_cpu.wo.weight.detach().clone(),
                              8, 2, bits=2, calibrate=False)
