@@ -26,7 +26,7 @@
 //   K3 combine  : merge the chunk partials (online-softmax rescale), round to the output dtype
 //
 // Eligibility (otherwise cq_decode_attn uses the general kernels): t_vis % 256 == 0,
-// no additive mask, 16-byte aligned operands.
+// 16-byte aligned operands.
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -70,6 +70,9 @@ struct Dims {
   int n_mm;            // min/max entries per row: n_ktiles * K1_WARPS
   int64_t fp_stride_b, fp_stride_h;
   const int32_t* t_fp_dev;   // optional: live number of fp tokens on the device (t_fp is then the capacity)
+  const void* mask;          // optional additive mask [batch][t_sys | t_vis | text] in the data dtype
+  int64_t mask_stride_b;
+  int t_sys;                 // fp tokens that precede the visual span in the mask's key order
 };
 
 // Number of full-precision tokens this launch works on: the by-value extent, or, when the caller keeps
@@ -104,6 +107,7 @@ template <> struct D16<__half> {
   static __device__ __forceinline__ uint32_t to_h2(uint32_t v) { return v; }
   static __device__ __forceinline__ T2 round2(float a, float b) { return __floats2half2_rn(a, b); }
   static __device__ __forceinline__ T2 bcast(float a) { return __float2half2_rn(a); }
+  static __device__ __forceinline__ T2 pair2(__half a, __half b) { return __halves2half2(a, b); }
   static __device__ __forceinline__ float2 to_f2(T2 v) { return __half22float2(v); }
   static __device__ __forceinline__ float big() { return 65504.f; }
   // rnd(x * c): fp16(c) is within 2^-12 of c, a packed multiply is accurate enough
@@ -117,6 +121,7 @@ template <> struct D16<__nv_bfloat16> {
   }
   static __device__ __forceinline__ T2 round2(float a, float b) { return __floats2bfloat162_rn(a, b); }
   static __device__ __forceinline__ T2 bcast(float a) { return __float2bfloat162_rn(a); }
+  static __device__ __forceinline__ T2 pair2(__nv_bfloat16 a, __nv_bfloat16 b) { return __halves2bfloat162(a, b); }
   static __device__ __forceinline__ float2 to_f2(T2 v) { return __bfloat1622float2(v); }
   static __device__ __forceinline__ float big() { return 3.0e38f; }
   // bf16(c) would be off by up to 2^-9 (a systematic error on every logit): multiply in fp32
@@ -516,6 +521,10 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
     if (k > 0 && ++chunk == dm.n_chunks) { chunk = 0; ++pair; }
     const int64_t row0 = (int64_t)pair * dm.n_rep;        // = b * hq + hk * n_rep
     const int tok_base = chunk * CHUNK_TOK;
+    // additive mask of this batch row, at the chunk's first visual key (added after calibration, rounded
+    // to the data dtype as the tensor addition of the reference is)
+    const T* mvis = dm.mask ? static_cast<const T*>(dm.mask) + (int64_t)(pair / dm.hkv) * dm.mask_stride_b +
+                              dm.t_sys + tok_base : nullptr;
     const int n_tok = min(CHUNK_TOK, dm.t_vis - tok_base);
 
     // ---- probabilities of the chunk: warp w serves heads w, w+4 --------------------------------
@@ -564,13 +573,15 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
             v = __hfma2(v, cal.rdenom, __hmul2(v, cal.rdenom_lo));   // ~ rnd(v / denom)
             v = __hadd2(__hmul2(v, cal.range), cal.mn);
           }
+          if (mvis && t < n_tok) v = __hadd2(v, D16<T>::pair2(mvis[t + 2 * e], mvis[t + 2 * e + 1]));
           x[j][e] = v;
           mx2 = __hmax2(mx2, v);
         }
       }
       const float2 fmx2 = D16<T>::to_f2(mx2);
-      const float m = warp_max(fmaxf(fmx2.x, fmx2.y));
-      if (lane == 0) m_s[h] = m;
+      const float m_true = warp_max(fmaxf(fmx2.x, fmx2.y));
+      if (lane == 0) m_s[h] = m_true;
+      const float m = m_true == -INFINITY ? 0.f : m_true;     // a fully masked chunk: all probabilities 0
 #pragma unroll
       for (int j = 0; j < CHUNK_TOK / 256; ++j) {
         const int t = (j * 32 + lane) * 8;
@@ -744,14 +755,20 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
     __syncthreads();
     for (int h = warp; h < dm.n_rep; h += 4) {
       const T* srow = scores + (row0 + h) * dm.pitch + dm.t_vis + t0;
-      float xv[4], m = -INFINITY;
+      const T* mrow = dm.mask ? static_cast<const T*>(dm.mask) + (int64_t)b * dm.mask_stride_b : nullptr;
+      float xv[4], m_true = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int t = j * 32 + lane;
         xv[j] = t < nt ? Elem<T>::to_f(srow[t]) : -INFINITY;
-        m = fmaxf(m, xv[j]);
+        if (mrow && t < nt) {      // fp token f sits before (system) or after (text) the visual span
+          const int f = t0 + t;
+          xv[j] = rnd<T>(xv[j] + Elem<T>::to_f(mrow[f < dm.t_sys ? f : dm.t_vis + f]));
+        }
+        m_true = fmaxf(m_true, xv[j]);
       }
-      m = warp_max(m);
+      m_true = warp_max(m_true);
+      const float m = m_true == -INFINITY ? 0.f : m_true;
       float l = 0.f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -761,7 +778,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         l += p;
       }
       l = warp_sum(l);
-      if (lane == 0) ml[(row0 + h) * dm.n_slots + dm.n_chunks + fc] = make_float2(m, l);
+      if (lane == 0) ml[(row0 + h) * dm.n_slots + dm.n_chunks + fc] = make_float2(m_true, l);
     }
     __syncthreads();
     // warp w takes tokens w, w+4, ...; a lane owns 4 channels; 8 token rows are in flight per batch
@@ -899,6 +916,7 @@ static Dims make_dims(const cq_decode_args* a) {
   d.n_mm = d.n_ktiles * K1_WARPS;
   d.fp_stride_b = a->fp_stride_b; d.fp_stride_h = a->fp_stride_h;
   d.t_fp_dev = a->t_fp_dev;
+  d.mask = a->mask; d.mask_stride_b = a->mask_stride_b; d.t_sys = a->t_sys;
   return d;
 }
 
@@ -1000,7 +1018,6 @@ bool mma_path_eligible(const cq_decode_args* a) {
   // CQ_DECODE_GENERAL=1 forces the general kernels (A/B comparison of the two paths).
   static const bool disabled = []() { const char* e = getenv("CQ_DECODE_GENERAL"); return e && e[0] == '1'; }();
   if (disabled) return false;
-  if (a->mask != nullptr) return false;
   if (a->t_vis <= 0 || a->t_vis % 256 != 0) return false;
   if (a->bits != 1 && a->bits != 2 && a->bits != 4) return false;
   const void* ptrs[] = {a->q, a->k_code, a->k_scale, a->k_mn, a->v_code, a->v_scale, a->v_mn};

@@ -6,7 +6,7 @@
 
 namespace cq {
 
-// True when the fast path implements this request (fp16, t_vis % 256 == 0, no mask, aligned).
+// True when the fast path implements this request (t_vis % 256 == 0, 16-byte aligned operands).
 bool mma_path_eligible(const cq_decode_args* args);
 size_t mma_path_workspace_bytes(const cq_decode_args* args);
 // The first 4 bytes of `workspace` are a sticky device status word (CQ_ERR_TIMEOUT when a bounded

@@ -3,6 +3,8 @@
 Tolerance: attention outputs rel-L2 <= 1e-2 in fp16/bf16 (the bar the path is specified
 with); the quantized product alone is held to 2e-3."""
 
+import math
+
 import pytest
 import torch
 
@@ -95,6 +97,37 @@ def test_tensor_core_path_shapes(ops, bits, t_vis, t_txt, n_rep):
     out, ref = _run_case(ops, 2, 2 * n_rep, 2, t_vis, t_txt, bits, torch.float16, seed=40 + bits + t_vis)
     assert rel_l2(out, ref) <= TOL_ATTN, rel_l2(out, ref)
     assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [1, 4])
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, TOL_ATTN), (torch.bfloat16, 4e-2)])
+@pytest.mark.parametrize("t_vis,t_txt", [(256, 9), (1280, 90)])
+def test_tensor_core_path_with_mask(ops, bits, dtype, tol, t_vis, t_txt):
+    """Additive mask (left padding on one row, one masked system key on another) on shapes the fast
+    path takes: the mask is added after calibration, in the data dtype, to visual and fp keys alike."""
+    out, ref = _run_case(ops, 2, 8, 2, t_vis, t_txt, bits, dtype, seed=90 + bits + t_vis, with_mask=True)
+    assert rel_l2(out, ref) <= tol, rel_l2(out, ref)
+    assert ops.device_status() == 0
+
+
+def test_mask_hiding_the_whole_visual_span(ops):
+    """Every visual key masked with -inf: the visual chunks contribute nothing and the output equals
+    attention over the fp keys alone."""
+    B, Hq, Hkv, t_vis, t_fp = 1, 8, 2, 512, 50
+    g = torch.Generator().manual_seed(17)
+    k = torch.randn(B, Hkv, t_vis, 128, generator=g).half().cuda()
+    v = torch.randn(B, Hkv, t_vis, 128, generator=g).half().cuda()
+    kf = torch.randn(B, Hkv, t_fp, 128, generator=g).half().cuda()
+    vf = torch.randn(B, Hkv, t_fp, 128, generator=g).half().cuda()
+    q = torch.randn(B, Hq, 1, 128, generator=g).half().cuda()
+    kp, vp = ops.pack_k_per_channel(k, 32, 1), ops.pack_last_dim(v, 32, 1)
+    mask = torch.zeros(B, 1, 1, t_vis + t_fp, dtype=torch.float16, device="cuda")
+    mask[..., 41:41 + t_vis] = float("-inf")
+    out = ops.decode_attention(q, kp, vp, kf, vf, 41, 1, mask=mask)
+    s = torch.matmul(q.float(), kf.float().repeat_interleave(4, 1).transpose(2, 3)) / math.sqrt(128)
+    ref = torch.matmul(torch.softmax(s, -1), vf.float().repeat_interleave(4, 1))
+    assert torch.isfinite(out.float()).all()
+    assert rel_l2(out, ref) <= 5e-3
 
 
 @pytest.mark.parametrize("bits", [1, 2, 4])
