@@ -18,11 +18,13 @@
 //     and the minima fold into one extra small MMA per tile (sum_d q*kmn, sum_t p*vmn), whose spare
 //     column also yields sum_t p (the softmax denominator).
 //
-// Three launches per decode step on the caller's stream (all persistent, grid = resident CTAs):
+// Three launches per decode step (four with full-precision tokens) on the caller's stream; the
+// streaming ones are persistent (grid = resident CTAs):
 //   K1 scores   : logits (fp16-rounded exactly where the reference rounds) -> workspace, plus
 //                 per-tile min/max of the visual logits for the calibration
-//   K2 attn.V   : per 1024-token chunk: calibrate, exp relative to the chunk max, accumulate,
+//   K2 attn.V   : per chunk of visual tokens: calibrate, exp relative to the chunk max, accumulate,
 //                 write (max, sum, acc[128]) partials
+//   K2 fp       : (only with full-precision tokens) the same partials for chunks of 128 fp tokens
 //   K3 combine  : merge the chunk partials (online-softmax rescale), round to the output dtype
 //
 // Eligibility (otherwise cq_decode_attn uses the general kernels): t_vis % 256 == 0,
@@ -409,6 +411,105 @@ struct CalibH {   // per head, as 16-bit pairs for packed arithmetic in the data
   typename D16<T>::T2 mn, rdenom, rdenom_lo, range;
 };
 
+// Full-precision tokens of attn.V, chunks of 128, as a launch of its own next to k2_attn_v:
+// out[h][d] = sum_t p[h][t] V[t][d] on the warp MMA in the data dtype.  A = probabilities (rows = heads,
+// from shared memory), B = V rows staged in shared memory and read through ldmatrix.trans; warp w owns
+// channels 32w .. 32w+31.  Writes the (max, sum, acc[128]) partials of the fp slots that k3 merges.
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+k2_fp_tokens(Dims dm, const T* __restrict__ scores, const T* __restrict__ v_fp,
+             float* __restrict__ partial, float2* __restrict__ ml) {
+  constexpr int PF_PITCH = 128 + 8;         // probability row pitch (elements): rows land on different banks
+  constexpr int VROW = kHeadDim * 2 + 16;   // staged V row pitch in bytes, for conflict-free ldmatrix
+  constexpr int FP_SUB = 128;               // tokens staged at a time
+  __shared__ __align__(16) unsigned char smem[FP_SUB * VROW];
+  __shared__ __align__(16) T pf_s[kMaxRep * PF_PITCH];    // probabilities, exact in the data dtype
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int n_pairs = dm.batch * dm.hkv;
+  const int t_fp = live_t_fp(dm);
+  const int n_fp_chunks = (t_fp + 127) / 128;
+  for (int it = blockIdx.x; it < n_pairs * n_fp_chunks; it += gridDim.x) {
+    const int pair = it / n_fp_chunks, fc = it % n_fp_chunks;
+    const int b = pair / dm.hkv, hk = pair % dm.hkv;
+    const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
+    const int t0 = fc * 128, nt = min(128, t_fp - t0);
+    __syncthreads();
+    for (int h = warp; h < dm.n_rep; h += 4) {
+      const T* srow = scores + (row0 + h) * dm.pitch + dm.t_vis + t0;
+      const T* mrow = dm.mask ? static_cast<const T*>(dm.mask) + (int64_t)b * dm.mask_stride_b : nullptr;
+      float xv[4], m_true = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = j * 32 + lane;
+        xv[j] = t < nt ? Elem<T>::to_f(srow[t]) : -INFINITY;
+        if (mrow && t < nt) {      // fp token f sits before (system) or after (text) the visual span
+          const int f = t0 + t;
+          xv[j] = rnd<T>(xv[j] + Elem<T>::to_f(mrow[f < dm.t_sys ? f : dm.t_vis + f]));
+        }
+        m_true = fmaxf(m_true, xv[j]);
+      }
+      m_true = warp_max(m_true);
+      const float m = m_true == -INFINITY ? 0.f : m_true;
+      float l = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = j * 32 + lane;
+        const float p = t < nt ? rnd<T>(exp2f((xv[j] - m) * LOG2E)) : 0.f;
+        pf_s[h * PF_PITCH + t] = Elem<T>::from_f(p);
+        l += p;
+      }
+      l = warp_sum(l);
+      if (lane == 0) ml[(row0 + h) * dm.n_slots + dm.n_chunks + fc] = make_float2(m_true, l);
+    }
+    __syncthreads();
+    float accf[4][4];                        // [n-tile of 8 channels][C fragment]
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) accf[j][e] = 0.f;
+    const T* vf = v_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h + (int64_t)t0 * kHeadDim;
+    const uint32_t vs_base = smem_u32(smem);
+    for (int ts = 0; ts < nt; ts += FP_SUB) {
+      if (ts > 0) __syncthreads();          // the previous sub-block has been multiplied
+      // stage FP_SUB rows (zeros past the last token: their probabilities are 0, but 0 * junk is not)
+      for (int i = tid; i < FP_SUB * 16; i += THREADS) {
+        const int t = i >> 4, cidx = i & 15;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (ts + t < nt) v = __ldg(reinterpret_cast<const uint4*>(vf + (int64_t)(ts + t) * kHeadDim) + cidx);
+        *reinterpret_cast<uint4*>(smem + t * VROW + cidx * 16) = v;
+      }
+      __syncthreads();
+#pragma unroll 2
+      for (int ks = 0; ks < FP_SUB / 16; ++ks) {
+        if (ts + ks * 16 >= nt) break;
+        const T* prow = pf_s + (g < dm.n_rep ? g : 0) * PF_PITCH + ts + ks * 16 + 2 * c;
+        uint32_t a0 = *reinterpret_cast<const uint32_t*>(prow), a2 = *reinterpret_cast<const uint32_t*>(prow + 8);
+        if (g >= dm.n_rep) { a0 = 0u; a2 = 0u; }
+        // matrix (lane >> 3): tokens +0/+8 x channels +0/+8 of this warp's 16-channel half
+        const uint32_t row_addr = vs_base + (uint32_t)(ks * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * VROW +
+                                  (uint32_t)(warp * 32 + 8 * (lane >> 4)) * 2u;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t b00, b01, b10, b11;
+          ldmatrix_x4_trans(row_addr + half * 32, b00, b01, b10, b11);
+          if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+            mma_bf16(accf[2 * half], a0, 0u, a2, 0u, b00, b01);
+            mma_bf16(accf[2 * half + 1], a0, 0u, a2, 0u, b10, b11);
+          } else {
+            mma_f16(accf[2 * half], a0, 0u, a2, 0u, b00, b01);
+            mma_f16(accf[2 * half + 1], a0, 0u, a2, 0u, b10, b11);
+          }
+        }
+      }
+    }
+    if (g < dm.n_rep) {
+      float* dst = partial + ((row0 + g) * dm.n_slots + dm.n_chunks + fc) * kHeadDim + warp * 32 + 2 * c;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) *reinterpret_cast<float2*>(dst + 8 * j) = make_float2(accf[j][0], accf[j][1]);
+    }
+  }
+}
+
 template <typename T, int BITS, int CHUNK_TOK, int VT_TOK>
 __global__ void __launch_bounds__(THREADS, CHUNK_TOK == CT_SMALL ? 4 : 3)
 k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile_mm,
@@ -743,90 +844,6 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
   }
   if (failed) return;
 
-  // ---- full-precision tokens: chunks of 128 ------------------------------------------------------
-  float* pf_s = red_s;                      // [kMaxRep][128] probabilities
-  const int t_fp = live_t_fp(dm);
-  const int n_fp_chunks = (t_fp + 127) / 128;
-  for (int it = blockIdx.x; it < n_pairs * n_fp_chunks; it += gridDim.x) {
-    const int pair = it / n_fp_chunks, fc = it % n_fp_chunks;
-    const int b = pair / dm.hkv, hk = pair % dm.hkv;
-    const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
-    const int t0 = fc * 128, nt = min(128, t_fp - t0);
-    __syncthreads();
-    for (int h = warp; h < dm.n_rep; h += 4) {
-      const T* srow = scores + (row0 + h) * dm.pitch + dm.t_vis + t0;
-      const T* mrow = dm.mask ? static_cast<const T*>(dm.mask) + (int64_t)b * dm.mask_stride_b : nullptr;
-      float xv[4], m_true = -INFINITY;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int t = j * 32 + lane;
-        xv[j] = t < nt ? Elem<T>::to_f(srow[t]) : -INFINITY;
-        if (mrow && t < nt) {      // fp token f sits before (system) or after (text) the visual span
-          const int f = t0 + t;
-          xv[j] = rnd<T>(xv[j] + Elem<T>::to_f(mrow[f < dm.t_sys ? f : dm.t_vis + f]));
-        }
-        m_true = fmaxf(m_true, xv[j]);
-      }
-      m_true = warp_max(m_true);
-      const float m = m_true == -INFINITY ? 0.f : m_true;
-      float l = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int t = j * 32 + lane;
-        const float p = t < nt ? rnd<T>(exp2f((xv[j] - m) * LOG2E)) : 0.f;
-        pf_s[h * 128 + t] = p;
-        l += p;
-      }
-      l = warp_sum(l);
-      if (lane == 0) ml[(row0 + h) * dm.n_slots + dm.n_chunks + fc] = make_float2(m_true, l);
-    }
-    __syncthreads();
-    // warp w takes tokens w, w+4, ...; a lane owns 4 channels; 8 token rows are in flight per batch
-    float accf[kMaxRep][4];
-#pragma unroll
-    for (int h = 0; h < kMaxRep; ++h)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) accf[h][e] = 0.f;
-    const T* vf = v_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h +
-                       (int64_t)t0 * kHeadDim + lane * 4;
-    for (int tb = warp; tb < nt; tb += 32) {
-      uint2 raw[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int t = tb + 4 * u;
-        raw[u] = t < nt ? __ldg(reinterpret_cast<const uint2*>(vf + (int64_t)t * kHeadDim)) : make_uint2(0u, 0u);
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int t = tb + 4 * u;
-        if (t < nt) {
-          const float2 v01 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw[u].x));
-          const float2 v23 = D16<T>::to_f2(*reinterpret_cast<const T2*>(&raw[u].y));
-#pragma unroll
-          for (int h = 0; h < kMaxRep; ++h)
-            if (h < dm.n_rep) {
-              const float p = pf_s[h * 128 + t];
-              accf[h][0] = fmaf(p, v01.x, accf[h][0]); accf[h][1] = fmaf(p, v01.y, accf[h][1]);
-              accf[h][2] = fmaf(p, v23.x, accf[h][2]); accf[h][3] = fmaf(p, v23.y, accf[h][3]);
-            }
-        }
-      }
-    }
-    // the stage buffers are idle by now (every tile issued has been consumed): [4][kMaxRep][128] floats
-    float* xs = reinterpret_cast<float*>(smem);
-#pragma unroll
-    for (int h = 0; h < kMaxRep; ++h)
-      if (h < dm.n_rep)
-        *reinterpret_cast<float4*>(xs + (warp * kMaxRep + h) * kHeadDim + lane * 4) =
-            make_float4(accf[h][0], accf[h][1], accf[h][2], accf[h][3]);
-    __syncthreads();
-    for (int h = 0; h < dm.n_rep; ++h) {
-      float o = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) o += xs[(w * kMaxRep + h) * kHeadDim + tid];
-      partial[((row0 + h) * dm.n_slots + dm.n_chunks + fc) * kHeadDim + tid] = o;
-    }
-  }
 }
 
 // =================================================================================================
@@ -991,13 +1008,19 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
     if (rc != CQ_OK) return rc;
   }
   if (stages & 2) {
-    const int items2 = n_pairs * (d.n_chunks + d.n_fp_chunks);
+    const int items2 = n_pairs * d.n_chunks;
     const int grid2 = max(1, min(items2, sm_count() * occ2));
     k2<<<grid2, THREADS, smem2, st>>>(d, scores, mm, a->v_code, static_cast<const T*>(a->v_scale),
                                       static_cast<const T*>(a->v_mn), static_cast<const T*>(a->v_fp),
                                       partial, ml, status);
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
+    if (d.n_fp_chunks > 0) {
+      k2_fp_tokens<T><<<n_pairs * d.n_fp_chunks, THREADS, 0, st>>>(d, scores, static_cast<const T*>(a->v_fp),
+                                                                 partial, ml);
+      rc = check_launch();
+      if (rc != CQ_OK) return rc;
+    }
   }
   if (stages & 4) {
     k3_combine<T><<<d.batch * d.hq, kHeadDim * K3_LANES, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));

@@ -37,7 +37,27 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
 
 
+class _OnDevice:
+    """Make ``device`` current for the duration of a call; a no-op (no driver calls) when it already is."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, device):
+        self.idx, self.prev = device.index, None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if self.idx is not None and cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+
+
 _workspaces = {}
+_decode_ws_bytes = {}      # problem extents -> bytes, so a decode loop asks the library once
 
 
 def _workspace(nbytes: int, device) -> torch.Tensor:
@@ -192,12 +212,19 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
     if out is None:
         out = torch.empty((B, Hq, D), dtype=q.dtype, device=q.device)
     a.out = out.data_ptr()
-    nbytes = lib().cq_decode_attn_workspace_bytes(ctypes.byref(a))
+    ref = ctypes.byref(a)
+    aligned = all((ptr or 0) % 16 == 0 for ptr in (a.q, a.k_code, a.k_scale, a.k_mn, a.v_code, a.v_scale, a.v_mn,
+                                                   a.k_fp, a.v_fp))      # decides which kernels serve the call
+    key = (B, Hq, Hkv, D, a.t_vis, a.t_fp, bits, group_size, a.dtype, a.mask is not None, a.t_fp_dev is not None,
+           a.k_code is not None, aligned)
+    nbytes = _decode_ws_bytes.get(key)
+    if nbytes is None:
+        nbytes = _decode_ws_bytes[key] = lib().cq_decode_attn_workspace_bytes(ref)
     if nbytes == 0:
-        check(lib().cq_decode_attn(ctypes.byref(a), None, 0, _stream()), "cq_decode_attn")
+        check(lib().cq_decode_attn(ref, None, 0, _stream()), "cq_decode_attn")
     ws = _workspace(nbytes, q.device)
-    with torch.cuda.device(q.device):
-        rc = lib().cq_decode_attn(ctypes.byref(a), _ptr(ws), ws.numel(), _stream())
+    with _OnDevice(q.device):
+        rc = lib().cq_decode_attn(ref, _ptr(ws), ws.numel(), _stream())
     check(rc, "cq_decode_attn")
     return out.reshape(shape)
 
