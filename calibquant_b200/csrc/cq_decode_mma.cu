@@ -592,30 +592,15 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
   }
 
   int cons = 0, cal_pair = -1;
-  CalibH<T> cal_h[2];      // calibration constants of the warp's heads (warp, warp + 4) for cal_pair
   bool failed = false;
-
-  // Logits of one item for head warp + 4*hh, 8 per lane per 256 tokens.  With one-vector items (the
-  // small shape) the next item's logits are fetched while the current item is being multiplied.
-  constexpr int NV = CHUNK_TOK / 256;
-  constexpr bool PREFETCH = NV == 1;
-  const T2 neg_big2 = D16<T>::bcast(-D16<T>::big());
-  const uint32_t nb = *reinterpret_cast<const uint32_t*>(&neg_big2);
-  // (pr, ck) = (KV head, chunk) of the item; score rows of a KV head's query heads are consecutive:
-  // row = pr * n_rep + head
-  auto fetch = [&](int pr, int ck, int hh, int j) -> uint4 {
-    const int64_t row = (int64_t)pr * dm.n_rep + warp + 4 * hh;
-    const int t = (j * 32 + lane) * 8;
-    if (t >= min(CHUNK_TOK, dm.t_vis - ck * CHUNK_TOK)) return make_uint4(nb, nb, nb, nb);
-    return *reinterpret_cast<const uint4*>(scores + row * dm.pitch + ck * CHUNK_TOK + t);
-  };
-  uint4 pre[2] = {make_uint4(nb, nb, nb, nb), make_uint4(nb, nb, nb, nb)};
+  // Per query head of the current KV head: calibration constants and the reference maximum of the
+  // softmax.  The reference maximum is the (calibrated) maximum over the WHOLE visual span, known from
+  // the per-tile min/max the score kernel left, so the probabilities of a chunk need no reduction of
+  // their own and every thread can take any (head, 8 tokens) vector of the chunk.
+  __shared__ CalibH<T> cal_s[kMaxRep];
+  constexpr int NVEC = CHUNK_TOK / 8;                                   // 8-token vectors per head and chunk
+  const T2 zero2 = D16<T>::bcast(0.f);
   int pair = it_first / dm.n_chunks, chunk = it_first % dm.n_chunks;   // advanced item by item below
-  if (PREFETCH && it_first < it_end) {
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh)
-      if (warp + 4 * hh < dm.n_rep) pre[hh] = fetch(pair, chunk, hh, 0);
-  }
   for (int k = 0; !failed; ++k) {
     const int it = it_first + k;
     if (it >= it_end) break;
@@ -628,13 +613,8 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
                               dm.t_sys + tok_base : nullptr;
     const int n_tok = min(CHUNK_TOK, dm.t_vis - tok_base);
 
-    // ---- probabilities of the chunk: warp w serves heads w, w+4 --------------------------------
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int h = warp + 4 * hh;
-      if (h >= dm.n_rep) break;
-      CalibH<T>& cal = cal_h[hh];
-      if (dm.calibrate && pair != cal_pair) {
+    if (pair != cal_pair) {      // uniform over the CTA; the previous item ended with a CTA barrier
+      for (int h = warp; h < dm.n_rep; h += 4) {
         float lo = INFINITY, hi = -INFINITY;
         for (int i = lane; i < dm.n_mm; i += 32) {
           const float2 v = tile_mm[(row0 + h) * dm.n_mm + i];
@@ -643,62 +623,56 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         }
         lo = warp_min(lo);
         hi = warp_max(hi);
-        const float denom = rnd<T>(rnd<T>(hi - lo) + 1e-8f);
-        const float range = rnd<T>(rnd<T>(hi + (-3.f)) - lo);
-        cal.mn = D16<T>::bcast(lo);
-        cal.rdenom = D16<T>::bcast(1.f / denom);
-        cal.rdenom_lo = D16<T>::bcast(1.f / denom - rnd<T>(1.f / denom));   // two-term reciprocal
-        cal.range = D16<T>::bcast(range);
-      }
-      T2 x[NV][4];
-      T2 mx2 = neg_big2;
-#pragma unroll
-      for (int j = 0; j < NV; ++j) {
-        const int t = (j * 32 + lane) * 8;
-        uint4 raw;
-        if (PREFETCH) {
-          raw = pre[hh];
-          if (it + 1 < it_end) {
-            const bool wrap = chunk + 1 == dm.n_chunks;
-            pre[hh] = fetch(wrap ? pair + 1 : pair, wrap ? 0 : chunk + 1, hh, 0);
-          }
-        } else {
-          raw = fetch(pair, chunk, hh, j);
+        CalibH<T> cal;
+        cal.mn = cal.rdenom = cal.rdenom_lo = cal.range = zero2;
+        float m_ref = hi;
+        if (dm.calibrate) {
+          const float denom = rnd<T>(rnd<T>(hi - lo) + 1e-8f);
+          const float range = rnd<T>(rnd<T>(hi + (-3.f)) - lo);
+          cal.mn = D16<T>::bcast(lo);
+          cal.rdenom = D16<T>::bcast(1.f / denom);
+          cal.rdenom_lo = D16<T>::bcast(1.f / denom - rnd<T>(1.f / denom));   // two-term reciprocal
+          cal.range = D16<T>::bcast(range);
+          T2 v = __hsub2(D16<T>::bcast(hi), cal.mn);                          // the maximum, calibrated like any logit
+          v = __hfma2(v, cal.rdenom, __hmul2(v, cal.rdenom_lo));
+          v = __hadd2(__hmul2(v, cal.range), cal.mn);
+          m_ref = D16<T>::to_f2(v).x;
         }
+        if (lane == 0) {
+          cal_s[h] = cal;
+          m_s[h] = m_ref;      // the calibration is monotone: no logit of the span exceeds it
+        }
+      }
+      cal_pair = pair;
+      __syncthreads();
+    }
+
+    // ---- probabilities of the chunk ------------------------------------------------------------
+    for (int vi = tid; vi < dm.n_rep * NVEC; vi += THREADS) {
+      const int h = vi / NVEC, t = (vi % NVEC) * 8;
+      uint4 out = make_uint4(0u, 0u, 0u, 0u);
+      if (t < n_tok) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(scores + (row0 + h) * dm.pitch + tok_base + t);
         const T2* r2 = reinterpret_cast<const T2*>(&raw);
+        const CalibH<T> cal = cal_s[h];
+        const float m = m_s[h];
+        __half2* o2 = reinterpret_cast<__half2*>(&out);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           T2 v = r2[e];
-          if (dm.calibrate && t < n_tok) {
+          if (dm.calibrate) {
             v = __hsub2(v, cal.mn);
             v = __hfma2(v, cal.rdenom, __hmul2(v, cal.rdenom_lo));   // ~ rnd(v / denom)
             v = __hadd2(__hmul2(v, cal.range), cal.mn);
           }
-          if (mvis && t < n_tok) v = __hadd2(v, D16<T>::pair2(mvis[t + 2 * e], mvis[t + 2 * e + 1]));
-          x[j][e] = v;
-          mx2 = __hmax2(mx2, v);
-        }
-      }
-      const float2 fmx2 = D16<T>::to_f2(mx2);
-      const float m_true = warp_max(fmaxf(fmx2.x, fmx2.y));
-      if (lane == 0) m_s[h] = m_true;
-      const float m = m_true == -INFINITY ? 0.f : m_true;     // a fully masked chunk: all probabilities 0
-#pragma unroll
-      for (int j = 0; j < CHUNK_TOK / 256; ++j) {
-        const int t = (j * 32 + lane) * 8;
-        uint4 out;
-        __half2* o2 = reinterpret_cast<__half2*>(&out);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f = D16<T>::to_f2(x[j][e]);
+          if (mvis) v = __hadd2(v, D16<T>::pair2(mvis[t + 2 * e], mvis[t + 2 * e + 1]));
+          const float2 f = D16<T>::to_f2(v);
           // the reference rounds the probabilities to the data dtype; they are then exact in fp16
-          o2[e] = t < n_tok ? __floats2half2_rn(rnd<T>(exp2f((f.x - m) * LOG2E)), rnd<T>(exp2f((f.y - m) * LOG2E)))
-                            : __float2half2_rn(0.f);
+          o2[e] = __floats2half2_rn(rnd<T>(exp2f((f.x - m) * LOG2E)), rnd<T>(exp2f((f.y - m) * LOG2E)));
         }
-        *reinterpret_cast<uint4*>(p_s + h * P_PITCH + t) = out;
       }
+      *reinterpret_cast<uint4*>(p_s + h * P_PITCH + t) = out;
     }
-    cal_pair = pair;
     __syncthreads();
 
     float acc[8][4];
@@ -849,8 +823,9 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
 // =================================================================================================
 // K3: combine
 // =================================================================================================
-constexpr int K3_LANES = 4;    // slot-parallel groups of 128 channel threads
-template <typename T>
+// K3_LANES slot-parallel groups of 128 channel threads: 4 when a row has many partials to merge (long
+// contexts), 1 when it has a handful (then four times as many rows fit on an SM at once)
+template <typename T, int K3_LANES>
 __global__ void __launch_bounds__(kHeadDim * K3_LANES)
 k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict__ ml,
            T* __restrict__ out) {
@@ -1023,7 +998,10 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
     }
   }
   if (stages & 4) {
-    k3_combine<T><<<d.batch * d.hq, kHeadDim * K3_LANES, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
+    if (d.n_slots >= 16)
+      k3_combine<T, 4><<<d.batch * d.hq, kHeadDim * 4, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
+    else
+      k3_combine<T, 1><<<d.batch * d.hq, kHeadDim, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
     return check_launch();
   }
   return CQ_OK;
