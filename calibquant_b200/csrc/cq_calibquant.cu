@@ -12,6 +12,7 @@
 // Layouts: x [B,T,H,D] (strided), codes/enc [B,H,T,*], scale/zp [B,H,D] (the reference keeps them
 // as [B,1,H,D]; same memory).  D == 128.
 #include "cq_common.cuh"
+#include "cq_ptx.cuh"
 
 namespace cq {
 namespace calib {
@@ -196,6 +197,308 @@ __global__ void lut_out_finalize_kernel(const float* __restrict__ partial, __hal
   out[i] = __float2half_rn(s);
 }
 
+using namespace ptx;
+
+// ---- s[b,h,t] = sum_d w[b,h,d] * LUT[code[b,hk,t,d]] on the warp MMA -------------------------------------
+// Valid when the LUT is affine in the code (LUT[c] = l0 + c*step, which the identity LUT is): then
+//   s = l0 * sum_d w[d] + step * sum_d w[d]*code[t,d]
+// and the second sum is an MMA with A = codes (rows = tokens, k = channels) and B = w.  The packed
+// dimension is the contracted one here, so an A register (two k values of one token) is one AND of
+// the token's code word: its low half takes a field of byte 0 (or 1), its high half the same field of
+// byte 2 (or 3); the channel each k index stands for follows from that, and B is gathered to match.
+// A field at bit p of a half is the fp16 subnormal code * 2^(p-24); B carries 2^(4-p), so every
+// product weighs 2^-20.
+template <int BITS>
+struct LutMap {
+  // channel that k-block kb, lane column c, slot (0: a0.lo, 1: a0.hi, 2: a2.lo, 3: a2.hi) reads, and the
+  // bit position of its field inside the 16-bit half
+  static __device__ __forceinline__ void get(int kb, int c, int slot, int& chan, int& pos) {
+    if (BITS == 1) {             // word j = kb/2 (32 channels), bytes s, s+2 with s = kb%2
+      const int j = kb >> 1, s = kb & 1;
+      const int byte = s + 2 * (slot & 1);
+      pos = 2 * c + (slot >> 1);
+      chan = 32 * j + 8 * byte + (7 - pos);
+    } else if (BITS == 2) {      // word kb (16 channels): a0 from bytes 0,2, a2 from bytes 1,3; field c
+      const int byte = (slot >> 1) + 2 * (slot & 1);
+      pos = 2 * c;
+      chan = 16 * kb + 4 * byte + (3 - c);
+    } else {                     // words 2kb (a0) and 2kb+1 (a2), 8 channels each; nibble (c&1) of byte c>>1 (+2)
+      const int word = 2 * kb + (slot >> 1);
+      const int byte = (c >> 1) + 2 * (slot & 1);
+      pos = 0;                   // shifted down to bit 0 before masking
+      chan = 8 * word + 2 * byte + (1 - (c & 1));
+    }
+  }
+};
+
+constexpr int LS_TOK = 64;       // tokens per warp iteration (4 m-tiles)
+
+template <typename T, int BITS>
+__global__ void __launch_bounds__(128)
+lut_scores_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const uint8_t* __restrict__ enc,
+                      int hq, int hkv_enc, int t_len, __half* __restrict__ out) {
+  constexpr int ROW_BYTES = kHeadDim * BITS / 8;          // 16 / 32 / 64
+  constexpr int WORDS = ROW_BYTES / 4;
+  __shared__ float w_s[kMaxRep][kHeadDim];
+  __shared__ float wsum_s[kMaxRep];
+  __shared__ float lut_s[16];
+  __shared__ __align__(16) __half out_s[4][kMaxRep][LS_TOK + 8];
+  const int bhk = blockIdx.y, b = bhk / hkv_enc, hk = bhk % hkv_enc;
+  const int n_rep = hq / hkv_enc;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int64_t row0 = (int64_t)b * hq + (int64_t)hk * n_rep;
+  for (int i = tid; i < kMaxRep * kHeadDim; i += 128) {
+    const int r = i >> 7, d = i & (kHeadDim - 1);
+    w_s[r][d] = r < n_rep ? Elem<T>::to_f(w[(row0 + r) * kHeadDim + d]) : 0.f;
+  }
+  if (tid < (1 << BITS)) lut_s[tid] = Elem<T>::to_f(lut[tid]);
+  __syncthreads();
+  for (int r = warp; r < kMaxRep; r += 4) {               // sum_d w[r][d], a warp per head
+    const float s = warp_sum(w_s[r][lane] + w_s[r][lane + 32] + w_s[r][lane + 64] + w_s[r][lane + 96]);
+    if (lane == 0) wsum_s[r] = s;
+  }
+  const float l0 = lut_s[0], step = lut_s[1] - lut_s[0];
+  bool affine = true;
+#pragma unroll
+  for (int i = 2; i < (1 << BITS); ++i) affine = affine && (lut_s[i] == l0 + (float)i * step);
+  __syncthreads();
+  const uint8_t* base = enc + (int64_t)bhk * t_len * ROW_BYTES;
+
+  if (!affine) {
+    // arbitrary LUT: one token per warp iteration, a lane owns 4 channels
+    for (int t = blockIdx.x * 4 + warp; t < t_len; t += gridDim.x * 4) {
+      const uint8_t* row = base + (int64_t)t * ROW_BYTES;
+      float v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int d = lane * 4 + i;
+        constexpr int DPE = 8 / BITS;
+        v[i] = lut_s[(row[d / DPE] >> (BITS * (DPE - 1 - d % DPE))) & ((1u << BITS) - 1u)];
+      }
+      for (int r = 0; r < n_rep; ++r) {
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dot = fmaf(w_s[r][lane * 4 + i], v[i], dot);
+        dot = warp_sum(dot);
+        if (lane == 0) out[(row0 + r) * t_len + t] = __float2half_rn(dot);
+      }
+    }
+    return;
+  }
+
+  // B fragments of this lane: head n = g, eight k-blocks
+  uint32_t b0[8], b1[8];
+#pragma unroll
+  for (int kb = 0; kb < 8; ++kb) {
+    float v[4];
+#pragma unroll
+    for (int slot = 0; slot < 4; ++slot) {
+      int chan, pos;
+      LutMap<BITS>::get(kb, c, slot, chan, pos);
+      v[slot] = g < n_rep ? w_s[g][chan] * exp2f((float)(4 - pos)) : 0.f;
+    }
+    const __half2 lo = __floats2half2_rn(v[0], v[1]), hi = __floats2half2_rn(v[2], v[3]);
+    b0[kb] = *reinterpret_cast<const uint32_t*>(&lo);
+    b1[kb] = *reinterpret_cast<const uint32_t*>(&hi);
+  }
+  // masks of the lane's fields: low half and high half of the register take the same field
+  constexpr uint32_t FIELD = (1u << BITS) - 1u;
+  const uint32_t m_a0 = BITS == 4 ? 0x000f000fu : (FIELD << (BITS == 1 ? 2 * c : 2 * c)) * 0x00010001u;
+  const uint32_t m_a2 = BITS == 1 ? (1u << (2 * c + 1)) * 0x00010001u : m_a0;
+  const int sh4 = 4 * (c & 1) + 8 * (c >> 1);             // 4 bits: shift that brings the lane's nibble to bit 0
+
+  const bool vec_ok = (t_len % 8) == 0;
+  for (int t0 = (blockIdx.x * 4 + warp) * LS_TOK; t0 < t_len; t0 += gridDim.x * 4 * LS_TOK) {
+    // m-tile mt: rows g and g+8 of tokens t0 + 16 mt ...; at 1 and 2 bits the loads of all four m-tiles
+    // are issued before the first product
+#pragma unroll(BITS == 4 ? 1 : 4)
+    for (int mt = 0; mt < 4; ++mt) {
+      uint32_t W[2][WORDS];
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const int t = min(t0 + 16 * mt + g + 8 * hf, t_len - 1);
+        const uint4* rp = reinterpret_cast<const uint4*>(base + (int64_t)t * ROW_BYTES);
+#pragma unroll
+        for (int q4 = 0; q4 < WORDS / 4; ++q4) {
+          const uint4 v = __ldg(rp + q4);
+          W[hf][4 * q4] = v.x; W[hf][4 * q4 + 1] = v.y; W[hf][4 * q4 + 2] = v.z; W[hf][4 * q4 + 3] = v.w;
+        }
+      }
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int kb = 0; kb < 8; ++kb) {
+        uint32_t a0, a1, a2, a3;
+        if (BITS == 1) {
+          const uint32_t x0 = W[0][kb >> 1] >> (8 * (kb & 1)), x1 = W[1][kb >> 1] >> (8 * (kb & 1));
+          a0 = x0 & m_a0; a1 = x1 & m_a0; a2 = x0 & m_a2; a3 = x1 & m_a2;
+        } else if (BITS == 2) {
+          const uint32_t x0 = W[0][kb], x1 = W[1][kb];
+          a0 = x0 & m_a0; a1 = x1 & m_a0; a2 = (x0 >> 8) & m_a0; a3 = (x1 >> 8) & m_a0;
+        } else {
+          a0 = (W[0][2 * kb] >> sh4) & m_a0; a1 = (W[1][2 * kb] >> sh4) & m_a0;
+          a2 = (W[0][2 * kb + 1] >> sh4) & m_a0; a3 = (W[1][2 * kb + 1] >> sh4) & m_a0;
+        }
+        mma_f16(acc, a0, a1, a2, a3, b0[kb], b1[kb]);
+      }
+      // acc[0..1] = (token 16mt+g, heads 2c, 2c+1), acc[2..3] = (token 16mt+g+8, same heads)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = 2 * c + (e & 1), tt = 16 * mt + g + 8 * (e >> 1);
+        if (r < n_rep) out_s[warp][r][tt] = __float2half_rn(fmaf(step * 1048576.f, acc[e], l0 * wsum_s[r]));
+      }
+    }
+    __syncwarp();
+    if (vec_ok && t0 + LS_TOK <= t_len) {
+      for (int i = lane; i < n_rep * (LS_TOK / 8); i += 32) {
+        const int r = i / (LS_TOK / 8), ch = i % (LS_TOK / 8);
+        *reinterpret_cast<uint4*>(out + (row0 + r) * t_len + t0 + 8 * ch) =
+            *reinterpret_cast<const uint4*>(&out_s[warp][r][8 * ch]);
+      }
+    } else {
+      for (int i = lane; i < n_rep * LS_TOK; i += 32) {
+        const int r = i / LS_TOK, tt = i % LS_TOK;
+        if (t0 + tt < t_len) out[(row0 + r) * t_len + t0 + tt] = out_s[warp][r][tt];
+      }
+    }
+    __syncwarp();
+  }
+}
+
+
+// ---- o[b,h,d] = sum_t w[b,h,t] * LUT[code[b,hk,t,d]] on the warp MMA (affine LUT, 1 or 2 bits) ----------
+// A = codes with rows = channels and k = tokens: the two tokens of an A register come from two token
+// rows, merged by one byte permute; rows g and g+8 of two m-tiles share that byte (1 bit: bits
+// 4(g&1)+2i+{0,1} of byte g>>1 of a 32-channel word; 2 bits: the two fields 2(g&1)+{0,1}... of byte g>>1 of a
+// 16-channel word), so the permute is shared.  B = w (k = tokens, n = heads).  Each CTA takes WO_TOK
+// tokens of one (batch, code head): its four warps take a quarter each, then reduce in shared memory
+// and write one fp32 partial per (row, channel); a second launch sums the partials.
+constexpr int WO_TOK = 1024;
+
+template <typename T, int BITS>
+__global__ void __launch_bounds__(128)
+lut_out_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const uint8_t* __restrict__ enc,
+                   int hq, int hkv_enc, int t_len, float* __restrict__ partial, int n_rows) {
+  static_assert(BITS == 1 || BITS == 2, "4-bit codes take the scalar kernel");
+  constexpr int ROW_BYTES = kHeadDim * BITS / 8;          // 16 / 32
+  constexpr int WORDS = ROW_BYTES / 4;                    // 4 / 8
+  constexpr int MT_PER_WORD = 2 / BITS;                   // m-tiles (16 channels) per code word: 2 / 1
+  __shared__ __align__(16) __half w_s[kMaxRep][WO_TOK + 8];
+  __shared__ float red_s[4][kMaxRep][kHeadDim + 4];
+  __shared__ float wsum_s[kMaxRep];
+  __shared__ float lut_s[4];
+  const int bhk = blockIdx.y, b = bhk / hkv_enc, hk = bhk % hkv_enc;
+  const int n_rep = hq / hkv_enc;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int64_t row0 = (int64_t)b * hq + (int64_t)hk * n_rep;
+  const int t0 = blockIdx.x * WO_TOK, nt = min(WO_TOK, t_len - t0);
+  for (int i = tid; i < n_rep * WO_TOK; i += 128) {        // rows past n_rep are never read
+    const int r = i / WO_TOK, tt = i % WO_TOK;
+    w_s[r][tt] = __float2half_rn(tt < nt ? Elem<T>::to_f(w[(row0 + r) * t_len + t0 + tt]) : 0.f);
+  }
+  if (tid < (1 << BITS)) lut_s[tid] = Elem<T>::to_f(lut[tid]);
+  __syncthreads();
+  for (int r = warp; r < n_rep; r += 4) {                 // sum_t w[r][t] over the CTA's tokens, a warp per head
+    float s = 0.f;
+    for (int tt = lane; tt < WO_TOK; tt += 32) s += __half2float(w_s[r][tt]);     // zero past nt
+    s = warp_sum(s);
+    if (lane == 0) wsum_s[r] = s;
+  }
+  const float l0 = lut_s[0], step = lut_s[1] - lut_s[0];
+  bool affine = true;
+#pragma unroll
+  for (int i = 2; i < (1 << BITS); ++i) affine = affine && (lut_s[i] == l0 + (float)i * step);
+  if (!affine) {
+    // arbitrary LUT: thread = channel, serial over the CTA's tokens
+    float a[kMaxRep];
+#pragma unroll
+    for (int r = 0; r < kMaxRep; ++r) a[r] = 0.f;
+    const uint8_t* rows = enc + ((int64_t)bhk * t_len + t0) * ROW_BYTES;
+    for (int tt = 0; tt < nt; ++tt) {
+      const float v = lut_s[code_at(rows + (int64_t)tt * ROW_BYTES, tid, BITS)];
+#pragma unroll
+      for (int r = 0; r < kMaxRep; ++r)
+        if (r < n_rep) a[r] = fmaf(__half2float(w_s[r][tt]), v, a[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < kMaxRep; ++r)
+      if (r < n_rep) partial[((int64_t)blockIdx.x * n_rows + row0 + r) * kHeadDim + tid] = a[r];
+    return;
+  }
+  __syncthreads();       // wsum_s
+
+  // lane constants: byte of the word, masks of rows g / g+8 for the m-tile(s) of a word, accumulator scales
+  constexpr uint32_t FIELD = (1u << BITS) - 1u;
+  const uint32_t sel = (uint32_t)((g >> 1) | ((g >> 1) << 4) | ((4 + (g >> 1)) << 8) | ((4 + (g >> 1)) << 12));
+  uint32_t m0[MT_PER_WORD], m1[MT_PER_WORD];
+  float sc0[MT_PER_WORD], sc1[MT_PER_WORD];
+  int ch0[MT_PER_WORD], ch1[MT_PER_WORD];                 // channel inside the word's span of rows g / g+8
+#pragma unroll
+  for (int i = 0; i < MT_PER_WORD; ++i) {
+    // bit offset inside the byte of the field row g stands for; row g+8 takes the next field
+    const int p0 = BITS == 1 ? 4 * (g & 1) + 2 * i : 4 * (g & 1), p1 = p0 + BITS;
+    m0[i] = (FIELD << p0) * 0x00010001u;
+    m1[i] = (FIELD << p1) * 0x00010001u;
+    sc0[i] = exp2f((float)(24 - p0));
+    sc1[i] = exp2f((float)(24 - p1));
+    // MSB-first: the field at bit offset p of byte y is channel (8/BITS)*y + (8/BITS - 1 - p/BITS)
+    ch0[i] = (8 / BITS) * (g >> 1) + (8 / BITS - 1 - p0 / BITS);
+    ch1[i] = (8 / BITS) * (g >> 1) + (8 / BITS - 1 - p1 / BITS);
+  }
+  float acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+  const uint8_t* base = enc + ((int64_t)bhk * t_len + t0) * ROW_BYTES;
+  const int tw0 = warp * (WO_TOK / 4);
+#pragma unroll 4
+  for (int ks = 0; ks < WO_TOK / 4 / 16; ++ks) {
+    const int tk = tw0 + ks * 16;                          // first token of the k-step inside the CTA's span
+    if (tk >= nt) break;
+    // token rows 2c, 2c+1, 2c+8, 2c+9 of the k-step (clamped: tokens past the end have w = 0)
+    uint32_t Wa[WORDS], Wb[WORDS], Wc[WORDS], Wd[WORDS];
+    {
+      const int last = nt - 1;
+      const uint4* ra = reinterpret_cast<const uint4*>(base + (int64_t)min(tk + 2 * c, last) * ROW_BYTES);
+      const uint4* rb = reinterpret_cast<const uint4*>(base + (int64_t)min(tk + 2 * c + 1, last) * ROW_BYTES);
+      const uint4* rc = reinterpret_cast<const uint4*>(base + (int64_t)min(tk + 2 * c + 8, last) * ROW_BYTES);
+      const uint4* rd = reinterpret_cast<const uint4*>(base + (int64_t)min(tk + 2 * c + 9, last) * ROW_BYTES);
+#pragma unroll
+      for (int q4 = 0; q4 < WORDS / 4; ++q4) {
+        const uint4 va = __ldg(ra + q4), vb = __ldg(rb + q4), vc = __ldg(rc + q4), vd = __ldg(rd + q4);
+        Wa[4 * q4] = va.x; Wa[4 * q4 + 1] = va.y; Wa[4 * q4 + 2] = va.z; Wa[4 * q4 + 3] = va.w;
+        Wb[4 * q4] = vb.x; Wb[4 * q4 + 1] = vb.y; Wb[4 * q4 + 2] = vb.z; Wb[4 * q4 + 3] = vb.w;
+        Wc[4 * q4] = vc.x; Wc[4 * q4 + 1] = vc.y; Wc[4 * q4 + 2] = vc.z; Wc[4 * q4 + 3] = vc.w;
+        Wd[4 * q4] = vd.x; Wd[4 * q4 + 1] = vd.y; Wd[4 * q4 + 2] = vd.z; Wd[4 * q4 + 3] = vd.w;
+      }
+    }
+    const __half* wr = &w_s[g < n_rep ? g : 0][tk + 2 * c];
+    uint32_t bq0 = *reinterpret_cast<const uint32_t*>(wr), bq1 = *reinterpret_cast<const uint32_t*>(wr + 8);
+    if (g >= n_rep) { bq0 = 0u; bq1 = 0u; }
+#pragma unroll
+    for (int wd = 0; wd < WORDS; ++wd) {
+      const uint32_t x01 = prmt(Wa[wd], Wb[wd], sel), x89 = prmt(Wc[wd], Wd[wd], sel);
+#pragma unroll
+      for (int i = 0; i < MT_PER_WORD; ++i)
+        mma_f16(acc[wd * MT_PER_WORD + i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bq0, bq1);
+    }
+  }
+  // ---- reduce the four warps: acc[j][0..1] = (row g, heads 2c, 2c+1), acc[j][2..3] = (row g+8, ...)
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = j % MT_PER_WORD, span = (j / MT_PER_WORD) * (32 / BITS);   // channels covered by the word
+    const int d0 = span + ch0[i], d1 = span + ch1[i];
+    if (2 * c < n_rep) { red_s[warp][2 * c][d0] = acc[j][0] * sc0[i]; red_s[warp][2 * c][d1] = acc[j][2] * sc1[i]; }
+    if (2 * c + 1 < n_rep) { red_s[warp][2 * c + 1][d0] = acc[j][1] * sc0[i]; red_s[warp][2 * c + 1][d1] = acc[j][3] * sc1[i]; }
+  }
+  __syncthreads();
+  for (int r = 0; r < n_rep; ++r) {
+    const float s = red_s[0][r][tid] + red_s[1][r][tid] + red_s[2][r][tid] + red_s[3][r][tid];
+    partial[((int64_t)blockIdx.x * n_rows + row0 + r) * kHeadDim + tid] = fmaf(step, s, l0 * wsum_s[r]);
+  }
+}
+
+
 }  // namespace calib
 }  // namespace cq
 
@@ -277,8 +580,26 @@ extern "C" int cq_lut_scores(const void* lut, const void* weights, const uint8_t
   if (!dtype_ok(dtype) || n_q_heads % n_enc_heads) return CQ_ERR_BAD_ARG;
   if (!bits_ok(bits) || head_dim != kHeadDim || n_q_heads / n_enc_heads > kMaxRep) return CQ_ERR_UNSUPPORTED;
   if ((int64_t)batch * n_enc_heads > 65535) return CQ_ERR_UNSUPPORTED;
-  dim3 grid((unsigned)min(1024, (t_len + 7) / 8), (unsigned)(batch * n_enc_heads));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (aligned16(enc)) {     // tensor-core kernel: 128-bit loads of the code rows
+    // a CTA sets up the B fragments of its heads once, so it should stream a few thousand tokens; still at
+    // least ~8 CTAs per SM over the whole grid
+    const int per_cta = 4 * calib::LS_TOK;
+    const int by_work = (t_len + 8 * per_cta - 1) / (8 * per_cta);
+    const int by_fill = (148 * 8 + batch * n_enc_heads - 1) / (batch * n_enc_heads);
+    const int max_x = (t_len + per_cta - 1) / per_cta;
+    dim3 grid((unsigned)max(1, min(max_x, max(by_work, by_fill))), (unsigned)(batch * n_enc_heads));
+    __half* o = static_cast<__half*>(out);
+#define CQ_LUT_SCORES(T, B)                                                                                   \
+  calib::lut_scores_mma_kernel<T, B><<<grid, 128, 0, st>>>(static_cast<const T*>(lut), static_cast<const T*>(weights), \
+                                                          enc, n_q_heads, n_enc_heads, t_len, o)
+#define CQ_LUT_SCORES_B(T) do { if (bits == 1) CQ_LUT_SCORES(T, 1); else if (bits == 2) CQ_LUT_SCORES(T, 2); else CQ_LUT_SCORES(T, 4); } while (0)
+    if (dtype == CQ_DTYPE_F16) CQ_LUT_SCORES_B(__half); else CQ_LUT_SCORES_B(__nv_bfloat16);
+#undef CQ_LUT_SCORES_B
+#undef CQ_LUT_SCORES
+    return check_launch();
+  }
+  dim3 grid((unsigned)min(1024, (t_len + 7) / 8), (unsigned)(batch * n_enc_heads));
   if (dtype == CQ_DTYPE_F16)
     calib::lut_scores_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(lut), static_cast<const __half*>(weights), enc,
                                                            n_q_heads, n_enc_heads, t_len, bits, static_cast<__half*>(out));
@@ -302,11 +623,26 @@ extern "C" int cq_lut_out(const void* lut, const void* weights, const uint8_t* e
   if (!bits_ok(bits) || head_dim != kHeadDim || n_q_heads / n_enc_heads > kMaxRep) return CQ_ERR_UNSUPPORTED;
   if ((int64_t)batch * n_enc_heads > 65535) return CQ_ERR_UNSUPPORTED;
   if (!workspace || workspace_bytes < cq_lut_out_workspace_bytes(batch, n_q_heads, t_len)) return CQ_ERR_WORKSPACE;
-  const int chunks = (t_len + calib::WV_TCHUNK - 1) / calib::WV_TCHUNK;
-  dim3 grid((unsigned)chunks, (unsigned)(batch * n_enc_heads));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* ws = static_cast<float*>(workspace);
   const int rows = batch * n_q_heads;
+  if (bits <= 2 && aligned16(enc)) {     // tensor-core kernel: WO_TOK tokens per CTA (fewer partials than the scalar one)
+    const int chunks = (t_len + calib::WO_TOK - 1) / calib::WO_TOK;
+    dim3 grid((unsigned)chunks, (unsigned)(batch * n_enc_heads));
+#define CQ_LUT_OUT(T, B)                                                                                      \
+  calib::lut_out_mma_kernel<T, B><<<grid, 128, 0, st>>>(static_cast<const T*>(lut), static_cast<const T*>(weights), enc, \
+                                                       n_q_heads, n_enc_heads, t_len, ws, rows)
+    if (dtype == CQ_DTYPE_F16) { if (bits == 1) CQ_LUT_OUT(__half, 1); else CQ_LUT_OUT(__half, 2); }
+    else { if (bits == 1) CQ_LUT_OUT(__nv_bfloat16, 1); else CQ_LUT_OUT(__nv_bfloat16, 2); }
+#undef CQ_LUT_OUT
+    int rc = check_launch();
+    if (rc != CQ_OK) return rc;
+    const int64_t total = (int64_t)rows * kHeadDim;
+    calib::lut_out_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(ws, static_cast<__half*>(out), chunks, total);
+    return check_launch();
+  }
+  const int chunks = (t_len + calib::WV_TCHUNK - 1) / calib::WV_TCHUNK;
+  dim3 grid((unsigned)chunks, (unsigned)(batch * n_enc_heads));
   if (dtype == CQ_DTYPE_F16)
     calib::lut_out_partial_kernel<__half><<<grid, kHeadDim, 0, st>>>(static_cast<const __half*>(lut), static_cast<const __half*>(weights), enc,
                                                                      n_q_heads, n_enc_heads, t_len, bits, ws, rows);
