@@ -11,7 +11,8 @@
 //     the row this lane owns.  The surviving pattern c << s (c the code, s < 8) read as fp16 is the
 //     subnormal c * 2^(s-24): exact, and linear in c.  The 2^(24-s) factor is applied to the fp32
 //     accumulator of that row afterwards.  Two rows of a lane (adjacent tokens / channels) share
-//     the PRMT, so an A operand register costs 1.5 integer instructions.
+//     the PRMT (at 1 bit the rows of two m-tiles do), so an A operand register costs 1.25-1.5 integer
+//     instructions.
 //   * "post-scaling": the other operand carries the scales, never the codes:
 //       scores : B[d][h] = q[h][d] * ks[d,G]          (per 32-token group G)
 //       attn.V : B[t][h] = p[h][t] * vs[t,g]          (per 32-channel group g)
@@ -205,6 +206,12 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   int cur_pair = -1;
   uint32_t qA[8], qB[8];
   bool failed = false;
+  // bf16 data with at most 4 query heads per KV head: the post-scaled operand q*ks is carried as two
+  // fp16 terms, hi = rnd(q*ks) in MMA columns 0-3 and lo = q*ks - hi in columns 4-7 (lanes g >= 4 hold
+  // head g-4 again), and the two column groups are added in the epilogue.  Without it the 2^-12 relative
+  // rounding of q*ks moves a few percent of the logits to the neighbouring bf16 value.
+  const bool split = std::is_same<T, __nv_bfloat16>::value && dm.n_rep <= 4;
+  const int q_head = split ? (g & 3) : g;
 
   for (int k = 0;; ++k) {
     const int it = it_first + k;
@@ -218,11 +225,11 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
     if (pair != cur_pair) {   // query fragments of this KV head's query heads (B operand, n = g)
       cur_pair = pair;
       const int b = pair / dm.hkv, hk = pair % dm.hkv;
-      const T* qrow = q + ((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + g) * kHeadDim;
+      const T* qrow = q + ((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + q_head) * kHeadDim;
 #pragma unroll
       for (int kt = 0; kt < 8; ++kt) {
-        qA[kt] = g < dm.n_rep ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c)) : 0u;
-        qB[kt] = g < dm.n_rep ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c + 8)) : 0u;
+        qA[kt] = q_head < dm.n_rep ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c)) : 0u;
+        qB[kt] = q_head < dm.n_rep ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 2 * c + 8)) : 0u;
       }
     }
     if (!mbar_wait_bounded(&full_bar[s], (uint32_t)((k / STAGES) & 1), WAIT_TRIES)) {
@@ -286,7 +293,11 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
             const int gi = g_in_col + u * GU + a;             // group within the 8 of the scale fragment
             const uint32_t ksa = __shfl_sync(0xffffffffu, ksA[kt], 4 * gi + c);
             const uint32_t ksb = __shfl_sync(0xffffffffu, ksB[kt], 4 * gi + c);
-            const uint32_t b0 = hmul2_u32(qA[kt], ksa), b1 = hmul2_u32(qB[kt], ksb);
+            uint32_t b0 = hmul2_u32(qA[kt], ksa), b1 = hmul2_u32(qB[kt], ksb);
+            if (split && g >= 4) {   // low-order term: the FMA forms q*ks exactly before subtracting the high one
+              b0 = hfma2_u32(qA[kt], ksa, b0 ^ 0x80008000u);
+              b1 = hfma2_u32(qB[kt], ksb, b1 ^ 0x80008000u);
+            }
             if (BITS == 1) {   // one byte of the group's word feeds both m-tiles
               const uint32_t x01 = prmt(W[0][a], W[1][a], sel[0]), x89 = prmt(W[2][a], W[3][a], sel[0]);
 #pragma unroll
@@ -322,6 +333,10 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
 #pragma unroll
           for (int i = 0; i < 2; ++i) {
             const int tok = tokg + Expand<BITS>::elem(i, g);      // rows g, g+8 = tokens tok, tok+1
+            if (split) {      // columns 4-7 (lanes c + 2) hold the low-order terms of heads 0-3
+#pragma unroll
+              for (int e = 0; e < 4; ++e) acc[a][i][e] += __shfl_down_sync(0xffffffffu, acc[a][i][e], 2);
+            }
             const T2 ra = D16<T>::round2(fmaf(acc[a][i][0], sc0[i], bias0), fmaf(acc[a][i][2], sc1[i], bias0));
             const T2 rb = D16<T>::round2(fmaf(acc[a][i][1], sc0[i], bias1), fmaf(acc[a][i][3], sc1[i], bias1));
             const T2 sa = D16<T>::scale2(ra, inv_sqrt_d), sb = D16<T>::scale2(rb, inv_sqrt_d);
@@ -514,7 +529,7 @@ template <typename T, int BITS, int CHUNK_TOK, int VT_TOK>
 __global__ void __launch_bounds__(THREADS, CHUNK_TOK == CT_SMALL ? 4 : 3)
 k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile_mm,
           const int32_t* __restrict__ v_code, const T* __restrict__ v_scale,
-          const T* __restrict__ v_mn, const T* __restrict__ v_fp,
+          const T* __restrict__ v_mn,
           float* __restrict__ partial, float2* __restrict__ ml, int* __restrict__ status) {
   using T2 = typename D16<T>::T2;
   constexpr int STAGES = k2_stages(BITS);
@@ -986,8 +1001,7 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
     const int items2 = n_pairs * d.n_chunks;
     const int grid2 = max(1, min(items2, sm_count() * occ2));
     k2<<<grid2, THREADS, smem2, st>>>(d, scores, mm, a->v_code, static_cast<const T*>(a->v_scale),
-                                      static_cast<const T*>(a->v_mn), static_cast<const T*>(a->v_fp),
-                                      partial, ml, status);
+                                      static_cast<const T*>(a->v_mn), partial, ml, status);
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
     if (d.n_fp_chunks > 0) {

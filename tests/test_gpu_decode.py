@@ -100,7 +100,7 @@ def test_tensor_core_path_shapes(ops, bits, t_vis, t_txt, n_rep):
 
 
 @pytest.mark.parametrize("bits", [1, 4])
-@pytest.mark.parametrize("dtype,tol", [(torch.float16, TOL_ATTN), (torch.bfloat16, 4e-2)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, TOL_ATTN), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("t_vis,t_txt", [(256, 9), (1280, 90)])
 def test_tensor_core_path_with_mask(ops, bits, dtype, tol, t_vis, t_txt):
     """Additive mask (left padding on one row, one masked system key on another) on shapes the fast
@@ -137,10 +137,12 @@ def test_tensor_core_path_bf16(ops, bits, t_vis, t_txt, n_rep):
     logits and probabilities are rounded to bf16 where the reference rounds them.  Tolerance 4e-2:
     raw scores near |300| have a bf16 spacing of 2 (0.18 after the 1/sqrt(D) scale), so the 2^-12
     relative rounding of the fp16 operand q*ks moves a few percent of the logits to the neighbouring
-    bf16 value; the general kernels (fp32 dequantisation) stay within 2e-2 on the same inputs."""
+    bf16 value; the general kernels (fp32 dequantisation) stay within 2e-2 on the same inputs, and so
+    does this path when it can split q*ks into two fp16 terms (n_rep <= 4)."""
     out, ref = _run_case(ops, 2, 2 * n_rep, 2, t_vis, t_txt, bits, torch.bfloat16, seed=70 + bits + t_vis)
     assert out.dtype == torch.bfloat16
-    assert rel_l2(out, ref) <= 4e-2, rel_l2(out, ref)
+    # with at most 4 query heads per KV head q*ks is carried as two fp16 terms and the bar is the general one
+    assert rel_l2(out, ref) <= (2e-2 if n_rep <= 4 else 4e-2), rel_l2(out, ref)
     assert ops.device_status() == 0
 
 
