@@ -219,6 +219,8 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
            a.k_code is not None, aligned)
     nbytes = _decode_ws_bytes.get(key)
     if nbytes is None:
+        if len(_decode_ws_bytes) > 4096:      # a long generation adds one entry per text-cache length
+            _decode_ws_bytes.clear()
         nbytes = _decode_ws_bytes[key] = lib().cq_decode_attn_workspace_bytes(ref)
     if nbytes == 0:
         check(lib().cq_decode_attn(ref, None, 0, _stream()), "cq_decode_attn")
