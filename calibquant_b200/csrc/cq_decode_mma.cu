@@ -850,11 +850,13 @@ k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict_
   const int d = threadIdx.x & (kHeadDim - 1), sl = threadIdx.x >> 7;
   const float2* r = ml + row * dm.n_slots;
   const int n_live = dm.n_chunks + (live_t_fp(dm) + 127) / 128;   // visual chunks, then fp chunks
+  // common maximum: the lanes of every warp share the slots, one or two loads each
   float M = -INFINITY;
-  for (int i = 0; i < n_live; ++i) M = fmaxf(M, __ldg(&r[i]).x);
+  for (int i = threadIdx.x & 31; i < n_live; i += 32) M = fmaxf(M, __ldg(&r[i]).x);
+  M = warp_max(M);
   float L = 0.f, o = 0.f;
   const float* p = partial + row * dm.n_slots * kHeadDim + d;
-#pragma unroll 4
+#pragma unroll 8
   for (int i = sl; i < n_live; i += K3_LANES) {
     const float2 mlv = __ldg(&r[i]);
     const float w = exp2f((mlv.x - M) * LOG2E);
