@@ -296,7 +296,7 @@ def run_ours(args, rank, world, device):
         "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(args, reps=2)
+        line["cpu_baseline"] = cpu_baseline(args, reps=10)
     return line
 
 

@@ -894,16 +894,35 @@ static EncodeTiledFn encode_fn() {
 }
 
 // rows x cols matrix (cols contiguous), box = 32 columns x 128 rows.
+// A decode loop asks for the same few descriptors at every step (one cache per layer), so the encoded
+// maps are remembered per host thread: a descriptor is a pure function of the key below.
 static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes,
                      uint64_t cols, uint64_t rows, CUtensorMapSwizzle sw) {
+  struct Entry { const void* base; uint64_t cols, rows; int dt, sw; CUtensorMap map; };
+  constexpr int N = 256;
+  thread_local Entry cache[N];
+  thread_local int used = 0, next = 0;
+  for (int i = 0; i < used; ++i) {
+    const Entry& e = cache[i];
+    if (e.base == base && e.cols == cols && e.rows == rows && e.dt == (int)dt && e.sw == (int)sw) {
+      *m = e.map;
+      return true;
+    }
+  }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
   cuuint32_t box[2] = {32, 128};
   cuuint32_t estr[2] = {1, 1};
-  return fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  Entry& e = cache[next];
+  e.base = base; e.cols = cols; e.rows = rows; e.dt = (int)dt; e.sw = (int)sw; e.map = *m;
+  next = (next + 1) % N;
+  if (used < N) ++used;
+  return true;
 }
 
 struct Layout {

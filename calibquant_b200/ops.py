@@ -60,10 +60,10 @@ _workspaces = {}
 _decode_ws_bytes = {}      # problem extents -> bytes, so a decode loop asks the library once
 
 
-def _workspace(nbytes: int, device) -> torch.Tensor:
+def _workspace(nbytes: int, device, stream_handle=None) -> torch.Tensor:
     """Grow-only scratch buffer per (device, stream), zeroed when created: its first word is
     the sticky device status the decode kernels set when a bounded wait runs out."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream if stream_handle is None else stream_handle)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
@@ -222,11 +222,12 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
         if len(_decode_ws_bytes) > 4096:      # a long generation adds one entry per text-cache length
             _decode_ws_bytes.clear()
         nbytes = _decode_ws_bytes[key] = lib().cq_decode_attn_workspace_bytes(ref)
+    handle = torch.cuda.current_stream(q.device).cuda_stream      # looked up once per call
     if nbytes == 0:
-        check(lib().cq_decode_attn(ref, None, 0, _stream()), "cq_decode_attn")
-    ws = _workspace(nbytes, q.device)
+        check(lib().cq_decode_attn(ref, None, 0, ctypes.c_void_p(handle)), "cq_decode_attn")
+    ws = _workspace(nbytes, q.device, handle)
     with _OnDevice(q.device):
-        rc = lib().cq_decode_attn(ref, _ptr(ws), ws.numel(), _stream())
+        rc = lib().cq_decode_attn(ref, _ptr(ws), ws.numel(), ctypes.c_void_p(handle))
     check(rc, "cq_decode_attn")
     return out.reshape(shape)
 
