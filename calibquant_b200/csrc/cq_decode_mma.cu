@@ -73,6 +73,7 @@ struct Dims {
   int n_mm;            // min/max entries per row: n_ktiles * K1_WARPS
   int64_t fp_stride_b, fp_stride_h;
   const int32_t* t_fp_dev;   // optional: live number of fp tokens on the device (t_fp is then the capacity)
+  int raw;                   // 1: plain quantized product (cq_qbmm): no 1/sqrt(D), no softmax, no normalisation
   const void* mask;          // optional additive mask [batch][t_sys | t_vis | text] in the data dtype
   int64_t mask_stride_b;
   int t_sys;                 // fp tokens that precede the visual span in the mask's key order
@@ -339,7 +340,8 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
             }
             const T2 ra = D16<T>::round2(fmaf(acc[a][i][0], sc0[i], bias0), fmaf(acc[a][i][2], sc1[i], bias0));
             const T2 rb = D16<T>::round2(fmaf(acc[a][i][1], sc0[i], bias1), fmaf(acc[a][i][3], sc1[i], bias1));
-            const T2 sa = D16<T>::scale2(ra, inv_sqrt_d), sb = D16<T>::scale2(rb, inv_sqrt_d);
+            // the attention logits are the rounded product times 1/sqrt(D); the plain product stops at the rounding
+            const T2 sa = dm.raw ? ra : D16<T>::scale2(ra, inv_sqrt_d), sb = dm.raw ? rb : D16<T>::scale2(rb, inv_sqrt_d);
             if (2 * c < dm.n_rep) {
               *reinterpret_cast<T2*>(scores + row_a + tok) = sa;
               mnA = __hmin2(mnA, sa); mxA = __hmax2(mxA, sa);
@@ -362,12 +364,12 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
         lo_b = fminf(lo_b, __shfl_xor_sync(0xffffffffu, lo_b, o));
         hi_b = fmaxf(hi_b, __shfl_xor_sync(0xffffffffu, hi_b, o));
       }
-      if (g == 0) {
+      if (g == 0 && !dm.raw) {
         const int64_t r0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + 2 * c;
         if (2 * c < dm.n_rep) tile_mm[r0 * dm.n_mm + tile * K1_WARPS + warp] = make_float2(lo_a, hi_a);
         if (2 * c + 1 < dm.n_rep) tile_mm[(r0 + 1) * dm.n_mm + tile * K1_WARPS + warp] = make_float2(lo_b, hi_b);
       }
-    } else if (lane < 2 * kMaxRep) {
+    } else if (lane < 2 * kMaxRep && !dm.raw) {
       // dead part of a ragged last tile: neutral min/max entries
       const int b = pair / dm.hkv, hk = pair % dm.hkv;
       if (lane < dm.n_rep)
@@ -631,7 +633,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
     if (pair != cal_pair) {      // uniform over the CTA; the previous item ended with a CTA barrier
       for (int h = warp; h < dm.n_rep; h += 4) {
         float lo = INFINITY, hi = -INFINITY;
-        for (int i = lane; i < dm.n_mm; i += 32) {
+        for (int i = lane; i < (dm.raw ? 0 : dm.n_mm); i += 32) {
           const float2 v = tile_mm[(row0 + h) * dm.n_mm + i];
           lo = fminf(lo, v.x);
           hi = fmaxf(hi, v.y);
@@ -655,7 +657,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         }
         if (lane == 0) {
           cal_s[h] = cal;
-          m_s[h] = m_ref;      // the calibration is monotone: no logit of the span exceeds it
+          m_s[h] = dm.raw ? 0.f : m_ref;      // the calibration is monotone: no logit of the span exceeds it
         }
       }
       cal_pair = pair;
@@ -682,8 +684,10 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
           }
           if (mvis) v = __hadd2(v, D16<T>::pair2(mvis[t + 2 * e], mvis[t + 2 * e + 1]));
           const float2 f = D16<T>::to_f2(v);
-          // the reference rounds the probabilities to the data dtype; they are then exact in fp16
-          o2[e] = __floats2half2_rn(rnd<T>(exp2f((f.x - m) * LOG2E)), rnd<T>(exp2f((f.y - m) * LOG2E)));
+          // the reference rounds the probabilities to the data dtype; they are then exact in fp16.
+          // Plain product: the row holds the weights themselves.
+          o2[e] = dm.raw ? __floats2half2_rn(f.x, f.y)
+                         : __floats2half2_rn(rnd<T>(exp2f((f.x - m) * LOG2E)), rnd<T>(exp2f((f.y - m) * LOG2E)));
         }
       }
       *reinterpret_cast<uint4*>(p_s + h * P_PITCH + t) = out;
@@ -869,7 +873,7 @@ k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict_
   if (sl == 0) {
 #pragma unroll
     for (int j = 1; j < K3_LANES; ++j) { o += o_s[j][d]; L += l_s[j]; }
-    out[row * kHeadDim + d] = Elem<T>::from_f(o / L);
+    out[row * kHeadDim + d] = Elem<T>::from_f(dm.raw ? o : o / L);
   }
 }
 
@@ -944,6 +948,7 @@ static Dims make_dims(const cq_decode_args* a) {
   d.n_mm = d.n_ktiles * K1_WARPS;
   d.fp_stride_b = a->fp_stride_b; d.fp_stride_h = a->fp_stride_h;
   d.t_fp_dev = a->t_fp_dev;
+  d.raw = 0;
   d.mask = a->mask; d.mask_stride_b = a->mask_stride_b; d.t_sys = a->t_sys;
   return d;
 }
@@ -1061,6 +1066,120 @@ bool mma_path_eligible(const cq_decode_args* a) {
     if (!aligned16(p)) return false;
   if (a->t_fp > 0 && (!aligned16(a->k_fp) || !aligned16(a->v_fp))) return false;
   return mma::encode_fn() != nullptr;
+}
+
+// ---- the stand-alone quantized product on the same kernels ----------------------------------------
+// out[b,h,n] = sum_k fA[b,h,k] * (scale[k, n/32] * code[k, n] + zero[k, n/32]) with the codes packed along n.
+//   K == 128, N % 256 == 0 ("q.K": rows = channels, n = tokens)   -> the score launch, rounding only
+//   N == 128, K % 256 == 0 ("att.V": rows = tokens, n = channels) -> the attn.V launch on given weights,
+//                                                                     then the merge without normalisation
+static bool qbmm_ptrs_ok(const void* fA, const void* qB, const void* s, const void* z, const void* out) {
+  return aligned16(fA) && aligned16(qB) && aligned16(s) && aligned16(z) && aligned16(out) && mma::encode_fn() != nullptr;
+}
+
+int mma_qbmm_kind(const void* fA, const void* qB, const void* scales, const void* zeros, const void* out,
+                  int n_q_heads, int n_kv_heads, int64_t K, int64_t N) {
+  static const bool disabled = []() { const char* e = getenv("CQ_DECODE_GENERAL"); return e && e[0] == '1'; }();
+  if (disabled || !qbmm_ptrs_ok(fA, qB, scales, zeros, out)) return 0;
+  if (n_q_heads / n_kv_heads > kMaxRep || K > 0x3fffffff || N > 0x3fffffff) return 0;
+  if (K == kHeadDim && N % 256 == 0) return 1;
+  if (N == kHeadDim && K % 256 == 0) return 2;
+  return 0;
+}
+
+static mma::Dims qbmm_dims(int kind, int batch, int hq, int hkv, int64_t K, int64_t N) {
+  cq_decode_args a = {};
+  a.batch = batch; a.n_q_heads = hq; a.n_kv_heads = hkv;
+  a.t_vis = (int)(kind == 1 ? N : K);
+  mma::Dims d = mma::make_dims(&a);
+  d.raw = 1;
+  d.pitch = a.t_vis;                       // the caller's rows are dense
+  d.calibrate = 0;
+  return d;
+}
+
+size_t mma_qbmm_workspace_bytes(int batch, int n_q_heads, int64_t K, int64_t N) {
+  // the attn.V route with the small work items (256 rows of k): one (acc[128], max, sum) partial per item
+  if (N != kHeadDim || K % 256) return 256;
+  const size_t rows = (size_t)batch * n_q_heads, slots = (size_t)(K / 256);
+  return 256 + align_up(rows * slots * sizeof(float2), 256) + rows * slots * kHeadDim * sizeof(float);
+}
+
+template <typename T, int BITS>
+static int qbmm_run_t(int kind, const mma::Dims& d, const void* fA, const int32_t* qB, const void* scales,
+                      const void* zeros, void* out, unsigned char* ws, cudaStream_t st) {
+  using namespace mma;
+  int* status = reinterpret_cast<int*>(ws);
+  const int n_pairs = d.batch * d.hkv;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CQ_ERR_LAUNCH;
+  if (kind == 1) {
+    auto k1 = k1_scores<T, BITS>;
+    const int smem1 = k1_stages(BITS) * k1_stage_bytes(BITS) + 1024;
+    static bool configured[64] = {};
+    static int occ[64];
+    if (!configured[dev]) {
+      if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1) != cudaSuccess) return CQ_ERR_LAUNCH;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[dev], k1, K1_THREADS, smem1) != cudaSuccess || occ[dev] < 1) return CQ_ERR_LAUNCH;
+      configured[dev] = true;
+    }
+    CUtensorMap tm_code, tm_ks, tm_kmn;
+    const uint64_t rows = (uint64_t)n_pairs * kHeadDim;
+    if (!make_map(&tm_code, qB, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)d.n_groups * BITS, rows, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !make_map(&tm_ks, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)d.n_groups, rows, CU_TENSOR_MAP_SWIZZLE_64B) ||
+        !make_map(&tm_kmn, zeros, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)d.n_groups, rows, CU_TENSOR_MAP_SWIZZLE_64B))
+      return CQ_ERR_LAUNCH;
+    const int grid = max(1, min(n_pairs * d.n_ktiles, sm_count() * occ[dev]));
+    k1<<<grid, K1_THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(fA), nullptr,
+                                        static_cast<T*>(out), nullptr, status);
+    return check_launch();
+  }
+  float2* ml = reinterpret_cast<float2*>(ws + 256);
+  const size_t rows = (size_t)d.batch * d.hq;
+  float* partial = reinterpret_cast<float*>(ws + 256 + align_up(rows * (size_t)d.n_slots * sizeof(float2), 256));
+  auto launch_k2 = [&](auto k2, int smem2) -> int {
+    static bool configured[64] = {};
+    static int occ[64];
+    if (!configured[dev]) {
+      if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return CQ_ERR_LAUNCH;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[dev], k2, THREADS, smem2) != cudaSuccess || occ[dev] < 1) return CQ_ERR_LAUNCH;
+      configured[dev] = true;
+    }
+    const int grid = max(1, min(n_pairs * d.n_chunks, sm_count() * occ[dev]));
+    k2<<<grid, THREADS, smem2, st>>>(d, static_cast<const T*>(fA), nullptr, qB, static_cast<const T*>(scales),
+                                     static_cast<const T*>(zeros), partial, ml, status);
+    return check_launch();
+  };
+  constexpr int red_bytes = 4 * kMaxRep * 136 * 4;
+  int rc;
+  if (d.chunk_tok == CT_LARGE) {
+    constexpr int p_bytes = kMaxRep * (CT_LARGE + 8) * 2;
+    rc = launch_k2(k2_attn_v<T, BITS, CT_LARGE, VT_LARGE>,
+                   k2_stages(BITS) * k2_stage_bytes(BITS, VT_LARGE) + (p_bytes > red_bytes ? p_bytes : red_bytes) + 1024);
+  } else {
+    constexpr int p_bytes = kMaxRep * (CT_SMALL + 8) * 2;
+    rc = launch_k2(k2_attn_v<T, BITS, CT_SMALL, VT_SMALL>,
+                   k2_stages(BITS) * k2_stage_bytes(BITS, VT_SMALL) + (p_bytes > red_bytes ? p_bytes : red_bytes) + 1024);
+  }
+  if (rc != CQ_OK) return rc;
+  if (d.n_slots >= 16)
+    k3_combine<T, 4><<<d.batch * d.hq, kHeadDim * 4, 0, st>>>(d, partial, ml, static_cast<T*>(out));
+  else
+    k3_combine<T, 1><<<d.batch * d.hq, kHeadDim, 0, st>>>(d, partial, ml, static_cast<T*>(out));
+  return check_launch();
+}
+
+int mma_qbmm_run(int kind, const void* fA, const int32_t* qB, const void* scales, const void* zeros, void* out,
+                 int batch, int n_q_heads, int n_kv_heads, int64_t K, int64_t N, int bits, int dtype,
+                 void* workspace, cudaStream_t st) {
+  const mma::Dims d = qbmm_dims(kind, batch, n_q_heads, n_kv_heads, K, N);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+#define CQ_QBMM(T)                                                                                          \
+  (bits == 1 ? qbmm_run_t<T, 1>(kind, d, fA, qB, scales, zeros, out, ws, st)                                 \
+   : bits == 2 ? qbmm_run_t<T, 2>(kind, d, fA, qB, scales, zeros, out, ws, st)                               \
+               : qbmm_run_t<T, 4>(kind, d, fA, qB, scales, zeros, out, ws, st))
+  return dtype == CQ_DTYPE_F16 ? CQ_QBMM(__half) : CQ_QBMM(__nv_bfloat16);
+#undef CQ_QBMM
 }
 
 size_t mma_path_workspace_bytes(const cq_decode_args* a) {

@@ -13,4 +13,15 @@ size_t mma_path_workspace_bytes(const cq_decode_args* args);
 // wait ran out); the caller zeroes the workspace once after allocating it.
 int mma_path_run(const cq_decode_args* args, void* workspace, cudaStream_t stream);
 
+
+// The stand-alone quantized product (cq_qbmm) on the same kernels.  mma_qbmm_kind returns 0 when the
+// shapes or pointers are not ones the fast kernels take, 1 for the "q.K" use (K == 128) and 2 for the
+// "att.V" use (N == 128); workspace as mma_qbmm_workspace_bytes says, its first word a status word.
+int mma_qbmm_kind(const void* fA, const void* qB, const void* scales, const void* zeros, const void* out,
+                  int n_q_heads, int n_kv_heads, int64_t K, int64_t N);
+size_t mma_qbmm_workspace_bytes(int batch, int n_q_heads, int64_t K, int64_t N);
+int mma_qbmm_run(int kind, const void* fA, const int32_t* qB, const void* scales, const void* zeros, void* out,
+                 int batch, int n_q_heads, int n_kv_heads, int64_t K, int64_t N, int bits, int dtype,
+                 void* workspace, cudaStream_t stream);
+
 }  // namespace cq

@@ -6,7 +6,11 @@
 //
 // Work split: thread = output column n, CTA = 128 columns x one chunk of KCHUNK rows of k,
 // partial sums land in an fp32 workspace [k_chunks][B*Hq][N]; a second kernel adds the chunks.
+// The two shapes the attention path calls the product with (K == 128 with N % 256 == 0, and N == 128
+// with K % 256 == 0) run instead on the tensor-core kernels of the decode step (cq_decode_mma.cu),
+// where the operand sides round to fp16 before the product (relative error about 2^-11 per term).
 #include "cq_common.cuh"
+#include "cq_decode_shared.cuh"
 
 namespace cq {
 
@@ -94,7 +98,9 @@ int launch_qbmm(const void* fA, const int32_t* qB, const void* scales, const voi
 extern "C" size_t cq_qbmm_workspace_bytes(int batch, int n_q_heads, int64_t K, int64_t N) {
   if (batch <= 0 || n_q_heads <= 0 || K <= 0 || N <= 0) return 0;
   const size_t k_chunks = (size_t)((K + cq::QB_KCHUNK - 1) / cq::QB_KCHUNK);
-  return k_chunks * (size_t)batch * (size_t)n_q_heads * (size_t)N * sizeof(float);
+  const size_t general = k_chunks * (size_t)batch * (size_t)n_q_heads * (size_t)N * sizeof(float);
+  const size_t fast = cq::mma_qbmm_workspace_bytes(batch, n_q_heads, K, N);
+  return general > fast ? general : fast;
 }
 
 extern "C" int cq_qbmm(const void* fA, const int32_t* qB, const void* scales, const void* zeros,
@@ -118,6 +124,11 @@ extern "C" int cq_qbmm(const void* fA, const int32_t* qB, const void* scales, co
   if (!workspace || workspace_bytes < cq_qbmm_workspace_bytes(batch, n_q_heads, K, N))
     return CQ_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the two shapes of the attention path run on the tensor-core kernels of the decode step
+  const int kind = cq::mma_qbmm_kind(fA, qB, scales, zeros, out, n_q_heads, n_kv_heads, K, N);
+  if (kind != 0 && cq::aligned16(workspace))
+    return cq::mma_qbmm_run(kind, fA, qB, scales, zeros, out, batch, n_q_heads, n_kv_heads, K, N, bits, dtype,
+                            workspace, st);
   float* ws = static_cast<float*>(workspace);
   if (dtype == CQ_DTYPE_F16)
     return cq::launch_qbmm<__half>(fA, qB, scales, zeros, out, batch, n_q_heads, n_kv_heads, K, N, bits, ws, st);

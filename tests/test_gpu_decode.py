@@ -200,6 +200,31 @@ def test_qbmm_both_orientations(ops, bits):
     assert rel_l2(got.cpu(), ref) <= TOL_QBMM
 
 
+@pytest.mark.parametrize("bits", [1, 2, 4])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (12, 2)])
+def test_qbmm_tensor_core_shapes(ops, bits, dtype, hq, hkv):
+    """The two shapes the attention path calls the product with (head dim 128 on one side, a multiple of
+    256 tokens on the other) run on the decode kernels; same tolerance as the general kernel."""
+    T = 1280
+    k, v, q = generator.make_kvq(2, hq, hkv, T, seed=40 + bits, dtype=dtype)
+    kp = gf.quantize_and_pack_last_dim(k.transpose(2, 3).contiguous(), 32, bits)
+    vp = gf.quantize_and_pack_last_dim(v.contiguous(), 32, bits)
+    rep = lambda t: gf.repeat_kv(t, hq // hkv)
+    ref = gf.qbmm(32, q, rep(kp[0]), rep(kp[1]), rep(kp[2]), bits)
+    got = ops.qbmm(32, q.cuda(), *_cuda(kp), bits)
+    assert got.shape == ref.shape and got.dtype == dtype
+    assert rel_l2(got.cpu(), ref) <= TOL_QBMM
+    g = torch.Generator().manual_seed(2)
+    att = torch.softmax(torch.randn(2, hq, 1, T, generator=g) * 2, -1).to(dtype)
+    ref = gf.qbmm(32, att, rep(vp[0]), rep(vp[1]), rep(vp[2]), bits)
+    got = ops.qbmm(32, att.cuda(), *_cuda(vp), bits)
+    assert got.shape == ref.shape and got.dtype == dtype
+    tol = TOL_QBMM if dtype == torch.float16 else 4e-3          # bf16: the weights and the output round at 2^-9
+    assert rel_l2(got.cpu(), ref) <= tol
+    assert ops.device_status() == 0
+
+
 def test_drop_in_module_names(ops):
     """The reference's import surface for this path resolves to the CUDA kernels."""
     from calibquant_b200.qjl.matmul import cuda_quantized_bmm_dynamic
