@@ -83,6 +83,8 @@ SIGNATURES = {
                                     _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _vp, _vp]),
     "cq_decode_attn_workspace_bytes": (_sz, [_c.POINTER(DecodeArgs)]),
     "cq_decode_attn": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _sz, _vp]),
+    "cq_decode_attn_host_workspace_bytes": (_sz, [_c.POINTER(DecodeArgs)]),
+    "cq_decode_attn_host": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _vp, _vp, _sz, _vp]),
 }
 
 _lib = None

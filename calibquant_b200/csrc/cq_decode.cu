@@ -459,3 +459,58 @@ extern "C" int cq_decode_attn(const cq_decode_args* args, void* workspace, size_
   if (args->dtype == CQ_DTYPE_F16) return cq::run_decode_bits<__half>(args, dm, w, ws, st);
   return cq::run_decode_bits<__nv_bfloat16>(args, dm, w, ws, st);
 }
+
+// ---- the same step for callers whose query and result live in host memory -------------------------
+namespace cq {
+static size_t host_stage_bytes(const cq_decode_args* a) {
+  return align_up((size_t)a->batch * a->n_q_heads * kHeadDim * 2, 256);
+}
+// device-visible address of a page-locked host buffer, or nullptr for pageable memory (asked on every
+// call: an address can change from page-locked to pageable between calls)
+static void* mapped_host_ptr(const void* p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) == cudaSuccess && attr.type == cudaMemoryTypeHost) return attr.devicePointer;
+  (void)cudaGetLastError();
+  return nullptr;
+}
+}  // namespace cq
+
+extern "C" size_t cq_decode_attn_host_workspace_bytes(const cq_decode_args* args) {
+  if (!args) return 0;
+  cq_decode_args a = *args;                       // q / out are not device operands here
+  a.q = reinterpret_cast<const void*>(uintptr_t(256));
+  a.out = reinterpret_cast<void*>(uintptr_t(256));
+  const size_t base = cq_decode_attn_workspace_bytes(&a);
+  if (base == 0) return 0;
+  return cq::align_up(base, 256) + 2 * cq::host_stage_bytes(&a);
+}
+
+extern "C" int cq_decode_attn_host(const cq_decode_args* args, const void* q_host, void* out_host,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
+  if (!args || !q_host || !out_host) return CQ_ERR_BAD_ARG;
+  if (!workspace) return CQ_ERR_WORKSPACE;
+  cq_decode_args a = *args;
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  a.q = ws; a.out = ws;                           // placeholders for the argument check
+  const int ok = cq::validate(&a);
+  if (ok != CQ_OK) return ok;
+  const size_t stage = cq::host_stage_bytes(&a);
+  const size_t base = cq_decode_attn_workspace_bytes(&a);
+  const size_t base_al = cq::align_up(base, 256);
+  if (!workspace || workspace_bytes < base_al + 2 * stage || !cq::aligned16(workspace)) return CQ_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  void* q_dev = ws + base_al;
+  void* out_stage = ws + base_al + stage;
+  const size_t bytes = (size_t)a.batch * a.n_q_heads * cq::kHeadDim * 2;
+  if (cudaMemcpyAsync(q_dev, q_host, bytes, cudaMemcpyHostToDevice, st) != cudaSuccess) return CQ_ERR_LAUNCH;
+  // page-locked result buffer: the last launch stores straight into it; pageable: staged copy
+  void* out_map = cq::aligned16(out_host) ? cq::mapped_host_ptr(out_host) : nullptr;
+  a.q = q_dev;
+  a.out = out_map ? out_map : out_stage;
+  int rc = cq_decode_attn(&a, workspace, base, st);
+  if (rc != CQ_OK) return rc;
+  if (!out_map && cudaMemcpyAsync(out_host, out_stage, bytes, cudaMemcpyDeviceToHost, st) != cudaSuccess)
+    return CQ_ERR_LAUNCH;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return CQ_ERR_LAUNCH;
+  return CQ_OK;
+}

@@ -154,7 +154,7 @@ def qbmm(group_size: int, fA: torch.Tensor, qB: torch.Tensor, scales: torch.Tens
 
 
 def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
-                     calibrate=None, mask=None, out=None, t_fp=None, _stages=0, t_fp_dev=None):
+                     calibrate=None, mask=None, out=None, t_fp=None, _stages=0, t_fp_dev=None, _prepare=False):
     """One decode step over [sys | visual (quantized) | text].
 
     q [B,Hq,1,D] or [B,Hq,D]; k_pack/v_pack = (code, scale, mn) in the group format (K per
@@ -163,8 +163,14 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
     text tokens; ``t_fp`` limits how many of their rows are valid (default: all).
     ``mask``: optional additive [B, T_fp+T_vis] in key order [sys | visual | text].
     Returns o with q's shape.
+
+    A ``q`` in host memory selects the host-buffer entry point: the query is copied in, the result
+    lands in ``out`` (a host tensor; page-locked memory is written by the kernel itself) and the call
+    returns once it is there.
     """
-    _need_cuda(q, k_fp, v_fp, mask)
+    host = not q.is_cuda
+    dev = (k_fp if k_fp is not None else k_pack[0]).device
+    _need_cuda(*(() if host else (q,)), k_fp, v_fp, mask, *(k_pack or ()), *(v_pack or ()))
     shape = q.shape
     B, Hq, D = shape[0], shape[1], shape[-1]
     q2 = q.reshape(B, Hq, D).contiguous()
@@ -174,7 +180,8 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
     a.bits, a.group_size, a.dtype = bits, group_size, _dtype_enum(q)
     a.calibrate = int(bits <= 2 if calibrate is None else calibrate)
     a.reserved = _stages      # profiling aid, see the header; 0 = the whole step
-    a.q = q2.data_ptr()
+    if not host:
+        a.q = q2.data_ptr()
     keep = [q2]
     if k_pack is not None and k_pack[0].numel() > 0:
         kc, ks, kmn = (t.contiguous() for t in k_pack)
@@ -210,26 +217,66 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
         keep.append(mask)
         a.mask, a.mask_stride_b = mask.data_ptr(), mask.stride(0)
     if out is None:
-        out = torch.empty((B, Hq, D), dtype=q.dtype, device=q.device)
-    a.out = out.data_ptr()
+        out = torch.empty((B, Hq, D), dtype=q.dtype, pin_memory=True) if host else \
+            torch.empty((B, Hq, D), dtype=q.dtype, device=dev)
+    if host:
+        if out.is_cuda or not out.is_contiguous() or out.dtype != q.dtype or out.numel() != B * Hq * D:
+            raise ValueError("with q in host memory, out must be a contiguous host tensor of q's size and dtype")
+    else:
+        a.out = out.data_ptr()
     ref = ctypes.byref(a)
     aligned = all((ptr or 0) % 16 == 0 for ptr in (a.q, a.k_code, a.k_scale, a.k_mn, a.v_code, a.v_scale, a.v_mn,
                                                    a.k_fp, a.v_fp))      # decides which kernels serve the call
     key = (B, Hq, Hkv, D, a.t_vis, a.t_fp, bits, group_size, a.dtype, a.mask is not None, a.t_fp_dev is not None,
-           a.k_code is not None, aligned)
+           a.k_code is not None, aligned, host)
     nbytes = _decode_ws_bytes.get(key)
     if nbytes is None:
         if len(_decode_ws_bytes) > 4096:      # a long generation adds one entry per text-cache length
             _decode_ws_bytes.clear()
-        nbytes = _decode_ws_bytes[key] = lib().cq_decode_attn_workspace_bytes(ref)
-    handle = torch.cuda.current_stream(q.device).cuda_stream      # looked up once per call
+        size_fn = lib().cq_decode_attn_host_workspace_bytes if host else lib().cq_decode_attn_workspace_bytes
+        nbytes = _decode_ws_bytes[key] = size_fn(ref)
+    handle = torch.cuda.current_stream(dev).cuda_stream      # looked up once per call
+    if host:
+        ws = _workspace(max(nbytes, 256), dev, handle)
+        fn, ws_ptr, ws_n, st = lib().cq_decode_attn_host, _ptr(ws), ws.numel() if nbytes else 0, ctypes.c_void_p(handle)
+        if _prepare:
+            n_el = B * Hq * D
+
+            def run(q_host, out_host):
+                if q_host.is_cuda or out_host.is_cuda or q_host.dtype != q.dtype or out_host.dtype != q.dtype or \
+                        q_host.numel() != n_el or out_host.numel() != n_el or \
+                        not (q_host.is_contiguous() and out_host.is_contiguous()):
+                    raise ValueError("prepared decode step: q_host/out_host must be contiguous host tensors of the "
+                                     "prepared size and dtype")
+                with _OnDevice(dev):
+                    rc = fn(ref, q_host.data_ptr(), out_host.data_ptr(), ws_ptr, ws_n, st)
+                if rc:
+                    check(rc, "cq_decode_attn_host")
+                return out_host
+            run._keep = (a, keep, ws)      # the argument block holds raw pointers into these
+            return run
+        with _OnDevice(dev):
+            rc = fn(ref, ctypes.c_void_p(q2.data_ptr()), ctypes.c_void_p(out.data_ptr()), ws_ptr, ws_n, st)
+        check(rc, "cq_decode_attn_host")
+        return out.reshape(shape)
     if nbytes == 0:
         check(lib().cq_decode_attn(ref, None, 0, ctypes.c_void_p(handle)), "cq_decode_attn")
-    ws = _workspace(nbytes, q.device, handle)
-    with _OnDevice(q.device):
+    ws = _workspace(nbytes, dev, handle)
+    with _OnDevice(dev):
         rc = lib().cq_decode_attn(ref, _ptr(ws), ws.numel(), ctypes.c_void_p(handle))
     check(rc, "cq_decode_attn")
     return out.reshape(shape)
+
+
+def prepare_host_decode(q_host, k_pack, v_pack, k_fp, v_fp, t_sys, bits, **kw):
+    """Decode step prepared once for a serving loop that keeps the cache fixed between calls and holds
+    the query and the result in host memory: returns ``step(q_host, out_host) -> out_host``, one C call
+    (``cq_decode_attn_host``) per step on the stream that was current here.  ``q_host`` gives shape and
+    dtype; arguments as for :func:`decode_attention`.  The cache tensors' addresses
+    are baked in: the caller keeps them alive and in place (their contents may change)."""
+    if q_host.is_cuda:
+        raise ValueError("prepare_host_decode wants the query in host memory")
+    return decode_attention(q_host, k_pack, v_pack, k_fp, v_fp, t_sys, bits, _prepare=True, **kw)
 
 
 def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out=None) -> torch.Tensor:

@@ -163,6 +163,18 @@ int cq_decode_attn(const cq_decode_args* args, void* workspace, size_t workspace
                    void* stream);
 
 /*
+ * The same step for a caller whose query and result live in HOST memory (the serving loop of
+ * patch_internvl.py:556-592 samples the next token on the host): `args->q` and `args->out` are
+ * ignored, q_host [B,Hq,D] is copied into the workspace, the last launch stores the result
+ * straight into out_host when that buffer is page-locked (cudaHostAlloc / cudaHostRegister; a
+ * staged copy otherwise), and the call returns after the stream has drained, i.e. with out_host
+ * valid.  The one entry point of this library that synchronises.
+ */
+size_t cq_decode_attn_host_workspace_bytes(const cq_decode_args* args);
+int cq_decode_attn_host(const cq_decode_args* args, const void* q_host, void* out_host,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Dense causal prefill attention over unquantized K/V with GQA head sharing.
  * Replaces the flash_attn calls of the reference prefill: patch_internvl.py:464-468
  * (self._flash_attention_forward in 1024-query chunks against the growing prefix) and :606-609

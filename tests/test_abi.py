@@ -26,7 +26,8 @@ def handle():
 def test_header_declares_entry_points():
     syms = _declared_symbols()
     for must in ("cq_pack_last_dim", "cq_pack_k_per_channel", "cq_qbmm", "cq_decode_attn",
-                 "cq_decode_attn_workspace_bytes", "cq_version", "cq_status_string"):
+                 "cq_decode_attn_workspace_bytes", "cq_decode_attn_host", "cq_decode_attn_host_workspace_bytes",
+                 "cq_version", "cq_status_string"):
         assert must in syms
 
 
@@ -78,3 +79,7 @@ def test_cpu_tensors_are_rejected():
     from calibquant_b200 import ops
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         ops.pack_last_dim(torch.zeros(1, 1, 1, 32, dtype=torch.float16), 32, 1)
+    # a host query is a legal input of the decode step (host-buffer entry point), a host cache is not
+    z = torch.zeros(1, 4, 8, 128, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        ops.decode_attention(z[:, :, :1], None, None, z[:, :1], z[:, :1], 0, 1)

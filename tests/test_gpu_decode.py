@@ -179,6 +179,40 @@ def test_edge_segments(ops):
     assert rel_l2(out.cpu(), ref) <= TOL_ATTN
 
 
+@pytest.mark.parametrize("t_vis", [96, 512])
+@pytest.mark.parametrize("pinned", [True, False])
+def test_host_buffer_entry_point(ops, t_vis, pinned):
+    """Query and result in host memory (page-locked: the kernel writes the result itself; pageable:
+    staged copy): bit-equal to the device-buffer call, valid on return, oracle tolerance."""
+    bits, sys_len, t_txt = 1, generator.SYS_LEN, 11
+    k, v, q = generator.make_kvq(2, 8, 2, sys_len + t_vis + t_txt, seed=77)
+    k_sys, k_vis, k_txt = generator.split_spans(k, t_vis, sys_len)
+    v_sys, v_vis, v_txt = generator.split_spans(v, t_vis, sys_len)
+    k_pack = gf.quantize_and_pack_last_dim(k_vis.transpose(2, 3).contiguous(), 32, bits)
+    v_pack = gf.quantize_and_pack_last_dim(v_vis.contiguous(), 32, bits)
+    ref = gf.decode_attention(q, k_pack, v_pack, k_sys, k_txt, v_sys, v_txt, bits)
+    k_fp, v_fp = torch.cat([k_sys, k_txt], 2).cuda(), torch.cat([v_sys, v_txt], 2).cuda()
+    kp, vp = _cuda(k_pack), _cuda(v_pack)
+    dev_out = ops.decode_attention(q.cuda(), kp, vp, k_fp, v_fp, sys_len, bits).cpu()
+    q_host = q.pin_memory() if pinned else q.clone()
+    out = torch.full((2, 8, 128), float("nan"), dtype=torch.float16)
+    out = out.pin_memory() if pinned else out
+    got = ops.decode_attention(q_host, kp, vp, k_fp, v_fp, sys_len, bits, out=out)   # no synchronize: valid on return
+    assert got.data_ptr() == out.data_ptr() and not got.is_cuda
+    assert torch.equal(got.view(torch.int16), dev_out.view(torch.int16))
+    assert rel_l2(got, ref) <= TOL_ATTN
+    got2 = ops.decode_attention(q_host, kp, vp, k_fp, v_fp, sys_len, bits)            # result buffer made by the call
+    assert torch.equal(got2.view(torch.int16), dev_out.view(torch.int16))
+    # the same step prepared once: one C call per step
+    step = ops.prepare_host_decode(q_host, kp, vp, k_fp, v_fp, sys_len, bits)
+    out.fill_(float("nan"))
+    assert step(q_host, out) is out
+    assert torch.equal(out.view(torch.int16).reshape(-1), dev_out.view(torch.int16).reshape(-1))
+    with pytest.raises(ValueError):
+        step(q_host[:1], out)
+    assert ops.device_status() == 0
+
+
 @pytest.mark.parametrize("bits", [1, 2, 4])
 def test_qbmm_both_orientations(ops, bits):
     k, v, q = generator.make_kvq(2, 8, 2, 384, seed=20 + bits)
