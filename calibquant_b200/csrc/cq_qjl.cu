@@ -7,9 +7,12 @@
 //     score = sqrt(pi/2)/s * |k_in| * sum_p sgn_p * (qS - q_out S)_p  +  sqrt(pi/2)/s_o * |k_out| * sum_{p<s_o} sgn'_p * (q_out S)_p
 // with q_out = q restricted to the group's outlier channels and |k_in| = sqrt(|k|^2 - |k_out|^2).
 //
-// Both kernels are CUDA-core kernels: one CTA per (group, chunk of 32 tokens); thread = (token, block
-// of 32 projections).  The sign sums run over "bit set" terms only: sum_p sgn_p x_p = 2 sum_{bit_p} x_p - sum_p x_p.
+// quant_kernel and score_kernel are CUDA-core kernels: one CTA per (group, chunk of 32 tokens); thread =
+// (token, block of 32 projections); the sign sums run over "bit set" terms only:
+// sum_p sgn_p x_p = 2 sum_{bit_p} x_p - sum_p x_p.  Sketch dims that are multiples of 128 take
+// score_mma_kernel instead: the sign sums on the warp MMA, several groups per CTA.
 #include "cq_common.cuh"
+#include "cq_ptx.cuh"
 
 namespace cq {
 namespace qjl {
@@ -144,12 +147,15 @@ score_kernel(const uint8_t* __restrict__ key_quant, const uint8_t* __restrict__ 
     }
   }
   __syncthreads();
-  if (tid < 2 * R) {                                        // totals: 2R threads, serial over p (sketch <= 256)
-    const int which = tid / R, r = tid % R;
-    float t = 0.f;
+  // totals per head over the projections: (which, head) pairs dealt over the warps, lanes stride p
+  for (int pr = warp; pr < 2 * R; pr += WARPS) {
+    const int which = pr / R, r = pr % R;
     const int lim = which == 0 ? sketch : o_sketch;
-    for (int p = 0; p < lim; ++p) t += which == 0 ? qin_s[p][r] : qout_s[p][r];
-    tot_s[which][r] = t;
+    float t = 0.f;
+    for (int p = lane; p < lim; p += 32) t += which == 0 ? qin_s[p][r] : qout_s[p][r];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) tot_s[which][r] = t;
   }
   // set-bit sums of this warp's 32 projections for token `lane`
   float s_in[R], s_out[R];
@@ -193,10 +199,181 @@ score_kernel(const uint8_t* __restrict__ key_quant, const uint8_t* __restrict__ 
   }
 }
 
+// The same estimate on the warp MMA (sketch dims multiples of 128).
+// One CTA walks GPC consecutive groups of one (batch, KV head); per group and chunk of 32 tokens:
+//   1. thread = projection p: the query-side terms x_p = (q S - q_out S)_p and (q_out S)_p per head, stored as
+//      fp16 pairs hi = fp16(x), lo = fp16(x - hi) in B-fragment order (the fp32 accumulator then holds the
+//      fp32-rounded sum).  With at most four query heads per KV head hi and lo share the eight MMA columns,
+//      otherwise two MMAs per step.
+//   2. eight warp tasks = (16-token tile) x (inlier | outlier sketch) x (half of the projections):
+//      A = the signs of 16 tokens x 16 projections as +-2^-24 (fp16 subnormal with the sign bit from the
+//      packed bit), so the MMA sums  sgn_p x_p  directly.
+//   3. thread = (token, head): norms, scale, store.
+// The B fragments and the partial sums are double-buffered: two CTA barriers per group; the sketch words
+// of the next group and the norms of this one are fetched before step 1.
+constexpr int GPC = 8;                  // groups per CTA
+constexpr int B_PITCH = 132;            // words per B-fragment column: lanes (g, c) of a fragment load hit 32 banks
+
+template <typename T, typename TP, int R>
+__global__ void __launch_bounds__(THREADS)
+score_mma_kernel(const uint8_t* __restrict__ key_quant, const uint8_t* __restrict__ key_outlier_quant,
+                 const T* __restrict__ key_norm, const T* __restrict__ key_outlier_norm,
+                 const uint8_t* __restrict__ outlier_idx, const float* __restrict__ query_sketch,
+                 const T* __restrict__ query, const TP* __restrict__ proj_score, float* __restrict__ scores,
+                 int n_groups, int G, int n_rep, int sketch, int o_sketch, int oc) {
+  constexpr int NV = R / 4;                                  // fragment arrays per sketch: hi|lo in one, or hi and lo
+  __shared__ __align__(16) float qd_s[kHeadDim][R];          // query values [channel][head]
+  __shared__ __align__(16) __half b_s[2][2][NV][8][B_PITCH * 2];           // [buffer][in|out][hi|lo][column][projection]
+  __shared__ float part_s[2][2][32][2 * R + 1];              // [buffer][projection half][token][in heads | out heads]
+  __shared__ uint8_t otl_s[GPC][kHeadDim];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, tid = threadIdx.x;
+  const int64_t kbh = blockIdx.x;
+  const int n0 = blockIdx.y * GPC, n_here = min(GPC, n_groups - n0);
+  const int tok0 = blockIdx.z * 32;
+  const int n_tok = min(32, G - tok0);
+  const int64_t qrow0 = kbh * n_rep;
+  for (int i = tid; i < R * kHeadDim; i += THREADS) {
+    const int r = i >> 7, d = i & (kHeadDim - 1);
+    qd_s[d][r] = r < n_rep ? Elem<T>::to_f(query[(qrow0 + r) * kHeadDim + d]) : 0.f;
+  }
+  for (int i = tid; i < n_here * oc; i += THREADS)
+    otl_s[i / oc][i % oc] = outlier_idx[(kbh * n_groups + n0) * oc + i] & (kHeadDim - 1);
+  // this thread's projection: the sketch of the whole query per head
+  const int p = tid;
+  float qs_reg[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) qs_reg[r] = (p < sketch && r < n_rep) ? query_sketch[(qrow0 + r) * sketch + p] : 0.f;
+  // this warp's MMA task and its sketch words
+  const int mt = warp & 1, io = (warp >> 1) & 1, kh = warp >> 2;
+  const int g = lane >> 2, c = lane & 3;
+  const int dim = io == 0 ? sketch : o_sketch;
+  const int n_ks = min(8, dim / 16 - kh * 8);                // k-steps of 16 projections in this half
+  const uint8_t* kbase = io == 0 ? key_quant : key_outlier_quant;
+  const int row_bytes = dim / 8;
+  const int t_lo = mt * 16 + g, t_hi = t_lo + 8;
+  auto load_words = [&](int gl, uint4& w_lo, uint4& w_hi) {
+    w_lo = make_uint4(0u, 0u, 0u, 0u); w_hi = make_uint4(0u, 0u, 0u, 0u);
+    if (n_ks <= 0 || gl >= n_here) return;
+    const int64_t tok = (kbh * n_groups + n0 + gl) * G + tok0;
+    if (t_lo < n_tok) w_lo = *reinterpret_cast<const uint4*>(kbase + (tok + t_lo) * row_bytes + kh * 16);
+    if (t_hi < n_tok) w_hi = *reinterpret_cast<const uint4*>(kbase + (tok + t_hi) * row_bytes + kh * 16);
+  };
+  uint4 cur_lo, cur_hi;
+  load_words(0, cur_lo, cur_hi);
+  // epilogue role: (token, head)
+  const int et = tid / R, er = tid % R;
+  const bool e_live = tid < 32 * R && et < n_tok && er < n_rep;
+  __syncthreads();
+
+  for (int gl = 0; gl < n_here; ++gl) {
+    const int buf = gl & 1;
+    const int64_t grp = kbh * n_groups + n0 + gl;
+    uint4 nxt_lo, nxt_hi;
+    load_words(gl + 1, nxt_lo, nxt_hi);
+    float norm_k = 0.f, norm_o = 0.f;
+    if (e_live) {
+      norm_k = Elem<T>::to_f(key_norm[grp * G + tok0 + et]);
+      norm_o = Elem<T>::to_f(key_outlier_norm[grp * G + tok0 + et]);
+    }
+    // ---- 1. query-side terms of projection p
+    if (p < sketch) {
+      float o[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) o[r] = 0.f;
+      for (int i = 0; i < oc; ++i) {
+        const int d = otl_s[gl][i];
+        const float pv = proj_f<TP>(proj_score[(int64_t)d * sketch + p]);
+#pragma unroll
+        for (int r4 = 0; r4 < R; r4 += 4) {
+          const float4 qv = *reinterpret_cast<const float4*>(&qd_s[d][r4]);
+          o[r4] = fmaf(qv.x, pv, o[r4]); o[r4 + 1] = fmaf(qv.y, pv, o[r4 + 1]);
+          o[r4 + 2] = fmaf(qv.z, pv, o[r4 + 2]); o[r4 + 3] = fmaf(qv.w, pv, o[r4 + 3]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          if (which == 1 && p >= o_sketch) continue;
+          const float x = which == 0 ? qs_reg[r] - o[r] : o[r];
+          const __half hi = __float2half_rn(x);
+          const __half lo = __float2half_rn(x - __half2float(hi));
+          if constexpr (R == 4) {
+            b_s[buf][which][0][r][p] = hi;
+            b_s[buf][which][0][r + 4][p] = lo;
+          } else {
+            b_s[buf][which][0][r][p] = hi;
+            b_s[buf][which][NV - 1][r][p] = lo;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    // ---- 2. sign sums on the MMA
+    {
+      float acc[NV][4];
+#pragma unroll
+      for (int v = 0; v < NV; ++v) { acc[v][0] = acc[v][1] = acc[v][2] = acc[v][3] = 0.f; }
+      if (n_ks > 0) {
+        const uint32_t wl[4] = {cur_lo.x, cur_lo.y, cur_lo.z, cur_lo.w}, wh[4] = {cur_hi.x, cur_hi.y, cur_hi.z, cur_hi.w};
+        const uint32_t* bw[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) bw[v] = reinterpret_cast<const uint32_t*>(&b_s[buf][io][v][g][0]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (j < n_ks) {
+            // inverted bits 2c, 2c+1 of the step's first byte and of its second byte give the sign bits of
+            // columns (2c, 2c+1) and (2c+8, 2c+9); the magnitude is one unit in the last place
+            const uint32_t zl = ~(wl[j >> 1] >> (16 * (j & 1) + 2 * c)) & 0x0303u;
+            const uint32_t zh = ~(wh[j >> 1] >> (16 * (j & 1) + 2 * c)) & 0x0303u;
+            const uint32_t a0 = (((zl << 15) | (zl << 30)) & 0x80008000u) | 0x00010001u;
+            const uint32_t a1 = (((zh << 15) | (zh << 30)) & 0x80008000u) | 0x00010001u;
+            const uint32_t a2 = (((zl << 7) | (zl << 22)) & 0x80008000u) | 0x00010001u;
+            const uint32_t a3 = (((zh << 7) | (zh << 22)) & 0x80008000u) | 0x00010001u;
+            const int pp = (kh * 8 + j) * 8 + c;                // pair of projections 2pp, 2pp+1
+#pragma unroll
+            for (int v = 0; v < NV; ++v) ptx::mma_f16(acc[v], a0, a1, a2, a3, bw[v][pp], bw[v][pp + 4]);
+          }
+        }
+      }
+      // acc[.][0..1] = (token g, columns 2c, 2c+1), acc[.][2..3] = (token g + 8, same columns)
+      constexpr float UNSCALE = 16777216.f;                    // the signs were +-2^-24
+      if constexpr (R == 4) {
+        // columns 0-3 hold the hi sums of heads 0-3, columns 4-7 the lo sums: lanes c and c+2 pair up
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[0][e] += __shfl_xor_sync(0xffffffffu, acc[0][e], 2);
+        if (c < 2) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            part_s[buf][kh][mt * 16 + g + 8 * (e >> 1)][io * R + 2 * c + (e & 1)] = acc[0][e] * UNSCALE;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          part_s[buf][kh][mt * 16 + g + 8 * (e >> 1)][io * R + 2 * c + (e & 1)] = (acc[0][e] + acc[NV - 1][e]) * UNSCALE;
+      }
+    }
+    __syncthreads();
+    // ---- 3. norms and scale
+    if (e_live) {
+      const float inner = part_s[buf][0][et][er] + part_s[buf][1][et][er];
+      const float outer = part_s[buf][0][et][R + er] + part_s[buf][1][et][R + er];
+      // |k_in|: the two norms are rounded separately, so the difference can dip below zero
+      const float norm_in = sqrtf(fmaxf(norm_k * norm_k - norm_o * norm_o, 0.f));
+      const float scl = 1.2533141373155001f / (float)sketch, scl_o = 1.2533141373155001f / (float)o_sketch;
+      scores[(qrow0 + er) * ((int64_t)n_groups * G) + (int64_t)(n0 + gl) * G + tok0 + et] =
+          scl * norm_in * inner + scl_o * norm_o * outer;
+    }
+    cur_lo = nxt_lo; cur_hi = nxt_hi;
+  }
+}
+
 static bool sizes_ok(int G, int sketch, int o_sketch, int oc) {
   return G > 0 && sketch > 0 && sketch <= MAX_SKETCH && sketch % 32 == 0 && o_sketch > 0 && o_sketch <= sketch &&
          o_sketch % 32 == 0 && oc >= 0 && oc <= kHeadDim;
 }
+
+static bool mma_ptrs_ok(const void* a, const void* b) { return aligned16(a) && aligned16(b); }
 
 }  // namespace qjl
 }  // namespace cq
@@ -248,11 +425,14 @@ extern "C" int cq_qjl_gqa_score(const uint8_t* key_quant, const uint8_t* key_out
   if (n_groups > 65535) return CQ_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   dim3 grid((unsigned)(batch * n_kv_heads), (unsigned)n_groups, (unsigned)((group_size + 31) / 32));
+  // sketch rows that are whole 16-byte words: the tensor-core variant, several groups per CTA
+  const bool use_mma = sketch_dim % 128 == 0 && outlier_sketch_dim % 128 == 0 && qjl::mma_ptrs_ok(key_quant, key_outlier_quant);
+  if (use_mma) grid.y = (unsigned)((n_groups + qjl::GPC - 1) / qjl::GPC);
 #define CQ_QJL_SCORE(T, TP, R)                                                                                 \
-  qjl::score_kernel<T, TP, R><<<grid, qjl::THREADS, 0, st>>>(key_quant, key_outlier_quant,                      \
+  do { (use_mma ? qjl::score_mma_kernel<T, TP, R> : qjl::score_kernel<T, TP, R>)<<<grid, qjl::THREADS, 0, st>>>(key_quant, key_outlier_quant, \
       static_cast<const T*>(key_norm), static_cast<const T*>(key_outlier_norm), outlier_indices, query_sketch,  \
       static_cast<const T*>(query), static_cast<const TP*>(proj_score), scores, n_groups, group_size, n_rep,    \
-      sketch_dim, outlier_sketch_dim, outlier_count)
+      sketch_dim, outlier_sketch_dim, outlier_count); } while (0)
 #define CQ_QJL_SCORE_R(T, TP) do { if (n_rep <= 4) CQ_QJL_SCORE(T, TP, 4); else CQ_QJL_SCORE(T, TP, 8); } while (0)
   if (dtype == CQ_DTYPE_F16) {
     if (proj_dtype == CQ_DTYPE_F32) CQ_QJL_SCORE_R(__half, float); else CQ_QJL_SCORE_R(__half, __half);
