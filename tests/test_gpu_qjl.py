@@ -64,6 +64,26 @@ def test_score_matches_oracle_on_the_same_bits(dtype, rep):
     assert rel_l2(got, ref) <= 1e-4
 
 
+@pytest.mark.parametrize("sketch_dim,outlier_dim,T,rep", [(256, 128, 352, 4), (256, 128, 352, 8), (128, 128, 288, 4),
+                                                         (96, 64, 96, 4), (224, 32, 64, 6)])
+def test_score_sketch_sizes_and_group_counts(sketch_dim, outlier_dim, T, rep):
+    """Outlier sketches shorter than the inlier one, group counts that are not a multiple of what one CTA
+    walks (tensor-core kernel: sketch dims multiples of 128), and sketch dims only the CUDA-core kernel takes."""
+    from calibquant_b200.qjl import qjl_kernel
+    from calibquant_b200.qjl.qjl_utils import QJLSketch
+    sk = QJLSketch((128, sketch_dim), outlier_dim, device=torch.device("cuda"),
+                   rng=torch.Generator(device="cuda").manual_seed(5), rot=True)
+    k, q = _data(1, 2, rep, T, torch.float16, seed=9)
+    groups, idx, knorm = oq.build_groups(k, 32, 8)
+    kq, koq, onorm = qjl_kernel.qjl_quant(groups.cuda(), idx.cuda(), sk.proj_dir_quant, outlier_dim)
+    assert kq.shape[-1] == sketch_dim // 8 and koq.shape[-1] == outlier_dim // 8
+    qs = torch.matmul(q.cuda().float(), sk.proj_dir_score)
+    got = qjl_kernel.qjl_gqa_score(kq, koq, knorm.cuda(), onorm, idx.cuda(), qs, q.cuda(), sk.proj_dir_score)
+    ref = oq.qjl_gqa_score(kq.cpu(), koq.cpu(), knorm, onorm.cpu(), idx, qs.cpu(), q, sk.proj_dir_score.cpu())
+    assert got.shape == ref.shape == (1, 2 * rep, T, 1)
+    assert rel_l2(got, ref) <= 1e-4
+
+
 def test_key_quantizer_streaming_and_estimate_quality():
     """build_sketch / update_sketch / attention_score of the sketch-backed quantizer: shapes, the fp
     residual that flushes every buffer_size keys, and an estimate that tracks q.k."""
