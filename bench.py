@@ -456,6 +456,53 @@ def run_pack(args, rank, world, device):
     }
 
 
+def run_qjl(args, rank, world, device):
+    """The QJL baseline's key path alone: sketch `batch` x 8 KV heads x `context` keys (256 + 256 sign bits per
+    key, 32 outlier channels per group of 32) once, then time the score estimate of one query per head."""
+    from calibquant_b200.qjl.qjl_utils import QJLSketch, QJLKeyQuantizer
+    B, T = args.batch, args.context
+    sk = QJLSketch((D, 256), 256, device=device, rng=torch.Generator(device=device).manual_seed(1))
+    g = torch.Generator(device=device).manual_seed(2 + rank)
+    k = torch.randn(B, HKV, T, D, generator=g, device=device).half()
+    q = torch.randn(B, HQ, 1, D, generator=g, device=device).half()
+    kq = QJLKeyQuantizer(sk, 32, 128, 32, 2)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kq.build_sketch(k)                                # first call also loads the kernels
+    kq = QJLKeyQuantizer(sk, 32, 128, 32, 2)
+    ev0.record()
+    kq.build_sketch(k)
+    ev1.record()
+    torch.cuda.synchronize()
+    build_ms = ev0.elapsed_time(ev1)
+    for _ in range(max(args.warmup, 1)):
+        kq.attention_score(q)
+    torch.cuda.synchronize()
+    ev0.record()
+    for _ in range(args.steps):
+        kq.attention_score(q)
+    ev1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=device, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms = float(t.item())
+    n_keys = B * HKV * (T - T % 128)
+    nbytes = n_keys * (32 + 32 + 2 + 2)               # sign bits of both sketches + the two norms
+    peak, which = measured_peak()
+    gbps = world * nbytes / ms / 1e6
+    return {
+        "metric": "qjl_score_GBps", "value": round(gbps, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"QJL score estimate, batch {B}/GPU, {HQ}q/{HKV}kv heads, {T} sketched keys, "
+                               "256+256-bit sketches, 32 outlier channels per group of 32 keys",
+                   "build_sketch_ms": round(build_ms, 3)},
+        "roofline": {"bound": "hbm", "kernel": "score_mma_kernel", "achieved": round(gbps / world, 1), "peak": peak,
+                     "unit": "GB/s", "frac": round(gbps / world / peak, 4), "peak_source": which, "traffic": None},
+        "gpu_launches": args.steps,
+    }
+
+
 def run_prefill(args, rank, world, device):
     """Dense causal prefill attention alone (tcgen05 kernel) on the 7B prefill shape: batch rows per
     GPU x 3392 tokens, 32 query / 8 KV heads, bf16."""
@@ -500,7 +547,7 @@ def run_prefill(args, rank, world, device):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="attn", choices=["attn", "model7b", "model20b", "pack", "prefill"])
+    ap.add_argument("--workload", default="attn", choices=["attn", "model7b", "model20b", "pack", "prefill", "qjl"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
@@ -532,7 +579,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=device)
     try:
-        runner = {"attn": run_ours, "pack": run_pack, "prefill": run_prefill}.get(args.workload, run_model)
+        runner = {"attn": run_ours, "pack": run_pack, "prefill": run_prefill, "qjl": run_qjl}.get(args.workload, run_model)
         line = runner(args, rank, world, device)
         if rank == 0:
             print(json.dumps(line), flush=True)
