@@ -210,6 +210,20 @@ def test_host_buffer_entry_point(ops, t_vis, pinned):
     assert torch.equal(out.view(torch.int16).reshape(-1), dev_out.view(torch.int16).reshape(-1))
     with pytest.raises(ValueError):
         step(q_host[:1], out)
+    # on a stream of its own, same buffers with new contents every step
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step_s = ops.prepare_host_decode(q_host, kp, vp, k_fp, v_fp, sys_len, bits)
+        for i in range(5):
+            q_i = (q * (1.0 + 0.25 * i)).half()
+            q_host.copy_(q_i)
+            out.fill_(float("nan"))
+            step_s(q_host, out)
+            want = ops.decode_attention(q_i.cuda(), kp, vp, k_fp, v_fp, sys_len, bits).cpu()
+            assert torch.equal(out.view(torch.int16).reshape(-1), want.view(torch.int16).reshape(-1)), i
+        assert ops.device_status() == 0
+    torch.cuda.current_stream().wait_stream(side)
     assert ops.device_status() == 0
 
 
