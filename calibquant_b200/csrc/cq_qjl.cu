@@ -9,8 +9,9 @@
 //
 // quant_kernel and score_kernel are CUDA-core kernels: one CTA per (group, chunk of 32 tokens); thread =
 // (token, block of 32 projections); the sign sums run over "bit set" terms only:
-// sum_p sgn_p x_p = 2 sum_{bit_p} x_p - sum_p x_p.  Sketch dims that are multiples of 128 take
-// score_mma_kernel instead: the sign sums on the warp MMA, several groups per CTA.
+// sum_p sgn_p x_p = 2 sum_{bit_p} x_p - sum_p x_p.  They serve unaligned buffers and sketch dims that are
+// not multiples of 128; otherwise quant_mma_kernel (persistent, projection resident in shared memory) and
+// score_mma_kernel (sign sums on the warp MMA, several groups per CTA) run.
 #include "cq_common.cuh"
 #include "cq_ptx.cuh"
 
@@ -368,6 +369,174 @@ score_mma_kernel(const uint8_t* __restrict__ key_quant, const uint8_t* __restric
   }
 }
 
+// ---- the quantizer on the warp MMA ---------------------------------------------------------------
+// The sums of a chunk are a [32 tokens x 128] x [128 x sketch] product.  A persistent CTA (one per SM)
+// keeps the whole projection in shared memory as fp16 hi/lo pairs in B-fragment order (hi = fp16(x),
+// lo = fp16(x - hi): the fp32 accumulator then holds the fp32-rounded sum) and walks (group, chunk)
+// items: keys staged as fp16 rows, A fragments by ldmatrix, once as they are (all channels) and once
+// ANDed with the group's outlier mask; inlier sum = all - outlier.  Warp = 16 projections.
+constexpr int QW = 16, QTHREADS = QW * 32;
+constexpr int KPITCH = 136;                           // halves per staged key row: ldmatrix rows hit distinct banks
+constexpr int Q_PF_BYTES = 2 * 32 * 8 * 32 * 8;       // [hi|lo][n-tile][k-step][lane] x (b0, b1)
+constexpr int Q_KEY_BYTES = 2 * 32 * KPITCH * 2;      // two staged chunks
+constexpr int Q_SMEM = Q_PF_BYTES + Q_KEY_BYTES + 32 + 128;
+
+template <typename T> struct Half8;
+template <> struct Half8<__half> {
+  static __device__ __forceinline__ uint4 conv(uint4 v) { return v; }
+};
+template <> struct Half8<__nv_bfloat16> {
+  static __device__ __forceinline__ uint32_t two(uint32_t w) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+    const __half2 h = __floats2half2_rn(f.x, f.y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ uint4 conv(uint4 v) { return make_uint4(two(v.x), two(v.y), two(v.z), two(v.w)); }
+};
+
+template <typename T, typename TP>
+__global__ void __launch_bounds__(QTHREADS, 1)
+quant_mma_kernel(const T* __restrict__ keys, const uint8_t* __restrict__ outlier_idx, const TP* __restrict__ proj,
+                 uint8_t* __restrict__ key_quant, uint8_t* __restrict__ key_outlier_quant,
+                 T* __restrict__ outlier_norm, int64_t n_groups, int G, int sketch, int o_sketch, int oc) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  uint2* pf = reinterpret_cast<uint2*>(smem);
+  __half* key_s = reinterpret_cast<__half*>(smem + Q_PF_BYTES);
+  uint32_t* mask_s = reinterpret_cast<uint32_t*>(smem + Q_PF_BYTES + Q_KEY_BYTES);     // [2][4]
+  uint8_t* byte_s = smem + Q_PF_BYTES + Q_KEY_BYTES + 32;                               // [128], warp 0 only
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, c = lane & 3;
+  // projection fragments: b0 = (P[p][d], P[p][d+1]), b1 = (P[p][d+8], P[p][d+9]) with p = 8 nt + g, d = 16 ks + 2c
+  for (int i = tid; i < 32 * 8 * 32; i += QTHREADS) {
+    const int nt = i >> 8, ks = (i >> 5) & 7, l = i & 31;
+    const int p = 8 * nt + (l >> 2), d = 16 * ks + 2 * (l & 3);
+    uint32_t hi[2] = {0u, 0u}, lo[2] = {0u, 0u};
+    if (p < sketch) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float x0 = proj_f<TP>(proj[(int64_t)p * kHeadDim + d + 8 * j]);
+        const float x1 = proj_f<TP>(proj[(int64_t)p * kHeadDim + d + 8 * j + 1]);
+        const __half h0 = __float2half_rn(x0), h1 = __float2half_rn(x1);
+        const __half l0 = __float2half_rn(x0 - __half2float(h0)), l1 = __float2half_rn(x1 - __half2float(h1));
+        hi[j] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+        lo[j] = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+      }
+    }
+    pf[((0 * 32 + nt) * 8 + ks) * 32 + l] = make_uint2(hi[0], hi[1]);
+    pf[((1 * 32 + nt) * 8 + ks) * 32 + l] = make_uint2(lo[0], lo[1]);
+  }
+  const int n_chunks = (G + 31) / 32;
+  const int64_t n_items = n_groups * n_chunks;
+  // loader role: token row lt, eight channels from 8 * seg
+  const int lt = tid >> 4, seg = tid & 15;
+  auto fetch = [&](int64_t item) -> uint4 {
+    const int64_t grp = item / n_chunks;
+    const int tok0 = (int)(item % n_chunks) * 32;
+    if (tok0 + lt >= G) return make_uint4(0u, 0u, 0u, 0u);
+    return *reinterpret_cast<const uint4*>(keys + ((grp * G + tok0 + lt) * kHeadDim + 8 * seg));
+  };
+  int64_t item = blockIdx.x;
+  uint4 cur = make_uint4(0u, 0u, 0u, 0u);
+  if (item < n_items) cur = fetch(item);
+  const int p0 = 16 * warp;
+  for (int it = 0; item < n_items; item += gridDim.x, ++it) {
+    const int buf = it & 1;
+    const int64_t grp = item / n_chunks;
+    const int tok0 = (int)(item % n_chunks) * 32;
+    const int n_tok = min(32, G - tok0);
+    *reinterpret_cast<uint4*>(key_s + (buf * 32 + lt) * KPITCH + 8 * seg) = Half8<T>::conv(cur);
+    if (warp == 0) {                                  // the group's outlier channels as a 128-bit mask
+      reinterpret_cast<uint32_t*>(byte_s)[lane] = 0u;
+      __syncwarp();
+      for (int i = lane; i < oc; i += 32) byte_s[outlier_idx[grp * oc + i] & (kHeadDim - 1)] = 1;
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t w = __ballot_sync(0xffffffffu, byte_s[32 * j + lane] != 0);
+        if (lane == 0) mask_s[buf * 4 + j] = w;
+      }
+      __syncwarp();
+    }
+    __syncthreads();
+    uint4 nxt = make_uint4(0u, 0u, 0u, 0u);
+    if (item + gridDim.x < n_items) nxt = fetch(item + gridDim.x);
+    const uint32_t mw[4] = {mask_s[buf * 4], mask_s[buf * 4 + 1], mask_s[buf * 4 + 2], mask_s[buf * 4 + 3]};
+    {  // norm of the outlier part, from the values as loaded
+      const uint32_t mbyte = (mw[seg >> 2] >> (8 * (seg & 3))) & 0xffu;
+      const T* e = reinterpret_cast<const T*>(&cur);
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float x = Elem<T>::to_f(e[j]);
+        if ((mbyte >> j) & 1u) ss = fmaf(x, x, ss);
+      }
+#pragma unroll
+      for (int o = 8; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (seg == 0 && lt < n_tok) outlier_norm[grp * G + tok0 + lt] = Elem<T>::from_f(sqrtf(ss));
+    }
+    if (p0 < sketch) {
+      float acc_t[2][2][4], acc_o[2][2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { acc_t[mt][nt][e] = 0.f; acc_o[mt][nt][e] = 0.f; }
+      const uint32_t a_base = ptx::smem_u32(key_s + (buf * 32 + (lane & 7) + 8 * ((lane >> 3) & 1)) * KPITCH + 8 * (lane >> 4));
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        // channels 16ks + (2c, 2c+1) and + (2c+8, 2c+9): all-ones halves where the channel is an outlier
+        const uint32_t m = mw[ks >> 1] >> (16 * (ks & 1) + 2 * c);
+        const uint32_t m_lo = ((m & 1u) ? 0x0000ffffu : 0u) | ((m & 2u) ? 0xffff0000u : 0u);
+        const uint32_t m_hi = ((m & 0x100u) ? 0x0000ffffu : 0u) | ((m & 0x200u) ? 0xffff0000u : 0u);
+        uint2 b[2][2];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int v = 0; v < 2; ++v) b[nt][v] = pf[((v * 32 + 2 * warp + nt) * 8 + ks) * 32 + lane];
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          uint32_t a0, a1, a2, a3;
+          ptx::ldmatrix_x4(a_base + (uint32_t)((mt * 16 * KPITCH + ks * 16) * 2), a0, a1, a2, a3);
+          const uint32_t o0 = a0 & m_lo, o1 = a1 & m_lo, o2 = a2 & m_hi, o3 = a3 & m_hi;
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+              ptx::mma_f16(acc_t[mt][nt], a0, a1, a2, a3, b[nt][v].x, b[nt][v].y);
+              ptx::mma_f16(acc_o[mt][nt], o0, o1, o2, o3, b[nt][v].x, b[nt][v].y);
+            }
+        }
+      }
+      // acc[..][0..1] = (token g, projections 2c, 2c+1 of the n-tile), acc[..][2..3] = (token g + 8, same)
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t bits_in = 0u, bits_out = 0u;
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float out = acc_o[mt][nt][2 * hh + e], in = acc_t[mt][nt][2 * hh + e] - out;
+              bits_in |= (in > 0.f ? 1u : 0u) << (8 * nt + 2 * c + e);
+              bits_out |= (out > 0.f ? 1u : 0u) << (8 * nt + 2 * c + e);
+            }
+          bits_in |= __shfl_xor_sync(0xffffffffu, bits_in, 1); bits_in |= __shfl_xor_sync(0xffffffffu, bits_in, 2);
+          bits_out |= __shfl_xor_sync(0xffffffffu, bits_out, 1); bits_out |= __shfl_xor_sync(0xffffffffu, bits_out, 2);
+          const int t = 16 * mt + g + 8 * hh;
+          if (c == 0 && t < n_tok) {
+            const int64_t tok = grp * G + tok0 + t;
+            *reinterpret_cast<uint16_t*>(key_quant + tok * (sketch / 8) + 2 * warp) = (uint16_t)bits_in;
+            if (p0 < o_sketch)
+              *reinterpret_cast<uint16_t*>(key_outlier_quant + tok * (o_sketch / 8) + 2 * warp) = (uint16_t)bits_out;
+          }
+        }
+    }
+    cur = nxt;
+  }
+}
+
 static bool sizes_ok(int G, int sketch, int o_sketch, int oc) {
   return G > 0 && sketch > 0 && sketch <= MAX_SKETCH && sketch % 32 == 0 && o_sketch > 0 && o_sketch <= sketch &&
          o_sketch % 32 == 0 && oc >= 0 && oc <= kHeadDim;
@@ -393,6 +562,32 @@ extern "C" int cq_qjl_quant(const void* keys, const uint8_t* outlier_indices, co
     return CQ_ERR_UNSUPPORTED;
   if (n_groups_total > 0x7fffffff) return CQ_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // aligned rows: the persistent tensor-core kernel, one CTA per SM
+  if (aligned16(keys) && (reinterpret_cast<uintptr_t>(key_quant) & 1u) == 0 &&
+      (reinterpret_cast<uintptr_t>(key_outlier_quant) & 1u) == 0) {
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+      return CQ_ERR_LAUNCH;
+    const int64_t items = n_groups_total * ((group_size + 31) / 32);
+    const unsigned grid_mma = (unsigned)(items < sms ? items : sms);
+#define CQ_QJL_QUANT_MMA(T, TP)                                                                                 \
+    do {                                                                                                        \
+      auto kern = qjl::quant_mma_kernel<T, TP>;                                                                 \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, qjl::Q_SMEM) != cudaSuccess)  \
+        return CQ_ERR_LAUNCH;                                                                                   \
+      kern<<<grid_mma, qjl::QTHREADS, qjl::Q_SMEM, st>>>(static_cast<const T*>(keys), outlier_indices,          \
+          static_cast<const TP*>(proj), key_quant, key_outlier_quant, static_cast<T*>(outlier_norms),           \
+          n_groups_total, group_size, sketch_dim, outlier_sketch_dim, outlier_count);                           \
+    } while (0)
+    if (dtype == CQ_DTYPE_F16) {
+      if (proj_dtype == CQ_DTYPE_F32) CQ_QJL_QUANT_MMA(__half, float); else CQ_QJL_QUANT_MMA(__half, __half);
+    } else {
+      if (proj_dtype == CQ_DTYPE_F32) CQ_QJL_QUANT_MMA(__nv_bfloat16, float); else CQ_QJL_QUANT_MMA(__nv_bfloat16, __nv_bfloat16);
+    }
+#undef CQ_QJL_QUANT_MMA
+    return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
+  }
   dim3 grid((unsigned)n_groups_total, (unsigned)((group_size + 31) / 32));
 #define CQ_QJL_QUANT(T, TP)                                                                                   \
   qjl::quant_kernel<T, TP><<<grid, qjl::THREADS, 0, st>>>(static_cast<const T*>(keys), outlier_indices,       \
