@@ -28,7 +28,9 @@ os.environ["TORCHDYNAMO_DISABLE"] = "1"
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set REFERENCE_ROOT to the reference checkout (see the docstring)")
 sys.path.insert(0, REF)
 
 import torch  # noqa: E402
