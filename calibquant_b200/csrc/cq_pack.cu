@@ -7,6 +7,7 @@
 //   code  = rint_half_even(clamp(y, 0, 2^b - 1))
 // word w of a row holds elements w*fpi .. w*fpi+fpi-1, element i in bits [i*b, (i+1)*b).
 #include "cq_common.cuh"
+#include <cstdlib>
 
 namespace cq {
 
@@ -168,6 +169,74 @@ __device__ __forceinline__ void pack_chunk(const uint4& raw, int64_t chunk, bool
   }
 }
 
+// ---- the same rows with a whole group of 32 per thread (four 128-bit loads): no exchange between lanes,
+// ---- the group's scale and break points computed once instead of once per lane of a quad.  A warp's four
+// ---- load instructions together cover 2 KB of consecutive bytes.
+template <typename T, int BITS>
+__global__ void __launch_bounds__(256)
+pack_last_dim_group_kernel(const T* __restrict__ data, int64_t n_groups, int32_t* __restrict__ code,
+                           T* __restrict__ scale_out, T* __restrict__ mn_out) {
+  using T2 = typename Pk<T>::T2;
+  constexpr int LEVELS = (1 << BITS) - 1;
+  const int64_t grp = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (grp >= n_groups) return;
+  uint4 raw[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) raw[k] = __ldg(reinterpret_cast<const uint4*>(data) + grp * 4 + k);
+  const T2* xv = reinterpret_cast<const T2*>(raw);              // 16 pairs
+  T2 mn2 = xv[0], mx2 = xv[0];
+#pragma unroll
+  for (int i = 1; i < 16; ++i) { mn2 = __hmin2(mn2, xv[i]); mx2 = __hmax2(mx2, xv[i]); }
+  const float2 fmn = Elem<T>::to_f2(mn2), fmx = Elem<T>::to_f2(mx2);
+  const float mn = fminf(fmn.x, fmn.y), mx = fmaxf(fmx.x, fmx.y);
+  float scale;
+  group_params<T>(mn, mx, LEVELS, scale);
+  unsigned words[BITS];
+#pragma unroll
+  for (int w = 0; w < BITS; ++w) words[w] = 0u;
+  if (mx != mn) {
+    if (BITS <= 2) {
+      T2 thr[3];
+#pragma unroll
+      for (int k = 0; k < 3; ++k) thr[k] = Pk<T>::floor2(break_point<T>(k) * scale);
+      const T2 mnb = Pk<T>::bcast(mn);
+      if (BITS == 1) {
+        // all-ones compare masks: pair i of a half gives bit 2i (low element) and bit 17+2i (high element)
+        unsigned r0 = 0, r1 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          r0 |= __hgt2_mask(__hsub2(xv[i], mnb), thr[0]) & (0x00020001u << (2 * i));
+          r1 |= __hgt2_mask(__hsub2(xv[8 + i], mnb), thr[0]) & (0x00020001u << (2 * i));
+        }
+        words[0] = ((r0 | (r0 >> 16)) & 0xffffu) | ((r1 | (r1 >> 16)) << 16);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const unsigned c = codes2<T, BITS>(__hsub2(xv[i], mnb), thr);   // x - mn: one rounding, as the reference
+          words[(2 * i * BITS) >> 5] |= ((c & 0xffffu) | (c >> (16 - BITS))) << ((2 * i * BITS) & 31);
+        }
+      }
+    } else {
+      const float rcp = __frcp_rn(scale);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float2 f = Elem<T>::to_f2(xv[i]);
+        words[(2 * i * BITS) >> 5] |= quantize_one<T>(f.x, mn, scale, rcp, LEVELS) << ((2 * i * BITS) & 31);
+        words[((2 * i + 1) * BITS) >> 5] |= quantize_one<T>(f.y, mn, scale, rcp, LEVELS) << (((2 * i + 1) * BITS) & 31);
+      }
+    }
+  }
+  if (BITS == 4) {
+    *reinterpret_cast<uint4*>(code + grp * 4) = make_uint4(words[0], words[1 % BITS], words[2 % BITS], words[3 % BITS]);
+  } else if (BITS == 2) {
+    *reinterpret_cast<uint2*>(code + grp * 2) = make_uint2(words[0], words[1 % BITS]);
+  } else {
+    code[grp] = (int32_t)words[0];
+  }
+  scale_out[grp] = Elem<T>::from_f(scale);
+  mn_out[grp] = Elem<T>::from_f(mn);
+}
+
 // ---- K per channel, transpose fused.  A CTA walks a span of 512 tokens (256 at 4 bits) of one
 // ---- (batch, head) in sub-tiles of 128 tokens x 128 channels: coalesced 128-bit loads into shared
 // ---- memory, then each thread reduces 32 tokens of two adjacent channels (one packed 16-bit pair
@@ -308,6 +377,19 @@ int launch_pack_last_dim(const void* data, int64_t rows, int64_t L, int bits, in
   const T* d = static_cast<const T*>(data);
   T* s = static_cast<T*>(scale);
   T* m = static_cast<T*>(mn);
+  // aligned outputs: one group per thread; otherwise the lane-quad kernel with scalar stores
+  static const bool quad = []() { const char* e = getenv("CQ_PACK_QUAD"); return e && e[0] == '1'; }();
+  if (!quad && aligned16(code) && aligned16(data)) {
+    const int64_t n_groups = n_chunks / 4;
+    const int64_t gblocks = (n_groups + 255) / 256;
+    if (gblocks > 0x7fffffffLL) return CQ_ERR_UNSUPPORTED;
+    switch (bits) {
+      case 1: pack_last_dim_group_kernel<T, 1><<<(unsigned)gblocks, 256, 0, st>>>(d, n_groups, code, s, m); break;
+      case 2: pack_last_dim_group_kernel<T, 2><<<(unsigned)gblocks, 256, 0, st>>>(d, n_groups, code, s, m); break;
+      default: pack_last_dim_group_kernel<T, 4><<<(unsigned)gblocks, 256, 0, st>>>(d, n_groups, code, s, m); break;
+    }
+    return check_launch();
+  }
   switch (bits) {
     case 1: pack_last_dim_kernel<T, 1><<<(unsigned)blocks, 256, 0, st>>>(d, n_chunks, code, s, m); break;
     case 2: pack_last_dim_kernel<T, 2><<<(unsigned)blocks, 256, 0, st>>>(d, n_chunks, code, s, m); break;
