@@ -321,11 +321,23 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
 #pragma unroll
       for (int kk = 0; kk < 3; ++kk)
         thr[kk] = Pk<T>::pair(break_point<T>(kk) * scale[0], break_point<T>(kk) * scale[1]);
+      if (BITS == 1) {
+        // all-ones compare masks: token t of a half gives bit t (first channel) and bit 16 + t (second channel)
+        unsigned ra = 0, rb = 0;
 #pragma unroll
-      for (int t = 0; t < 32; ++t) {
-        const unsigned c = codes2<T, BITS>(__hsub2(xv[t], mn2), thr);
-        words[0][t / FPI] |= (c & 0xffffu) << ((t % FPI) * BITS);
-        words[1][t / FPI] |= (c >> 16) << ((t % FPI) * BITS);
+        for (int t = 0; t < 16; ++t) {
+          ra |= __hgt2_mask(__hsub2(xv[t], mn2), thr[0]) & (0x00010001u << t);
+          rb |= __hgt2_mask(__hsub2(xv[16 + t], mn2), thr[0]) & (0x00010001u << t);
+        }
+        words[0][0] = (ra & 0xffffu) | (rb << 16);
+        words[1][0] = (ra >> 16) | (rb & 0xffff0000u);
+      } else {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          const unsigned c = codes2<T, BITS>(__hsub2(xv[t], mn2), thr);
+          words[0][t / FPI] |= (c & 0xffffu) << ((t % FPI) * BITS);
+          words[1][t / FPI] |= (c >> 16) << ((t % FPI) * BITS);
+        }
       }
     } else {
       const float mnf[2] = {fmn.x, fmn.y};
