@@ -243,6 +243,15 @@ pack_last_dim_group_kernel(const T* __restrict__ data, int64_t n_groups, int32_t
 // ---- per token).  Words, scales and minima of the span collect in shared memory and leave with
 // ---- the lanes running along each channel's row, so a store instruction covers whole sectors.
 constexpr int KT_TOKENS = 128;
+// 16-byte asynchronous copy into shared memory; !valid writes zeros and reads nothing
+__device__ __forceinline__ void pack_cp_async16(void* dst, const void* src, bool valid) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void pack_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void pack_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __host__ __device__ constexpr int kt_span(int bits) { return bits == 4 ? 256 : 512; }
 
 template <typename T, int BITS>
@@ -260,9 +269,10 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
   constexpr int WPR = SPAN_GROUPS * BITS;    // code words per channel row per span
   constexpr int CP = WPR + 1, SP = SPAN_GROUPS + 2;    // padded row pitches: rows on different banks
   extern __shared__ __align__(16) unsigned char pack_smem[];
-  T (*tile)[kHeadDim] = reinterpret_cast<T (*)[kHeadDim]>(pack_smem);
-  unsigned (*code_s)[CP] = reinterpret_cast<unsigned (*)[CP]>(pack_smem + KT_TOKENS * kHeadDim * sizeof(T));
-  T (*scale_s)[SP] = reinterpret_cast<T (*)[SP]>(pack_smem + KT_TOKENS * kHeadDim * sizeof(T) + kHeadDim * CP * 4);
+  constexpr int TILES_BYTES = 2 * KT_TOKENS * kHeadDim * sizeof(T);      // two sub-tiles: one lands while one is read
+  T (*tiles)[kHeadDim] = reinterpret_cast<T (*)[kHeadDim]>(pack_smem);  // [2 * KT_TOKENS][kHeadDim]
+  unsigned (*code_s)[CP] = reinterpret_cast<unsigned (*)[CP]>(pack_smem + TILES_BYTES);
+  T (*scale_s)[SP] = reinterpret_cast<T (*)[SP]>(pack_smem + TILES_BYTES + kHeadDim * CP * 4);
   T (*mn_s)[SP] = scale_s + kHeadDim;
 
   const int bh = blockIdx.y;
@@ -273,27 +283,32 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
   const int gq = threadIdx.x / 64;        // group (of 32 tokens) inside the sub-tile
   const int cp = threadIdx.x % 64;        // channel pair
 
-  for (int sub = 0; sub * KT_TOKENS < span_tok; ++sub) {
+  // 2048 16-byte pieces per sub-tile, 8 per thread, copied asynchronously: sub-tile s+1 lands while s is read
+  auto issue = [&](int sub) {
     const int64_t t0 = span0 + sub * KT_TOKENS;
     const int n_tok = min(KT_TOKENS, span_tok - sub * KT_TOKENS);
-    __syncthreads();                       // previous sub-tile fully consumed
-    {
-      // 2048 16-byte pieces, 8 per thread: all loads are issued before the first store
-      uint4 v[8];
+    T (*dst)[kHeadDim] = tiles + (sub & 1) * KT_TOKENS;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int i = threadIdx.x + j * 256;
-        const int row = i / (kHeadDim / 8), col = i % (kHeadDim / 8);
-        v[j] = make_uint4(0, 0, 0, 0);
-        if (row < n_tok) v[j] = __ldg(reinterpret_cast<const uint4*>(src + (t0 + row) * stride_t) + col);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int i = threadIdx.x + j * 256;
-        *reinterpret_cast<uint4*>(&tile[i / (kHeadDim / 8)][(i % (kHeadDim / 8)) * 8]) = v[j];
-      }
+    for (int j = 0; j < 8; ++j) {
+      const int i = threadIdx.x + j * 256;
+      const int row = i / (kHeadDim / 8), col = i % (kHeadDim / 8);
+      const bool valid = row < n_tok;
+      pack_cp_async16(&dst[row][col * 8], src + (t0 + (valid ? row : 0)) * stride_t + col * 8, valid);
     }
-    __syncthreads();
+    pack_cp_async_commit();
+  };
+  issue(0);
+  for (int sub = 0; sub * KT_TOKENS < span_tok; ++sub) {
+    const int n_tok = min(KT_TOKENS, span_tok - sub * KT_TOKENS);
+    T (*tile)[kHeadDim] = tiles + (sub & 1) * KT_TOKENS;
+    __syncthreads();                       // sub-tile sub-1 fully consumed: its buffer may be refilled
+    if ((sub + 1) * KT_TOKENS < span_tok) {
+      issue(sub + 1);
+      pack_cp_async_wait<1>();
+    } else {
+      pack_cp_async_wait<0>();
+    }
+    __syncthreads();                       // every thread's pieces of this sub-tile have landed
     if (gq * 32 >= n_tok) continue;
 
     T2 xv[32];
@@ -416,7 +431,7 @@ int launch_pack_k(const void* k, int batch, int heads, int64_t T_len, int64_t sb
   const int span = kt_span(bits);
   dim3 grid((unsigned)((T_len + span - 1) / span), (unsigned)(batch * heads));
   const int wpr = span / 32 * bits;
-  const size_t smem = (size_t)KT_TOKENS * kHeadDim * 2 + (size_t)kHeadDim * (wpr + 1) * 4 +
+  const size_t smem = 2 * (size_t)KT_TOKENS * kHeadDim * 2 + (size_t)kHeadDim * (wpr + 1) * 4 +
                       2 * (size_t)kHeadDim * (span / 32 + 2) * 2;
   cudaError_t e;
   switch (bits) {
