@@ -50,6 +50,115 @@ minmax_kernel(const T* __restrict__ x, int heads, int t_len, int64_t sb, int64_t
   }
 }
 
+// ---- the same reduction spread over the whole GPU ---------------------------------------------------
+// One (batch, head) per CTA leaves most SMs idle when there are few heads, so the token axis is cut into
+// slices: CTA = (slice, batch x head), thread = 8 channels (one 128-bit load) of every 16th token, packed
+// 16-bit min/max (exact).  The slices meet in the output arrays themselves, which hold the running
+// minimum (scale array) and maximum (zero-point array) as order-preserving 16-bit keys updated by
+// compare-and-swap; a last launch turns them into scale and zero point with the arithmetic of minmax_kernel.
+__device__ __forceinline__ unsigned short key16(unsigned short b) {
+  return (b & 0x8000u) ? (unsigned short)~b : (unsigned short)(b | 0x8000u);
+}
+__device__ __forceinline__ unsigned short unkey16(unsigned short k) {
+  return (k & 0x8000u) ? (unsigned short)(k & 0x7fffu) : (unsigned short)~k;
+}
+__global__ void minmax_init_kernel(unsigned short* __restrict__ mn_key, unsigned short* __restrict__ mx_key, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) { mn_key[i] = 0xffffu; mx_key[i] = 0u; }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+minmax_slice_kernel(const T* __restrict__ x, int heads, int t_len, int64_t sb, int64_t st, int64_t sh,
+                    unsigned short* __restrict__ mn_key, unsigned short* __restrict__ mx_key) {
+  using T2 = typename Elem<T>::T2;
+  __shared__ uint32_t red_s[8][16][8];
+  const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
+  const int tid = threadIdx.x, col = tid & 15, tl = tid >> 4;
+  const int per = (t_len + gridDim.x - 1) / gridDim.x;
+  const int t_begin = blockIdx.x * per, t_end = min(t_len, t_begin + per);
+  if (t_begin >= t_end) return;                       // uniform over the CTA
+  const T* base = x + b * sb + h * sh + col * 8;
+  // every thread starts from a row of its slice, so no neutral element is needed
+  uint4 first = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)min(t_begin + tl, t_end - 1) * st));
+  T2 mn[4], mx[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) mn[i] = mx[i] = reinterpret_cast<const T2*>(&first)[i];
+  for (int t = t_begin + tl; t < t_end; t += 64) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int tt = t + 16 * u < t_end ? t + 16 * u : t;
+      v[u] = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)tt * st));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        mn[i] = __hmin2(mn[i], reinterpret_cast<const T2*>(&v[u])[i]);
+        mx[i] = __hmax2(mx[i], reinterpret_cast<const T2*>(&v[u])[i]);
+      }
+  }
+  // the two token lanes of a warp, then the eight warps
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t a = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<uint32_t*>(&mn[i]), 16);
+    uint32_t c = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<uint32_t*>(&mx[i]), 16);
+    mn[i] = __hmin2(mn[i], *reinterpret_cast<T2*>(&a));
+    mx[i] = __hmax2(mx[i], *reinterpret_cast<T2*>(&c));
+  }
+  if ((tid & 31) < 16) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      red_s[tid >> 5][col][i] = *reinterpret_cast<uint32_t*>(&mn[i]);
+      red_s[tid >> 5][col][4 + i] = *reinterpret_cast<uint32_t*>(&mx[i]);
+    }
+  }
+  __syncthreads();
+  if (tid < kHeadDim) {
+    const int c8 = tid >> 3, e = tid & 7;
+    float lo = INFINITY, hi = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const float2 a = Elem<T>::to_f2(*reinterpret_cast<const T2*>(&red_s[w][c8][e >> 1]));
+      const float2 c = Elem<T>::to_f2(*reinterpret_cast<const T2*>(&red_s[w][c8][4 + (e >> 1)]));
+      lo = fminf(lo, (e & 1) ? a.y : a.x);
+      hi = fmaxf(hi, (e & 1) ? c.y : c.x);
+    }
+    const T lo_t = Elem<T>::from_f(lo), hi_t = Elem<T>::from_f(hi);      // exact: they are elements of x
+    const unsigned short klo = key16(*reinterpret_cast<const unsigned short*>(&lo_t));
+    const unsigned short khi = key16(*reinterpret_cast<const unsigned short*>(&hi_t));
+    unsigned short* pmn = mn_key + (int64_t)bh * kHeadDim + tid;
+    unsigned short* pmx = mx_key + (int64_t)bh * kHeadDim + tid;
+    unsigned short old = *pmn;
+    while (klo < old) {
+      const unsigned short seen = atomicCAS(pmn, old, klo);
+      if (seen == old) break;
+      old = seen;
+    }
+    old = *pmx;
+    while (khi > old) {
+      const unsigned short seen = atomicCAS(pmx, old, khi);
+      if (seen == old) break;
+      old = seen;
+    }
+  }
+}
+
+template <typename T>
+__global__ void minmax_finish_kernel(T* __restrict__ scale, T* __restrict__ zp, int n, float clip, int levels) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned short bl = unkey16(reinterpret_cast<const unsigned short*>(scale)[i]);
+  const unsigned short bh = unkey16(reinterpret_cast<const unsigned short*>(zp)[i]);
+  const float mn = Elem<T>::to_f(*reinterpret_cast<const T*>(&bl)), mx = Elem<T>::to_f(*reinterpret_cast<const T*>(&bh));
+  const float x_min = rnd<T>(mn * clip), x_max = rnd<T>(mx * clip);
+  const float s = rnd<T>(__fdiv_rn(rnd<T>(x_max - x_min), (float)levels));
+  const float z = rnd<T>(__fdiv_rn(-x_min, s));
+  scale[i] = Elem<T>::from_f(s);
+  zp[i] = Elem<T>::from_f(z);
+}
+
 // ---- quantize (+ optional dequantize) and/or encode ---------------------------------------------
 // thread = 8 consecutive channels of one token.  xq_out (optional, layout of x, contiguous
 // [B,T,H,D]) receives the codes as numbers of the data dtype (post_scale) or the dequantized values;
@@ -515,6 +624,29 @@ extern "C" int cq_calib_minmax(const void* x, int batch, int t_len, int heads, i
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int levels = (1 << bits) - 1;
   const unsigned grid = (unsigned)(batch * heads);
+  // rows of eight channels that can be read as 16-byte words: the sliced reduction over the whole GPU
+  if (aligned16(x) && strides[0] % 8 == 0 && strides[1] % 8 == 0 && strides[2] % 8 == 0 && t_len >= 256 &&
+      grid <= 65535u && (int64_t)grid * kHeadDim <= 0x7fffffff) {
+    const int n = (int)(grid * kHeadDim);
+    int slices = (int)((4 * 148 + grid - 1) / grid);
+    slices = max(1, min(slices, (t_len + 63) / 64));
+    unsigned short* kmn = static_cast<unsigned short*>(scale);
+    unsigned short* kmx = static_cast<unsigned short*>(zero_point);
+    calib::minmax_init_kernel<<<(n + 255) / 256, 256, 0, st>>>(kmn, kmx, n);
+    const dim3 g2((unsigned)slices, grid);
+    if (dtype == CQ_DTYPE_F16) {
+      calib::minmax_slice_kernel<__half><<<g2, 256, 0, st>>>(static_cast<const __half*>(x), heads, t_len, strides[0],
+                                                            strides[1], strides[2], kmn, kmx);
+      calib::minmax_finish_kernel<__half><<<(n + 255) / 256, 256, 0, st>>>(static_cast<__half*>(scale),
+                                                                          static_cast<__half*>(zero_point), n, clip, levels);
+    } else {
+      calib::minmax_slice_kernel<__nv_bfloat16><<<g2, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), heads, t_len,
+                                                                   strides[0], strides[1], strides[2], kmn, kmx);
+      calib::minmax_finish_kernel<__nv_bfloat16><<<(n + 255) / 256, 256, 0, st>>>(
+          static_cast<__nv_bfloat16*>(scale), static_cast<__nv_bfloat16*>(zero_point), n, clip, levels);
+    }
+    return check_launch();
+  }
   if (dtype == CQ_DTYPE_F16)
     calib::minmax_kernel<__half><<<grid, kHeadDim * calib::MM_SLICES, 0, st>>>(
         static_cast<const __half*>(x), heads, t_len, strides[0], strides[1], strides[2], clip, levels,

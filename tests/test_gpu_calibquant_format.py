@@ -81,6 +81,25 @@ def test_quant_dequant_paths(cq, bits, dtype):
         cq.quant(x.cuda(), bits)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("T", [1000, 4096 + 40])
+def test_quant_long_spans(cq, dtype, T):
+    """Spans long enough for the sliced min/max reduction (token axis cut over many CTAs, ragged last
+    slice), contiguous and as the [B,T,H,D] view of a [B,H,T,D] cache: bit-exact scale, zero point, codes
+    and bytes."""
+    k, _, _ = generator.make_kvq(2, 8, 2, T, seed=T % 97, dtype=dtype)
+    x = k.transpose(1, 2).contiguous()                     # [B,T,H,D]
+    ref = cqf.quant(x, 1, per_channel=True, scale=0.5, post_scale=True)
+    for src in (x.cuda(), k.cuda().transpose(1, 2)):
+        got = cq.quant(src, 1, per_channel=True, scale=0.5, post_scale=True)
+        for a, b in zip(got, ref):
+            assert bits_equal(a, b)
+    enc, s, z = cq.quant_encode(x.cuda(), 2, scale=1)
+    ref2 = cqf.quant(x, 2, per_channel=True, scale=1, post_scale=True)
+    assert bits_equal(s, ref2[1]) and bits_equal(z, ref2[2])
+    assert torch.equal(enc.cpu(), cqf.encode(ref2[0].transpose(1, 2).to(torch.int64), 2, 4))
+
+
 @pytest.mark.parametrize("bits", [1, 2, 4])
 def test_decode_composition(cq, bits):
     """Full decode step in the uint8 format against the oracle of patch_internvl.py:356-436."""
