@@ -17,6 +17,10 @@
 namespace cq {
 namespace calib {
 
+template <typename T> struct Pk2;
+template <> struct Pk2<__half> { static __device__ __forceinline__ __half2 magic() { return __float2half2_rn(1024.f); } };
+template <> struct Pk2<__nv_bfloat16> { static __device__ __forceinline__ __nv_bfloat162 magic() { return __float2bfloat162_rn(128.f); } };
+
 constexpr int MM_SLICES = 8;   // token slices per (b,h) in the min/max kernel
 
 // ---- per-channel min/max over tokens -> scale, zero point -----------------------------------------
@@ -211,6 +215,147 @@ quantize_kernel(const T* __restrict__ x, int heads, int t_len, int64_t sb, int64
 #pragma unroll
       for (int j = 0; j < 4; ++j) v |= ((codes[2 * j] << 4) | codes[2 * j + 1]) << (8 * j);
       *reinterpret_cast<uint32_t*>(dst) = v;
+    }
+  }
+}
+
+// ---- 1- and 2-bit codes without a division per element ----------------------------------------------
+// With scale > 0 the reference's code  rint(clamp(rnd(rnd(x / s) + z)))  is a non-decreasing step function
+// of x, and s, z are fixed per channel for the whole span.  So per channel and level k there is a largest
+// number theta_k of the data type whose code is <= k, found once per CTA by bisection over the ordered
+// 16-bit patterns with the reference arithmetic itself (IEEE division), and  code(x) = sum_k [x > theta_k]
+// holds exactly for every x.  CTA = (token range, batch x head); thread = the same 8 channels of every
+// 16th token, thresholds in registers; channels with a degenerate scale make the CTA fall back to the
+// per-element arithmetic.
+constexpr int QT_TOKENS = 2048;        // tokens per CTA
+
+template <typename T>
+__device__ __forceinline__ float ref_code(float x, float s, float z, int levels) {
+  const float y = rnd<T>(rnd<T>(__fdiv_rn(x, s)) + z);
+  return rintf(fminf(fmaxf(y, 0.f), (float)levels));
+}
+template <typename T> struct Finite16;
+template <> struct Finite16<__half> { static constexpr unsigned short MAXPOS = 0x7bffu; };
+template <> struct Finite16<__nv_bfloat16> { static constexpr unsigned short MAXPOS = 0x7f7fu; };
+
+template <typename T, int BITS>
+__global__ void __launch_bounds__(256)
+quantize_thr_kernel(const T* __restrict__ x, int heads, int t_len, int64_t sb, int64_t st, int64_t sh,
+                    const T* __restrict__ scale, const T* __restrict__ zp,
+                    T* __restrict__ xq_out, uint8_t* __restrict__ enc_out) {
+  using T2 = typename Elem<T>::T2;
+  constexpr int LEVELS = (1 << BITS) - 1;
+  __shared__ __align__(16) T thr_s[LEVELS][kHeadDim];
+  const int bh = blockIdx.y, b = bh / heads, h = bh % heads;
+  const int tid = threadIdx.x;
+  const int t0 = blockIdx.x * QT_TOKENS, n_tok = min(QT_TOKENS, t_len - t0);
+  int bad = 0;
+  if (tid < kHeadDim) {
+    const float s = Elem<T>::to_f(scale[(int64_t)bh * kHeadDim + tid]);
+    const float z = Elem<T>::to_f(zp[(int64_t)bh * kHeadDim + tid]);
+    bad = !(s > 0.f) || isinf(s) || isnan(z) || isinf(z);
+    if (!bad) {
+      const unsigned short k_min = key16((unsigned short)(Finite16<T>::MAXPOS | 0x8000u)), k_max = key16(Finite16<T>::MAXPOS);
+#pragma unroll
+      for (int k = 0; k < LEVELS; ++k) {
+        unsigned lo = k_min, hi = k_max;
+        unsigned short theta;
+        const unsigned short b_lo = unkey16((unsigned short)lo), b_hi = unkey16((unsigned short)hi);
+        if (ref_code<T>(Elem<T>::to_f(*reinterpret_cast<const T*>(&b_lo)), s, z, LEVELS) > (float)k) {
+          theta = 0xfc00u;                              // every finite number exceeds level k: -inf
+          if (sizeof(T) == 2 && Finite16<T>::MAXPOS == 0x7f7fu) theta = 0xff80u;
+        } else if (ref_code<T>(Elem<T>::to_f(*reinterpret_cast<const T*>(&b_hi)), s, z, LEVELS) <= (float)k) {
+          theta = b_hi;                                 // only +inf exceeds the largest finite number
+        } else {
+          while (hi - lo > 1) {
+            const unsigned mid = (lo + hi) >> 1;
+            const unsigned short bm = unkey16((unsigned short)mid);
+            if (ref_code<T>(Elem<T>::to_f(*reinterpret_cast<const T*>(&bm)), s, z, LEVELS) <= (float)k) lo = mid; else hi = mid;
+          }
+          theta = unkey16((unsigned short)lo);
+        }
+        thr_s[k][tid] = *reinterpret_cast<const T*>(&theta);
+      }
+    }
+  }
+  const int any_bad = __syncthreads_or(bad);
+  const int c8 = tid & 15, tl = tid >> 4;
+  const T* src = x + b * sb + h * sh + c8 * 8;
+  if (any_bad) {                                       // uniform: the reference arithmetic per element
+    const uint4 sraw = *reinterpret_cast<const uint4*>(scale + (int64_t)bh * kHeadDim + c8 * 8);
+    const uint4 zraw = *reinterpret_cast<const uint4*>(zp + (int64_t)bh * kHeadDim + c8 * 8);
+    const T* sv = reinterpret_cast<const T*>(&sraw);
+    const T* zv = reinterpret_cast<const T*>(&zraw);
+    for (int t = tl; t < n_tok; t += 16) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)(t0 + t) * st));
+      const T* xv = reinterpret_cast<const T*>(&raw);
+      unsigned codes[8];
+      uint4 outw;
+      T* ov = reinterpret_cast<T*>(&outw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float y = ref_code<T>(Elem<T>::to_f(xv[i]), Elem<T>::to_f(sv[i]), Elem<T>::to_f(zv[i]), LEVELS);
+        codes[i] = (unsigned)y;
+        ov[i] = Elem<T>::from_f(y);
+      }
+      const int64_t chunk = (((int64_t)b * t_len + t0 + t) * heads + h) * 16 + c8;
+      if (xq_out) reinterpret_cast<uint4*>(xq_out)[chunk] = outw;
+      if (enc_out) {
+        uint8_t* dst = enc_out + (((int64_t)bh * t_len + t0 + t) * (kHeadDim * BITS / 8)) + c8 * BITS;
+        if (BITS == 1) {
+          unsigned v = 0;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v |= codes[i] << (7 - i);
+          dst[0] = (uint8_t)v;
+        } else {
+          const unsigned v0 = (codes[0] << 6) | (codes[1] << 4) | (codes[2] << 2) | codes[3];
+          const unsigned v1 = (codes[4] << 6) | (codes[5] << 4) | (codes[6] << 2) | codes[7];
+          *reinterpret_cast<uint16_t*>(dst) = (uint16_t)(v0 | (v1 << 8));
+        }
+      }
+    }
+    return;
+  }
+  T2 thr[LEVELS][4];
+#pragma unroll
+  for (int k = 0; k < LEVELS; ++k) {
+    const uint4 w = *reinterpret_cast<const uint4*>(&thr_s[k][c8 * 8]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) thr[k][i] = reinterpret_cast<const T2*>(&w)[i];
+  }
+  for (int t = tl; t < n_tok; t += 16) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + (int64_t)(t0 + t) * st));
+    const T2* xv = reinterpret_cast<const T2*>(&raw);
+    T2 cnt[4];                                         // codes as numbers of the data type
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      cnt[i] = __hgt2(xv[i], thr[0][i]);
+#pragma unroll
+      for (int k = 1; k < LEVELS; ++k) cnt[i] = __hadd2(cnt[i], __hgt2(xv[i], thr[k][i]));
+    }
+    if (xq_out) {
+      const int64_t chunk = (((int64_t)b * t_len + t0 + t) * heads + h) * 16 + c8;
+      reinterpret_cast<uint4*>(xq_out)[chunk] = *reinterpret_cast<const uint4*>(cnt);
+    }
+    if (enc_out) {
+      uint8_t* dst = enc_out + (((int64_t)bh * t_len + t0 + t) * (kHeadDim * BITS / 8)) + c8 * BITS;
+      if (BITS == 1) {
+        // MSB-first: channel i at bit 7 - i; pair p = channels (2p, 2p+1) -> bits 7-2p (low half), 22-2p (high half)
+        unsigned r = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          r |= __hgt2_mask(xv[i], thr[0][i]) & ((0x80u >> (2 * i)) | (0x400000u >> (2 * i)));
+        dst[0] = (uint8_t)((r | (r >> 16)) & 0xffu);
+      } else {
+        unsigned c[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const T2 m = __hadd2(cnt[i], Pk2<T>::magic());          // 0..3 in the low mantissa bits
+          const unsigned u = *reinterpret_cast<const unsigned*>(&m) & 0x00030003u;
+          c[i] = ((u & 0xffffu) << 2) | (u >> 16);                // (code 2i, code 2i+1) as four bits
+        }
+        *reinterpret_cast<uint16_t*>(dst) = (uint16_t)(((c[0] << 4) | c[1]) | (((c[2] << 4) | c[3]) << 8));
+      }
     }
   }
 }
@@ -668,6 +813,13 @@ static int launch_quantize(const void* x, int batch, int t_len, int heads, const
   const T* sp = static_cast<const T*>(scale);
   const T* zpp = static_cast<const T*>(zp);
   T* xo = static_cast<T*>(xq);
+  // codes only (no dequantized output) at 1 or 2 bits: per-channel thresholds instead of divisions
+  if (!dequantize && bits <= 2 && (int64_t)batch * heads <= 65535) {
+    const dim3 g2((unsigned)((t_len + calib::QT_TOKENS - 1) / calib::QT_TOKENS), (unsigned)(batch * heads));
+    if (bits == 1) calib::quantize_thr_kernel<T, 1><<<g2, 256, 0, st>>>(xp, heads, t_len, s[0], s[1], s[2], sp, zpp, xo, enc);
+    else calib::quantize_thr_kernel<T, 2><<<g2, 256, 0, st>>>(xp, heads, t_len, s[0], s[1], s[2], sp, zpp, xo, enc);
+    return check_launch();
+  }
   switch (bits) {
     case 1: calib::quantize_kernel<T, 1><<<grid, 256, 0, st>>>(xp, heads, t_len, s[0], s[1], s[2], sp, zpp, dequantize, xo, enc, n_chunks); break;
     case 2: calib::quantize_kernel<T, 2><<<grid, 256, 0, st>>>(xp, heads, t_len, s[0], s[1], s[2], sp, zpp, dequantize, xo, enc, n_chunks); break;

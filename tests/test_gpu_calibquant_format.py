@@ -100,6 +100,24 @@ def test_quant_long_spans(cq, dtype, T):
     assert torch.equal(enc.cpu(), cqf.encode(ref2[0].transpose(1, 2).to(torch.int64), 2, 4))
 
 
+@pytest.mark.parametrize("bits", [1, 2])
+def test_quant_with_a_constant_channel(cq, bits):
+    """A channel that is constant over the span has scale 0 (the reference divides by it): the kernel
+    then computes that (batch, head) with the per-element arithmetic; every other channel stays bit-exact."""
+    k, _, _ = generator.make_kvq(1, 8, 2, 300, seed=5)
+    x = k.transpose(1, 2).contiguous()                     # [B,T,H,D]
+    x[:, :, 1, 7] = 0.25
+    ref = cqf.quant(x, bits, per_channel=True, scale=1, post_scale=True)
+    got = cq.quant(x.cuda(), bits, per_channel=True, scale=1, post_scale=True)
+    keep = torch.ones(128, dtype=torch.bool)
+    keep[7] = False
+    for a, b in zip(got, ref):
+        a, b = a.cpu(), b
+        assert bits_equal(a[:, :, 0], b[:, :, 0])
+        assert bits_equal(a[:, :, 1][..., keep], b[:, :, 1][..., keep])
+    assert float(got[1][0, 0, 1, 7]) == 0.0                # the degenerate scale itself
+
+
 @pytest.mark.parametrize("bits", [1, 2, 4])
 def test_decode_composition(cq, bits):
     """Full decode step in the uint8 format against the oracle of patch_internvl.py:356-436."""
