@@ -77,6 +77,20 @@ __device__ __forceinline__ unsigned codes2(typename Pk<T>::T2 d2, const typename
   return *reinterpret_cast<unsigned*>(&c) & 0x00030003u;
 }
 
+// 4-bit codes of two elements (low half -> bits [0,4), high half -> bits [16,20)) with the reference's rounding
+// points kept: d = x - mn rounded once to the data type, the quotient rounded to the data type, clamp and
+// round-half-even there; only the quotient itself runs in fp32 (see quotient()).
+template <typename T>
+__device__ __forceinline__ unsigned codes4_pair(typename Pk<T>::T2 x2, typename Pk<T>::T2 mn2, float s0, float r0,
+                                                float s1, float r1) {
+  using T2 = typename Pk<T>::T2;
+  const float2 d = Elem<T>::to_f2(__hsub2(x2, mn2));
+  T2 y = Pk<T>::pair_rn(quotient(d.x, s0, r0), quotient(d.y, s1, r1));
+  y = __hmin2(__hmax2(y, Pk<T>::bcast(0.f)), Pk<T>::bcast(15.f));   // the maximum drops the NaN of inf * 0 to 0
+  y = __hadd2(h2rint(y), Pk<T>::magic());                          // 0..15 in the low mantissa bits
+  return *reinterpret_cast<unsigned*>(&y) & 0x000f000fu;
+}
+
 // ---- rows of L contiguous elements; a thread owns 8 consecutive elements (one 128-bit load),
 // ---- four neighbouring lanes own one group of 32.
 constexpr int PACK_CHUNKS_PER_THREAD = 4;   // independent 128-bit loads in flight per thread
@@ -218,11 +232,11 @@ pack_last_dim_group_kernel(const T* __restrict__ data, int64_t n_groups, int32_t
       }
     } else {
       const float rcp = __frcp_rn(scale);
+      const T2 mnb = Pk<T>::bcast(mn);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float2 f = Elem<T>::to_f2(xv[i]);
-        words[(2 * i * BITS) >> 5] |= quantize_one<T>(f.x, mn, scale, rcp, LEVELS) << ((2 * i * BITS) & 31);
-        words[((2 * i + 1) * BITS) >> 5] |= quantize_one<T>(f.y, mn, scale, rcp, LEVELS) << (((2 * i + 1) * BITS) & 31);
+        const unsigned c = codes4_pair<T>(xv[i], mnb, scale, rcp, scale, rcp);
+        words[(2 * i * BITS) >> 5] |= ((c & 0xfu) | (c >> 12)) << ((2 * i * BITS) & 31);
       }
     }
   }
@@ -355,13 +369,12 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
         }
       }
     } else {
-      const float mnf[2] = {fmn.x, fmn.y};
       const float rcp[2] = {__frcp_rn(scale[0]), __frcp_rn(scale[1])};
 #pragma unroll
       for (int t = 0; t < 32; ++t) {
-        const float2 f = Elem<T>::to_f2(xv[t]);
-        words[0][t / FPI] |= quantize_one<T>(f.x, mnf[0], scale[0], rcp[0], LEVELS) << ((t % FPI) * BITS);
-        words[1][t / FPI] |= quantize_one<T>(f.y, mnf[1], scale[1], rcp[1], LEVELS) << ((t % FPI) * BITS);
+        const unsigned c = codes4_pair<T>(xv[t], mn2, scale[0], rcp[0], scale[1], rcp[1]);
+        words[0][t / FPI] |= (c & 0xffffu) << ((t % FPI) * BITS);
+        words[1][t / FPI] |= (c >> 16) << ((t % FPI) * BITS);
       }
     }
     const int gs = sub * (KT_TOKENS / 32) + gq;            // group inside the span
