@@ -28,6 +28,18 @@ __device__ __forceinline__ float quotient(float d, float scale, float rcp) {
   return fmaf(fmaf(-scale, q, d), rcp, q);
 }
 
+// quotient() of two elements at once on fp32 register pairs (same operations, same roundings)
+__device__ __forceinline__ void quotient_pair(float d0, float d1, float s0, float s1, float r0, float r1,
+                                              float& q0, float& q1) {
+  asm("{\n\t.reg .b64 rd, rs, rr, rq, re;\n\t"
+      "mov.b64 rd, {%2, %3};\n\tmov.b64 rs, {%4, %5};\n\tmov.b64 rr, {%6, %7};\n\t"
+      "mul.rn.f32x2 rq, rd, rr;\n\t"
+      "fma.rn.f32x2 re, rs, rq, rd;\n\t"
+      "fma.rn.f32x2 rq, re, rr, rq;\n\t"
+      "mov.b64 {%0, %1}, rq;\n\t}"
+      : "=f"(q0), "=f"(q1) : "f"(d0), "f"(d1), "f"(-s0), "f"(-s1), "f"(r0), "f"(r1));
+}
+
 template <typename T>
 __device__ __forceinline__ unsigned quantize_one(float x, float mn, float scale, float rcp, int levels) {
   float d = rnd<T>(x - mn);
@@ -80,12 +92,19 @@ __device__ __forceinline__ unsigned codes2(typename Pk<T>::T2 d2, const typename
 // 4-bit codes of two elements (low half -> bits [0,4), high half -> bits [16,20)) with the reference's rounding
 // points kept: d = x - mn rounded once to the data type, the quotient rounded to the data type, clamp and
 // round-half-even there; only the quotient itself runs in fp32 (see quotient()).
-template <typename T>
+template <typename T, bool PAIRED>
 __device__ __forceinline__ unsigned codes4_pair(typename Pk<T>::T2 x2, typename Pk<T>::T2 mn2, float s0, float r0,
                                                 float s1, float r1) {
   using T2 = typename Pk<T>::T2;
   const float2 d = Elem<T>::to_f2(__hsub2(x2, mn2));
-  T2 y = Pk<T>::pair_rn(quotient(d.x, s0, r0), quotient(d.y, s1, r1));
+  float q0, q1;
+  if (PAIRED) {          // measured: a gain where both elements share the scale, a loss where they do not
+    quotient_pair(d.x, d.y, s0, s1, r0, r1, q0, q1);
+  } else {
+    q0 = quotient(d.x, s0, r0);
+    q1 = quotient(d.y, s1, r1);
+  }
+  T2 y = Pk<T>::pair_rn(q0, q1);
   y = __hmin2(__hmax2(y, Pk<T>::bcast(0.f)), Pk<T>::bcast(15.f));   // the maximum drops the NaN of inf * 0 to 0
   y = __hadd2(h2rint(y), Pk<T>::magic());                          // 0..15 in the low mantissa bits
   return *reinterpret_cast<unsigned*>(&y) & 0x000f000fu;
@@ -235,7 +254,7 @@ pack_last_dim_group_kernel(const T* __restrict__ data, int64_t n_groups, int32_t
       const T2 mnb = Pk<T>::bcast(mn);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const unsigned c = codes4_pair<T>(xv[i], mnb, scale, rcp, scale, rcp);
+        const unsigned c = codes4_pair<T, true>(xv[i], mnb, scale, rcp, scale, rcp);
         words[(2 * i * BITS) >> 5] |= ((c & 0xfu) | (c >> 12)) << ((2 * i * BITS) & 31);
       }
     }
@@ -372,7 +391,7 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
       const float rcp[2] = {__frcp_rn(scale[0]), __frcp_rn(scale[1])};
 #pragma unroll
       for (int t = 0; t < 32; ++t) {
-        const unsigned c = codes4_pair<T>(xv[t], mn2, scale[0], rcp[0], scale[1], rcp[1]);
+        const unsigned c = codes4_pair<T, false>(xv[t], mn2, scale[0], rcp[0], scale[1], rcp[1]);
         words[0][t / FPI] |= (c & 0xffffu) << ((t % FPI) * BITS);
         words[1][t / FPI] |= (c >> 16) << ((t % FPI) * BITS);
       }
