@@ -380,20 +380,28 @@ pack_k_per_channel_kernel(const T* __restrict__ k, int heads, int64_t T_len,
         words[0][0] = (ra & 0xffffu) | (rb << 16);
         words[1][0] = (ra >> 16) | (rb & 0xffff0000u);
       } else {
+        // codes of 16/BITS tokens collect in one register (first channel in the low half, second in the high
+        // half: one multiply-add per token), then the halves go to the two channels' words
+        constexpr int TPA = 16 / BITS;
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          const unsigned c = codes2<T, BITS>(__hsub2(xv[t], mn2), thr);
-          words[0][t / FPI] |= (c & 0xffffu) << ((t % FPI) * BITS);
-          words[1][t / FPI] |= (c >> 16) << ((t % FPI) * BITS);
+        for (int t0 = 0; t0 < 32; t0 += TPA) {
+          unsigned acc = 0;
+#pragma unroll
+          for (int j = 0; j < TPA; ++j) acc += codes2<T, BITS>(__hsub2(xv[t0 + j], mn2), thr) << (j * BITS);
+          words[0][t0 / FPI] |= (acc & 0xffffu) << ((t0 % FPI) * BITS);
+          words[1][t0 / FPI] |= (acc >> 16) << ((t0 % FPI) * BITS);
         }
       }
     } else {
       const float rcp[2] = {__frcp_rn(scale[0]), __frcp_rn(scale[1])};
 #pragma unroll
-      for (int t = 0; t < 32; ++t) {
-        const unsigned c = codes4_pair<T, false>(xv[t], mn2, scale[0], rcp[0], scale[1], rcp[1]);
-        words[0][t / FPI] |= (c & 0xffffu) << ((t % FPI) * BITS);
-        words[1][t / FPI] |= (c >> 16) << ((t % FPI) * BITS);
+      for (int t0 = 0; t0 < 32; t0 += 4) {               // four tokens per register, as above
+        unsigned acc = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          acc += codes4_pair<T, false>(xv[t0 + j], mn2, scale[0], rcp[0], scale[1], rcp[1]) << (j * BITS);
+        words[0][t0 / FPI] |= (acc & 0xffffu) << ((t0 % FPI) * BITS);
+        words[1][t0 / FPI] |= (acc >> 16) << ((t0 % FPI) * BITS);
       }
     }
     const int gs = sub * (KT_TOKENS / 32) + gq;            // group inside the span
