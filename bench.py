@@ -43,8 +43,8 @@ L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (kernel, bits, context, batch) -> bytes
 NCU_TRAFFIC = {
-    ("k2_attn_v", 1, 32768, 8): 87_182_336,
-    ("k1_scores", 1, 32768, 8): 70_405_888,
+    ("k2_attn_v", 1, 32768, 8): 88_595_968,
+    ("k1_scores", 1, 32768, 8): 70_022_912,
 }
 
 
