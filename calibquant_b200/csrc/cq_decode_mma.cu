@@ -33,6 +33,7 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <mutex>
 #include <type_traits>
 
 #include "cq_common.cuh"
@@ -45,10 +46,13 @@ namespace mma {
 using namespace ptx;
 
 constexpr int THREADS = 128;
-constexpr int K1_WARPS = 4;            // warps of a score CTA; each owns 32 / K1_WARPS groups of a K tile
-constexpr int K1_THREADS = K1_WARPS * 32;
-constexpr int K1_GPW = 32 / K1_WARPS;
-constexpr int TILE_G = 32;             // 32-token groups per K tile (1024 tokens)
+#ifndef CQ_K1_TILE_G
+#define CQ_K1_TILE_G 32
+#endif
+constexpr int K1_WARPS = 4;            // computing warps of a score CTA; each owns TILE_G / K1_WARPS groups of a K tile
+constexpr int K1_THREADS = (K1_WARPS + 1) * 32;   // + the TMA producer warp
+constexpr int TILE_G = CQ_K1_TILE_G;   // 32-token groups per K tile
+constexpr int K1_GPW = TILE_G / K1_WARPS;
 // attn.V work items: CT tokens per item, streamed as tiles of VT tokens.  Two shapes are compiled: the
 // large one for long contexts, the small one when the large one would leave CTAs without work.
 constexpr int CT_LARGE = 1024, VT_LARGE = 512, CT_SMALL = 256, VT_SMALL = 256;
@@ -56,8 +60,12 @@ constexpr int K2_RESIDENT = 444;       // attn.V CTAs resident on the device (3 
 constexpr uint32_t WAIT_TRIES = 1u << 22;
 constexpr float LOG2E = 1.4426950408889634f;
 
-__host__ __device__ constexpr int k1_stages(int bits) { return bits == 1 ? 3 : 2; }
-__host__ __device__ constexpr int k1_stage_bytes(int bits) { return bits * 16384 + 2 * 8192; }
+__host__ __device__ constexpr int k1_stage_bytes(int bits) { return TILE_G * (bits * 512 + 512); }
+__host__ __device__ constexpr int k1_stages(int bits) { return 3 * k1_stage_bytes(bits) <= 100 * 1024 ? 3 : 2; }
+__host__ __device__ constexpr int k1_min_ctas(int bits) {
+  return (220 * 1024) / (k1_stages(bits) * k1_stage_bytes(bits) + 2048) > 4 ? 4 : (220 * 1024) / (k1_stages(bits) * k1_stage_bytes(bits) + 2048);
+}
+__host__ __device__ constexpr int k1_code_row_bytes(int bits) { return TILE_G * bits * 4 < 128 ? TILE_G * bits * 4 : 128; }
 __host__ __device__ constexpr int k2_stages(int bits) { return bits == 4 ? 2 : 3; }
 __host__ __device__ constexpr int k2_stage_bytes(int bits, int vt) { return vt * 16 * bits + 2 * vt * 8; }
 
@@ -114,8 +122,14 @@ template <> struct D16<__half> {
   static __device__ __forceinline__ T2 pair2(__half a, __half b) { return __halves2half2(a, b); }
   static __device__ __forceinline__ float2 to_f2(T2 v) { return __half22float2(v); }
   static __device__ __forceinline__ float big() { return 65504.f; }
-  // rnd(x * c): fp16(c) is within 2^-12 of c, a packed multiply is accurate enough
-  static __device__ __forceinline__ T2 scale2(T2 x, float c) { return __hmul2(x, __float2half2_rn(c)); }
+  // rnd(x / sqrt(128)) as the reference's division gives it: 1/sqrt(128) as two fp16 terms (the
+  // second one carries the 1e-4 relative error of the first), product formed by one FMA, one rounding.
+  // A plain multiply by fp16(1/sqrt(128)) lands on the neighbouring fp16 value for one logit in ten.
+  static __device__ __forceinline__ T2 inv_sqrt_d(T2 x) {
+    const __half2 c_hi = __float2half2_rn(0.08837890625f);                       // fp16(1/sqrt(128))
+    const __half2 c_lo = __float2half2_rn(0.08838834764831845f - 0.08837890625f);
+    return __hfma2(x, c_hi, __hmul2(x, c_lo));
+  }
 };
 template <> struct D16<__nv_bfloat16> {
   using T2 = __nv_bfloat162;
@@ -128,18 +142,29 @@ template <> struct D16<__nv_bfloat16> {
   static __device__ __forceinline__ T2 pair2(__nv_bfloat16 a, __nv_bfloat16 b) { return __halves2bfloat162(a, b); }
   static __device__ __forceinline__ float2 to_f2(T2 v) { return __bfloat1622float2(v); }
   static __device__ __forceinline__ float big() { return 3.0e38f; }
-  // bf16(c) would be off by up to 2^-9 (a systematic error on every logit): multiply in fp32
-  static __device__ __forceinline__ T2 scale2(T2 x, float c) {
+  // bf16(1/sqrt(128)) would be off by up to 2^-9 (a systematic error on every logit): multiply in fp32
+  static __device__ __forceinline__ T2 inv_sqrt_d(T2 x) {
     const float2 f = __bfloat1622float2(x);
-    return __floats2bfloat162_rn(f.x * c, f.y * c);
+    return __floats2bfloat162_rn(f.x * 0.08838834764831845f, f.y * 0.08838834764831845f);
   }
 };
 
 // =================================================================================================
 // K1: scores
 // =================================================================================================
-template <typename T, int BITS>
-__global__ void __launch_bounds__(K1_THREADS, 2)
+// Rows g / g+8 of m-tile i of a group are the adjacent tokens Expand::elem(i, g), +1.  The B operand
+// carries q * ks (post-scaling).  With at most four query heads per KV head (SPLIT) the product is
+// carried as two fp16 terms in neighbouring MMA columns, hi = rnd(q*ks) in column 2h and the exact
+// remainder lo = q*ks - hi in column 2h+1 (lanes with odd g build the remainder), and the two columns
+// are added in the epilogue: a single fp16 rounding of q*ks (2^-12 relative) moves one raw score in eight
+// across an fp16 rounding boundary of the reference, 2% of a probability each.  With five to eight heads
+// all eight columns carry heads and q*ks is rounded once.
+//
+// Warps 0-3 compute, warp 4 is the TMA producer: stages are handed over through a full barrier (bytes
+// landed) and an empty barrier (one arrival per computing warp), so no warp waits for another warp's
+// arithmetic, only for data.
+template <typename T, int BITS, bool SPLIT>
+__global__ void __launch_bounds__(K1_THREADS, k1_min_ctas(BITS))
 k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ CUtensorMap tm_ks,
           const __grid_constant__ CUtensorMap tm_kmn, Dims dm, const T* __restrict__ q,
           const T* __restrict__ k_fp, T* __restrict__ scores, float2* __restrict__ tile_mm,
@@ -147,21 +172,25 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   using T2 = typename D16<T>::T2;
   constexpr int STAGES = k1_stages(BITS);
   constexpr int STAGE_BYTES = k1_stage_bytes(BITS);
-  constexpr int CODE_BYTES = BITS * 16384;
+  constexpr int CODE_BYTES = TILE_G * BITS * 512;
+  constexpr int KS_BYTES = TILE_G * 256;
+  constexpr int ROW_BYTES = k1_code_row_bytes(BITS);   // bytes of a channel row inside one TMA box
+  constexpr int N_BOXES = TILE_G * BITS * 4 / ROW_BYTES;
+  constexpr int KS_ROW = TILE_G * 2;                   // bytes of a scale row
   constexpr int GU = 4 / BITS;             // groups per 16-byte chunk of a channel row
   constexpr int UNITS = K1_GPW / GU;       // chunks per warp
   constexpr uint32_t FIELD = (1u << BITS) - 1u;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int n_pairs = dm.batch * dm.hkv;
   const int n_items = n_pairs * dm.n_ktiles;
-  const float inv_sqrt_d = 0.08838834764831845f;
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], K1_WARPS); }
     mbar_fence_init();
   }
   __syncthreads();
@@ -170,22 +199,29 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   // only when the KV head changes, and neighbouring CTAs stream neighbouring tiles
   const int it_first = (int)(((int64_t)blockIdx.x * n_items) / gridDim.x);
   const int it_end = (int)(((int64_t)(blockIdx.x + 1) * n_items) / gridDim.x);
-  auto issue = [&](int k) {
-    const int it = it_first + k;
-    if (it >= it_end) return;
-    const int s = k % STAGES;
-    const int pair = it / dm.n_ktiles, tile = it % dm.n_ktiles;
-    unsigned char* base = smem + s * STAGE_BYTES;
-    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+
+  if (warp == K1_WARPS) {
+    // ---- producer: one thread streams the CTA's tiles through the ring
+    if (lane == 0) {
+      fence_proxy_async_smem();
+      for (int k = 0; it_first + k < it_end; ++k) {
+        const int it = it_first + k, s = k % STAGES;
+        if (k >= STAGES && !mbar_wait_bounded(&empty_bar[s], (uint32_t)((k / STAGES - 1) & 1), WAIT_TRIES)) {
+          atomicExch(status, CQ_ERR_TIMEOUT);
+          break;
+        }
+        const int pair = it / dm.n_ktiles, tile = it % dm.n_ktiles;
+        unsigned char* base = smem + s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
 #pragma unroll
-    for (int bx = 0; bx < BITS; ++bx)
-      tma_load_2d(base + bx * 16384, &tm_code, (tile * TILE_G * BITS) + bx * 32, pair * kHeadDim, &full_bar[s]);
-    tma_load_2d(base + CODE_BYTES, &tm_ks, tile * TILE_G, pair * kHeadDim, &full_bar[s]);
-    tma_load_2d(base + CODE_BYTES + 8192, &tm_kmn, tile * TILE_G, pair * kHeadDim, &full_bar[s]);
-  };
-  if (tid == 0) {
-    fence_proxy_async_smem();
-    for (int k = 0; k < STAGES - 1; ++k) issue(k);
+        for (int bx = 0; bx < N_BOXES; ++bx)
+          tma_load_2d(base + bx * (128 * ROW_BYTES), &tm_code, tile * TILE_G * BITS + bx * (ROW_BYTES / 4), pair * kHeadDim,
+                      &full_bar[s]);
+        tma_load_2d(base + CODE_BYTES, &tm_ks, tile * TILE_G, pair * kHeadDim, &full_bar[s]);
+        tma_load_2d(base + CODE_BYTES + KS_BYTES, &tm_kmn, tile * TILE_G, pair * kHeadDim, &full_bar[s]);
+      }
+    }
+    return;
   }
 
   // lane constants: selectors / masks / accumulator scales for the two m-tiles of a group
@@ -203,26 +239,21 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
     sc0[i] = exp2f((float)(24 - sh));
     sc1[i] = exp2f((float)(24 - sh - BITS));
   }
+  (void)word_in_group;
 
   int cur_pair = -1;
   uint32_t qA[8], qB[8];
   bool failed = false;
-  // bf16 data with at most 4 query heads per KV head: the post-scaled operand q*ks is carried as two
-  // fp16 terms, hi = rnd(q*ks) in MMA columns 0-3 and lo = q*ks - hi in columns 4-7 (lanes g >= 4 hold
-  // head g-4 again), and the two column groups are added in the epilogue.  Without it the 2^-12 relative
-  // rounding of q*ks moves a few percent of the logits to the neighbouring bf16 value.
-  const bool split = std::is_same<T, __nv_bfloat16>::value && dm.n_rep <= 4;
-  const int q_head = split ? (g & 3) : g;
+  const int q_head = SPLIT ? (g >> 1) : g;        // the head whose query this lane's B column carries
+  const bool lo_lane = SPLIT && (g & 1);
+  // heads this lane's accumulator columns stand for: SPLIT: head c (columns 2c = hi, 2c+1 = lo); else heads 2c, 2c+1
+  const int out_head = SPLIT ? c : 2 * c;
 
   for (int k = 0;; ++k) {
     const int it = it_first + k;
     if (it >= it_end) break;
     const int s = k % STAGES;
     const int pair = it / dm.n_ktiles, tile = it % dm.n_ktiles;
-    if (tid == 0) {
-      fence_proxy_async_smem();
-      issue(k + STAGES - 1);
-    }
     if (pair != cur_pair) {   // query fragments of this KV head's query heads (B operand, n = g)
       cur_pair = pair;
       const int b = pair / dm.hkv, hk = pair % dm.hkv;
@@ -239,20 +270,24 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
       break;
     }
     const uint32_t code_base = smem_u32(smem + s * STAGE_BYTES);
-    const uint32_t ks_base = code_base + CODE_BYTES, kmn_base = ks_base + 8192;
+    const uint32_t ks_base = code_base + CODE_BYTES, kmn_base = ks_base + KS_BYTES;
     const int live_groups = min(TILE_G, dm.n_groups - tile * TILE_G);
+    const int b = pair / dm.hkv, hk = pair % dm.hkv;
 
     if (warp * K1_GPW < live_groups) {
-      // ---- scale fragments: ksA/ksB[kt] = (ks[16kt+2c][G], ks[16kt+2c+1][G]) / (+8), G = 8*col8+g
+      // ---- scale fragments: ksA/ksB[kt] = (ks[16kt+2c][G], ks[16kt+2c+1][G]) / (+8), G = 8*col8+g.
+      // Scale rows carry the TMA swizzle of their width (64 bytes: 16-byte chunk ^= bits 1-2 of the row;
+      // 32 bytes: chunk ^= bit 2 of the row).
       const int col8 = (warp * K1_GPW) >> 3, g_in_col = (warp * K1_GPW) & 7;
       uint32_t ksA[8], ksB[8];
-      float cb[4] = {0.f, 0.f, 0.f, 0.f};   // bias[G = 8*warp+g][heads 2c, 2c+1]
+      float cb[4] = {0.f, 0.f, 0.f, 0.f};   // bias[G = 8*col8+g][columns 2c, 2c+1]
       {
         const int mat = lane >> 3, r = lane & 7;
 #pragma unroll
         for (int kp = 0; kp < 4; ++kp) {
           const int d = 16 * (2 * kp + (mat >> 1)) + 8 * (mat & 1) + r;
-          const uint32_t off = (uint32_t)(d * 64 + ((col8 ^ ((d >> 1) & 3)) << 4));
+          const int sw = KS_ROW == 64 ? ((d >> 1) & 3) : ((d >> 2) & 1);
+          const uint32_t off = (uint32_t)(d * KS_ROW + ((col8 ^ sw) << 4));
           ldmatrix_x4_trans(ks_base + off, ksA[2 * kp], ksB[2 * kp], ksA[2 * kp + 1], ksB[2 * kp + 1]);
           uint32_t z0, z1, z2, z3;
           ldmatrix_x4_trans(kmn_base + off, z0, z1, z2, z3);
@@ -263,16 +298,15 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
           mma_f16(cb, z2, 0u, z3, 0u, qA[2 * kp + 1], qB[2 * kp + 1]);
         }
       }
-      const int b = pair / dm.hkv, hk = pair % dm.hkv;
-      const int64_t row_a = ((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + 2 * c) * dm.pitch;
+      const int64_t row_a = ((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + out_head) * dm.pitch;
       const int64_t row_b = row_a + dm.pitch;
       T2 mnA = D16<T>::bcast(D16<T>::big()), mxA = D16<T>::bcast(-D16<T>::big()), mnB = mnA, mxB = mxA;
 
 #pragma unroll 1
       for (int u = 0; u < UNITS; ++u) {
         const int cidx = warp * UNITS + u;                    // 16-byte chunk of the channel row
-        const uint32_t box_off = (uint32_t)(cidx >> 3) * 16384u;
-        const int ch = cidx & 7;
+        const uint32_t box_off = (uint32_t)(cidx / (ROW_BYTES / 16)) * (uint32_t)(128 * ROW_BYTES);
+        const int ch = cidx % (ROW_BYTES / 16);
         float acc[GU][2][4];
 #pragma unroll
         for (int a = 0; a < GU; ++a)
@@ -286,7 +320,8 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
 #pragma unroll
           for (int rr = 0; rr < 4; ++rr) {
             const int d = 16 * kt + 2 * c + (rr & 1) + 8 * (rr >> 1);
-            const uint4 v = lds128(code_base + box_off + (uint32_t)(d * 128 + ((ch ^ (d & 7)) << 4)));
+            const int sw = ROW_BYTES == 64 ? ((d >> 1) & 3) : (d & 7);
+            const uint4 v = lds128(code_base + box_off + (uint32_t)(d * ROW_BYTES + ((ch ^ sw) << 4)));
             W[rr][0] = v.x; W[rr][1] = v.y; W[rr][2] = v.z; W[rr][3] = v.w;
           }
 #pragma unroll
@@ -295,15 +330,17 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
             const uint32_t ksa = __shfl_sync(0xffffffffu, ksA[kt], 4 * gi + c);
             const uint32_t ksb = __shfl_sync(0xffffffffu, ksB[kt], 4 * gi + c);
             uint32_t b0 = hmul2_u32(qA[kt], ksa), b1 = hmul2_u32(qB[kt], ksb);
-            if (split && g >= 4) {   // low-order term: the FMA forms q*ks exactly before subtracting the high one
-              b0 = hfma2_u32(qA[kt], ksa, b0 ^ 0x80008000u);
-              b1 = hfma2_u32(qB[kt], ksb, b1 ^ 0x80008000u);
+            if (lo_lane) {   // remainder term: the FMA forms q*ks exactly before subtracting the rounded product
+              b0 = hfma2_neg_u32(qA[kt], ksa, b0);
+              b1 = hfma2_neg_u32(qB[kt], ksb, b1);
             }
             if (BITS == 1) {   // one byte of the group's word feeds both m-tiles
               const uint32_t x01 = prmt(W[0][a], W[1][a], sel[0]), x89 = prmt(W[2][a], W[3][a], sel[0]);
 #pragma unroll
-              for (int i = 0; i < 2; ++i)
-                mma_f16(acc[a][i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], b0, b1);
+              for (int i = 0; i < 2; ++i) {
+                const uint32_t a0 = x01 & m0[i], a1 = x01 & m1[i], a2 = x89 & m0[i], a3 = x89 & m1[i];
+                mma_f16(acc[a][i], a0, a1, a2, a3, b0, b1);
+              }
             } else {
 #pragma unroll
               for (int i = 0; i < 2; ++i) {
@@ -319,40 +356,62 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
                   w0 = W[0][wi]; w1 = W[1][wi]; w8 = W[2][wi]; w9 = W[3][wi];
                 }
                 const uint32_t x01 = prmt(w0, w1, sel[i]), x89 = prmt(w8, w9, sel[i]);
-                mma_f16(acc[a][i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], b0, b1);
+                const uint32_t a0 = x01 & m0[i], a1 = x01 & m1[i], a2 = x89 & m0[i], a3 = x89 & m1[i];
+                mma_f16(acc[a][i], a0, a1, a2, a3, b0, b1);
               }
             }
           }
         }
-        // ---- epilogue: rows g / g+8 are the adjacent tokens Expand::elem(i, g), +1 of the group
+        // ---- epilogue
 #pragma unroll
         for (int a = 0; a < GU; ++a) {
           const int gi = g_in_col + u * GU + a;
           const float bias0 = __shfl_sync(0xffffffffu, cb[0], 4 * gi + c);
-          const float bias1 = __shfl_sync(0xffffffffu, cb[1], 4 * gi + c);
+          const float bias1 = SPLIT ? 0.f : __shfl_sync(0xffffffffu, cb[1], 4 * gi + c);
           const int tokg = (tile * TILE_G + col8 * 8 + gi) * 32;
+          if (SPLIT) {      // one head per lane: columns 2c, 2c+1 are its two terms
+            T2 sa[2];
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int tok = tokg + Expand<BITS>::elem(i, g);      // rows g, g+8 = tokens tok, tok+1
-            if (split) {      // columns 4-7 (lanes c + 2) hold the low-order terms of heads 0-3
+            for (int i = 0; i < 2; ++i) {
+              const T2 ra = D16<T>::round2(fmaf(acc[a][i][0] + acc[a][i][1], sc0[i], bias0),
+                                           fmaf(acc[a][i][2] + acc[a][i][3], sc1[i], bias0));
+              sa[i] = dm.raw ? ra : D16<T>::inv_sqrt_d(ra);
+            }
+            if (c < dm.n_rep) {
+              if (BITS == 1) {   // the lane's four tokens 4g .. 4g+3 are adjacent: one 8-byte store
+                uint2 v;
+                v.x = *reinterpret_cast<const uint32_t*>(&sa[0]); v.y = *reinterpret_cast<const uint32_t*>(&sa[1]);
+                *reinterpret_cast<uint2*>(scores + row_a + tokg + 4 * g) = v;
+              } else {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) acc[a][i][e] += __shfl_down_sync(0xffffffffu, acc[a][i][e], 2);
+                for (int i = 0; i < 2; ++i)
+                  *reinterpret_cast<T2*>(scores + row_a + tokg + Expand<BITS>::elem(i, g)) = sa[i];
+              }
+              mnA = __hmin2(mnA, __hmin2(sa[0], sa[1])); mxA = __hmax2(mxA, __hmax2(sa[0], sa[1]));
             }
-            const T2 ra = D16<T>::round2(fmaf(acc[a][i][0], sc0[i], bias0), fmaf(acc[a][i][2], sc1[i], bias0));
-            const T2 rb = D16<T>::round2(fmaf(acc[a][i][1], sc0[i], bias1), fmaf(acc[a][i][3], sc1[i], bias1));
-            // the attention logits are the rounded product times 1/sqrt(D); the plain product stops at the rounding
-            const T2 sa = dm.raw ? ra : D16<T>::scale2(ra, inv_sqrt_d), sb = dm.raw ? rb : D16<T>::scale2(rb, inv_sqrt_d);
-            if (2 * c < dm.n_rep) {
-              *reinterpret_cast<T2*>(scores + row_a + tok) = sa;
-              mnA = __hmin2(mnA, sa); mxA = __hmax2(mxA, sa);
-            }
-            if (2 * c + 1 < dm.n_rep) {
-              *reinterpret_cast<T2*>(scores + row_b + tok) = sb;
-              mnB = __hmin2(mnB, sb); mxB = __hmax2(mxB, sb);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const int tok = tokg + Expand<BITS>::elem(i, g);      // rows g, g+8 = tokens tok, tok+1
+              const T2 ra = D16<T>::round2(fmaf(acc[a][i][0], sc0[i], bias0), fmaf(acc[a][i][2], sc1[i], bias0));
+              const T2 rb = D16<T>::round2(fmaf(acc[a][i][1], sc0[i], bias1), fmaf(acc[a][i][3], sc1[i], bias1));
+              // the attention logits are the rounded product times 1/sqrt(D); the plain product stops at the rounding
+              const T2 sva = dm.raw ? ra : D16<T>::inv_sqrt_d(ra), svb = dm.raw ? rb : D16<T>::inv_sqrt_d(rb);
+              if (2 * c < dm.n_rep) {
+                *reinterpret_cast<T2*>(scores + row_a + tok) = sva;
+                mnA = __hmin2(mnA, sva); mxA = __hmax2(mxA, sva);
+              }
+              if (2 * c + 1 < dm.n_rep) {
+                *reinterpret_cast<T2*>(scores + row_b + tok) = svb;
+                mnB = __hmin2(mnB, svb); mxB = __hmax2(mxB, svb);
+              }
             }
           }
         }
       }
+      // the stage has been read: hand it back to the producer
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
       // ---- per-warp min/max of this tile, per head
       const float2 fmnA = D16<T>::to_f2(mnA), fmxA = D16<T>::to_f2(mxA), fmnB = D16<T>::to_f2(mnB), fmxB = D16<T>::to_f2(mxB);
       float lo_a = fminf(fmnA.x, fmnA.y), hi_a = fmaxf(fmxA.x, fmxA.y);
@@ -361,22 +420,22 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
       for (int o = 4; o < 32; o <<= 1) {
         lo_a = fminf(lo_a, __shfl_xor_sync(0xffffffffu, lo_a, o));
         hi_a = fmaxf(hi_a, __shfl_xor_sync(0xffffffffu, hi_a, o));
-        lo_b = fminf(lo_b, __shfl_xor_sync(0xffffffffu, lo_b, o));
-        hi_b = fmaxf(hi_b, __shfl_xor_sync(0xffffffffu, hi_b, o));
+        if (!SPLIT) {
+          lo_b = fminf(lo_b, __shfl_xor_sync(0xffffffffu, lo_b, o));
+          hi_b = fmaxf(hi_b, __shfl_xor_sync(0xffffffffu, hi_b, o));
+        }
       }
       if (g == 0 && !dm.raw) {
-        const int64_t r0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + 2 * c;
-        if (2 * c < dm.n_rep) tile_mm[r0 * dm.n_mm + tile * K1_WARPS + warp] = make_float2(lo_a, hi_a);
-        if (2 * c + 1 < dm.n_rep) tile_mm[(r0 + 1) * dm.n_mm + tile * K1_WARPS + warp] = make_float2(lo_b, hi_b);
+        const int64_t r0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + out_head;
+        if (out_head < dm.n_rep) tile_mm[r0 * dm.n_mm + tile * K1_WARPS + warp] = make_float2(lo_a, hi_a);
+        if (!SPLIT && out_head + 1 < dm.n_rep) tile_mm[(r0 + 1) * dm.n_mm + tile * K1_WARPS + warp] = make_float2(lo_b, hi_b);
       }
-    } else if (lane < 2 * kMaxRep && !dm.raw) {
-      // dead part of a ragged last tile: neutral min/max entries
-      const int b = pair / dm.hkv, hk = pair % dm.hkv;
-      if (lane < dm.n_rep)
+    } else {
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+      if (lane < dm.n_rep && !dm.raw)      // dead part of a ragged last tile: neutral min/max entries
         tile_mm[((int64_t)b * dm.hq + (int64_t)hk * dm.n_rep + lane) * dm.n_mm + tile * K1_WARPS + warp] =
             make_float2(INFINITY, -INFINITY);
     }
-    __syncthreads();
   }
   if (failed) return;
 
@@ -384,7 +443,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   // as A fragments (all loads of a tile are independent), query heads as B; MMA in the data dtype.
   const int t_fp = live_t_fp(dm);
   const int n_fp_tiles = (t_fp + 15) / 16;
-  for (int it = blockIdx.x * K1_WARPS + warp; it < n_pairs * n_fp_tiles; it += gridDim.x * K1_WARPS) {
+  for (int it = blockIdx.x * K1_WARPS + warp; it < n_pairs * n_fp_tiles; it += gridDim.x * K1_WARPS) {   // (the producer warp has left)
     const int pair = it / n_fp_tiles, t0 = (it % n_fp_tiles) * 16;
     const int b = pair / dm.hkv, hk = pair % dm.hkv;
     const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
@@ -424,9 +483,22 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
 // K2: attn.V partials
 // =================================================================================================
 template <typename T>
-struct CalibH {   // per head, as 16-bit pairs for packed arithmetic in the data dtype
-  typename D16<T>::T2 mn, rdenom, rdenom_lo, range;
+struct CalibH {   // per head: 16-bit pairs for packed arithmetic in the data dtype, the reciprocal in fp32
+  typename D16<T>::T2 mn, range;
+  float rdenom;
 };
+
+// rnd((s - mn) / denom) * range + mn with the reference's rounding after every operation.  The quotient is
+// formed in fp32 (float(x) * (1/denom) is within an fp32 ulp of the quotient, so its rounding to 16 bits
+// differs from the reference's in one case in thousands): in bf16 one ulp of the quotient is a fifth of a
+// logit, so an approximate 16-bit reciprocal is not good enough.
+template <typename T>
+__device__ __forceinline__ typename D16<T>::T2 calibrate2(typename D16<T>::T2 v, const CalibH<T>& cal) {
+  v = __hsub2(v, cal.mn);
+  const float2 f = D16<T>::to_f2(v);
+  v = D16<T>::round2(f.x * cal.rdenom, f.y * cal.rdenom);
+  return __hadd2(__hmul2(v, cal.range), cal.mn);
+}
 
 // Full-precision tokens of attn.V, chunks of 128, as a launch of its own next to k2_attn_v:
 // out[h][d] = sum_t p[h][t] V[t][d] on the warp MMA in the data dtype.  A = probabilities (rows = heads,
@@ -641,19 +713,16 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         lo = warp_min(lo);
         hi = warp_max(hi);
         CalibH<T> cal;
-        cal.mn = cal.rdenom = cal.rdenom_lo = cal.range = zero2;
+        cal.mn = cal.range = zero2;
+        cal.rdenom = 0.f;
         float m_ref = hi;
         if (dm.calibrate) {
           const float denom = rnd<T>(rnd<T>(hi - lo) + 1e-8f);
           const float range = rnd<T>(rnd<T>(hi + (-3.f)) - lo);
           cal.mn = D16<T>::bcast(lo);
-          cal.rdenom = D16<T>::bcast(1.f / denom);
-          cal.rdenom_lo = D16<T>::bcast(1.f / denom - rnd<T>(1.f / denom));   // two-term reciprocal
+          cal.rdenom = 1.f / denom;
           cal.range = D16<T>::bcast(range);
-          T2 v = __hsub2(D16<T>::bcast(hi), cal.mn);                          // the maximum, calibrated like any logit
-          v = __hfma2(v, cal.rdenom, __hmul2(v, cal.rdenom_lo));
-          v = __hadd2(__hmul2(v, cal.range), cal.mn);
-          m_ref = D16<T>::to_f2(v).x;
+          m_ref = D16<T>::to_f2(calibrate2<T>(D16<T>::bcast(hi), cal)).x;     // the maximum, calibrated like any logit
         }
         if (lane == 0) {
           cal_s[h] = cal;
@@ -677,11 +746,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           T2 v = r2[e];
-          if (dm.calibrate) {
-            v = __hsub2(v, cal.mn);
-            v = __hfma2(v, cal.rdenom, __hmul2(v, cal.rdenom_lo));   // ~ rnd(v / denom)
-            v = __hadd2(__hmul2(v, cal.range), cal.mn);
-          }
+          if (dm.calibrate) v = calibrate2<T>(v, cal);
           if (mvis) v = __hadd2(v, D16<T>::pair2(mvis[t + 2 * e], mvis[t + 2 * e + 1]));
           const float2 f = D16<T>::to_f2(v);
           // the reference rounds the probabilities to the data dtype; they are then exact in fp16.
@@ -897,18 +962,18 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// rows x cols matrix (cols contiguous), box = 32 columns x 128 rows.
+// rows x cols matrix (cols contiguous), box = box_cols columns x 128 rows.
 // A decode loop asks for the same few descriptors at every step (one cache per layer), so the encoded
 // maps are remembered per host thread: a descriptor is a pure function of the key below.
 static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes,
-                     uint64_t cols, uint64_t rows, CUtensorMapSwizzle sw) {
-  struct Entry { const void* base; uint64_t cols, rows; int dt, sw; CUtensorMap map; };
+                     uint64_t cols, uint64_t rows, CUtensorMapSwizzle sw, uint32_t box_cols) {
+  struct Entry { const void* base; uint64_t cols, rows; int dt, sw; uint32_t box_cols; CUtensorMap map; };
   constexpr int N = 256;
   thread_local Entry cache[N];
   thread_local int used = 0, next = 0;
   for (int i = 0; i < used; ++i) {
     const Entry& e = cache[i];
-    if (e.base == base && e.cols == cols && e.rows == rows && e.dt == (int)dt && e.sw == (int)sw) {
+    if (e.base == base && e.cols == cols && e.rows == rows && e.dt == (int)dt && e.sw == (int)sw && e.box_cols == box_cols) {
       *m = e.map;
       return true;
     }
@@ -917,16 +982,29 @@ static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, i
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
-  cuuint32_t box[2] = {32, 128};
+  cuuint32_t box[2] = {box_cols, 128};
   cuuint32_t estr[2] = {1, 1};
   if (fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return false;
   Entry& e = cache[next];
-  e.base = base; e.cols = cols; e.rows = rows; e.dt = (int)dt; e.sw = (int)sw; e.map = *m;
+  e.base = base; e.cols = cols; e.rows = rows; e.dt = (int)dt; e.sw = (int)sw; e.box_cols = box_cols; e.map = *m;
   next = (next + 1) % N;
   if (used < N) ++used;
   return true;
+}
+
+// The three tensor maps of the score kernel: code words (boxes of at most 128 bytes per channel row, swizzled
+// over their width), scales and minima (one box of TILE_G values per channel row, swizzled over its width).
+template <int BITS>
+static bool make_k_maps(CUtensorMap* tm_code, CUtensorMap* tm_ks, CUtensorMap* tm_kmn, const void* code,
+                        const void* ks, const void* kmn, uint64_t n_groups, uint64_t rows) {
+  constexpr int row = k1_code_row_bytes(BITS);
+  const CUtensorMapSwizzle sw_ks = TILE_G * 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+  return make_map(tm_code, code, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, n_groups * BITS, rows,
+                  row == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, row / 4) &&
+         make_map(tm_ks, ks, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, n_groups, rows, sw_ks, TILE_G) &&
+         make_map(tm_kmn, kmn, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, n_groups, rows, sw_ks, TILE_G);
 }
 
 struct Layout {
@@ -965,14 +1043,11 @@ static Layout make_layout(const Dims& d) {
   return l;
 }
 
-static int sm_count() {
-  static int n = []() {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-    return v;
-  }();
-  return n;
+static int sm_count() {      // of the current device
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+  return v;
 }
 
 template <typename T, int BITS, int CT, int VT>
@@ -984,18 +1059,21 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
   float* partial = reinterpret_cast<float*>(ws + l.partial_off);
   const int n_pairs = d.batch * d.hkv;
 
-  auto k1 = k1_scores<T, BITS>;
+  auto k1 = d.n_rep <= 4 ? k1_scores<T, BITS, true> : k1_scores<T, BITS, false>;
   auto k2 = k2_attn_v<T, BITS, CT, VT>;
   const int smem1 = k1_stages(BITS) * k1_stage_bytes(BITS) + 1024;
   constexpr int p_bytes = kMaxRep * (CT + 8) * 2, red_bytes = 4 * kMaxRep * 136 * 4;
   const int smem2 = k2_stages(BITS) * k2_stage_bytes(BITS, VT) + (p_bytes > red_bytes ? p_bytes : red_bytes) + 1024;
-  static bool configured_dev[64] = {};   // per template instance and device
-  static int occ1_dev[64], occ2_dev[64];
+  static bool configured_dev[64][2] = {};   // per template instance, device and score-kernel variant
+  static int occ1_dev[64][2], occ2_dev[64][2];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CQ_ERR_LAUNCH;
-  bool& configured = configured_dev[dev];
-  int& occ1 = occ1_dev[dev];
-  int& occ2 = occ2_dev[dev];
+  static std::mutex config_mu;                // host threads may share a device
+  std::lock_guard<std::mutex> config_lock(config_mu);
+  const int variant = d.n_rep <= 4 ? 1 : 0;
+  bool& configured = configured_dev[dev][variant];
+  int& occ1 = occ1_dev[dev][variant];
+  int& occ2 = occ2_dev[dev][variant];
   if (!configured) {
     if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1) != cudaSuccess) return CQ_ERR_LAUNCH;
     if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return CQ_ERR_LAUNCH;
@@ -1009,12 +1087,7 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
   if (d.t_vis > 0 && (stages & 1)) {
     CUtensorMap tm_code, tm_ks, tm_kmn;
     const uint64_t rows = (uint64_t)n_pairs * kHeadDim;
-    if (!make_map(&tm_code, a->k_code, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)d.n_groups * BITS, rows,
-                  CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&tm_ks, a->k_scale, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)d.n_groups, rows,
-                  CU_TENSOR_MAP_SWIZZLE_64B) ||
-        !make_map(&tm_kmn, a->k_mn, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)d.n_groups, rows,
-                  CU_TENSOR_MAP_SWIZZLE_64B))
+    if (!make_k_maps<BITS>(&tm_code, &tm_ks, &tm_kmn, a->k_code, a->k_scale, a->k_mn, (uint64_t)d.n_groups, rows))
       return CQ_ERR_LAUNCH;
     const int items1 = n_pairs * d.n_ktiles;
     const int grid1 = max(1, min(items1 + n_pairs * ((d.t_fp + 63) / 64), sm_count() * occ1));
@@ -1114,22 +1187,22 @@ static int qbmm_run_t(int kind, const mma::Dims& d, const void* fA, const int32_
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CQ_ERR_LAUNCH;
   if (kind == 1) {
-    auto k1 = k1_scores<T, BITS>;
+    const int variant = d.n_rep <= 4 ? 1 : 0;
+    auto k1 = variant ? k1_scores<T, BITS, true> : k1_scores<T, BITS, false>;
     const int smem1 = k1_stages(BITS) * k1_stage_bytes(BITS) + 1024;
-    static bool configured[64] = {};
-    static int occ[64];
-    if (!configured[dev]) {
+    static bool configured[64][2] = {};
+    static int occ[64][2];
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!configured[dev][variant]) {
       if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1) != cudaSuccess) return CQ_ERR_LAUNCH;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[dev], k1, K1_THREADS, smem1) != cudaSuccess || occ[dev] < 1) return CQ_ERR_LAUNCH;
-      configured[dev] = true;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[dev][variant], k1, K1_THREADS, smem1) != cudaSuccess || occ[dev][variant] < 1) return CQ_ERR_LAUNCH;
+      configured[dev][variant] = true;
     }
     CUtensorMap tm_code, tm_ks, tm_kmn;
     const uint64_t rows = (uint64_t)n_pairs * kHeadDim;
-    if (!make_map(&tm_code, qB, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)d.n_groups * BITS, rows, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !make_map(&tm_ks, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)d.n_groups, rows, CU_TENSOR_MAP_SWIZZLE_64B) ||
-        !make_map(&tm_kmn, zeros, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)d.n_groups, rows, CU_TENSOR_MAP_SWIZZLE_64B))
-      return CQ_ERR_LAUNCH;
-    const int grid = max(1, min(n_pairs * d.n_ktiles, sm_count() * occ[dev]));
+    if (!make_k_maps<BITS>(&tm_code, &tm_ks, &tm_kmn, qB, scales, zeros, (uint64_t)d.n_groups, rows)) return CQ_ERR_LAUNCH;
+    const int grid = max(1, min(n_pairs * d.n_ktiles, sm_count() * occ[dev][variant]));
     k1<<<grid, K1_THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(fA), nullptr,
                                         static_cast<T*>(out), nullptr, status);
     return check_launch();
@@ -1140,6 +1213,8 @@ static int qbmm_run_t(int kind, const mma::Dims& d, const void* fA, const int32_
   auto launch_k2 = [&](auto k2, int smem2) -> int {
     static bool configured[64] = {};
     static int occ[64];
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
     if (!configured[dev]) {
       if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return CQ_ERR_LAUNCH;
       if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[dev], k2, THREADS, smem2) != cudaSuccess || occ[dev] < 1) return CQ_ERR_LAUNCH;

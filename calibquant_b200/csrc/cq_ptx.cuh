@@ -137,6 +137,13 @@ __device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c
   return r;
 }
 
+// a * b - c on packed fp16 pairs, one rounding (the negation folds into the instruction)
+__device__ __forceinline__ uint32_t hfma2_neg_u32(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t r;
+  asm("{\n\t.reg .b32 n;\n\tneg.f16x2 n, %3;\n\tfma.rn.f16x2 %0, %1, %2, n;\n\t}" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));

@@ -259,8 +259,9 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
             rc = fn(ref, ctypes.c_void_p(q2.data_ptr()), ctypes.c_void_p(out.data_ptr()), ws_ptr, ws_n, st)
         check(rc, "cq_decode_attn_host")
         return out.reshape(shape)
-    if nbytes == 0:
-        check(lib().cq_decode_attn(ref, None, 0, ctypes.c_void_p(handle)), "cq_decode_attn")
+    if nbytes == 0:      # the size query refused the arguments: let the call itself say why
+        rc = lib().cq_decode_attn(ref, None, 0, ctypes.c_void_p(handle))
+        check(rc if rc else _lib.CQ_ERR_WORKSPACE, "cq_decode_attn")
     ws = _workspace(nbytes, dev, handle)
     with _OnDevice(dev):
         rc = lib().cq_decode_attn(ref, _ptr(ws), ws.numel(), ctypes.c_void_p(handle))
