@@ -83,6 +83,10 @@ SIGNATURES = {
                                     _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _vp, _vp]),
     "cq_decode_attn_workspace_bytes": (_sz, [_c.POINTER(DecodeArgs)]),
     "cq_decode_attn": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _sz, _vp]),
+    "cq_decode_attn_profile": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _sz, _vp, _c.POINTER(_c.c_float)]),
+    "cq_workspace_status": (_c.c_int, [_vp, _vp]),
+    "cq_host_status_word": (_c.POINTER(_c.c_int), []),
+    "cq_qbmm_static_status": (_c.c_int, [_vp]),
     "cq_decode_attn_host_workspace_bytes": (_sz, [_c.POINTER(DecodeArgs)]),
     "cq_decode_attn_host": (_c.c_int, [_c.POINTER(DecodeArgs), _vp, _vp, _vp, _sz, _vp]),
 }

@@ -16,6 +16,8 @@
 //   2 stats   : per (batch, q head): calibration constants, running max, 1/sum(exp)
 //   3 attn.V  : split over tokens, fp32 partial outputs -> workspace
 //   4 combine : add the splits, round to the dtype
+#include <mutex>
+
 #include "cq_common.cuh"
 #include "cq_decode_shared.cuh"
 
@@ -385,7 +387,6 @@ static int validate(const cq_decode_args* a) {
   if (a->bits != 1 && a->bits != 2 && a->bits != 4) return CQ_ERR_UNSUPPORTED;
   if (a->t_vis % kGroup) return CQ_ERR_UNSUPPORTED;
   if (a->n_q_heads / a->n_kv_heads > kMaxRep) return CQ_ERR_UNSUPPORTED;
-  if ((int64_t)a->batch * a->n_kv_heads > 65535) return CQ_ERR_UNSUPPORTED;
   if (a->t_fp > 0 && (!aligned16(a->k_fp) || a->fp_stride_b % 8 || a->fp_stride_h % 8)) return CQ_ERR_BAD_ARG;
   return CQ_OK;
 }
@@ -441,23 +442,61 @@ extern "C" size_t cq_decode_attn_workspace_bytes(const cq_decode_args* args) {
   return cq::make_layout(cq::make_dims(args)).total;
 }
 
-extern "C" int cq_decode_attn(const cq_decode_args* args, void* workspace, size_t workspace_bytes,
-                              void* stream) {
+static int decode_attn_impl(const cq_decode_args* args, void* workspace, size_t workspace_bytes, void* stream,
+                            int* status_word) {
   int rc = cq::validate(args);
   if (rc != CQ_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cq::mma_path_eligible(args)) {
     if (!workspace || workspace_bytes < cq::mma_path_workspace_bytes(args) || !cq::aligned16(workspace))
       return CQ_ERR_WORKSPACE;
-    return cq::mma_path_run(args, workspace, st);
+    return cq::mma_path_run(args, workspace, st, nullptr, status_word);
   }
   if (args->t_fp_dev) return CQ_ERR_UNSUPPORTED;   // device-side token count: tensor-core path only
+  if ((int64_t)args->batch * args->n_kv_heads > 65535) return CQ_ERR_UNSUPPORTED;   // grid.y of the general kernels
   const cq::DecodeDims dm = cq::make_dims(args);
   const cq::WsLayout w = cq::make_layout(dm);
   if (!workspace || workspace_bytes < w.total || !cq::aligned16(workspace)) return CQ_ERR_WORKSPACE;
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   if (args->dtype == CQ_DTYPE_F16) return cq::run_decode_bits<__half>(args, dm, w, ws, st);
   return cq::run_decode_bits<__nv_bfloat16>(args, dm, w, ws, st);
+}
+
+extern "C" int cq_decode_attn(const cq_decode_args* args, void* workspace, size_t workspace_bytes,
+                              void* stream) {
+  return decode_attn_impl(args, workspace, workspace_bytes, stream, nullptr);
+}
+
+// ---- per-launch timing of one step (tensor-core path) ------------------------------------------------
+extern "C" int cq_decode_attn_profile(const cq_decode_args* args, void* workspace, size_t workspace_bytes,
+                                      void* stream, float* launch_ms) {
+  if (!launch_ms) return CQ_ERR_BAD_ARG;
+  int rc = cq::validate(args);
+  if (rc != CQ_OK) return rc;
+  if (!cq::mma_path_eligible(args)) return CQ_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < cq::mma_path_workspace_bytes(args) || !cq::aligned16(workspace))
+    return CQ_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaEvent_t ev[5] = {};
+  for (int i = 0; i < 5; ++i)
+    if (cudaEventCreate(&ev[i]) != cudaSuccess) rc = CQ_ERR_LAUNCH;
+  if (rc == CQ_OK) rc = cq::mma_path_run(args, workspace, st, ev);
+  if (rc == CQ_OK && cudaEventSynchronize(ev[4]) != cudaSuccess) rc = CQ_ERR_LAUNCH;
+  for (int i = 0; i < 4 && rc == CQ_OK; ++i)
+    if (cudaEventElapsedTime(&launch_ms[i], ev[i], ev[i + 1]) != cudaSuccess) rc = CQ_ERR_LAUNCH;
+  for (int i = 0; i < 5; ++i)
+    if (ev[i]) cudaEventDestroy(ev[i]);
+  return rc;
+}
+
+// ---- sticky device status of a workspace --------------------------------------------------------------
+extern "C" int cq_workspace_status(const void* workspace, void* stream) {
+  if (!workspace) return CQ_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int word = 0;
+  if (cudaMemcpyAsync(&word, workspace, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return CQ_ERR_LAUNCH;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return CQ_ERR_LAUNCH;
+  return word == 0 ? CQ_OK : (word == CQ_ERR_TIMEOUT ? CQ_ERR_TIMEOUT : CQ_ERR_LAUNCH);
 }
 
 // ---- the same step for callers whose query and result live in host memory -------------------------
@@ -473,7 +512,33 @@ static void* mapped_host_ptr(const void* p) {
   (void)cudaGetLastError();
   return nullptr;
 }
+// One page-locked, device-mapped status word per device for the host-buffer entry point: a kernel whose
+// bounded wait runs out stores into it directly, and the host reads it after the stream has drained, without
+// a copy of its own.  Made on the first call on a device (the one allocation of this entry point) and kept.
+struct HostStatus { volatile int* host; int* dev; };
+static int host_status_word(HostStatus* out) {
+  static std::mutex mu;
+  static HostStatus words[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CQ_ERR_LAUNCH;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!words[dev].host) {
+    void* h = nullptr; void* d = nullptr;
+    if (cudaHostAlloc(&h, 64, cudaHostAllocMapped) != cudaSuccess) return CQ_ERR_LAUNCH;
+    if (cudaHostGetDevicePointer(&d, h, 0) != cudaSuccess) { cudaFreeHost(h); return CQ_ERR_LAUNCH; }
+    *static_cast<int*>(h) = 0;
+    words[dev].host = static_cast<volatile int*>(h);
+    words[dev].dev = static_cast<int*>(d);
+  }
+  *out = words[dev];
+  return CQ_OK;
+}
 }  // namespace cq
+
+extern "C" int* cq_host_status_word(void) {
+  cq::HostStatus hs;
+  return cq::host_status_word(&hs) == CQ_OK ? const_cast<int*>(hs.host) : nullptr;
+}
 
 extern "C" size_t cq_decode_attn_host_workspace_bytes(const cq_decode_args* args) {
   if (!args) return 0;
@@ -507,10 +572,15 @@ extern "C" int cq_decode_attn_host(const cq_decode_args* args, const void* q_hos
   void* out_map = cq::aligned16(out_host) ? cq::mapped_host_ptr(out_host) : nullptr;
   a.q = q_dev;
   a.out = out_map ? out_map : out_stage;
-  int rc = cq_decode_attn(&a, workspace, base, st);
+  // a bounded device-side wait that runs out leaves out_host unwritten or stale: the kernels report it in a
+  // host-visible word that is read once the stream has drained (sticky, like the word of a workspace)
+  cq::HostStatus hs;
+  int rc = cq::host_status_word(&hs);
+  if (rc != CQ_OK) return rc;
+  rc = decode_attn_impl(&a, workspace, base, st, hs.dev);
   if (rc != CQ_OK) return rc;
   if (!out_map && cudaMemcpyAsync(out_host, out_stage, bytes, cudaMemcpyDeviceToHost, st) != cudaSuccess)
     return CQ_ERR_LAUNCH;
   if (cudaStreamSynchronize(st) != cudaSuccess) return CQ_ERR_LAUNCH;
-  return CQ_OK;
+  return *hs.host == 0 ? CQ_OK : CQ_ERR_TIMEOUT;
 }

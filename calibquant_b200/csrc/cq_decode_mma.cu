@@ -55,8 +55,10 @@ constexpr int TILE_G = CQ_K1_TILE_G;   // 32-token groups per K tile
 constexpr int K1_GPW = TILE_G / K1_WARPS;
 // attn.V work items: CT tokens per item, streamed as tiles of VT tokens.  Two shapes are compiled: the
 // large one for long contexts, the small one when the large one would leave CTAs without work.
-constexpr int CT_LARGE = 1024, VT_LARGE = 512, CT_SMALL = 256, VT_SMALL = 256;
-constexpr int K2_RESIDENT = 444;       // attn.V CTAs resident on the device (3 per SM), for the choice below
+constexpr int VT_LARGE = 512, VT_SMALL = 256;
+constexpr int K2_WARPS = 4;            // computing warps of an attn.V CTA
+constexpr int K2_THREADS = (K2_WARPS + 1) * 32;   // + the producer warp
+constexpr int K2_RESIDENT = 296;       // attn.V CTAs resident on the device (2 per SM), for the choice below
 constexpr uint32_t WAIT_TRIES = 1u << 22;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -66,15 +68,20 @@ __host__ __device__ constexpr int k1_min_ctas(int bits) {
   return (220 * 1024) / (k1_stages(bits) * k1_stage_bytes(bits) + 2048) > 4 ? 4 : (220 * 1024) / (k1_stages(bits) * k1_stage_bytes(bits) + 2048);
 }
 __host__ __device__ constexpr int k1_code_row_bytes(int bits) { return TILE_G * bits * 4 < 128 ? TILE_G * bits * 4 : 128; }
-__host__ __device__ constexpr int k2_stages(int bits) { return bits == 4 ? 2 : 3; }
-__host__ __device__ constexpr int k2_stage_bytes(int bits, int vt) { return vt * 16 * bits + 2 * vt * 8; }
+// an attn.V stage: codes, scales, minima, and the logits of kMaxRep heads for the tile's tokens
+// (logit rows are 16 bytes longer than a tile so that the heads fall on different banks)
+__host__ __device__ constexpr int k2_stage_bytes(int bits, int vt) { return vt * (16 * bits + 16) + kMaxRep * (2 * vt + 16); }
+__host__ __device__ constexpr int k2_stages(int bits, int vt) { return 3 * k2_stage_bytes(bits, vt) <= 76 * 1024 ? 3 : 2; }
+__host__ __device__ constexpr int k2_smem_bytes(int bits, int vt) {
+  return k2_stages(bits, vt) * k2_stage_bytes(bits, vt) + K2_WARPS * kMaxRep * 136 * 4 + 1024;
+}
 
 struct Dims {
   int batch, hq, hkv, n_rep, t_vis, t_fp, calibrate;
   int n_groups;        // t_vis / 32
   int n_ktiles;        // ceil(n_groups / 32)
-  int chunk_tok;       // tokens per attn.V work item: CT_LARGE or CT_SMALL
-  int n_chunks;        // ceil(t_vis / chunk_tok)
+  int chunk_tok;       // tokens per attn.V tile: VT_LARGE or VT_SMALL
+  int n_chunks;        // tiles per KV head: ceil(t_vis / chunk_tok); one partial slot each
   int n_fp_chunks;     // ceil(t_fp / 128)
   int n_slots;         // n_chunks + n_fp_chunks
   int pitch;           // score row pitch in elements (multiple of 8)
@@ -110,6 +117,11 @@ __device__ __forceinline__ uint32_t prmt_sel(int byte) {
   return (uint32_t)(byte | (byte << 4) | ((4 + byte) << 8) | ((4 + byte) << 12));
 }
 
+// barrier among a subset of the CTA's warps (the producer warp takes no part)
+__device__ __forceinline__ void named_barrier_sync(int id, int n_threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+
 // ---- data-dtype helpers.  The MMA operands are always fp16: bf16 scales, minima and queries fit
 // ---- fp16 exactly (8 significant bits) within its range, so they are converted on the way in,
 // ---- while every value the reference rounds to the data dtype is rounded to T here too.
@@ -122,6 +134,11 @@ template <> struct D16<__half> {
   static __device__ __forceinline__ T2 pair2(__half a, __half b) { return __halves2half2(a, b); }
   static __device__ __forceinline__ float2 to_f2(T2 v) { return __half22float2(v); }
   static __device__ __forceinline__ float big() { return 65504.f; }
+  // two probabilities rounded to the data dtype, as an fp16 pair
+  static __device__ __forceinline__ uint32_t prob_pair(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
   // rnd(x / sqrt(128)) as the reference's division gives it: 1/sqrt(128) as two fp16 terms (the
   // second one carries the 1e-4 relative error of the first), product formed by one FMA, one rounding.
   // A plain multiply by fp16(1/sqrt(128)) lands on the neighbouring fp16 value for one logit in ten.
@@ -142,6 +159,10 @@ template <> struct D16<__nv_bfloat16> {
   static __device__ __forceinline__ T2 pair2(__nv_bfloat16 a, __nv_bfloat16 b) { return __halves2bfloat162(a, b); }
   static __device__ __forceinline__ float2 to_f2(T2 v) { return __bfloat1622float2(v); }
   static __device__ __forceinline__ float big() { return 3.0e38f; }
+  static __device__ __forceinline__ uint32_t prob_pair(float a, float b) {
+    const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
+    return to_h2(*reinterpret_cast<const uint32_t*>(&r));
+  }
   // bf16(1/sqrt(128)) would be off by up to 2^-9 (a systematic error on every logit): multiply in fp32
   static __device__ __forceinline__ T2 inv_sqrt_d(T2 x) {
     const float2 f = __bfloat1622float2(x);
@@ -483,21 +504,35 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
 // K2: attn.V partials
 // =================================================================================================
 template <typename T>
-struct CalibH {   // per head: 16-bit pairs for packed arithmetic in the data dtype, the reciprocal in fp32
-  typename D16<T>::T2 mn, range;
-  float rdenom;
+struct CalibH {   // per head: 16-bit pairs for packed arithmetic in the data dtype
+  typename D16<T>::T2 mn, range, rdenom, rdenom_lo;
 };
 
-// rnd((s - mn) / denom) * range + mn with the reference's rounding after every operation.  The quotient is
-// formed in fp32 (float(x) * (1/denom) is within an fp32 ulp of the quotient, so its rounding to 16 bits
-// differs from the reference's in one case in thousands): in bf16 one ulp of the quotient is a fifth of a
-// logit, so an approximate 16-bit reciprocal is not good enough.
+// rnd(rnd(rnd(s - mn) / denom) * range) + mn with the reference's rounding after every operation.  The
+// quotient is a product with the reciprocal carried as two 16-bit terms, formed by one FMA: it differs from
+// the rounded quotient in one case in 2^11 (fp16).
 template <typename T>
 __device__ __forceinline__ typename D16<T>::T2 calibrate2(typename D16<T>::T2 v, const CalibH<T>& cal) {
   v = __hsub2(v, cal.mn);
-  const float2 f = D16<T>::to_f2(v);
-  v = D16<T>::round2(f.x * cal.rdenom, f.y * cal.rdenom);
+  v = __hfma2(v, cal.rdenom, __hmul2(v, cal.rdenom_lo));
   return __hadd2(__hmul2(v, cal.range), cal.mn);
+}
+
+template <typename T>
+__device__ __forceinline__ void set_calib(CalibH<T>& cal, float lo, float hi) {
+  const float denom = rnd<T>(rnd<T>(hi - lo) + 1e-8f);
+  const float range = rnd<T>(rnd<T>(hi + (-3.f)) - lo);
+  cal.mn = D16<T>::bcast(lo);
+  cal.rdenom = D16<T>::bcast(1.f / denom);
+  cal.rdenom_lo = D16<T>::bcast(1.f / denom - rnd<T>(1.f / denom));
+  cal.range = D16<T>::bcast(range);
+}
+
+// 2^x by the hardware approximation (relative error 2^-22, far below the 16-bit rounding that follows)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
 }
 
 // Full-precision tokens of attn.V, chunks of 128, as a launch of its own next to k2_attn_v:
@@ -599,69 +634,78 @@ k2_fp_tokens(Dims dm, const T* __restrict__ scores, const T* __restrict__ v_fp,
   }
 }
 
-template <typename T, int BITS, int CHUNK_TOK, int VT_TOK>
-__global__ void __launch_bounds__(THREADS, CHUNK_TOK == CT_SMALL ? 4 : 3)
+// Warps 0-3 compute, warp 4 streams the tiles (V codes, scales, minima and the logits of the tile's tokens
+// for every query head of the KV head) through a ring of shared-memory stages.  Every computing warp owns a
+// quarter of a tile's tokens: it turns its logits into probabilities in registers, directly in the MMA
+// fragment order, and accumulates P.(codes) for all 128 channels.  The accumulators live across all the
+// tiles of a KV head that the CTA walks (the softmax reference is the calibrated maximum of the whole
+// visual span, known before the first tile, so no rescaling is needed); the four warps are summed and one
+// partial (max, sum, acc[128]) is written per head when the KV head changes or the CTA's range ends, into
+// the slot of the range's first tile; the other tile slots of the range are marked empty (max = -inf).
+template <typename T, int BITS, int VT>
+__global__ void __launch_bounds__(K2_THREADS, 2)
 k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile_mm,
           const int32_t* __restrict__ v_code, const T* __restrict__ v_scale,
           const T* __restrict__ v_mn,
           float* __restrict__ partial, float2* __restrict__ ml, int* __restrict__ status) {
   using T2 = typename D16<T>::T2;
-  constexpr int STAGES = k2_stages(BITS);
-  constexpr int STAGE_BYTES = k2_stage_bytes(BITS, VT_TOK);
-  constexpr int P_PITCH = CHUNK_TOK + 8;    // probability row pitch (halves): +16 B keeps the heads on different banks
-  constexpr int CODE_BYTES = VT_TOK * 16 * BITS;
+  constexpr int STAGES = k2_stages(BITS, VT);
+  constexpr int STAGE_BYTES = k2_stage_bytes(BITS, VT);
+  constexpr int CODE_BYTES = VT * 16 * BITS;
+  constexpr int LOGIT_OFF = CODE_BYTES + VT * 16;      // after the scales and the minima
+  constexpr int LROW = VT * 2 + 16;                    // bytes between the logit rows of two heads
   constexpr int TOK_BYTES = 16 * BITS;      // code bytes per token
   constexpr int WPT = 4 * BITS;             // code words per token
+  constexpr int QTOK = VT / K2_WARPS;       // tokens of a tile each warp owns
   constexpr uint32_t FIELD = (1u << BITS) - 1u;
+  constexpr int RED_STRIDE = 136;           // 128 channels + 4 group biases + 1 sum + pad
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  // dynamic smem: [stages][STAGE_BYTES] | p_s [kMaxRep][CHUNK_TOK] half | red_s [4][kMaxRep][136] float
-  __half* p_s = reinterpret_cast<__half*>(smem + STAGES * STAGE_BYTES);
-  // the cross-warp reduction buffer [4][kMaxRep][136] float reuses the probability buffer
-  float* red_s = reinterpret_cast<float*>(p_s);
-  constexpr int RED_STRIDE = 136;           // 128 channels + 4 group biases + 1 sum + pad
+  float* red_s = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES);   // [4 warps][kMaxRep][RED_STRIDE]
   __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
   __shared__ float m_s[kMaxRep];
+  // per computing warp and head: {mn, range, 1/denom (two terms)} as 16-bit pairs, then -max*log2(e) in fp32
+  __shared__ __align__(16) uint32_t cal_w[K2_WARPS][kMaxRep][8];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int n_pairs = dm.batch * dm.hkv;
-  const int n_items = n_pairs * dm.n_chunks;
-  const int n_vtiles = (dm.t_vis + VT_TOK - 1) / VT_TOK;
+  const int n_vt = dm.n_chunks;             // tiles per KV head
+  const int n_items = n_pairs * n_vt;
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], K2_WARPS); }
     mbar_fence_init();
   }
   __syncthreads();
 
-  // every CTA takes a contiguous range of (KV head, chunk) items, so that the calibration constants
-  // of a head are computed once per run of chunks
+  // every CTA takes a contiguous range of (KV head, tile) items
   const int it_first = (int)(((int64_t)blockIdx.x * n_items) / gridDim.x);
   const int it_end = (int)(((int64_t)(blockIdx.x + 1) * n_items) / gridDim.x);
-  // producer state (thread 0): next live tile to issue
-  int p_k = 0, p_ti = 0, prod = 0;
-  auto issue_next = [&]() -> bool {
-    for (;;) {
-      const int it = it_first + p_k;
-      if (it >= it_end) return false;
-      const int pair = it / dm.n_chunks, chunk = it % dm.n_chunks;
-      const int vt = chunk * (CHUNK_TOK / VT_TOK) + p_ti;
-      if (p_ti >= CHUNK_TOK / VT_TOK || vt >= n_vtiles) { ++p_k; p_ti = 0; continue; }
-      const int s = prod % STAGES;
-      unsigned char* base = smem + s * STAGE_BYTES;
-      const int64_t tok = (int64_t)pair * dm.t_vis + (int64_t)vt * VT_TOK;
-      const int nt = min(VT_TOK, dm.t_vis - vt * VT_TOK);      // a ragged last tile holds 256 tokens
-      mbar_expect_tx(&full_bar[s], (uint32_t)(nt * (TOK_BYTES + 16)));
-      bulk_load_1d(base, v_code + tok * WPT, (uint32_t)(nt * TOK_BYTES), &full_bar[s]);
-      bulk_load_1d(base + CODE_BYTES, v_scale + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
-      bulk_load_1d(base + CODE_BYTES + VT_TOK * 8, v_mn + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
-      ++prod; ++p_ti;
-      return true;
+
+  if (warp == K2_WARPS) {
+    if (lane == 0) {
+      fence_proxy_async_smem();
+      for (int k = 0; it_first + k < it_end; ++k) {
+        const int it = it_first + k, s = k % STAGES;
+        if (k >= STAGES && !mbar_wait_bounded(&empty_bar[s], (uint32_t)((k / STAGES - 1) & 1), WAIT_TRIES)) {
+          atomicExch(status, CQ_ERR_TIMEOUT);
+          break;
+        }
+        const int pair = it / n_vt, vt = it % n_vt;
+        unsigned char* base = smem + s * STAGE_BYTES;
+        const int64_t tok = (int64_t)pair * dm.t_vis + (int64_t)vt * VT;
+        const int nt = min(VT, dm.t_vis - vt * VT);
+        mbar_expect_tx(&full_bar[s], (uint32_t)(nt * (TOK_BYTES + 16) + dm.n_rep * nt * 2));
+        bulk_load_1d(base, v_code + tok * WPT, (uint32_t)(nt * TOK_BYTES), &full_bar[s]);
+        bulk_load_1d(base + CODE_BYTES, v_scale + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
+        bulk_load_1d(base + CODE_BYTES + VT * 8, v_mn + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
+        const T* srow = scores + (int64_t)pair * dm.n_rep * dm.pitch + (int64_t)vt * VT;
+        for (int h = 0; h < dm.n_rep; ++h)
+          bulk_load_1d(base + LOGIT_OFF + h * LROW, srow + (int64_t)h * dm.pitch, (uint32_t)(nt * 2), &full_bar[s]);
+      }
     }
-  };
-  if (tid == 0) {
-    fence_proxy_async_smem();
-    for (int i = 0; i < STAGES - 1; ++i) issue_next();
+    return;
   }
 
   // lane constants for expanding the channel pair that rows g, g+8 of m-tile j stand for
@@ -680,228 +724,229 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
     sc1[i] = exp2f((float)(24 - sh - BITS));
   }
 
-  int cons = 0, cal_pair = -1;
+  float acc[8][4];
+  float cb[4];
+  int seg_pair = -1, seg_first = 0, seg_end = 0;     // the run of tiles of one KV head accumulated so far
   bool failed = false;
-  // Per query head of the current KV head: calibration constants and the reference maximum of the
-  // softmax.  The reference maximum is the (calibrated) maximum over the WHOLE visual span, known from
-  // the per-tile min/max the score kernel left, so the probabilities of a chunk need no reduction of
-  // their own and every thread can take any (head, 8 tokens) vector of the chunk.
-  __shared__ CalibH<T> cal_s[kMaxRep];
-  constexpr int NVEC = CHUNK_TOK / 8;                                   // 8-token vectors per head and chunk
-  const T2 zero2 = D16<T>::bcast(0.f);
-  int pair = it_first / dm.n_chunks, chunk = it_first % dm.n_chunks;   // advanced item by item below
-  for (int k = 0; !failed; ++k) {
-    const int it = it_first + k;
-    if (it >= it_end) break;
-    if (k > 0 && ++chunk == dm.n_chunks) { chunk = 0; ++pair; }
-    const int64_t row0 = (int64_t)pair * dm.n_rep;        // = b * hq + hk * n_rep
-    const int tok_base = chunk * CHUNK_TOK;
-    // additive mask of this batch row, at the chunk's first visual key (added after calibration, rounded
-    // to the data dtype as the tensor addition of the reference is)
-    const T* mvis = dm.mask ? static_cast<const T*>(dm.mask) + (int64_t)(pair / dm.hkv) * dm.mask_stride_b +
-                              dm.t_sys + tok_base : nullptr;
-    const int n_tok = min(CHUNK_TOK, dm.t_vis - tok_base);
+  // calibration constants and softmax reference of the head this lane's probabilities belong to (head g)
+  CalibH<T> cal;
+  cal.mn = cal.range = cal.rdenom = cal.rdenom_lo = D16<T>::bcast(0.f);
+  float m_ref = 0.f;
 
-    if (pair != cal_pair) {      // uniform over the CTA; the previous item ended with a CTA barrier
-      for (int h = warp; h < dm.n_rep; h += 4) {
-        float lo = INFINITY, hi = -INFINITY;
-        for (int i = lane; i < (dm.raw ? 0 : dm.n_mm); i += 32) {
-          const float2 v = tile_mm[(row0 + h) * dm.n_mm + i];
-          lo = fminf(lo, v.x);
-          hi = fmaxf(hi, v.y);
-        }
-        lo = warp_min(lo);
-        hi = warp_max(hi);
-        CalibH<T> cal;
-        cal.mn = cal.range = zero2;
-        cal.rdenom = 0.f;
-        float m_ref = hi;
-        if (dm.calibrate) {
-          const float denom = rnd<T>(rnd<T>(hi - lo) + 1e-8f);
-          const float range = rnd<T>(rnd<T>(hi + (-3.f)) - lo);
-          cal.mn = D16<T>::bcast(lo);
-          cal.rdenom = 1.f / denom;
-          cal.range = D16<T>::bcast(range);
-          m_ref = D16<T>::to_f2(calibrate2<T>(D16<T>::bcast(hi), cal)).x;     // the maximum, calibrated like any logit
-        }
-        if (lane == 0) {
-          cal_s[h] = cal;
-          m_s[h] = dm.raw ? 0.f : m_ref;      // the calibration is monotone: no logit of the span exceeds it
-        }
+  // sum the four warps' accumulators of the finished run and write its partial
+  auto flush = [&]() {
+    const int64_t row0 = (int64_t)seg_pair * dm.n_rep;
+    float* mine = red_s + warp * kMaxRep * RED_STRIDE;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = (BITS == 1) ? (j & 1) : 0;
+      const int ch = BITS == 1 ? 32 * (j >> 1) + Expand<1>::elem(i, g) : 16 * j + 2 * g;
+      if (2 * c < dm.n_rep) {
+        mine[(2 * c) * RED_STRIDE + ch] = acc[j][0] * sc0[i];
+        mine[(2 * c) * RED_STRIDE + ch + 1] = acc[j][2] * sc1[i];
       }
-      cal_pair = pair;
-      __syncthreads();
-    }
-
-    // ---- probabilities of the chunk ------------------------------------------------------------
-    for (int vi = tid; vi < dm.n_rep * NVEC; vi += THREADS) {
-      const int h = vi / NVEC, t = (vi % NVEC) * 8;
-      uint4 out = make_uint4(0u, 0u, 0u, 0u);
-      if (t < n_tok) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(scores + (row0 + h) * dm.pitch + tok_base + t);
-        const T2* r2 = reinterpret_cast<const T2*>(&raw);
-        const CalibH<T> cal = cal_s[h];
-        const float m = m_s[h];
-        __half2* o2 = reinterpret_cast<__half2*>(&out);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          T2 v = r2[e];
-          if (dm.calibrate) v = calibrate2<T>(v, cal);
-          if (mvis) v = __hadd2(v, D16<T>::pair2(mvis[t + 2 * e], mvis[t + 2 * e + 1]));
-          const float2 f = D16<T>::to_f2(v);
-          // the reference rounds the probabilities to the data dtype; they are then exact in fp16.
-          // Plain product: the row holds the weights themselves.
-          o2[e] = dm.raw ? __floats2half2_rn(f.x, f.y)
-                         : __floats2half2_rn(rnd<T>(exp2f((f.x - m) * LOG2E)), rnd<T>(exp2f((f.y - m) * LOG2E)));
-        }
-      }
-      *reinterpret_cast<uint4*>(p_s + h * P_PITCH + t) = out;
-    }
-    __syncthreads();
-
-    float acc[8][4];
-    float cb[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int j = 0; j < 8; ++j)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
-
-    for (int ti = 0; ti < CHUNK_TOK / VT_TOK; ++ti) {
-      const int vt = chunk * (CHUNK_TOK / VT_TOK) + ti;
-      if (vt >= n_vtiles) break;
-      if (tid == 0) {
-        fence_proxy_async_smem();
-        while (prod < cons + STAGES) if (!issue_next()) break;
-      }
-      const int s = cons % STAGES;
-      if (!mbar_wait_bounded(&full_bar[s], (uint32_t)((cons / STAGES) & 1), WAIT_TRIES)) {
-        atomicExch(status, CQ_ERR_TIMEOUT);
-        failed = true;
-        break;
-      }
-      ++cons;
-      const uint32_t code_b = smem_u32(smem + s * STAGE_BYTES);
-      const uint32_t vs_b = code_b + CODE_BYTES, vmn_b = vs_b + VT_TOK * 8;
-      const uint32_t p_b = smem_u32(p_s) + (uint32_t)((g < dm.n_rep ? g : 0) * P_PITCH + ti * VT_TOK) * 2u;
-
-      const int nt_tile = min(VT_TOK, dm.t_vis - vt * VT_TOK);
-      {
-        // Scales and minima of this warp's quarter of the tile, re-laid out in place: each 16-byte
-        // unit holds two tokens x four channel groups; it becomes four (token, token+1) pairs, one
-        // per group, which is the MMA B-fragment order, so the main loop needs no permutes.  bf16
-        // values are converted to fp16 on the way.
-#pragma unroll
-        for (int arr = 0; arr < 2; ++arr) {
-          const uint32_t base = (arr == 0 ? vs_b : vmn_b) + (uint32_t)(warp * (VT_TOK / 4)) * 8u;
-#pragma unroll
-          for (int i = 0; i < VT_TOK / 256; ++i) {
-            const uint32_t addr = base + (uint32_t)(i * 32 + lane) * 16u;
-            uint4 v = lds128(addr);
-            v.x = D16<T>::to_h2(v.x); v.y = D16<T>::to_h2(v.y); v.z = D16<T>::to_h2(v.z); v.w = D16<T>::to_h2(v.w);
-            const uint32_t o0 = prmt(v.x, v.z, 0x5410), o1 = prmt(v.x, v.z, 0x7632);
-            const uint32_t o2 = prmt(v.y, v.w, 0x5410), o3 = prmt(v.y, v.w, 0x7632);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
-          }
-        }
-        __syncwarp();
-      }
-      const uint32_t zoff = (uint32_t)(g < 4 ? g : 0) * 4u;   // this lane's column of the minima MMA
-      const uint32_t z_and = g < 4 ? 0xffffffffu : 0u, z_or = g == 4 ? 0x3c003c00u : 0u;   // column 4 = ones
-#pragma unroll
-      for (int kq = 0; kq < VT_TOK / 64; ++kq) {
-        if (warp * (VT_TOK / 4) + kq * 16 >= nt_tile) break;
-        const int t0 = warp * (VT_TOK / 4) + kq * 16 + 2 * c;   // token (in tile) of the lane's first k pair
-        uint32_t pp0 = lds32(p_b + (uint32_t)t0 * 2u), pp1 = lds32(p_b + (uint32_t)(t0 + 8) * 2u);
-        if (g >= dm.n_rep) { pp0 = 0u; pp1 = 0u; }
-        // scale pairs of tokens (t0, t0+1) and (t0+8, t0+9), one register per channel group
-        const uint4 s0 = lds128(vs_b + (uint32_t)t0 * 8u), s1 = lds128(vs_b + (uint32_t)(t0 + 8) * 8u);
-        uint32_t bA[4], bB[4];
-        bA[0] = hmul2_u32(pp0, s0.x); bA[1] = hmul2_u32(pp0, s0.y); bA[2] = hmul2_u32(pp0, s0.z); bA[3] = hmul2_u32(pp0, s0.w);
-        bB[0] = hmul2_u32(pp1, s1.x); bB[1] = hmul2_u32(pp1, s1.y); bB[2] = hmul2_u32(pp1, s1.z); bB[3] = hmul2_u32(pp1, s1.w);
-        // minima + row sum: A = p (rows = heads), B column n = g: n<4 -> vmn[.][n], n==4 -> 1
-        {
-          const uint32_t zb0 = (lds32(vmn_b + (uint32_t)t0 * 8u + zoff) & z_and) | z_or;
-          const uint32_t zb1 = (lds32(vmn_b + (uint32_t)(t0 + 8) * 8u + zoff) & z_and) | z_or;
-          mma_f16(cb, pp0, 0u, pp1, 0u, zb0, zb1);
-        }
-        // code words of the lane's four tokens
-        const uint32_t tb = code_b + (uint32_t)t0 * TOK_BYTES;
-#pragma unroll
-        for (int part = 0; part < BITS; ++part) {      // 16 bytes of every token row at a time
-          const uint4 wa = lds128(tb + part * 16), wb = lds128(tb + TOK_BYTES + part * 16);
-          const uint4 wc = lds128(tb + 8 * TOK_BYTES + part * 16), wd = lds128(tb + 9 * TOK_BYTES + part * 16);
-          const uint32_t Wa[4] = {wa.x, wa.y, wa.z, wa.w}, Wb[4] = {wb.x, wb.y, wb.z, wb.w};
-          const uint32_t Wc[4] = {wc.x, wc.y, wc.z, wc.w}, Wd[4] = {wd.x, wd.y, wd.z, wd.w};
-          // m-tiles covered by these 4 words: 128/BITS channels = 8/BITS m-tiles
-          if (BITS == 1) {      // word m = channels 32m .. 32m+31 = m-tiles 2m, 2m+1, one byte permute for both
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-              const uint32_t x01 = prmt(Wa[m], Wb[m], sel[0]), x89 = prmt(Wc[m], Wd[m], sel[0]);
-#pragma unroll
-              for (int i = 0; i < 2; ++i)
-                mma_f16(acc[2 * m + i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bA[m], bB[m]);
-            }
-          } else
-#pragma unroll
-          for (int jj = 0; jj < 8 / BITS; ++jj) {
-            const int j = part * (8 / BITS) + jj;          // m-tile = channels 16j .. 16j+15
-            const int gq = j >> 1;                         // 32-channel group -> scale
-            const int wi = BITS == 2 ? jj : 2 * jj + (g >> 2), i = 0;
-            uint32_t a, bw, cw, dw;
-            if (BITS == 4) {
-              const bool hi = g >> 2;
-              a = hi ? Wa[2 * jj + 1] : Wa[2 * jj]; bw = hi ? Wb[2 * jj + 1] : Wb[2 * jj];
-              cw = hi ? Wc[2 * jj + 1] : Wc[2 * jj]; dw = hi ? Wd[2 * jj + 1] : Wd[2 * jj];
-              (void)wi;
-            } else {
-              a = Wa[wi]; bw = Wb[wi]; cw = Wc[wi]; dw = Wd[wi];
-            }
-            const uint32_t x01 = prmt(a, bw, sel[i]), x89 = prmt(cw, dw, sel[i]);
-            mma_f16(acc[j], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bA[gq], bB[gq]);
-          }
-        }
-      }
-      __syncthreads();
-    }
-    if (failed) break;
-
-    // ---- reduce the four warps, write the partial of this chunk --------------------------------
-    {
-      float* mine = red_s + warp * kMaxRep * RED_STRIDE;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int i = (BITS == 1) ? (j & 1) : 0;
-        const int ch = BITS == 1 ? 32 * (j >> 1) + Expand<1>::elem(i, g) : 16 * j + 2 * g;
-        if (2 * c < dm.n_rep) {
-          mine[(2 * c) * RED_STRIDE + ch] = acc[j][0] * sc0[i];
-          mine[(2 * c) * RED_STRIDE + ch + 1] = acc[j][2] * sc1[i];
-        }
-        if (2 * c + 1 < dm.n_rep) {
-          mine[(2 * c + 1) * RED_STRIDE + ch] = acc[j][1] * sc0[i];
-          mine[(2 * c + 1) * RED_STRIDE + ch + 1] = acc[j][3] * sc1[i];
-        }
-      }
-      if (g < dm.n_rep && c < 3) {      // bias columns 0..3 (c = 0,1) and the row sum (c = 2, col 4)
-        mine[g * RED_STRIDE + 128 + 2 * c] = cb[0];
-        if (c < 2) mine[g * RED_STRIDE + 128 + 2 * c + 1] = cb[1];
+      if (2 * c + 1 < dm.n_rep) {
+        mine[(2 * c + 1) * RED_STRIDE + ch] = acc[j][1] * sc0[i];
+        mine[(2 * c + 1) * RED_STRIDE + ch + 1] = acc[j][3] * sc1[i];
       }
     }
-    __syncthreads();
+    if (g < dm.n_rep && c < 3) {      // bias columns 0..3 (c = 0,1) and the row sum (c = 2, col 4)
+      mine[g * RED_STRIDE + 128 + 2 * c] = cb[0];
+      if (c < 2) mine[g * RED_STRIDE + 128 + 2 * c + 1] = cb[1];
+    }
+    named_barrier_sync(1, K2_WARPS * 32);
     for (int h = 0; h < dm.n_rep; ++h) {
       float o = 0.f, l = 0.f;
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+      for (int w = 0; w < K2_WARPS; ++w) {
         const float* r = red_s + (w * kMaxRep + h) * RED_STRIDE;
         o += r[tid] + r[128 + (tid >> 5)];
         l += r[132];
       }
-      partial[((row0 + h) * dm.n_slots + chunk) * kHeadDim + tid] = o;
-      if (tid == 0) ml[(row0 + h) * dm.n_slots + chunk] = make_float2(m_s[h], l);
+      partial[((row0 + h) * dm.n_slots + seg_first) * kHeadDim + tid] = o;
+      if (tid == 0) ml[(row0 + h) * dm.n_slots + seg_first] = make_float2(m_s[h], l);
     }
-    __syncthreads();
+    // the other tile slots of the run hold nothing
+    for (int i = tid; i < dm.n_rep * (seg_end - seg_first - 1); i += K2_WARPS * 32) {
+      const int h = i / (seg_end - seg_first - 1), sl = seg_first + 1 + i % (seg_end - seg_first - 1);
+      ml[(row0 + h) * dm.n_slots + sl] = make_float2(-INFINITY, 0.f);
+    }
+    named_barrier_sync(1, K2_WARPS * 32);
+  };
+
+  for (int k = 0;; ++k) {
+    const int it = it_first + k;
+    if (it >= it_end) break;
+    const int s = k % STAGES;
+    const int pair = it / n_vt, vt = it % n_vt;
+    if (pair != seg_pair) {
+      if (seg_pair >= 0) flush();
+      seg_pair = pair; seg_first = vt;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+      cb[0] = cb[1] = cb[2] = cb[3] = 0.f;
+      // calibration constants of head g: the four lanes of a head share the per-tile min/max entries
+      float lo = INFINITY, hi = -INFINITY;
+      if (g < dm.n_rep && !dm.raw) {
+        const float2* mm = tile_mm + ((int64_t)pair * dm.n_rep + g) * dm.n_mm;
+        for (int i = c; i < dm.n_mm; i += 4) {
+          const float2 v = mm[i];
+          lo = fminf(lo, v.x);
+          hi = fmaxf(hi, v.y);
+        }
+      }
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, 1)); hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, 1));
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, 2)); hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, 2));
+      m_ref = dm.raw ? 0.f : hi;
+      if (dm.calibrate && g < dm.n_rep && !dm.raw) {
+        set_calib<T>(cal, lo, hi);
+        m_ref = D16<T>::to_f2(calibrate2<T>(D16<T>::bcast(hi), cal)).x;     // the maximum, calibrated like any logit
+      }
+      if (warp == 0 && c == 0 && g < dm.n_rep) m_s[g] = m_ref;              // read back by thread 0 in flush()
+      // the lanes of the warp share out the (head, token pair) logits of a tile: the constants of every
+      // head go to this warp's table
+      __syncwarp();
+      if (c == 0 && g < dm.n_rep) {
+        uint32_t* e = cal_w[warp][g];
+        e[0] = *reinterpret_cast<const uint32_t*>(&cal.mn); e[1] = *reinterpret_cast<const uint32_t*>(&cal.range);
+        e[2] = *reinterpret_cast<const uint32_t*>(&cal.rdenom); e[3] = *reinterpret_cast<const uint32_t*>(&cal.rdenom_lo);
+        e[4] = __float_as_uint(-m_ref * LOG2E);
+      }
+      __syncwarp();
+    }
+    seg_end = vt + 1;
+    // additive mask of this batch row, at the tile's first visual key (added after calibration, rounded
+    // to the data dtype as the tensor addition of the reference is)
+    const T* mvis = dm.mask ? static_cast<const T*>(dm.mask) + (int64_t)(pair / dm.hkv) * dm.mask_stride_b +
+                              dm.t_sys + vt * VT : nullptr;
+    if (!mbar_wait_bounded(&full_bar[s], (uint32_t)((k / STAGES) & 1), WAIT_TRIES)) {
+      atomicExch(status, CQ_ERR_TIMEOUT);
+      failed = true;
+      break;
+    }
+    const uint32_t code_b = smem_u32(smem + s * STAGE_BYTES);
+    const uint32_t vs_b = code_b + CODE_BYTES, vmn_b = vs_b + VT * 8;
+    const uint32_t lg_b = code_b + LOGIT_OFF + (uint32_t)((g < dm.n_rep ? g : 0) * LROW);
+    const int nt_tile = min(VT, dm.t_vis - vt * VT);
+    {
+      // Scales and minima of this warp's quarter of the tile, re-laid out in place: each 16-byte
+      // unit holds two tokens x four channel groups; it becomes four (token, token+1) pairs, one
+      // per group, which is the MMA B-fragment order, so the main loop needs no permutes.  bf16
+      // values are converted to fp16 on the way.
+#pragma unroll
+      for (int arr = 0; arr < 2; ++arr) {
+        const uint32_t base = (arr == 0 ? vs_b : vmn_b) + (uint32_t)(warp * QTOK) * 8u;
+#pragma unroll
+        for (int i = 0; i < QTOK / 64; ++i) {
+          const uint32_t addr = base + (uint32_t)(i * 32 + lane) * 16u;
+          uint4 v = lds128(addr);
+          v.x = D16<T>::to_h2(v.x); v.y = D16<T>::to_h2(v.y); v.z = D16<T>::to_h2(v.z); v.w = D16<T>::to_h2(v.w);
+          const uint32_t o0 = prmt(v.x, v.z, 0x5410), o1 = prmt(v.x, v.z, 0x7632);
+          const uint32_t o2 = prmt(v.y, v.w, 0x5410), o3 = prmt(v.y, v.w, 0x7632);
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
+        }
+      }
+      __syncwarp();
+    }
+    // ---- probabilities of this warp's quarter, all heads, in place over the logits: the lanes share out
+    // the (head, token pair) elements; the head is uniform over the warp in every pass.  The reference rounds
+    // the probabilities to the data dtype; they are then exact in fp16, the type the MMA takes.
+    if (!(dm.raw && std::is_same<T, __half>::value)) {
+      const uint32_t q_b = code_b + LOGIT_OFF + (uint32_t)(warp * QTOK) * 2u;
+      const uint32_t cal_b = smem_u32(&cal_w[warp][0][0]);
+#pragma unroll 2
+      for (int h = 0; h < dm.n_rep; ++h) {
+        const uint4 cw = lds128(cal_b + (uint32_t)h * 32u);
+        const float mneg = __uint_as_float(lds32(cal_b + (uint32_t)h * 32u + 16u));
+        CalibH<T> ch;
+        ch.mn = *reinterpret_cast<const T2*>(&cw.x); ch.range = *reinterpret_cast<const T2*>(&cw.y);
+        ch.rdenom = *reinterpret_cast<const T2*>(&cw.z); ch.rdenom_lo = *reinterpret_cast<const T2*>(&cw.w);
+#pragma unroll
+        for (int j = 0; j < QTOK / 64; ++j) {
+          const int tp = (j * 32 + lane) * 2;                 // first token of the pair, within the quarter
+          if (warp * QTOK + tp < nt_tile) {
+            const uint32_t addr = q_b + (uint32_t)(h * LROW + tp * 2);
+            const uint32_t x = lds32(addr);
+            uint32_t pp;
+            if (dm.raw) {                                     // plain product: the row holds the weights themselves
+              pp = D16<T>::to_h2(x);
+            } else {
+              T2 v = *reinterpret_cast<const T2*>(&x);
+              if (dm.calibrate) v = calibrate2<T>(v, ch);
+              if (mvis) v = __hadd2(v, D16<T>::pair2(mvis[warp * QTOK + tp], mvis[warp * QTOK + tp + 1]));
+              const float2 f = D16<T>::to_f2(v);
+              pp = D16<T>::prob_pair(ex2_approx(fmaf(f.x, LOG2E, mneg)), ex2_approx(fmaf(f.y, LOG2E, mneg)));
+            }
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(pp) : "memory");
+          }
+        }
+      }
+      __syncwarp();
+    }
+    const uint32_t zoff = (uint32_t)(g < 4 ? g : 0) * 4u;   // this lane's column of the minima MMA
+    const uint32_t z_and = g < 4 ? 0xffffffffu : 0u, z_or = g == 4 ? 0x3c003c00u : 0u;   // column 4 = ones
+#pragma unroll
+    for (int kq = 0; kq < QTOK / 16; ++kq) {
+      if (warp * QTOK + kq * 16 >= nt_tile) break;
+      const int t0 = warp * QTOK + kq * 16 + 2 * c;   // token (in tile) of the lane's first k pair
+      uint32_t pp0 = lds32(lg_b + (uint32_t)t0 * 2u), pp1 = lds32(lg_b + (uint32_t)(t0 + 8) * 2u);
+      if (g >= dm.n_rep) { pp0 = 0u; pp1 = 0u; }
+      // scale pairs of tokens (t0, t0+1) and (t0+8, t0+9), one register per channel group
+      const uint4 s0 = lds128(vs_b + (uint32_t)t0 * 8u), s1 = lds128(vs_b + (uint32_t)(t0 + 8) * 8u);
+      uint32_t bA[4], bB[4];
+      bA[0] = hmul2_u32(pp0, s0.x); bA[1] = hmul2_u32(pp0, s0.y); bA[2] = hmul2_u32(pp0, s0.z); bA[3] = hmul2_u32(pp0, s0.w);
+      bB[0] = hmul2_u32(pp1, s1.x); bB[1] = hmul2_u32(pp1, s1.y); bB[2] = hmul2_u32(pp1, s1.z); bB[3] = hmul2_u32(pp1, s1.w);
+      // minima + row sum: A = p (rows = heads), B column n = g: n<4 -> vmn[.][n], n==4 -> 1
+      {
+        const uint32_t zb0 = (lds32(vmn_b + (uint32_t)t0 * 8u + zoff) & z_and) | z_or;
+        const uint32_t zb1 = (lds32(vmn_b + (uint32_t)(t0 + 8) * 8u + zoff) & z_and) | z_or;
+        mma_f16(cb, pp0, 0u, pp1, 0u, zb0, zb1);
+      }
+      // code words of the lane's four tokens
+      const uint32_t tb = code_b + (uint32_t)t0 * TOK_BYTES;
+#pragma unroll
+      for (int part = 0; part < BITS; ++part) {      // 16 bytes of every token row at a time
+        const uint4 wa = lds128(tb + part * 16), wb = lds128(tb + TOK_BYTES + part * 16);
+        const uint4 wc = lds128(tb + 8 * TOK_BYTES + part * 16), wd = lds128(tb + 9 * TOK_BYTES + part * 16);
+        const uint32_t Wa[4] = {wa.x, wa.y, wa.z, wa.w}, Wb[4] = {wb.x, wb.y, wb.z, wb.w};
+        const uint32_t Wc[4] = {wc.x, wc.y, wc.z, wc.w}, Wd[4] = {wd.x, wd.y, wd.z, wd.w};
+        // m-tiles covered by these 4 words: 128/BITS channels = 8/BITS m-tiles
+        if (BITS == 1) {      // word m = channels 32m .. 32m+31 = m-tiles 2m, 2m+1, one byte permute for both
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const uint32_t x01 = prmt(Wa[m], Wb[m], sel[0]), x89 = prmt(Wc[m], Wd[m], sel[0]);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              mma_f16(acc[2 * m + i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bA[m], bB[m]);
+          }
+        } else
+#pragma unroll
+        for (int jj = 0; jj < 8 / BITS; ++jj) {
+          const int j = part * (8 / BITS) + jj;          // m-tile = channels 16j .. 16j+15
+          const int gq = j >> 1;                         // 32-channel group -> scale
+          const int wi = BITS == 2 ? jj : 2 * jj + (g >> 2), i = 0;
+          uint32_t a, bw, cw, dw;
+          if (BITS == 4) {
+            const bool hi = g >> 2;
+            a = hi ? Wa[2 * jj + 1] : Wa[2 * jj]; bw = hi ? Wb[2 * jj + 1] : Wb[2 * jj];
+            cw = hi ? Wc[2 * jj + 1] : Wc[2 * jj]; dw = hi ? Wd[2 * jj + 1] : Wd[2 * jj];
+            (void)wi;
+          } else {
+            a = Wa[wi]; bw = Wb[wi]; cw = Wc[wi]; dw = Wd[wi];
+          }
+          const uint32_t x01 = prmt(a, bw, sel[i]), x89 = prmt(cw, dw, sel[i]);
+          mma_f16(acc[j], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bA[gq], bB[gq]);
+        }
+      }
+    }
+    // the stage has been read: hand it back to the producer
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
   }
   if (failed) return;
-
+  if (seg_pair >= 0) flush();
 }
 
 // =================================================================================================
@@ -928,6 +973,7 @@ k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict_
 #pragma unroll 8
   for (int i = sl; i < n_live; i += K3_LANES) {
     const float2 mlv = __ldg(&r[i]);
+    if (mlv.x == -INFINITY) continue;      // an empty slot (its run of tiles was accumulated into an earlier one)
     const float w = exp2f((mlv.x - M) * LOG2E);
     L = fmaf(mlv.y, w, L);
     o = fmaf(__ldg(p + (int64_t)i * kHeadDim), w, o);
@@ -1017,8 +1063,8 @@ static Dims make_dims(const cq_decode_args* a) {
   d.t_vis = a->t_vis; d.t_fp = a->t_fp; d.calibrate = a->calibrate ? 1 : 0;
   d.n_groups = d.t_vis / 32;
   d.n_ktiles = (d.n_groups + TILE_G - 1) / TILE_G;
-  // the large items only when they fill the resident CTAs about three times over
-  d.chunk_tok = (int64_t)d.batch * d.hkv * ((d.t_vis + CT_LARGE - 1) / CT_LARGE) >= 3 * K2_RESIDENT ? CT_LARGE : CT_SMALL;
+  // the large tiles only when they give every resident CTA a few of them
+  d.chunk_tok = (int64_t)d.batch * d.hkv * ((d.t_vis + VT_LARGE - 1) / VT_LARGE) >= 2 * K2_RESIDENT ? VT_LARGE : VT_SMALL;
   d.n_chunks = (d.t_vis + d.chunk_tok - 1) / d.chunk_tok;
   d.n_fp_chunks = (d.t_fp + 127) / 128;
   d.n_slots = d.n_chunks + d.n_fp_chunks;
@@ -1050,9 +1096,10 @@ static int sm_count() {      // of the current device
   return v;
 }
 
-template <typename T, int BITS, int CT, int VT>
-static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st) {
-  int* status = reinterpret_cast<int*>(ws + l.status_off);
+template <typename T, int BITS, int VT>
+static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st,
+                     cudaEvent_t* ev, int* status_word) {
+  int* status = status_word ? status_word : reinterpret_cast<int*>(ws + l.status_off);
   T* scores = reinterpret_cast<T*>(ws + l.scores_off);
   float2* mm = reinterpret_cast<float2*>(ws + l.mm_off);
   float2* ml = reinterpret_cast<float2*>(ws + l.ml_off);
@@ -1060,10 +1107,9 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
   const int n_pairs = d.batch * d.hkv;
 
   auto k1 = d.n_rep <= 4 ? k1_scores<T, BITS, true> : k1_scores<T, BITS, false>;
-  auto k2 = k2_attn_v<T, BITS, CT, VT>;
+  auto k2 = k2_attn_v<T, BITS, VT>;
   const int smem1 = k1_stages(BITS) * k1_stage_bytes(BITS) + 1024;
-  constexpr int p_bytes = kMaxRep * (CT + 8) * 2, red_bytes = 4 * kMaxRep * 136 * 4;
-  const int smem2 = k2_stages(BITS) * k2_stage_bytes(BITS, VT) + (p_bytes > red_bytes ? p_bytes : red_bytes) + 1024;
+  const int smem2 = k2_smem_bytes(BITS, VT);
   static bool configured_dev[64][2] = {};   // per template instance, device and score-kernel variant
   static int occ1_dev[64][2], occ2_dev[64][2];
   int dev = 0;
@@ -1078,13 +1124,13 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
     if (cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1) != cudaSuccess) return CQ_ERR_LAUNCH;
     if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return CQ_ERR_LAUNCH;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ1, k1, K1_THREADS, smem1) != cudaSuccess || occ1 < 1) return CQ_ERR_LAUNCH;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ2, k2, THREADS, smem2) != cudaSuccess || occ2 < 1) return CQ_ERR_LAUNCH;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ2, k2, K2_THREADS, smem2) != cudaSuccess || occ2 < 1) return CQ_ERR_LAUNCH;
     configured = true;
   }
-  // args->reserved is a profiling aid: 0 runs all three launches, otherwise bit 0/1/2 selects the
-  // scores / attn.V / combine launch to run alone on buffers a full call has already filled.
-  const int stages = a->reserved ? a->reserved : 7;
-  if (d.t_vis > 0 && (stages & 1)) {
+  // `ev` (profiling entry point only): five events recorded around the four launches
+  auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], st); };
+  mark(0);
+  if (d.t_vis > 0) {
     CUtensorMap tm_code, tm_ks, tm_kmn;
     const uint64_t rows = (uint64_t)n_pairs * kHeadDim;
     if (!make_k_maps<BITS>(&tm_code, &tm_ks, &tm_kmn, a->k_code, a->k_scale, a->k_mn, (uint64_t)d.n_groups, rows))
@@ -1096,42 +1142,42 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
   }
-  if (stages & 2) {
+  mark(1);
+  {
     const int items2 = n_pairs * d.n_chunks;
     const int grid2 = max(1, min(items2, sm_count() * occ2));
-    k2<<<grid2, THREADS, smem2, st>>>(d, scores, mm, a->v_code, static_cast<const T*>(a->v_scale),
+    k2<<<grid2, K2_THREADS, smem2, st>>>(d, scores, mm, a->v_code, static_cast<const T*>(a->v_scale),
                                       static_cast<const T*>(a->v_mn), partial, ml, status);
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
+    mark(2);
     if (d.n_fp_chunks > 0) {
       k2_fp_tokens<T><<<n_pairs * d.n_fp_chunks, THREADS, 0, st>>>(d, scores, static_cast<const T*>(a->v_fp),
                                                                  partial, ml);
       rc = check_launch();
       if (rc != CQ_OK) return rc;
     }
+    mark(3);
   }
-  if (stages & 4) {
-    if (d.n_slots >= 16)
-      k3_combine<T, 4><<<d.batch * d.hq, kHeadDim * 4, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
-    else
-      k3_combine<T, 1><<<d.batch * d.hq, kHeadDim, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
-    return check_launch();
-  }
-  return CQ_OK;
+  if (d.n_slots >= 16)
+    k3_combine<T, 4><<<d.batch * d.hq, kHeadDim * 4, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
+  else
+    k3_combine<T, 1><<<d.batch * d.hq, kHeadDim, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
+  const int rc3 = check_launch();
+  mark(4);
+  return rc3;
 }
 
 template <typename T, int BITS>
-static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st) {
-  return d.chunk_tok == CT_LARGE ? run_shape<T, BITS, CT_LARGE, VT_LARGE>(a, d, l, ws, st)
-                                 : run_shape<T, BITS, CT_SMALL, VT_SMALL>(a, d, l, ws, st);
+static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st,
+               cudaEvent_t* ev, int* status_word) {
+  return d.chunk_tok == VT_LARGE ? run_shape<T, BITS, VT_LARGE>(a, d, l, ws, st, ev, status_word)
+                                 : run_shape<T, BITS, VT_SMALL>(a, d, l, ws, st, ev, status_word);
 }
 
 }  // namespace mma
 
 bool mma_path_eligible(const cq_decode_args* a) {
-  // CQ_DECODE_GENERAL=1 forces the general kernels (A/B comparison of the two paths).
-  static const bool disabled = []() { const char* e = getenv("CQ_DECODE_GENERAL"); return e && e[0] == '1'; }();
-  if (disabled) return false;
   if (a->t_vis <= 0 || a->t_vis % 256 != 0) return false;
   if (a->bits != 1 && a->bits != 2 && a->bits != 4) return false;
   const void* ptrs[] = {a->q, a->k_code, a->k_scale, a->k_mn, a->v_code, a->v_scale, a->v_mn};
@@ -1152,8 +1198,7 @@ static bool qbmm_ptrs_ok(const void* fA, const void* qB, const void* s, const vo
 
 int mma_qbmm_kind(const void* fA, const void* qB, const void* scales, const void* zeros, const void* out,
                   int n_q_heads, int n_kv_heads, int64_t K, int64_t N) {
-  static const bool disabled = []() { const char* e = getenv("CQ_DECODE_GENERAL"); return e && e[0] == '1'; }();
-  if (disabled || !qbmm_ptrs_ok(fA, qB, scales, zeros, out)) return 0;
+  if (!qbmm_ptrs_ok(fA, qB, scales, zeros, out)) return 0;
   if (n_q_heads / n_kv_heads > kMaxRep || K > 0x3fffffff || N > 0x3fffffff) return 0;
   if (K == kHeadDim && N % 256 == 0) return 1;
   if (N == kHeadDim && K % 256 == 0) return 2;
@@ -1217,25 +1262,19 @@ static int qbmm_run_t(int kind, const mma::Dims& d, const void* fA, const int32_
     std::lock_guard<std::mutex> lock(mu);
     if (!configured[dev]) {
       if (cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess) return CQ_ERR_LAUNCH;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[dev], k2, THREADS, smem2) != cudaSuccess || occ[dev] < 1) return CQ_ERR_LAUNCH;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ[dev], k2, K2_THREADS, smem2) != cudaSuccess || occ[dev] < 1) return CQ_ERR_LAUNCH;
       configured[dev] = true;
     }
     const int grid = max(1, min(n_pairs * d.n_chunks, sm_count() * occ[dev]));
-    k2<<<grid, THREADS, smem2, st>>>(d, static_cast<const T*>(fA), nullptr, qB, static_cast<const T*>(scales),
+    k2<<<grid, K2_THREADS, smem2, st>>>(d, static_cast<const T*>(fA), nullptr, qB, static_cast<const T*>(scales),
                                      static_cast<const T*>(zeros), partial, ml, status);
     return check_launch();
   };
-  constexpr int red_bytes = 4 * kMaxRep * 136 * 4;
   int rc;
-  if (d.chunk_tok == CT_LARGE) {
-    constexpr int p_bytes = kMaxRep * (CT_LARGE + 8) * 2;
-    rc = launch_k2(k2_attn_v<T, BITS, CT_LARGE, VT_LARGE>,
-                   k2_stages(BITS) * k2_stage_bytes(BITS, VT_LARGE) + (p_bytes > red_bytes ? p_bytes : red_bytes) + 1024);
-  } else {
-    constexpr int p_bytes = kMaxRep * (CT_SMALL + 8) * 2;
-    rc = launch_k2(k2_attn_v<T, BITS, CT_SMALL, VT_SMALL>,
-                   k2_stages(BITS) * k2_stage_bytes(BITS, VT_SMALL) + (p_bytes > red_bytes ? p_bytes : red_bytes) + 1024);
-  }
+  if (d.chunk_tok == VT_LARGE)
+    rc = launch_k2(k2_attn_v<T, BITS, VT_LARGE>, k2_smem_bytes(BITS, VT_LARGE));
+  else
+    rc = launch_k2(k2_attn_v<T, BITS, VT_SMALL>, k2_smem_bytes(BITS, VT_SMALL));
   if (rc != CQ_OK) return rc;
   if (d.n_slots >= 16)
     k3_combine<T, 4><<<d.batch * d.hq, kHeadDim * 4, 0, st>>>(d, partial, ml, static_cast<T*>(out));
@@ -1261,21 +1300,21 @@ size_t mma_path_workspace_bytes(const cq_decode_args* a) {
   return mma::make_layout(mma::make_dims(a)).total;
 }
 
-int mma_path_run(const cq_decode_args* a, void* workspace, cudaStream_t st) {
+int mma_path_run(const cq_decode_args* a, void* workspace, cudaStream_t st, cudaEvent_t* ev, int* status_word) {
   const mma::Dims d = mma::make_dims(a);
   const mma::Layout l = mma::make_layout(d);
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   if (a->dtype == CQ_DTYPE_F16) {
     switch (a->bits) {
-      case 1: return mma::run<__half, 1>(a, d, l, ws, st);
-      case 2: return mma::run<__half, 2>(a, d, l, ws, st);
-      default: return mma::run<__half, 4>(a, d, l, ws, st);
+      case 1: return mma::run<__half, 1>(a, d, l, ws, st, ev, status_word);
+      case 2: return mma::run<__half, 2>(a, d, l, ws, st, ev, status_word);
+      default: return mma::run<__half, 4>(a, d, l, ws, st, ev, status_word);
     }
   }
   switch (a->bits) {
-    case 1: return mma::run<__nv_bfloat16, 1>(a, d, l, ws, st);
-    case 2: return mma::run<__nv_bfloat16, 2>(a, d, l, ws, st);
-    default: return mma::run<__nv_bfloat16, 4>(a, d, l, ws, st);
+    case 1: return mma::run<__nv_bfloat16, 1>(a, d, l, ws, st, ev, status_word);
+    case 2: return mma::run<__nv_bfloat16, 2>(a, d, l, ws, st, ev, status_word);
+    default: return mma::run<__nv_bfloat16, 4>(a, d, l, ws, st, ev, status_word);
   }
 }
 

@@ -11,7 +11,12 @@ bool mma_path_eligible(const cq_decode_args* args);
 size_t mma_path_workspace_bytes(const cq_decode_args* args);
 // The first 4 bytes of `workspace` are a sticky device status word (CQ_ERR_TIMEOUT when a bounded
 // wait ran out); the caller zeroes the workspace once after allocating it.
-int mma_path_run(const cq_decode_args* args, void* workspace, cudaStream_t stream);
+// `events`, when given, are five events recorded before the first launch and after each of the four
+// launches (scores, attn.V, attn.V of the full-precision tokens, combine).
+// `status_word`, when given, replaces the workspace's first word as the place a timed-out wait is reported
+// (a device-visible address, e.g. mapped page-locked host memory).
+int mma_path_run(const cq_decode_args* args, void* workspace, cudaStream_t stream, cudaEvent_t* events = nullptr,
+                 int* status_word = nullptr);
 
 
 // The stand-alone quantized product (cq_qbmm) on the same kernels.  mma_qbmm_kind returns 0 when the

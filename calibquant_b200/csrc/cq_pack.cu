@@ -445,8 +445,7 @@ int launch_pack_last_dim(const void* data, int64_t rows, int64_t L, int bits, in
   T* s = static_cast<T*>(scale);
   T* m = static_cast<T*>(mn);
   // aligned outputs: one group per thread; otherwise the lane-quad kernel with scalar stores
-  static const bool quad = []() { const char* e = getenv("CQ_PACK_QUAD"); return e && e[0] == '1'; }();
-  if (!quad && aligned16(code) && aligned16(data)) {
+  if (aligned16(code) && aligned16(data)) {
     const int64_t n_groups = n_chunks / 4;
     const int64_t gblocks = (n_groups + 255) / 256;
     if (gblocks > 0x7fffffffLL) return CQ_ERR_UNSUPPORTED;

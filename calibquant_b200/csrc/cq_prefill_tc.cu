@@ -457,8 +457,7 @@ static uint32_t make_idesc(int is_bf16, int b_mn_major) {
 }  // namespace prefill_tc
 
 bool prefill_tc_eligible(const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os) {
-  static const bool disabled = []() { const char* e = getenv("CQ_PREFILL_GENERAL"); return e && e[0] == '1'; }();
-  if (disabled || !prefill_tc::encode_fn()) return false;
+  if (!prefill_tc::encode_fn()) return false;
   const int64_t* all[] = {qs, ks, vs, os};
   for (const int64_t* s : all)
     for (int i = 0; i < 3; ++i)

@@ -98,7 +98,8 @@ int launch_qbmm(const void* fA, const int32_t* qB, const void* scales, const voi
 extern "C" size_t cq_qbmm_workspace_bytes(int batch, int n_q_heads, int64_t K, int64_t N) {
   if (batch <= 0 || n_q_heads <= 0 || K <= 0 || N <= 0) return 0;
   const size_t k_chunks = (size_t)((K + cq::QB_KCHUNK - 1) / cq::QB_KCHUNK);
-  const size_t general = k_chunks * (size_t)batch * (size_t)n_q_heads * (size_t)N * sizeof(float);
+  // [status word, padded to 256 bytes][fp32 partial sums]
+  const size_t general = 256 + k_chunks * (size_t)batch * (size_t)n_q_heads * (size_t)N * sizeof(float);
   const size_t fast = cq::mma_qbmm_workspace_bytes(batch, n_q_heads, K, N);
   return general > fast ? general : fast;
 }
@@ -129,7 +130,7 @@ extern "C" int cq_qbmm(const void* fA, const int32_t* qB, const void* scales, co
   if (kind != 0 && cq::aligned16(workspace))
     return cq::mma_qbmm_run(kind, fA, qB, scales, zeros, out, batch, n_q_heads, n_kv_heads, K, N, bits, dtype,
                             workspace, st);
-  float* ws = static_cast<float*>(workspace);
+  float* ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + 256);   // after the status word
   if (dtype == CQ_DTYPE_F16)
     return cq::launch_qbmm<__half>(fA, qB, scales, zeros, out, batch, n_q_heads, n_kv_heads, K, N, bits, ws, st);
   return cq::launch_qbmm<__nv_bfloat16>(fA, qB, scales, zeros, out, batch, n_q_heads, n_kv_heads, K, N, bits, ws, st);
@@ -175,6 +176,13 @@ static int static_scratch_address(float** out) {
 }  // namespace cq
 
 extern "C" size_t cq_qbmm_static_capacity_bytes(void) { return cq::QB_STATIC_BYTES; }
+
+extern "C" int cq_qbmm_static_status(void* stream) {
+  float* scratch = nullptr;
+  const int rc = cq::static_scratch_address(&scratch);
+  if (rc != CQ_OK) return rc;
+  return cq_workspace_status(scratch, stream);
+}
 
 extern "C" int cq_qbmm_static(const void* fA, const int32_t* qB, const void* scales,
                               const void* zeros, void* out, int batch, int n_q_heads,

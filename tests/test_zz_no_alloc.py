@@ -6,8 +6,11 @@ entry point instead of cq_qbmm: the fp32 scratch is a fixed 8 MiB array inside t
 The test drives it through the C ABI only (ctypes, raw device pointers), twice in a row with
 different inputs -- the array is shared and keeps the previous call's contents, so the second
 call would expose any dependence on stale scratch -- and requires bit-identical outputs to
-cq_qbmm, which runs the same kernels on a caller-provided workspace.  It also checks that a
-problem beyond the fixed capacity is refused.  This file sorts last on purpose.
+cq_qbmm, which runs the same kernels on a caller-provided workspace, and agreement with the CPU
+oracle.  The shapes cover the three routes of the product: the general kernels, the score kernel
+(128 reduction rows) and the attn.V kernels (128 output columns, the route that really parks its
+partial sums in the array).  It also checks that a problem beyond the fixed capacity is refused
+and that the array's status word reads clean.  This file sorts last on purpose.
 """
 
 import ctypes
@@ -28,7 +31,9 @@ def _case(seed, B, Hq, Hkv, K, N, bits):
     w = torch.randn(B, Hkv, K, N, generator=g).half()
     code, scale, mn = gf.quantize_and_pack_last_dim(w, 32, bits)
     a = torch.softmax(torch.randn(B, Hq, 1, K, generator=g) * 2, -1).half()
-    return a.cuda(), code.cuda(), scale.cuda(), mn.cuda()
+    rep = lambda t: gf.repeat_kv(t, Hq // Hkv)
+    want = gf.qbmm(32, a, rep(code), rep(scale), rep(mn), bits).reshape(B, Hq, N)
+    return a.cuda(), code.cuda(), scale.cuda(), mn.cuda(), want
 
 
 def test_static_scratch_matches_workspace_variant_twice():
@@ -36,17 +41,22 @@ def test_static_scratch_matches_workspace_variant_twice():
     lib = _lib.lib()
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     assert lib.cq_qbmm_static_capacity_bytes() == 8 << 20
-    shapes = [(11, 2, 8, 2, 700, 128, 1), (12, 1, 12, 2, 128, 2048, 2)]   # attn.V-like, q.K-like
+    # general kernels (K not a multiple of 256), score kernel (K = 128), attn.V kernels (N = 128, K % 256 = 0)
+    shapes = [(11, 2, 8, 2, 700, 128, 1), (12, 1, 12, 2, 128, 2048, 2), (13, 2, 8, 2, 512, 128, 1),
+              (14, 1, 8, 2, 1536, 128, 2)]
     cases = []
     for seed, B, Hq, Hkv, K, N, bits in shapes:                           # references first
-        a, code, scale, mn = _case(seed, B, Hq, Hkv, K, N, bits)
+        a, code, scale, mn, want = _case(seed, B, Hq, Hkv, K, N, bits)
         need = lib.cq_qbmm_workspace_bytes(B, Hq, K, N)
         assert 0 < need <= 8 << 20
-        ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+        ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
         ref = torch.empty(B, Hq, N, dtype=torch.float16, device="cuda")
         rc = lib.cq_qbmm(_p(a), _p(code), _p(scale), _p(mn), _p(ref), B, Hq, Hkv, K, N, 32, bits,
                          _lib.CQ_DTYPE_F16, _p(ws), need, stream)
         assert rc == _lib.CQ_OK
+        assert lib.cq_workspace_status(_p(ws), stream) == _lib.CQ_OK
+        err = float((ref.cpu().double() - want.double()).norm() / want.double().norm())
+        assert err <= 2e-3, err                                           # the tolerance of the product's own tests
         cases.append((a, code, scale, mn, ref, torch.full_like(ref, float("nan")),
                       (B, Hq, Hkv, K, N, bits)))
     for a, code, scale, mn, ref, out, (B, Hq, Hkv, K, N, bits) in cases:  # two static calls in a row
@@ -54,6 +64,7 @@ def test_static_scratch_matches_workspace_variant_twice():
                                 bits, _lib.CQ_DTYPE_F16, stream)
         assert rc == _lib.CQ_OK, lib.cq_status_string(rc)
     torch.cuda.synchronize()
+    assert lib.cq_qbmm_static_status(stream) == _lib.CQ_OK
     for a, code, scale, mn, ref, out, dims in cases:
         assert torch.isfinite(out.float()).all()
         assert torch.equal(out.view(torch.int16), ref.view(torch.int16))   # tolerance: bit-identical
