@@ -1,0 +1,44 @@
+"""Build the reference's own CUDA extension for the quantized product into ``oracle/_ref/`` (test infrastructure).
+
+    python oracle/build_ref.py [path/to/reference]
+
+Compiles ``qjl/csrc/quantization.cu`` of ActiveSky/calibquant, unchanged and where it lies in the reference
+checkout (default ``/root/reference``), with the flags of the reference's ``qjl/setup.py:5-15`` plus the
+sm_100a code generation flag, into ``oracle/_ref/quantization.so``.  Nothing of the reference is copied into
+this repository: ``oracle/_ref/`` is ignored by git and holds build outputs only.
+
+The extension is the only executable definition of ``cuda_quantized_bmm_dynamic``'s arithmetic
+(``qjl/csrc/quantization.cu:67-169``).  ``tests/test_gpu_ref_pin.py`` runs it on a GPU for 2 and 4 bits (its
+``psum[16]`` array cannot hold the 32 codes of a 1-bit word) and compares it with the CPU oracle and with
+``cq_qbmm``.  The product never loads it.
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+OUT = os.path.join(HERE, "_ref")
+
+
+def build(reference_root: str = "/root/reference", verbose: bool = False) -> str | None:
+    src = os.path.join(reference_root, "qjl", "csrc", "quantization.cu")
+    target = os.path.join(OUT, "quantization.so")
+    if not os.path.exists(src):
+        return target if os.path.exists(target) else None
+    if os.path.exists(target) and os.path.getmtime(target) >= os.path.getmtime(src):
+        return target
+    os.makedirs(OUT, exist_ok=True)
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")      # no GPU is needed to compile
+    from torch.utils.cpp_extension import load
+    load(name="quantization", sources=[src], build_directory=OUT, verbose=verbose,
+         extra_cflags=["-O3"],
+         extra_cuda_cflags=["-O3", "-std=c++17", "--expt-relaxed-constexpr", "--expt-extended-lambda",
+                            "--use_fast_math", "-gencode", "arch=compute_100a,code=sm_100a"])
+    return target if os.path.exists(target) else None
+
+
+if __name__ == "__main__":
+    path = build(*(sys.argv[1:2]), verbose=True)
+    print(path or "reference sources not found; nothing built")
