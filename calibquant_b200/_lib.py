@@ -77,6 +77,17 @@ SIGNATURES = {
                                         _vp, _vp, _vp, _i64, _i64, _c.c_int, _c.c_int, _vp, _c.c_int, _vp]),
     "cq_add_rmsnorm": (_c.c_int, [_vp, _vp, _vp, _vp, _i64, _c.c_int, _c.c_float, _c.c_int, _vp]),
     "cq_swiglu": (_c.c_int, [_vp, _vp, _vp, _i64, _c.c_int, _vp]),
+    "cq_swiglu_packed": (_c.c_int, [_vp, _vp, _i64, _i64, _c.c_int, _vp]),
+    "cq_comm_buffer_bytes": (_sz, [_c.c_int, _sz]),
+    "cq_comm_alloc": (_c.c_int, [_sz, _c.POINTER(_vp), _vp]),
+    "cq_comm_open": (_c.c_int, [_vp, _c.POINTER(_vp)]),
+    "cq_comm_close": (_c.c_int, [_vp]),
+    "cq_comm_free": (_c.c_int, [_vp]),
+    "cq_comm_status": (_c.c_int, [_vp, _vp]),
+    "cq_comm_push": (_c.c_int, [_vp, _sz, _c.POINTER(_vp), _c.c_int, _c.c_int, _sz, _vp]),
+    "cq_comm_reduce_add_rmsnorm": (_c.c_int, [_vp, _c.c_int, _sz, _vp, _vp, _vp, _i64, _c.c_int, _c.c_float,
+                                              _c.c_int, _vp]),
+    "cq_comm_gather": (_c.c_int, [_vp, _c.c_int, _sz, _vp, _sz, _vp]),
     "cq_qjl_quant": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _i64, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                 _c.c_int, _vp, _vp, _vp, _vp]),
     "cq_qjl_gqa_score": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int,

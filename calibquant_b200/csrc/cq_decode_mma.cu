@@ -725,7 +725,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
   }
 
   float acc[8][4];
-  float cb[4];
+  float cb[4] = {0.f, 0.f, 0.f, 0.f};
   int seg_pair = -1, seg_first = 0, seg_end = 0;     // the run of tiles of one KV head accumulated so far
   bool failed = false;
   // calibration constants and softmax reference of the head this lane's probabilities belong to (head g)

@@ -133,6 +133,30 @@ swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restric
   }
 }
 
+// the same gate on one matrix [rows, 2n] that holds the gate columns first and the up columns after them
+// (the output of one GEMM against the stacked w1 / w3 weights): out [rows, n]
+template <typename T>
+__global__ void __launch_bounds__(256)
+swiglu_packed_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t rows, int64_t n_vec_row) {
+  const int64_t total = rows * n_vec_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / n_vec_row, j = i % n_vec_row;
+    const uint4 graw = reinterpret_cast<const uint4*>(gate_up)[r * 2 * n_vec_row + j];
+    const uint4 uraw = reinterpret_cast<const uint4*>(gate_up)[r * 2 * n_vec_row + n_vec_row + j];
+    const T* g = reinterpret_cast<const T*>(&graw);
+    const T* u = reinterpret_cast<const T*>(&uraw);
+    uint4 res;
+    T* o = reinterpret_cast<T*>(&res);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float x = Elem<T>::to_f(g[e]);
+      const float s = rnd<T>(x / (1.f + expf(-x)));
+      o[e] = Elem<T>::from_f(s * Elem<T>::to_f(u[e]));
+    }
+    reinterpret_cast<uint4*>(out)[i] = res;
+  }
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace step
@@ -207,5 +231,23 @@ extern "C" int cq_swiglu(const void* gate, const void* up, void* out, int64_t n,
     step::swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gate),
                                                              static_cast<const __nv_bfloat16*>(up),
                                                              static_cast<__nv_bfloat16*>(out), n_vec);
+  return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
+}
+
+extern "C" int cq_swiglu_packed(const void* gate_up, void* out, int64_t rows, int64_t n, int dtype, void* stream) {
+  if (rows == 0 || n == 0) return CQ_OK;
+  if (!gate_up || !out || rows < 0 || n < 0) return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (n % 8) return CQ_ERR_UNSUPPORTED;
+  if (!step::aligned16(gate_up) || !step::aligned16(out)) return CQ_ERR_BAD_ARG;
+  const int64_t n_vec = n / 8, total = rows * n_vec;
+  const unsigned grid = (unsigned)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CQ_DTYPE_F16)
+    step::swiglu_packed_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(gate_up),
+                                                             static_cast<__half*>(out), rows, n_vec);
+  else
+    step::swiglu_packed_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gate_up),
+                                                                    static_cast<__nv_bfloat16*>(out), rows, n_vec);
   return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
 }

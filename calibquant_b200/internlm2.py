@@ -101,6 +101,10 @@ class InternLM2MLP(nn.Module):
         self.w2 = nn.Linear(config.intermediate_size, config.hidden_size, bias=False)
 
     def forward(self, x):
+        if self.w1 is None:      # tensor-parallel shard: w1 / w3 slices stacked in `w13` (calibquant_b200.tp)
+            gu = self.w13(x)
+            n = gu.shape[-1] // 2
+            return self.w2(nn.functional.silu(gu[..., :n]) * gu[..., n:])
         return self.w2(nn.functional.silu(self.w1(x)) * self.w3(x))
 
 
@@ -117,8 +121,14 @@ class InternLM2DecoderLayer(nn.Module):
         h, _, present = self.attention(self.attention_norm(hidden_states), attention_mask=attention_mask,
                                        position_ids=position_ids, past_key_value=past_key_value,
                                        output_attentions=False, use_cache=use_cache)
+        tp = getattr(self.attention, "_shard_rowparallel", False)     # partial sums: add up over the ranks
+        if tp:
+            torch.distributed.all_reduce(h, group=self.attention._shard[2])
         hidden_states = hidden_states + h
-        hidden_states = hidden_states + self.feed_forward(self.ffn_norm(hidden_states))
+        f = self.feed_forward(self.ffn_norm(hidden_states))
+        if tp:
+            torch.distributed.all_reduce(f, group=self.attention._shard[2])
+        hidden_states = hidden_states + f
         return hidden_states, present
 
 
@@ -154,11 +164,56 @@ class InternLM2ForCausalLM(nn.Module):
         h = self.model.norm(h[:, -1:])
         return self.output(h), presents
 
+    def next_token(self, logits):
+        """Greedy token from the last position's logits (vocabulary-sharded under tensor parallelism)."""
+        tp = getattr(self, "_tp", None)
+        if tp is None:
+            return logits[:, -1].argmax(-1)
+        from . import tp as _tp
+        rank, world, _, group, v_per = tp
+        return _tp.global_argmax_torch(logits[:, -1], rank, world, v_per, group)
+
     @torch.no_grad()
-    def forward_step_fused(self, inputs_embeds, position_ids, past_key_values):
-        """Decode step (one token per row) with the elementwise blocks of every layer fused: residual
-        add + RMSNorm in one launch, SwiGLU gate in one launch.  Same arithmetic and rounding points
-        as ``forward_step``; the attention modules are called as usual."""
+    def decode_token_fused(self, inputs_embeds, position_ids, past_key_values):
+        """One fused decode step; returns the next token [B].  Under tensor parallelism every sum over the
+        ranks rides on the step's own launches: the partial rows are pushed into the peers' buffers and the
+        next layer norm adds them up (``calibquant_b200.tp``)."""
+        tp = getattr(self, "_tp", None)
+        if tp is None:
+            return self.forward_step_fused(inputs_embeds, position_ids, past_key_values)[:, -1].argmax(-1)
+        from . import tp as _tp
+        x = self.decode_hidden_fused_tp(inputs_embeds, position_ids, past_key_values)
+        return _tp.global_argmax_peer(self.output(x[:, -1]), tp[2], tp[4])
+
+    @torch.no_grad()
+    def decode_hidden_fused_tp(self, inputs_embeds, position_ids, past_key_values):
+        """The tensor-parallel decode step up to the final norm: [B, 1, hidden], identical on every rank."""
+        from . import ops
+        rank, world, comm, _, v_per = self._tp
+        eps = self.config.rms_norm_eps
+        h = inputs_embeds.contiguous().clone()
+        first = True
+        for i, layer in enumerate(self.model.layers):
+            if first:
+                x = ops.add_rmsnorm(h, None, layer.attention_norm.weight, eps)
+                first = False
+            else:
+                x = comm.reduce_add_rmsnorm(h, layer.attention_norm.weight, eps)
+            a, _, _ = layer.attention(x, position_ids=position_ids, past_key_value=past_key_values[i],
+                                      output_attentions=False, use_cache=True)
+            comm.push(a)
+            x = comm.reduce_add_rmsnorm(h, layer.ffn_norm.weight, eps)
+            ff = layer.feed_forward
+            comm.push(ff.w2(ops.swiglu_packed(ff.w13(x))))
+        return comm.reduce_add_rmsnorm(h, self.model.norm.weight, eps)
+
+    @torch.no_grad()
+    def decode_hidden_fused(self, inputs_embeds, position_ids, past_key_values):
+        """Decode step (one token per row) up to the final norm, with the elementwise blocks of every layer
+        fused: residual add + RMSNorm in one launch, SwiGLU gate in one launch.  Same arithmetic and rounding
+        points as ``forward_step``; the attention modules are called as usual.  Returns [B, 1, hidden]."""
+        if getattr(self, "_tp", None) is not None:
+            return self.decode_hidden_fused_tp(inputs_embeds, position_ids, past_key_values)
         from . import ops
         eps = self.config.rms_norm_eps
         h = inputs_embeds.contiguous().clone()      # running residual stream, updated in place
@@ -170,8 +225,12 @@ class InternLM2ForCausalLM(nn.Module):
             x = ops.add_rmsnorm(h, a.contiguous(), layer.ffn_norm.weight, eps)
             ff = layer.feed_forward
             delta = ff.w2(ops.swiglu(ff.w1(x), ff.w3(x)))
-        x = ops.add_rmsnorm(h, delta, self.model.norm.weight, eps)
-        return self.output(x[:, -1:])
+        return ops.add_rmsnorm(h, delta, self.model.norm.weight, eps)
+
+    @torch.no_grad()
+    def forward_step_fused(self, inputs_embeds, position_ids, past_key_values):
+        """Logits [B, 1, vocab] of one fused decode step (see ``decode_hidden_fused``)."""
+        return self.output(self.decode_hidden_fused(inputs_embeds, position_ids, past_key_values)[:, -1:])
 
     @torch.no_grad()
     def generate(self, inputs_embeds, max_new_tokens, **_):
@@ -181,7 +240,7 @@ class InternLM2ForCausalLM(nn.Module):
         logits, past = self.forward_step(inputs_embeds, pos, None)
         tokens = []
         for step in range(max_new_tokens):
-            nxt = logits[:, -1].argmax(-1)
+            nxt = self.next_token(logits)
             tokens.append(nxt)
             if step == max_new_tokens - 1:
                 break
@@ -238,16 +297,18 @@ class GraphedDecoder:
         emb = self.lm.model.tok_embeddings(self.tok).unsqueeze(1)
         self.len_dev += 1                 # the caches now count the token this step appends
         if self.fused:
-            logits = self.lm.forward_step_fused(emb, self.pos, self.past)
+            nxt = self.lm.decode_token_fused(emb, self.pos, self.past)
         else:
-            logits, _ = self.lm.forward_step(emb, self.pos, self.past)
-        self.tok.copy_(logits[:, -1].argmax(-1))
+            nxt = self.lm.next_token(self.lm.forward_step(emb, self.pos, self.past)[0])
+        self.tok.copy_(nxt)
         self.out.index_copy_(0, self.step_idx, self.tok.unsqueeze(0))
         self.pos += 1
         self.step_idx += 1
 
     def run(self, n_steps: int):
         """Replay ``n_steps`` decode steps; returns the generated tokens [B, n_steps]."""
+        if n_steps > self.out.shape[0]:
+            raise ValueError(f"the decoder was captured for {self.out.shape[0]} steps, {n_steps} requested")
         for _ in range(n_steps):
             self.graph.replay()
         return self.out[:n_steps].t()

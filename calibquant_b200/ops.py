@@ -397,6 +397,23 @@ def swiglu(gate, up, out=None):
     return out
 
 
+def swiglu_packed(gate_up, out=None):
+    """``silu(gate) * up`` for ``gate_up`` [..., 2n] holding the gate columns first, then the up columns (the
+    output of one GEMM against stacked ``w1`` / ``w3`` weights).  Returns [..., n]."""
+    _need_cuda(gate_up)
+    n2 = gate_up.shape[-1]
+    if n2 % 2 or not gate_up.is_contiguous():
+        raise ValueError("gate_up must be contiguous with an even last dimension")
+    n = n2 // 2
+    rows = gate_up.numel() // n2 if n2 else 0
+    if out is None:
+        out = torch.empty((*gate_up.shape[:-1], n), dtype=gate_up.dtype, device=gate_up.device)
+    with torch.cuda.device(gate_up.device):
+        rc = lib().cq_swiglu_packed(_ptr(gate_up), _ptr(out), rows, n, _dtype_enum(gate_up), _stream())
+    check(rc, "cq_swiglu_packed")
+    return out
+
+
 def _proj_dtype_enum(proj, data):
     if proj.dtype == torch.float32:
         return _lib.CQ_DTYPE_F32

@@ -166,8 +166,8 @@ def _gather_heads(self, x):
     """x [B,q,Hq_local*D] -> [B,q,Hq*D].  Identity unless ``shard_attention_`` split this layer by KV
     head across ranks; then the single collective of the layer: an all-gather of the head outputs."""
     shard = getattr(self, "_shard", None)
-    if not shard:
-        return x
+    if not shard or getattr(self, "_shard_rowparallel", False):
+        return x          # not sharded, or `wo` holds only the columns of the local heads (calibquant_b200.tp)
     from . import sharding
     return sharding.all_gather_last_dim(x, shard[2])
 
@@ -237,7 +237,7 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
                                     BITS_KV, group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
                                     t_fp_dev=tc.len_dev)
         attn = _gather_heads(self, attn.transpose(1, 2).reshape(bsz, q_len, -1))
-        return self.wo(attn.reshape(bsz, q_len, self.hidden_size)), None, past_key_value
+        return self.wo(attn.reshape(bsz, q_len, -1)), None, past_key_value
 
     q, k, v = _split_qkv(self, hidden_states)
     q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)          # [B,H,q,D] views
@@ -264,7 +264,7 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
         past_key_value = self._text_cache.views() if use_cache else None
         attn = ops.prefill_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
         attn = _gather_heads(self, attn.reshape(bsz, q_len, -1))
-        attn_output = self.wo(attn.reshape(bsz, q_len, self.hidden_size))
+        attn_output = self.wo(attn.reshape(bsz, q_len, -1))
         return attn_output, None, past_key_value
 
     # ---- decode step -------------------------------------------------------------------------
@@ -283,7 +283,7 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
         raise ValueError(f"`attn_output` should be of size {(bsz, local_heads, q_len, self.head_dim)}, "
                          f"but is {attn.size()}")
     attn = _gather_heads(self, attn.transpose(1, 2).reshape(bsz, q_len, -1))
-    attn_output = self.wo(attn.reshape(bsz, q_len, self.hidden_size))
+    attn_output = self.wo(attn.reshape(bsz, q_len, -1))
     return attn_output, None, past_key_value
 
 

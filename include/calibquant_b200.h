@@ -295,6 +295,46 @@ int cq_rope_split_append(const void* qkv, int64_t qkv_stride_b, const void* cos_
 int cq_add_rmsnorm(const void* delta, void* residual, const void* weight, void* out, int64_t rows, int hidden,
                    float eps, int dtype, void* stream);
 int cq_swiglu(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream);
+/* cq_swiglu on one matrix gate_up [rows, 2n] whose first n columns are the gate and last n the up projection
+ * (one GEMM against the stacked w1 / w3 weights): out [rows, n].  n % 8 == 0. */
+int cq_swiglu_packed(const void* gate_up, void* out, int64_t rows, int64_t n, int dtype, void* stream);
+
+/*
+ * ---- tensor-parallel decode step: one-shot all-reduce / all-gather over peer memory -----------------------
+ *
+ * No counterpart in the reference, which runs on one device (infer.py:200 `device_map='auto'` only).  With the
+ * model sharded by KV head over `world` GPUs of a node (one process per GPU), every sharded block of a decode
+ * step ends in a partial [batch, hidden] sum per rank; these entry points exchange such rows through buffers
+ * the peers can write directly (CUDA IPC over NVLink), in two halves that ride on the step's own launches:
+ *   cq_comm_push               copies `bytes` of this rank's rows into slot `rank` of every rank's buffer
+ *                              (plain peer stores) and publishes the collective's sequence number there;
+ *   cq_comm_reduce_add_rmsnorm waits until all `world` slots of this rank's buffer carry that number, then
+ *                              residual += sum of the slots (fp32 sum, one rounding) and, if out != NULL,
+ *                              out = RMSNorm(residual) * weight exactly as cq_add_rmsnorm;
+ *   cq_comm_gather             the same wait, then out[q] = slot q for every rank q (an all-gather).
+ * Every collective is one push on every rank followed by one reduce or gather on every rank, in the same order
+ * on all ranks.  The sequence number lives in the buffer and advances on the device, so a captured CUDA graph
+ * replays the step.  Waits are bounded (two seconds): a timeout stores CQ_ERR_TIMEOUT in the buffer's status
+ * word (cq_comm_status, synchronises) and the kernel leaves its outputs untouched.
+ *
+ *   cq_comm_buffer_bytes(world, slot_bytes)  size of one rank's buffer for rows of at most slot_bytes
+ *   cq_comm_alloc   allocates and clears a buffer on the current device (set-up time: cudaMalloc) and fills
+ *                   the 64-byte IPC handle that lets the other processes map it
+ *   cq_comm_open    maps a peer's buffer from its handle; cq_comm_close unmaps it; cq_comm_free frees one's own
+ *   peer_buffers    host array of `world` device pointers, entry q = rank q's buffer as seen from this process
+ * world <= 8.  slot_bytes must be the same in every call on a buffer.
+ */
+size_t cq_comm_buffer_bytes(int world, size_t slot_bytes);
+int cq_comm_alloc(size_t bytes, void** buffer, void* ipc_handle);
+int cq_comm_open(const void* ipc_handle, void** buffer);
+int cq_comm_close(void* buffer);
+int cq_comm_free(void* buffer);
+int cq_comm_status(const void* buffer, void* stream);
+int cq_comm_push(const void* src, size_t bytes, void* const* peer_buffers, int rank, int world, size_t slot_bytes,
+                 void* stream);
+int cq_comm_reduce_add_rmsnorm(void* buffer, int world, size_t slot_bytes, void* residual, const void* weight,
+                               void* out, int64_t rows, int hidden, float eps, int dtype, void* stream);
+int cq_comm_gather(void* buffer, int world, size_t slot_bytes, void* out, size_t bytes, void* stream);
 
 /*
  * ---- QJL sign-sketch key quantizer (the reference's `qjl` baseline method) ---------------------------

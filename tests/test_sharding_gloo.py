@@ -71,6 +71,54 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
+def _tp_worker(rank, world, port, out_dir):
+    """Tensor-parallel slices of one decoder layer: partial products summed over the ranks (gloo) reproduce the
+    unsharded layer's linear algebra; the vocabulary-sharded arg-max picks the same token."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from calibquant_b200 import tp
+        from calibquant_b200.internlm2 import InternLM2Config, InternLM2DecoderLayer, init_weights_
+        cfg = InternLM2Config(hidden_size=256, num_attention_heads=8, num_key_value_heads=4, intermediate_size=384,
+                              num_hidden_layers=1, vocab_size=64)
+        full = InternLM2DecoderLayer(cfg).double()
+        init_weights_(full, 3, std=0.1)
+        mine = InternLM2DecoderLayer(cfg).double()
+        mine.load_state_dict(full.state_dict())
+        tp.shard_layer_(mine, rank, world)
+        g = torch.Generator().manual_seed(9)
+        x = torch.randn(5, 1, 256, generator=g, dtype=torch.float64)
+        # feed-forward block: stacked w1/w3 slice + w2 column slice give a partial sum
+        part = mine.feed_forward(x)
+        dist.all_reduce(part)
+        assert torch.allclose(part, full.feed_forward(x), atol=1e-12)
+        # wqkv rows -> this rank's heads; wo columns of those heads -> a partial sum of the full wo product
+        n_rep, D = 2, 32
+        h0, h1 = sharding.kv_head_range(rank, world, 4)
+        qkv_full = full.attention.wqkv(x).view(5, 1, 4, n_rep + 2, D)
+        qkv_mine = mine.attention.wqkv(x).view(5, 1, -1, n_rep + 2, D)
+        assert torch.equal(qkv_mine, qkv_full[:, :, h0:h1])
+        o = torch.randn(5, 1, 8 * D, generator=g, dtype=torch.float64)      # stand-in for all heads' outputs
+        part = mine.attention.wo(o[..., h0 * n_rep * D:h1 * n_rep * D])
+        dist.all_reduce(part)
+        assert torch.allclose(part, full.attention.wo(o), atol=1e-12)
+        # vocabulary-sharded arg-max
+        logits = torch.randn(5, 64, generator=g)
+        v = 64 // world
+        tok = tp.global_argmax_torch(logits[:, rank * v:(rank + 1) * v], rank, world, v)
+        assert torch.equal(tok, logits.argmax(-1))
+        open(os.path.join(out_dir, f"tp{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_tensor_parallel_slices(tmp_path):
+    world = 2
+    mp.spawn(_tp_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"tp{r}").exists() for r in range(world))
+
+
 def test_two_rank_head_sharding(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
