@@ -354,6 +354,14 @@ def run_ours(args, rank, world, device):
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args, reps=10)
+    # ---- the second half of the metric: end-to-end decode tok/s of the 7B-architecture backbone on these N GPUs
+    if not args.no_model:
+        del caches, prepared
+        torch.cuda.empty_cache()
+        try:
+            line["model_decode"] = model_decode(rank, world, device, steps=64)
+        except Exception as e:      # the attention numbers above stand on their own
+            line["model_decode"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     return line
 
 
@@ -410,16 +418,16 @@ def run_reference(args, rank, world):
     }
 
 
-def run_model(args, rank, world, device):
-    """End-to-end decode throughput of an InternLM2-architecture backbone with the quantized-KV
-    attention path: random-init bf16 weights, prefill of 41 system + 3328 (6656) visual + text
-    embeddings, then greedy decode steps.  N > 1: attention sharded by KV head with one all-gather
-    of head outputs per layer (everything else replicated); tok/s = batch * steps / decode time."""
-    from calibquant_b200 import patch_internvl as pi
-    from calibquant_b200.internlm2 import INTERNLM2_5_7B, INTERNLM2_20B, ChatModelShell
-    big = args.workload == "model20b"
+def model_decode(rank, world, device, big=False, batch=None, steps=64, bits=1, eager=False):
+    """End-to-end decode throughput of an InternLM2-architecture backbone with the quantized-KV attention path:
+    random-init bf16 weights, prefill of 41 system + 3328 (6656) visual + text embeddings, then greedy decode
+    steps replayed from a CUDA graph.  N > 1: tensor parallel by KV head (calibquant_b200.tp): every weight
+    sliced with the heads, two sums over the ranks per layer, exchanged through peer buffers over NVLink and
+    added up inside the next layer-norm launch.  tok/s = batch * steps / decode time (max over ranks)."""
+    from calibquant_b200 import patch_internvl as pi, tp
+    from calibquant_b200.internlm2 import INTERNLM2_5_7B, INTERNLM2_20B, ChatModelShell, GraphedDecoder
     cfg = INTERNLM2_20B if big else INTERNLM2_5_7B
-    batch = args.batch if args.batch != 8 else (64 if big else 16)
+    batch = batch or (64 if big else 16)
     t_vis, t_txt = (6656, 128 - 41) if big else (3328, 64 - 41)
     torch.manual_seed(1234)
     with torch.device(device):
@@ -428,52 +436,83 @@ def run_model(args, rank, world, device):
         if prm.dim() >= 2:
             torch.nn.init.normal_(prm, std=0.02)
     pi.patch_model(shell, "calibquant")
-    pi.BITS_KV = args.bits
-    if world > 1:
-        for layer in shell.language_model.model.layers:
-            pi.shard_attention_(layer.attention, rank, world)
+    bits_before, pi.BITS_KV = pi.BITS_KV, bits
     lm = shell.language_model
-    T = 41 + t_vis + t_txt
-    emb = torch.randn(batch, T, cfg.hidden_size, device=device, dtype=torch.bfloat16) * 0.02
-    os.environ["IMAGE_TOKEN_NUM"] = str(t_vis)
-    pos = torch.arange(T, device=device).unsqueeze(0).expand(batch, T)
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    torch.cuda.synchronize()
-    ev[0].record()
-    with torch.no_grad():
-        logits, past = lm.forward_step(emb, pos, None)
-        ev[1].record()
-        steps = args.steps
-        if args.eager:
-            for step in range(steps):
-                nxt = logits[:, -1].argmax(-1)
-                e = lm.model.tok_embeddings(nxt).unsqueeze(1)
-                p1 = torch.full((batch, 1), T + step, device=device, dtype=torch.long)
-                logits, past = lm.forward_step(e, p1, past)
-        else:
-            from calibquant_b200.internlm2 import GraphedDecoder
-            dec = GraphedDecoder(lm, past, logits[:, -1].argmax(-1), T, steps)   # capture: not timed
-            torch.cuda.synchronize()
+    comm = None
+    try:
+        if world > 1:
+            comm = tp.PeerComm(rank, world, batch * cfg.hidden_size * 2, device)
+            tp.shard_model_(lm, rank, world, comm)
+        T = 41 + t_vis + t_txt
+        emb = torch.randn(batch, T, cfg.hidden_size, device=device, dtype=torch.bfloat16) * 0.02
+        os.environ["IMAGE_TOKEN_NUM"] = str(t_vis)
+        pos = torch.arange(T, device=device).unsqueeze(0).expand(batch, T)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        torch.cuda.synchronize()
+        ev[0].record()
+        with torch.no_grad():
+            logits, past = lm.forward_step(emb, pos, None)
+            first = lm.next_token(logits)
             ev[1].record()
-            dec.run(steps)
-    ev[2].record()
-    torch.cuda.synchronize()
-    t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], device=device, dtype=torch.float64)
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    prefill_ms, decode_ms = t.tolist()
-    tok_s = batch * steps / (decode_ms * 1e-3)
+            torch.cuda.synchronize()
+            prefill_ms = ev[0].elapsed_time(ev[1])
+            if eager:
+                tok = first
+                for step in range(steps):
+                    e = lm.model.tok_embeddings(tok).unsqueeze(1)
+                    p1 = torch.full((batch, 1), T + step, device=device, dtype=torch.long)
+                    logits, past = lm.forward_step(e, p1, past)
+                    tok = lm.next_token(logits)
+            else:
+                dec = GraphedDecoder(lm, past, first, T, steps + 3)   # capture: not timed
+                dec.run(3)                                            # warm replays
+                torch.cuda.synchronize()
+                if world > 1:
+                    torch.distributed.barrier()
+                ev[1].record()
+                dec.run(steps)
+        ev[2].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([ev[1].elapsed_time(ev[2])], device=device, dtype=torch.float64)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        decode_ms = float(t.item())
+        status = comm.status() if comm is not None else 0
+        if status:
+            raise RuntimeError("a wait for a peer's partial sums timed out during the decode steps")
+    finally:
+        pi.BITS_KV = bits_before
+        if comm is not None:
+            torch.distributed.barrier()
+            comm.close()
     return {
-        "metric": "decode_tok_per_s", "value": round(tok_s, 1), "unit": "tok/s", "n_gpus": world,
-        "steps": steps, "warmup": 0, "ms_per_step": round(decode_ms / steps, 3), "higher_is_better": True,
+        "model": f"{'InternLM2-20B' if big else 'InternLM2.5-7B'} architecture, random-init bf16",
+        "tok_s": round(batch * steps / (decode_ms * 1e-3), 1), "ms_per_step": round(decode_ms / steps, 4),
+        "batch": batch, "steps": steps, "prefill_tokens": T, "prefill_ms": round(prefill_ms, 1), "kv_bits": bits,
+        "parallelism": "single GPU" if world == 1 else
+                       f"tensor parallel by KV head x{world}: wqkv/wo/w1/w3/w2 and the cache sliced with the heads",
+        "collectives_per_layer": 0 if world == 1 else 2,
+        "collective": None if world == 1 else
+                      "one-shot all-reduce of the [batch, hidden] partial sums: peer stores over NVLink "
+                      "(cq_comm_push) + sum inside the next layer-norm launch (cq_comm_reduce_add_rmsnorm)",
+        "decode_loop": "eager launches" if eager else "one CUDA graph replayed per token",
+    }
+
+
+def run_model(args, rank, world, device):
+    """``--workload model7b|model20b``: the line's value is the end-to-end decode tok/s (see model_decode)."""
+    big = args.workload == "model20b"
+    res = model_decode(rank, world, device, big=big, batch=None if args.batch == 8 else args.batch,
+                       steps=args.steps, bits=args.bits, eager=args.eager)
+    return {
+        "metric": "decode_tok_per_s", "value": res["tok_s"], "unit": "tok/s", "n_gpus": world,
+        "steps": args.steps, "warmup": 3, "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{'InternLM2-20B' if big else 'InternLM2.5-7B'} architecture, random-init bf16, "
-                               f"batch {batch}, prefill 41+{t_vis}+{t_txt} tokens, {steps} greedy steps, "
-                               f"{args.bits}-bit KV (group 32)",
-                   "parallelism": "single GPU" if world == 1 else f"attention sharded by KV head x{world}, "
-                                  "NCCL all-gather of head outputs per layer, rest replicated",
-                   "prefill_ms": round(prefill_ms, 1) if args.eager else None,
-                   "decode_loop": "eager launches" if args.eager else "one CUDA graph replayed per token"},
+        "config": {"workload": f"{res['model']}, batch {res['batch']}, prefill {res['prefill_tokens']} tokens, "
+                               f"{args.steps} greedy steps, {args.bits}-bit KV (group 32)",
+                   "parallelism": res["parallelism"], "decode_loop": res["decode_loop"],
+                   "prefill_ms": res["prefill_ms"]},
+        "model_decode": res,
     }
 
 
@@ -609,6 +648,7 @@ def main():
     ap.add_argument("--fp-tokens", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of one row before timing")
+    ap.add_argument("--no-model", action="store_true", help="skip the end-to-end model decode after the attention measurement")
     ap.add_argument("--eager", action="store_true", help="model workloads: no CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -629,7 +669,8 @@ def main():
     torch.cuda.set_device(device)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        torch.distributed.init_process_group("nccl", device_id=device)
+        import datetime
+        torch.distributed.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=240))
     try:
         runner = {"attn": run_ours, "pack": run_pack, "prefill": run_prefill, "qjl": run_qjl}.get(args.workload, run_model)
         line = runner(args, rank, world, device)

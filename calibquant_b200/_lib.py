@@ -88,6 +88,8 @@ SIGNATURES = {
     "cq_comm_reduce_add_rmsnorm": (_c.c_int, [_vp, _c.c_int, _sz, _vp, _vp, _vp, _i64, _c.c_int, _c.c_float,
                                               _c.c_int, _vp]),
     "cq_comm_gather": (_c.c_int, [_vp, _c.c_int, _sz, _vp, _sz, _vp]),
+    "cq_comm_allreduce_add_rmsnorm": (_c.c_int, [_vp, _c.POINTER(_vp), _c.c_int, _c.c_int, _sz, _vp, _vp, _vp, _i64,
+                                                 _c.c_int, _c.c_float, _c.c_int, _vp]),
     "cq_qjl_quant": (_c.c_int, [_vp, _vp, _vp, _c.c_int, _i64, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                 _c.c_int, _vp, _vp, _vp, _vp]),
     "cq_qjl_gqa_score": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int,

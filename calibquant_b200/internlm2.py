@@ -192,20 +192,24 @@ class InternLM2ForCausalLM(nn.Module):
         rank, world, comm, _, v_per = self._tp
         eps = self.config.rms_norm_eps
         h = inputs_embeds.contiguous().clone()
-        first = True
+        fused = h.shape[0] * h.shape[1] <= 64 and hasattr(comm, "allreduce_add_rmsnorm")   # one launch per collective
+
+        def reduce(partial, weight):
+            if fused:
+                return comm.allreduce_add_rmsnorm(partial, h, weight, eps)
+            comm.push(partial)
+            return comm.reduce_add_rmsnorm(h, weight, eps)
+
+        pending = None
         for i, layer in enumerate(self.model.layers):
-            if first:
-                x = ops.add_rmsnorm(h, None, layer.attention_norm.weight, eps)
-                first = False
-            else:
-                x = comm.reduce_add_rmsnorm(h, layer.attention_norm.weight, eps)
+            x = ops.add_rmsnorm(h, None, layer.attention_norm.weight, eps) if pending is None else \
+                reduce(pending, layer.attention_norm.weight)
             a, _, _ = layer.attention(x, position_ids=position_ids, past_key_value=past_key_values[i],
                                       output_attentions=False, use_cache=True)
-            comm.push(a)
-            x = comm.reduce_add_rmsnorm(h, layer.ffn_norm.weight, eps)
+            x = reduce(a, layer.ffn_norm.weight)
             ff = layer.feed_forward
-            comm.push(ff.w2(ops.swiglu_packed(ff.w13(x))))
-        return comm.reduce_add_rmsnorm(h, self.model.norm.weight, eps)
+            pending = ff.w2(ops.swiglu_packed(ff.w13(x)))
+        return reduce(pending, self.model.norm.weight)
 
     @torch.no_grad()
     def decode_hidden_fused(self, inputs_embeds, position_ids, past_key_values):
@@ -307,11 +311,14 @@ class GraphedDecoder:
 
     def run(self, n_steps: int):
         """Replay ``n_steps`` decode steps; returns the generated tokens [B, n_steps]."""
-        if n_steps > self.out.shape[0]:
-            raise ValueError(f"the decoder was captured for {self.out.shape[0]} steps, {n_steps} requested")
+        done = getattr(self, "_steps_done", 0)
+        if done + n_steps > self.out.shape[0]:
+            raise ValueError(f"the decoder holds room for {self.out.shape[0]} steps, {done} are done, "
+                             f"{n_steps} more requested")
         for _ in range(n_steps):
             self.graph.replay()
-        return self.out[:n_steps].t()
+        self._steps_done = done + n_steps
+        return self.out[done:done + n_steps].t()
 
     def close(self):
         for layer, tc in zip(self.lm.model.layers, self.caches):

@@ -104,6 +104,23 @@ class PeerComm:
               "cq_comm_reduce_add_rmsnorm")
         return out if normalize else None
 
+    def allreduce_add_rmsnorm(self, partial, residual, weight, eps, out=None, normalize=True):
+        """A whole collective in one launch: ``residual += sum over the ranks of partial`` in place, then RMSNorm.
+        Every rank calls it with its own ``partial`` [rows, hidden] (rows <= 64)."""
+        hidden = residual.shape[-1]
+        rows = residual.numel() // hidden
+        if not partial.is_contiguous():
+            partial = partial.contiguous()
+        if normalize and out is None:
+            out = torch.empty_like(residual)
+        check(lib().cq_comm_allreduce_add_rmsnorm(ctypes.c_void_p(partial.data_ptr()), self.ptrs, self.rank, self.world,
+                                                  self.slot_bytes, ctypes.c_void_p(residual.data_ptr()),
+                                                  ctypes.c_void_p(weight.data_ptr()) if normalize else None,
+                                                  ctypes.c_void_p(out.data_ptr()) if normalize else None,
+                                                  rows, hidden, float(eps), ops._dtype_enum(residual), self._stream()),
+              "cq_comm_allreduce_add_rmsnorm")
+        return out if normalize else None
+
     def gather(self, like: torch.Tensor) -> torch.Tensor:
         """Second half: the pushed rows of all ranks, ``[world, *like.shape]``."""
         out = torch.empty((self.world, *like.shape), dtype=like.dtype, device=like.device)

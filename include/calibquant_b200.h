@@ -311,7 +311,10 @@ int cq_swiglu_packed(const void* gate_up, void* out, int64_t rows, int64_t n, in
  *   cq_comm_reduce_add_rmsnorm waits until all `world` slots of this rank's buffer carry that number, then
  *                              residual += sum of the slots (fp32 sum, one rounding) and, if out != NULL,
  *                              out = RMSNorm(residual) * weight exactly as cq_add_rmsnorm;
- *   cq_comm_gather             the same wait, then out[q] = slot q for every rank q (an all-gather).
+ *   cq_comm_gather             the same wait, then out[q] = slot q for every rank q (an all-gather);
+ *   cq_comm_allreduce_add_rmsnorm  push and reduce in ONE launch, row by row (rows <= 64): the CTA of a row
+ *                              stores the row of `src` into the peers' buffers, publishes it, waits for the
+ *                              peers' copies of that row and finishes as cq_comm_reduce_add_rmsnorm does.
  * Every collective is one push on every rank followed by one reduce or gather on every rank, in the same order
  * on all ranks.  The sequence number lives in the buffer and advances on the device, so a captured CUDA graph
  * replays the step.  Waits are bounded (two seconds): a timeout stores CQ_ERR_TIMEOUT in the buffer's status
@@ -335,6 +338,9 @@ int cq_comm_push(const void* src, size_t bytes, void* const* peer_buffers, int r
 int cq_comm_reduce_add_rmsnorm(void* buffer, int world, size_t slot_bytes, void* residual, const void* weight,
                                void* out, int64_t rows, int hidden, float eps, int dtype, void* stream);
 int cq_comm_gather(void* buffer, int world, size_t slot_bytes, void* out, size_t bytes, void* stream);
+int cq_comm_allreduce_add_rmsnorm(const void* src, void* const* peer_buffers, int rank, int world, size_t slot_bytes,
+                                  void* residual, const void* weight, void* out, int64_t rows, int hidden,
+                                  float eps, int dtype, void* stream);
 
 /*
  * ---- QJL sign-sketch key quantizer (the reference's `qjl` baseline method) ---------------------------

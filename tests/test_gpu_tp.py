@@ -63,6 +63,30 @@ def test_push_reduce_add_rmsnorm(world, dtype):
             c.close()
 
 
+def test_fused_allreduce_with_one_rank():
+    """The one-launch collective with a single rank (no peer to wait for): residual += partial, then the norm.
+    With more ranks its CTAs wait for their peers' CTAs, which only separate GPUs can run at the same time:
+    that is the two-GPU test's part."""
+    from calibquant_b200 import tp
+    dev = torch.device("cuda")
+    B, hidden = 16, 4096
+    comm = tp.PeerComm.local_group(1, B * hidden * 2, dev)[0]
+    try:
+        g = torch.Generator(device=dev).manual_seed(3)
+        weight = (1 + 0.1 * torch.randn(hidden, generator=g, device=dev)).to(torch.bfloat16)
+        res = torch.randn(B, 1, hidden, generator=g, device=dev).to(torch.bfloat16)
+        want_res = res.clone()
+        for _ in range(3):
+            part = (torch.randn(B, 1, hidden, generator=g, device=dev) * 0.3).to(torch.bfloat16)
+            want_res, want_out = _ref_add_norm(want_res, [part], weight, 1e-5)
+            out = comm.allreduce_add_rmsnorm(part, res, weight, 1e-5)
+            assert torch.equal(res, want_res)
+            assert float((out.float() - want_out.float()).abs().max()) <= 2e-2 * float(want_out.float().abs().max())
+        assert comm.status() == 0
+    finally:
+        comm.close()
+
+
 def test_swiglu_packed_matches_two_tensor_form():
     from calibquant_b200 import ops
     g = torch.Generator(device="cuda").manual_seed(2)
@@ -75,7 +99,7 @@ def test_argument_checks():
     from calibquant_b200 import _lib, tp
     lib = _lib.lib()
     assert lib.cq_comm_buffer_bytes(9, 1024) == 0
-    assert lib.cq_comm_buffer_bytes(2, 1000) == 512 + 2 * 2 * 1024
+    assert lib.cq_comm_buffer_bytes(2, 1000) == 4096 + 256 + 2 * 2 * 1024
     comms = tp.PeerComm.local_group(2, 4096, torch.device("cuda"))
     try:
         x = torch.zeros(4096, dtype=torch.float16, device="cuda")          # 8192 bytes > the slot
