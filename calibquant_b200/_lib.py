@@ -53,6 +53,8 @@ SIGNATURES = {
     "cq_pack_last_dim": (_c.c_int, [_vp, _i64, _i64, _c.c_int, _c.c_int, _c.c_int, _vp, _vp, _vp, _vp]),
     "cq_pack_k_per_channel": (_c.c_int, [_vp, _c.c_int, _c.c_int, _i64, _c.c_int, _i64, _i64, _i64,
                                          _c.c_int, _c.c_int, _c.c_int, _vp, _vp, _vp, _vp]),
+    "cq_pack_v_per_token": (_c.c_int, [_vp, _c.c_int, _c.c_int, _i64, _c.c_int, _i64, _i64, _i64,
+                                       _c.c_int, _c.c_int, _c.c_int, _vp, _vp, _vp, _vp]),
     "cq_qbmm_workspace_bytes": (_sz, [_c.c_int, _c.c_int, _i64, _i64]),
     "cq_qbmm": (_c.c_int, [_vp, _vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _i64, _i64,
                            _c.c_int, _c.c_int, _c.c_int, _vp, _sz, _vp]),
@@ -75,6 +77,9 @@ SIGNATURES = {
                               _c.c_int, _c.c_int, _vp, _sz, _vp]),
     "cq_rope_split_append": (_c.c_int, [_vp, _i64, _vp, _vp, _c.c_int, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                         _vp, _vp, _vp, _i64, _i64, _c.c_int, _c.c_int, _vp, _c.c_int, _vp]),
+    "cq_prefill_rope_split": (_c.c_int, [_vp, _i64, _i64, _vp, _vp, _c.c_int, _vp, _c.c_int, _c.c_int, _c.c_int,
+                                         _c.c_int, _c.c_int, _vp, _vp, _vp, _vp, _i64, _i64, _c.c_int, _c.c_int,
+                                         _c.c_int, _c.c_int, _vp]),
     "cq_add_rmsnorm": (_c.c_int, [_vp, _vp, _vp, _vp, _i64, _c.c_int, _c.c_float, _c.c_int, _vp]),
     "cq_swiglu": (_c.c_int, [_vp, _vp, _vp, _i64, _c.c_int, _vp]),
     "cq_swiglu_packed": (_c.c_int, [_vp, _vp, _i64, _i64, _c.c_int, _vp]),

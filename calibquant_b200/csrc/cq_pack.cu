@@ -202,20 +202,29 @@ __device__ __forceinline__ void pack_chunk(const uint4& raw, int64_t chunk, bool
   }
 }
 
+// Rows of a [B,H,T,128] tensor given by element strides (t_len == 0: the rows are contiguous).
+struct RowView { int64_t t_len = 0; int heads = 1; int64_t stride_b = 0, stride_h = 0, stride_t = 0; };
+
 // ---- the same rows with a whole group of 32 per thread (four 128-bit loads): no exchange between lanes,
 // ---- the group's scale and break points computed once instead of once per lane of a quad.  A warp's four
 // ---- load instructions together cover 2 KB of consecutive bytes.
 template <typename T, int BITS>
 __global__ void __launch_bounds__(256)
 pack_last_dim_group_kernel(const T* __restrict__ data, int64_t n_groups, int32_t* __restrict__ code,
-                           T* __restrict__ scale_out, T* __restrict__ mn_out) {
+                           T* __restrict__ scale_out, T* __restrict__ mn_out, RowView view = RowView{}) {
   using T2 = typename Pk<T>::T2;
   constexpr int LEVELS = (1 << BITS) - 1;
   const int64_t grp = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (grp >= n_groups) return;
   uint4 raw[4];
+  const uint4* src = reinterpret_cast<const uint4*>(data) + grp * 4;
+  if (view.t_len) {            // [B,H,T,128] rows addressed through element strides; outputs stay contiguous
+    const int64_t row = grp >> 2, t = row % view.t_len, bh = row / view.t_len;
+    src = reinterpret_cast<const uint4*>(data + (bh / view.heads) * view.stride_b + (bh % view.heads) * view.stride_h +
+                                         t * view.stride_t + (grp & 3) * 32);
+  }
 #pragma unroll
-  for (int k = 0; k < 4; ++k) raw[k] = __ldg(reinterpret_cast<const uint4*>(data) + grp * 4 + k);
+  for (int k = 0; k < 4; ++k) raw[k] = __ldg(src + k);
   const T2* xv = reinterpret_cast<const T2*>(raw);              // 16 pairs
   T2 mn2 = xv[0], mx2 = xv[0];
 #pragma unroll
@@ -506,6 +515,35 @@ extern "C" int cq_pack_last_dim(const void* data, int64_t rows, int64_t L, int g
   if (dtype == CQ_DTYPE_F16)
     return cq::launch_pack_last_dim<__half>(data, rows, L, bits, code, scale, mn, st);
   return cq::launch_pack_last_dim<__nv_bfloat16>(data, rows, L, bits, code, scale, mn, st);
+}
+
+extern "C" int cq_pack_v_per_token(const void* v, int batch, int heads, int64_t T, int D, int64_t stride_b,
+                                   int64_t stride_h, int64_t stride_t, int group_size, int bits, int dtype,
+                                   int32_t* code, void* scale, void* mn, void* stream) {
+  if (batch < 0 || heads < 0 || T < 0) return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (bits != 1 && bits != 2 && bits != 4) return CQ_ERR_UNSUPPORTED;
+  if (group_size != cq::kGroup || D != cq::kHeadDim) return CQ_ERR_UNSUPPORTED;
+  if (batch == 0 || heads == 0 || T == 0) return CQ_OK;   // empty input
+  if (!v || !code || !scale || !mn) return CQ_ERR_BAD_ARG;
+  if (!cq::aligned16(v) || stride_b % 8 || stride_h % 8 || stride_t % 8) return CQ_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cq::RowView view;
+  view.t_len = T; view.heads = heads; view.stride_b = stride_b; view.stride_h = stride_h; view.stride_t = stride_t;
+  const int64_t n_groups = (int64_t)batch * heads * T * 4;
+  const int64_t gblocks = (n_groups + 255) / 256;
+  if (gblocks > 0x7fffffffLL) return CQ_ERR_UNSUPPORTED;
+#define CQ_LAUNCH_V(TYPE, B)                                                                              \
+  cq::pack_last_dim_group_kernel<TYPE, B><<<(unsigned)gblocks, 256, 0, st>>>(                              \
+      static_cast<const TYPE*>(v), n_groups, code, static_cast<TYPE*>(scale), static_cast<TYPE*>(mn), view)
+  if (dtype == CQ_DTYPE_F16) {
+    if (bits == 1) CQ_LAUNCH_V(__half, 1); else if (bits == 2) CQ_LAUNCH_V(__half, 2); else CQ_LAUNCH_V(__half, 4);
+  } else {
+    if (bits == 1) CQ_LAUNCH_V(__nv_bfloat16, 1); else if (bits == 2) CQ_LAUNCH_V(__nv_bfloat16, 2);
+    else CQ_LAUNCH_V(__nv_bfloat16, 4);
+  }
+#undef CQ_LAUNCH_V
+  return cq::check_launch();
 }
 
 extern "C" int cq_pack_k_per_channel(const void* k, int batch, int heads, int64_t T, int D,

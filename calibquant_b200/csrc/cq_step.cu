@@ -157,6 +157,72 @@ swiglu_packed_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t
   }
 }
 
+// ---- prefill: split + rotary embedding of the whole prompt in one pass over the wqkv output ----------------
+// One thread owns the channel chunks [8c, 8c+8) and [64+8c, 64+8c+8) of one 128-channel row (a query head, the
+// key or the value of one KV head of one token): two 16-byte loads, the rotation of both chunks (they are each
+// other's rotate_half partners), 16-byte stores.  Queries go to q_out, keys to k_out (both [B,T,H,128], what
+// the prefill attention reads) and, for tokens outside the quantized span, to the full-precision cache together
+// with the values.  Values inside the span are not copied at all (the pack kernel reads them in place).
+template <typename T>
+__global__ void __launch_bounds__(256)
+prefill_rope_split_kernel(const T* __restrict__ qkv, int64_t stride_b, int64_t stride_t, const T* __restrict__ cos_t,
+                          const T* __restrict__ sin_t, int rope_len, const int64_t* __restrict__ position_ids,
+                          int t_len, int n_kv_heads, int n_rep, T* __restrict__ q_out, T* __restrict__ k_out,
+                          T* __restrict__ k_cache, T* __restrict__ v_cache, int64_t cache_stride_b,
+                          int64_t cache_stride_h, int capacity, int vis_start, int vis_len, int64_t total) {
+  const int slots = n_kv_heads * (n_rep + 2);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i & 7);
+    const int64_t row = i >> 3;                       // (b, t, slot)
+    const int slot_all = (int)(row % slots);
+    const int64_t bt = row / slots;
+    const int t = (int)(bt % t_len);
+    const int64_t b = bt / t_len;
+    const int hk = slot_all / (n_rep + 2), slot = slot_all % (n_rep + 2);
+    const T* src = qkv + b * stride_b + (int64_t)t * stride_t + (int64_t)slot_all * kHeadDim;
+    const int fp_idx = t < vis_start ? t : (t >= vis_start + vis_len ? t - vis_len : -1);   // row in the fp cache
+    const bool to_cache = fp_idx >= 0 && fp_idx < capacity && k_cache != nullptr;
+    const uint4 lo = *reinterpret_cast<const uint4*>(src + 8 * c), hi = *reinterpret_cast<const uint4*>(src + 64 + 8 * c);
+    if (slot == n_rep + 1) {                          // value: only the full-precision tokens are copied
+      if (to_cache) {
+        T* dst = v_cache + b * cache_stride_b + hk * cache_stride_h + (int64_t)fp_idx * kHeadDim;
+        *reinterpret_cast<uint4*>(dst + 8 * c) = lo;
+        *reinterpret_cast<uint4*>(dst + 64 + 8 * c) = hi;
+      }
+      continue;
+    }
+    int64_t pos = position_ids ? position_ids[b * t_len + t] : t;
+    pos = pos < 0 ? 0 : (pos >= rope_len ? rope_len - 1 : pos);
+    const T* cr = cos_t + pos * kHeadDim;
+    const T* sr = sin_t + pos * kHeadDim;
+    const uint4 c_lo = *reinterpret_cast<const uint4*>(cr + 8 * c), c_hi = *reinterpret_cast<const uint4*>(cr + 64 + 8 * c);
+    const uint4 s_lo = *reinterpret_cast<const uint4*>(sr + 8 * c), s_hi = *reinterpret_cast<const uint4*>(sr + 64 + 8 * c);
+    const T* x0 = reinterpret_cast<const T*>(&lo);  const T* x1 = reinterpret_cast<const T*>(&hi);
+    const T* cl = reinterpret_cast<const T*>(&c_lo); const T* chh = reinterpret_cast<const T*>(&c_hi);
+    const T* sl = reinterpret_cast<const T*>(&s_lo); const T* sh = reinterpret_cast<const T*>(&s_hi);
+    uint4 o_lo, o_hi;
+    T* ol = reinterpret_cast<T*>(&o_lo); T* oh = reinterpret_cast<T*>(&o_hi);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      // x*cos rounded, then + rotate_half(x)*sin with one more rounding (torch.addcmul on the rounded product)
+      const float a = Elem<T>::to_f(x0[e]), bb = Elem<T>::to_f(x1[e]);
+      const float p0 = rnd<T>(a * Elem<T>::to_f(cl[e])), p1 = rnd<T>(bb * Elem<T>::to_f(chh[e]));
+      ol[e] = Elem<T>::from_f(__fadd_rn(p0, __fmul_rn(-bb, Elem<T>::to_f(sl[e]))));
+      oh[e] = Elem<T>::from_f(__fadd_rn(p1, __fmul_rn(a, Elem<T>::to_f(sh[e]))));
+    }
+    T* dst;
+    if (slot < n_rep) dst = q_out + ((b * t_len + t) * (int64_t)(n_kv_heads * n_rep) + (int64_t)hk * n_rep + slot) * kHeadDim;
+    else dst = k_out + ((b * t_len + t) * (int64_t)n_kv_heads + hk) * kHeadDim;
+    *reinterpret_cast<uint4*>(dst + 8 * c) = o_lo;
+    *reinterpret_cast<uint4*>(dst + 64 + 8 * c) = o_hi;
+    if (slot == n_rep && to_cache) {
+      T* kc = k_cache + b * cache_stride_b + hk * cache_stride_h + (int64_t)fp_idx * kHeadDim;
+      *reinterpret_cast<uint4*>(kc + 8 * c) = o_lo;
+      *reinterpret_cast<uint4*>(kc + 64 + 8 * c) = o_hi;
+    }
+  }
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace step
@@ -249,5 +315,40 @@ extern "C" int cq_swiglu_packed(const void* gate_up, void* out, int64_t rows, in
   else
     step::swiglu_packed_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gate_up),
                                                                     static_cast<__nv_bfloat16*>(out), rows, n_vec);
+  return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
+}
+
+extern "C" int cq_prefill_rope_split(const void* qkv, int64_t qkv_stride_b, int64_t qkv_stride_t, const void* cos_table,
+                                     const void* sin_table, int rope_len, const int64_t* position_ids, int batch,
+                                     int t_len, int n_kv_heads, int n_rep, int head_dim, void* q_out, void* k_out,
+                                     void* k_cache, void* v_cache, int64_t cache_stride_b, int64_t cache_stride_h,
+                                     int capacity, int vis_start, int vis_len, int dtype, void* stream) {
+  if (batch == 0 || t_len == 0) return CQ_OK;
+  if (!qkv || !cos_table || !sin_table || !q_out || !k_out) return CQ_ERR_BAD_ARG;
+  if (batch < 0 || t_len < 0 || n_kv_heads <= 0 || n_rep <= 0 || rope_len <= 0) return CQ_ERR_BAD_ARG;
+  if (vis_start < 0 || vis_len < 0 || vis_start + vis_len > t_len) return CQ_ERR_BAD_ARG;
+  if ((k_cache == nullptr) != (v_cache == nullptr) || (k_cache && capacity <= 0)) return CQ_ERR_BAD_ARG;
+  if (dtype != CQ_DTYPE_F16 && dtype != CQ_DTYPE_BF16) return CQ_ERR_BAD_ARG;
+  if (head_dim != kHeadDim) return CQ_ERR_UNSUPPORTED;
+  if (qkv_stride_b % 8 || qkv_stride_t % 8 || cache_stride_b % 8 || cache_stride_h % 8) return CQ_ERR_BAD_ARG;
+  if (!step::aligned16(qkv) || !step::aligned16(cos_table) || !step::aligned16(sin_table) || !step::aligned16(q_out) ||
+      !step::aligned16(k_out) || !step::aligned16(k_cache) || !step::aligned16(v_cache))
+    return CQ_ERR_BAD_ARG;
+  const int64_t total = (int64_t)batch * t_len * n_kv_heads * (n_rep + 2) * 8;
+  const int64_t blocks = (total + 255) / 256;
+  const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == CQ_DTYPE_F16)
+    step::prefill_rope_split_kernel<__half><<<grid, 256, 0, st>>>(
+        static_cast<const __half*>(qkv), qkv_stride_b, qkv_stride_t, static_cast<const __half*>(cos_table),
+        static_cast<const __half*>(sin_table), rope_len, position_ids, t_len, n_kv_heads, n_rep,
+        static_cast<__half*>(q_out), static_cast<__half*>(k_out), static_cast<__half*>(k_cache),
+        static_cast<__half*>(v_cache), cache_stride_b, cache_stride_h, capacity, vis_start, vis_len, total);
+  else
+    step::prefill_rope_split_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(qkv), qkv_stride_b, qkv_stride_t, static_cast<const __nv_bfloat16*>(cos_table),
+        static_cast<const __nv_bfloat16*>(sin_table), rope_len, position_ids, t_len, n_kv_heads, n_rep,
+        static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out), static_cast<__nv_bfloat16*>(k_cache),
+        static_cast<__nv_bfloat16*>(v_cache), cache_stride_b, cache_stride_h, capacity, vis_start, vis_len, total);
   return cudaGetLastError() == cudaSuccess ? CQ_OK : CQ_ERR_LAUNCH;
 }

@@ -128,6 +128,28 @@ def pack_k_per_channel(k: torch.Tensor, group_size: int, bits: int):
     return code, scale, mn
 
 
+def pack_v_per_token(v: torch.Tensor, group_size: int, bits: int):
+    """Per-token quantize + pack of V given as [B,H,T,D] through its strides (channels contiguous),
+    as ``pack_last_dim(v.contiguous())`` without the copy.
+
+    Returns (code [B,H,T,D*bits/32], scale [B,H,T,D/g], mn [B,H,T,D/g]).
+    """
+    _need_cuda(v)
+    assert v.dim() == 4
+    B, H, T, D = v.shape
+    if v.stride(3) != 1 or any(s % 8 for s in v.stride()[:3]) or v.data_ptr() % 16:
+        v = v.contiguous()
+    code = torch.empty((B, H, T, D * bits // 32), dtype=torch.int32, device=v.device)
+    scale = torch.empty((B, H, T, D // group_size), dtype=v.dtype, device=v.device)
+    mn = torch.empty_like(scale)
+    with torch.cuda.device(v.device):
+        rc = lib().cq_pack_v_per_token(_ptr(v), B, H, T, D, v.stride(0), v.stride(1), v.stride(2),
+                                       group_size, bits, _dtype_enum(v),
+                                       _ptr(code), _ptr(scale), _ptr(mn), _stream())
+    check(rc, "cq_pack_v_per_token")
+    return code, scale, mn
+
+
 def qbmm(group_size: int, fA: torch.Tensor, qB: torch.Tensor, scales: torch.Tensor,
          zeros: torch.Tensor, bits: int) -> torch.Tensor:
     """out[b,h,0,n] = sum_k fA[b,h,0,k]*(scales*code+zeros)[b,h//n_rep,k,n].
@@ -313,6 +335,58 @@ def prefill_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out=Non
                                    arr(q), arr(k), arr(v), arr(out), _dtype_enum(q), _stream())
     check(rc, "cq_prefill_attn")
     return out
+
+
+def prefill_rope_split(qkv, cos, sin, position_ids, n_kv_heads, n_rep, k_cache=None, v_cache=None,
+                       vis_start=0, vis_len=0):
+    """A whole prompt: split the ``wqkv`` output ``qkv`` [B,T,Hkv*(n_rep+2)*D], rotate queries and keys
+    with the ``cos``/``sin`` tables [S,D] at ``position_ids`` [B,T] (None: 0..T-1) in one launch.
+
+    Returns (q [B,T,Hq,D], k [B,T,Hkv,D], v [B,T,Hkv,D]); ``v`` is a strided view into ``qkv``.  When
+    the fp caches ``k_cache``/``v_cache`` [B,Hkv,capacity,D] are given, every token outside
+    ``[vis_start, vis_start+vis_len)`` is also written there (rotated key, value), the tokens after the
+    span following the ones before it."""
+    _need_cuda(qkv, cos, sin)
+    B, T = qkv.shape[0], qkv.shape[1]
+    D = cos.shape[-1]
+    per_tok = n_kv_heads * (n_rep + 2) * D
+    if qkv.dim() != 3 or qkv.shape[2] != per_tok:
+        raise ValueError(f"qkv must be [B,T,{per_tok}], got {tuple(qkv.shape)}")
+    if qkv.stride(2) != 1 or qkv.stride(0) % 8 or qkv.stride(1) % 8 or qkv.data_ptr() % 16:
+        qkv = qkv.contiguous()
+    if cos.dtype != qkv.dtype or sin.dtype != qkv.dtype:
+        raise TypeError("qkv and rotary tables must share one dtype")
+    cos, sin = cos.contiguous(), sin.contiguous()
+    pos = None
+    if position_ids is not None:
+        pos = position_ids.reshape(-1, T)
+        if pos.shape[0] == 1 and B > 1:
+            pos = pos.expand(B, T)
+        if pos.dtype != torch.int64 or pos.shape[0] != B:
+            raise ValueError("position_ids must be int64 [B,T]")
+        pos = pos.contiguous()
+    if (k_cache is None) != (v_cache is None):
+        raise ValueError("give both caches or neither")
+    cap = sb = sh = 0
+    if k_cache is not None:
+        for t in (k_cache, v_cache):
+            if t.dtype != qkv.dtype or t.stride(3) != 1 or t.stride(2) != D:
+                raise ValueError("caches must be [B,Hkv,capacity,D] of the data dtype with contiguous token rows")
+        if k_cache.stride() != v_cache.stride():
+            raise ValueError("k_cache and v_cache must share strides")
+        cap, sb, sh = k_cache.shape[2], k_cache.stride(0), k_cache.stride(1)
+        if T - vis_len > cap:
+            raise ValueError(f"{T - vis_len} full-precision tokens do not fit a cache of {cap}")
+    q = torch.empty((B, T, n_kv_heads * n_rep, D), dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty((B, T, n_kv_heads, D), dtype=qkv.dtype, device=qkv.device)
+    with torch.cuda.device(qkv.device):
+        rc = lib().cq_prefill_rope_split(_ptr(qkv), qkv.stride(0), qkv.stride(1), _ptr(cos), _ptr(sin), cos.shape[0],
+                                         _ptr(pos), B, T, n_kv_heads, n_rep, D, _ptr(q), _ptr(k), _ptr(k_cache),
+                                         _ptr(v_cache), sb, sh, cap, int(vis_start), int(vis_len),
+                                         _dtype_enum(qkv), _stream())
+    check(rc, "cq_prefill_rope_split")
+    v = qkv.view(B, T, n_kv_heads, n_rep + 2, D)[:, :, :, n_rep + 1]
+    return q, k, v
 
 
 def rope_split_append(qkv, cos, sin, position_ids, n_kv_heads, n_rep, k_cache, v_cache,

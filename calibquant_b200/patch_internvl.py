@@ -119,6 +119,15 @@ class _TextCache:
         self.v[:, :, :T] = v
         self.length = T
 
+    @classmethod
+    def empty(cls, batch, heads, length, head_dim, dtype, device):
+        """Buffers for ``length`` tokens that the caller fills (the fused prefill kernel writes them)."""
+        self = cls.__new__(cls)
+        self.k = torch.empty((batch, heads, length + TEXT_CAPACITY_STEP, head_dim), dtype=dtype, device=device)
+        self.v = torch.empty_like(self.k)
+        self.length = length
+        return self
+
     def append(self, k, v):
         n = k.shape[2]
         if self.length + n > self.k.shape[2]:
@@ -239,6 +248,35 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
         attn = _gather_heads(self, attn.transpose(1, 2).reshape(bsz, q_len, -1))
         return self.wo(attn.reshape(bsz, q_len, -1)), None, past_key_value
 
+    if q_len > 1:
+        # prefill: one launch splits the projection, rotates q and k and writes the system + text rows
+        # of the fp cache; the pack kernels then read the visual span of the rotated keys and (in
+        # place, through strides) of the values; the dense attention reads the same buffers.
+        if past_key_value is not None:
+            raise NotImplementedError("chunked prefill on top of an existing cache is not supported")
+        n_rep = self.num_key_value_groups
+        n_kv = self.wqkv.out_features // ((n_rep + 2) * self.head_dim)
+        s0, n_vis = (self.sprompt_len, self.image_token_num) if LOW_BITS else (0, 0)
+        if n_vis % GROUP_SIZE:
+            raise ValueError(f"IMAGE_TOKEN_NUM must be a multiple of {GROUP_SIZE}, got {n_vis}")
+        if s0 + n_vis > q_len:
+            raise ValueError(f"the visual span [{s0}, {s0 + n_vis}) does not fit a prompt of {q_len} tokens")
+        cos, sin = self.rotary_emb(hidden_states, seq_len=q_len)
+        tc = _TextCache.empty(bsz, n_kv, q_len - n_vis, self.head_dim, hidden_states.dtype, hidden_states.device)
+        q, k, v = ops.prefill_rope_split(self.wqkv(hidden_states), cos, sin, position_ids, n_kv, n_rep,
+                                         tc.k, tc.v, s0, n_vis)
+        if LOW_BITS:
+            self.k_pack = ops.pack_k_per_channel(k.transpose(1, 2)[:, :, s0:s0 + n_vis], GROUP_SIZE, BITS_KV)
+            self.v_pack = ops.pack_v_per_token(v.transpose(1, 2)[:, :, s0:s0 + n_vis], GROUP_SIZE, BITS_KV)
+        else:
+            self.k_pack = self.v_pack = None
+        self._text_cache = tc
+        past_key_value = tc.views() if use_cache else None
+        attn = ops.prefill_attention(q, k, v)
+        attn = _gather_heads(self, attn.reshape(bsz, q_len, -1))
+        attn_output = self.wo(attn.reshape(bsz, q_len, -1))
+        return attn_output, None, past_key_value
+
     q, k, v = _split_qkv(self, hidden_states)
     q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)          # [B,H,q,D] views
     kv_seq_len = q_len
@@ -246,26 +284,6 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
         kv_seq_len += past_key_value[0].shape[-2] + (self.image_token_num if LOW_BITS else 0)
     cos, sin = self.rotary_emb(v, seq_len=kv_seq_len)
     q, k = apply_rotary_pos_emb(q, k, cos, sin, position_ids)
-
-    if q_len > 1:
-        if past_key_value is not None:
-            raise NotImplementedError("chunked prefill on top of an existing cache is not supported")
-        s0, s1 = self.sprompt_len, self.sprompt_len + self.image_token_num
-        if LOW_BITS:
-            if self.image_token_num % GROUP_SIZE:
-                raise ValueError(f"IMAGE_TOKEN_NUM must be a multiple of {GROUP_SIZE}, got {self.image_token_num}")
-            self.k_pack = ops.pack_k_per_channel(k[:, :, s0:s1], GROUP_SIZE, BITS_KV)
-            self.v_pack = ops.pack_last_dim(v[:, :, s0:s1].contiguous(), GROUP_SIZE, BITS_KV)
-            self._text_cache = _TextCache(torch.cat([k[:, :, :s0], k[:, :, s1:]], dim=2),
-                                          torch.cat([v[:, :, :s0], v[:, :, s1:]], dim=2))
-        else:
-            self.k_pack = self.v_pack = None
-            self._text_cache = _TextCache(k, v)
-        past_key_value = self._text_cache.views() if use_cache else None
-        attn = ops.prefill_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
-        attn = _gather_heads(self, attn.reshape(bsz, q_len, -1))
-        attn_output = self.wo(attn.reshape(bsz, q_len, -1))
-        return attn_output, None, past_key_value
 
     # ---- decode step -------------------------------------------------------------------------
     self._text_cache.append(k, v)

@@ -76,6 +76,19 @@ int cq_pack_k_per_channel(const void* k, int batch, int heads, int64_t T, int D,
                           int32_t* code, void* scale, void* mn, void* stream);
 
 /*
+ * Per-token V quantize-and-pack read through strides: the result of cq_pack_last_dim on
+ * `v.contiguous()` (patch_internvl.py:271 `prefill_V(value_states[:, :, s0:s1])`) without that copy,
+ * so the visual span of V can be packed straight out of the wqkv output.
+ *   v     : element (b,h,t,d) at v[b*stride_b + h*stride_h + t*stride_t + d], strides in elements,
+ *           last dimension contiguous, D == 128, every row 16-byte aligned
+ *   code  : [B,H,T,4*bits] int32      scale, mn : [B,H,T,4]
+ */
+int cq_pack_v_per_token(const void* v, int batch, int heads, int64_t T, int D,
+                        int64_t stride_b, int64_t stride_h, int64_t stride_t,
+                        int group_size, int bits, int dtype,
+                        int32_t* code, void* scale, void* mn, void* stream);
+
+/*
  * Quantized batched vector-matrix product with dequantize-on-the-fly (M == 1).
  * Replaces qjl/matmul.py:4-35 cuda_quantized_bmm_dynamic and the CUDA kernel
  * qjl/csrc/quantization.cu:67-169 (batchedQuantizedMultiplyAccumulate<T>).
@@ -292,6 +305,23 @@ int cq_rope_split_append(const void* qkv, int64_t qkv_stride_b, const void* cos_
                          int head_dim, void* q_out, void* k_cache, void* v_cache, int64_t cache_stride_b,
                          int64_t cache_stride_h, int capacity, int append_index, const int32_t* t_fp_dev,
                          int dtype, void* stream);
+/*
+ * cq_prefill_rope_split is the same step for a whole prompt (patch_internvl.py:214-260 on q_len tokens,
+ * and the `text_k`/`text_v` concatenations of :281-284): one pass over the wqkv output
+ *   qkv      : token (b,t) at qkv + b*qkv_stride_b + t*qkv_stride_t, laid out as above
+ *   position_ids : int64 [batch, t_len] on the device, or NULL for 0..t_len-1
+ *   q_out    : [batch, t_len, n_kv_heads*n_rep, 128] rotated queries
+ *   k_out    : [batch, t_len, n_kv_heads, 128] rotated keys (what the prefill attention and
+ *              cq_pack_k_per_channel read; values are read in place from qkv)
+ *   k_cache/v_cache : optional fp caches laid out as above; tokens before vis_start go to rows
+ *              0..vis_start-1, tokens from vis_start+vis_len on follow them (the visual span
+ *              [vis_start, vis_start+vis_len) is left to the pack kernels).  NULL: not written.
+ */
+int cq_prefill_rope_split(const void* qkv, int64_t qkv_stride_b, int64_t qkv_stride_t, const void* cos_table,
+                          const void* sin_table, int rope_len, const int64_t* position_ids, int batch, int t_len,
+                          int n_kv_heads, int n_rep, int head_dim, void* q_out, void* k_out, void* k_cache,
+                          void* v_cache, int64_t cache_stride_b, int64_t cache_stride_h, int capacity,
+                          int vis_start, int vis_len, int dtype, void* stream);
 int cq_add_rmsnorm(const void* delta, void* residual, const void* weight, void* out, int64_t rows, int hidden,
                    float eps, int dtype, void* stream);
 int cq_swiglu(const void* gate, const void* up, void* out, int64_t n, int dtype, void* stream);
