@@ -354,6 +354,11 @@ def run_ours(args, rank, world, device):
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args, reps=10)
+    if not args.no_model:
+        try:
+            line["prefill"] = prefill_key(device, world)
+        except Exception as e:
+            line["prefill"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     # ---- the second half of the metric: end-to-end decode tok/s of the 7B-architecture backbone on these N GPUs
     if not args.no_model:
         del caches, prepared
@@ -593,42 +598,59 @@ def run_qjl(args, rank, world, device):
     }
 
 
-def run_prefill(args, rank, world, device):
-    """Dense causal prefill attention alone (tcgen05 kernel) on the 7B prefill shape: batch rows per
-    GPU x 3392 tokens, 32 query / 8 KV heads, bf16."""
+def time_prefill(device, world, B=16, T=3392, HQ=32, steps=5, warmup=3):
+    """Time the dense causal prefill attention (tcgen05 kernel) on B rows x T tokens per GPU, 32 query / 8 KV
+    heads, bf16.  Returns (ms per pass as the max over ranks, TFLOP/s of one GPU, peak, peak source, MB per pass)."""
     from calibquant_b200 import ops
-    B, T, HQ = (args.batch if args.batch != 8 else 16), 3392, 32
     g = torch.Generator(device=device).manual_seed(3)
     q = torch.randn(B, T, HQ, D, generator=g, device=device).to(torch.bfloat16)
     k = torch.randn(B, T, HKV, D, generator=g, device=device).to(torch.bfloat16)
     v = torch.randn(B, T, HKV, D, generator=g, device=device).to(torch.bfloat16)
     out = torch.empty_like(q)
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         ops.prefill_attention(q, k, v, out=out)
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         ops.prefill_attention(q, k, v, out=out)
     ev1.record()
     torch.cuda.synchronize()
-    t = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=device, dtype=torch.float64)
+    t = torch.tensor([ev0.elapsed_time(ev1) / steps], device=device, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     ms = float(t.item())
     flops = 4.0 * B * HQ * T * T * D / 2
-    tf = world * flops / ms / 1e9
     pk_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(pk_path):
         peak, which = float(json.load(open(pk_path))["bf16_tflops"]), "measured (cuBLAS bf16 burst)"
     else:
         peak, which = 1590.0, "fallback"
+    return ms, flops / ms / 1e9, peak, which, (2 * q.numel() + 2 * k.numel()) * 2 / 1e6
+
+
+def prefill_key(device, world):
+    """The `prefill` entry of the default line: config 2's prefill attention, batch 16 x 3392 tokens, 5 passes."""
+    ms, tf, peak, which, mb = time_prefill(device, world)
+    return {"metric": "prefill_attn_TFLOPs", "value": round(tf * world, 1), "unit": "TFLOP/s", "ms_per_pass": round(ms, 4),
+            "config": "causal prefill attention, batch 16/GPU, 3392 tokens, 32q/8kv heads, head_dim 128, bf16; 5 passes "
+                      f"after 3 warm-up; q+k+v+out = {mb:.0f} MB per pass (> L2)",
+            "flops": "4*B*Hq*T^2*D/2 (causal half)", "kernel": "prefill_tc_kernel",
+            "frac_of_peak": round(tf / peak, 4), "peak": peak, "peak_source": which}
+
+
+def run_prefill(args, rank, world, device):
+    """Dense causal prefill attention alone (tcgen05 kernel) on the 7B prefill shape: batch rows per
+    GPU x 3392 tokens, 32 query / 8 KV heads, bf16."""
+    B, T, HQ = (args.batch if args.batch != 8 else 16), 3392, 32
+    ms, tf1, peak, which, mb = time_prefill(device, world, B, T, HQ, args.steps, args.warmup)
+    tf = world * tf1
     return {
         "metric": "prefill_attn_TFLOPs", "value": round(tf, 1), "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"causal prefill attention, batch {B}/GPU, {T} tokens, 32q/8kv heads, head_dim 128",
-                   "flops": "4*B*Hq*T^2*D/2 (causal half)", "l2": "q+k+v+out = %.0f MB per pass" % ((2 * q.numel() + 2 * k.numel()) * 2 / 1e6)},
+                   "flops": "4*B*Hq*T^2*D/2 (causal half)", "l2": "q+k+v+out = %.0f MB per pass" % mb},
         "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": round(tf / world, 1), "peak": peak,
                      "unit": "TFLOP/s", "frac": round(tf / world / peak, 4), "peak_source": which, "traffic": None},
         "gpu_launches": args.steps,

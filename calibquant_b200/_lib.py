@@ -46,6 +46,22 @@ class DecodeArgs(_c.Structure):
     ]
 
 
+class U8DecodeArgs(_c.Structure):
+    """Mirror of ``struct cq_u8_decode_args``."""
+
+    _fields_ = [
+        ("batch", _i32), ("n_q_heads", _i32), ("n_kv_heads", _i32), ("head_dim", _i32),
+        ("t_vis", _i32), ("t_fp", _i32), ("t_sys", _i32),
+        ("bits", _i32), ("dtype", _i32), ("calibrate", _i32), ("n_scale_heads", _i32), ("reserved", _i32),
+        ("q", _vp), ("enc_k", _vp), ("enc_v", _vp),
+        ("scale_key", _vp), ("zero_point_key", _vp), ("scale_value", _vp), ("zero_point_value", _vp),
+        ("k_fp", _vp), ("v_fp", _vp),
+        ("fp_stride_b", _i64), ("fp_stride_h", _i64),
+        ("mask", _vp), ("mask_stride_b", _i64),
+        ("out", _vp),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/calibquant_b200.h declares.
 SIGNATURES = {
     "cq_version": (_c.c_int, []),
@@ -75,6 +91,8 @@ SIGNATURES = {
     "cq_lut_out_workspace_bytes": (_sz, [_c.c_int, _c.c_int, _c.c_int]),
     "cq_lut_out": (_c.c_int, [_vp, _vp, _vp, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                               _c.c_int, _c.c_int, _vp, _sz, _vp]),
+    "cq_u8_decode_attn_workspace_bytes": (_sz, [_c.POINTER(U8DecodeArgs)]),
+    "cq_u8_decode_attn": (_c.c_int, [_c.POINTER(U8DecodeArgs), _vp, _sz, _vp]),
     "cq_rope_split_append": (_c.c_int, [_vp, _i64, _vp, _vp, _c.c_int, _vp, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                         _vp, _vp, _vp, _i64, _i64, _c.c_int, _c.c_int, _vp, _c.c_int, _vp]),
     "cq_prefill_rope_split": (_c.c_int, [_vp, _i64, _i64, _vp, _vp, _c.c_int, _vp, _c.c_int, _c.c_int, _c.c_int,

@@ -53,20 +53,29 @@ def quant_params(x: torch.Tensor, bits: int, scale=1):
 
 def quant(x, bits, per_channel=False, scale=1, post_scale=False):
     """``quant(x [B,T,H,D], bits, per_channel=True, scale=clip, post_scale)`` ->
-    ``(x_q or dequantized x, scale, zero_point)``.  Only ``per_channel=True`` is implemented (the only
-    mode the reference's attention forward uses, ``patch_internvl.py:292,297``)."""
-    if not per_channel:
-        raise NotImplementedError("only per_channel=True (min/max over tokens per channel) is implemented")
+    ``(x_q or dequantized x, scale, zero_point)``.  ``per_channel=True`` (min/max over tokens per channel) is
+    the mode the reference's attention forward uses (``patch_internvl.py:292,297``); ``per_channel=False``
+    takes one scale and zero point for the whole tensor and returns them as 0-dim tensors."""
     _need_cuda(x)
     x = _prep(x)
     B, T, H, D = x.shape
-    s, zp = quant_params(x, bits, scale)
+    if per_channel:
+        s, zp = quant_params(x, bits, scale)
+        s_ret, zp_ret = s, zp
+    else:
+        # one scale for the whole tensor (calibquant.py:29-31): the two reductions and the four scalar ops run
+        # as the reference writes them, the per-element pass is the same kernel with the scalars broadcast
+        x_min, x_max = x.min() * scale, x.max() * scale
+        s_ret = (x_max - x_min) / (2 ** bits - 1)
+        zp_ret = -x_min / s_ret
+        s = s_ret.to(x.dtype).expand(B, 1, H, D).contiguous()
+        zp = zp_ret.to(x.dtype).expand(B, 1, H, D).contiguous()
     out = torch.empty((B, T, H, D), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         rc = lib().cq_calib_quantize(_ptr(x), B, T, H, D, _strides3(x), bits, _dtype_enum(x), _ptr(s), _ptr(zp),
                                      0 if post_scale else 1, _ptr(out), None, _stream())
     check(rc, "cq_calib_quantize")
-    return out, s, zp
+    return out, s_ret, zp_ret
 
 
 def quant_encode(x, bits, scale=1):
@@ -132,12 +141,61 @@ def fused_kernel_wv(unique_values, weights, features_enc, BITS=BITS_KV, DATUM_PE
     return out
 
 
-def decode_attention(q, state, k_fp, v_fp, bits, sys_len, normalize=None):
-    """Decode step of the reference's calibquant forward (``patch_internvl.py:356-436``) on the
-    uint8 format: post-scaling (scale folded into the query, zero point into a scalar bias), logit
-    calibration, fp32 softmax, LUT products, fp16 system/text segments.  ``state`` holds ``enc_k, enc_v``
-    [B,Hkv,T,D*bits/8] and ``scale_key, zero_point_key, scale_value, zero_point_value`` [B,Hq,1,D].
+def decode_attention(q, state, k_fp, v_fp, bits, sys_len, normalize=None, mask=None):
+    """Decode step of the reference's calibquant forward (``patch_internvl.py:356-436``) on the uint8
+    format as ONE library call of four launches: post-scaling (scale folded into the query, zero point
+    into a scalar bias), logit calibration, fp32 softmax, the two code products, the full-precision
+    system/text segments.  ``state`` holds ``enc_k, enc_v`` [B,Hkv,T,D*bits/8] and ``scale_key,
+    zero_point_key, scale_value, zero_point_value`` as [B,Hq,1,D] (the reference's repeated layout) or
+    [B,1,Hkv,D] / [B,Hkv,1,D] (one row per KV head).  ``k_fp``/``v_fp`` [B,Hkv,T_fp,D] hold
+    [system | text]; ``mask`` is the optional additive mask [B,1,1,T] over [system | visual | text].
     Returns [B,Hq,1,D] in bfloat16 as the reference does."""
+    from ._lib import U8DecodeArgs
+    _need_cuda(q, k_fp, v_fp)
+    B, Hq, _, D = q.shape
+    Hkv, t_fp = k_fp.shape[1], k_fp.shape[2]
+    normalize = (bits <= 2) if normalize is None else normalize
+    enc_k, enc_v = state["enc_k"].contiguous(), state["enc_v"].contiguous()
+    t_vis = enc_k.shape[2]
+    params = [state[n] for n in ("scale_key", "zero_point_key", "scale_value", "zero_point_value")]
+    hs = params[0].numel() // (B * D)
+    if hs not in (Hq, Hkv) or any(p.numel() != B * hs * D or p.dtype != q.dtype for p in params):
+        raise ValueError("scale / zero point must hold one row of D values per query head or per KV head")
+    params = [p.contiguous() for p in params]
+    for t in (k_fp, v_fp):
+        if t_fp and (t.stride(3) != 1 or t.stride(2) != D):
+            raise ValueError("k_fp / v_fp token rows must be contiguous")
+    q3 = q.reshape(B, Hq, D).contiguous()
+    mask2 = None
+    if mask is not None:
+        mask2 = mask.reshape(B, -1).to(q.dtype).contiguous()
+        if mask2.shape[1] != t_vis + t_fp:
+            raise ValueError(f"mask must cover {t_vis + t_fp} keys, got {mask2.shape[1]}")
+    out = torch.empty((B, Hq, 1, D), dtype=torch.bfloat16, device=q.device)
+    a = U8DecodeArgs(batch=B, n_q_heads=Hq, n_kv_heads=Hkv, head_dim=D, t_vis=t_vis, t_fp=t_fp, t_sys=sys_len,
+                     bits=bits, dtype=_dtype_enum(q), calibrate=int(bool(normalize)), n_scale_heads=hs, reserved=0,
+                     q=q3.data_ptr(), enc_k=enc_k.data_ptr(), enc_v=enc_v.data_ptr(),
+                     scale_key=params[0].data_ptr(), zero_point_key=params[1].data_ptr(),
+                     scale_value=params[2].data_ptr(), zero_point_value=params[3].data_ptr(),
+                     k_fp=k_fp.data_ptr() if t_fp else None, v_fp=v_fp.data_ptr() if t_fp else None,
+                     fp_stride_b=k_fp.stride(0), fp_stride_h=k_fp.stride(1),
+                     mask=mask2.data_ptr() if mask2 is not None else None,
+                     mask_stride_b=mask2.stride(0) if mask2 is not None else 0, out=out.data_ptr())
+    if k_fp.stride() != v_fp.stride():
+        raise ValueError("k_fp and v_fp must share strides")
+    nbytes = lib().cq_u8_decode_attn_workspace_bytes(ctypes.byref(a))
+    if nbytes == 0:
+        raise ValueError("cq_u8_decode_attn rejects this request (sizes, head counts or more than 51200 keys)")
+    ws = _workspace(nbytes + 256, q.device)
+    with torch.cuda.device(q.device):
+        rc = lib().cq_u8_decode_attn(ctypes.byref(a), ctypes.c_void_p(ws.data_ptr() + 256), nbytes, _stream())
+    check(rc, "cq_u8_decode_attn")
+    return out
+
+
+def decode_attention_unfused(q, state, k_fp, v_fp, bits, sys_len, normalize=None):
+    """The same step as the reference writes it: eager torch around ``fused_kernel`` and
+    ``fused_kernel_wv``.  Kept as a cross-check of ``decode_attention``."""
     import math
     from .patch_internvl import repeat_kv
     n_rep = q.shape[1] // k_fp.shape[1]

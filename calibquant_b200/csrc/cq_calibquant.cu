@@ -11,6 +11,8 @@
 //   fused_kernel_wv calibquant.py:192-276  o[d] = sum_t w[t]*LUT[code[t,d]]   fp32 acc, fp16 out
 // Layouts: x [B,T,H,D] (strided), codes/enc [B,H,T,*], scale/zp [B,H,D] (the reference keeps them
 // as [B,1,H,D]; same memory).  D == 128.
+#include <type_traits>
+
 #include "cq_common.cuh"
 #include "cq_ptx.cuh"
 
@@ -487,29 +489,83 @@ struct LutMap {
 
 constexpr int LS_TOK = 64;       // tokens per warp iteration (4 m-tiles)
 
-template <typename T, int BITS>
+// Score type of the fused decode step: `fused_kernel(...) / sd - bias_k` is an fp16 tensor minus a tensor of
+// the data dtype, so torch keeps fp16 for fp16 data and promotes to fp32 for bf16 data.
+template <typename T> struct StepScore;
+template <> struct StepScore<__half> {
+  using type = __half;
+  static __device__ __forceinline__ float r(float v) { return rnd<__half>(v); }
+  static __device__ __forceinline__ __half make(float v) { return __float2half_rn(v); }
+  static __device__ __forceinline__ float load(__half v) { return __half2float(v); }
+};
+template <> struct StepScore<__nv_bfloat16> {
+  using type = float;
+  static __device__ __forceinline__ float r(float v) { return v; }
+  static __device__ __forceinline__ float make(float v) { return v; }
+  static __device__ __forceinline__ float load(float v) { return v; }
+};
+
+__device__ __forceinline__ void put_score(__half& dst, float v) { dst = __float2half_rn(v); }
+__device__ __forceinline__ void put_score(float& dst, float v) { dst = v; }
+
+// With STEP set this is the visual-score launch of the fused decode step (patch_internvl.py:366-372):
+// `w` is the query, the weights become rnd(q * scale_key), the table is the identity and the epilogue
+// applies `/ sqrt(D) - bias_k` with bias_k = sum_d(scale_key*zero_point_key*q) / sqrt(D).
+struct StepScoreArgs {
+  const void* scale;      // [B, scale_heads, D]
+  const void* zero_point;
+  int scale_heads;        // the query-head count (as the reference keeps them) or the code-head count
+  void* out;              // [B,Hq,T] of StepScore<T>::type
+  uint16_t* lut_out;      // receives the fp16 identity table 0..15 for the later attn.V launch
+};
+
+template <typename T, int BITS, bool STEP = false>
 __global__ void __launch_bounds__(128)
 lut_scores_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const uint8_t* __restrict__ enc,
-                      int hq, int hkv_enc, int t_len, __half* __restrict__ out) {
+                      int hq, int hkv_enc, int t_len, __half* __restrict__ out, StepScoreArgs sa = StepScoreArgs{}) {
+  using SOut = typename std::conditional<STEP, typename StepScore<T>::type, __half>::type;
   constexpr int ROW_BYTES = kHeadDim * BITS / 8;          // 16 / 32 / 64
   constexpr int WORDS = ROW_BYTES / 4;
   __shared__ float w_s[kMaxRep][kHeadDim];
   __shared__ float wsum_s[kMaxRep];
   __shared__ float lut_s[16];
-  __shared__ __align__(16) __half out_s[4][kMaxRep][LS_TOK + 8];
+  __shared__ __align__(16) SOut out_s[4][kMaxRep][LS_TOK + 8];
+  __shared__ float bias_s[STEP ? kMaxRep : 1][STEP ? kHeadDim : 1];
   const int bhk = blockIdx.y, b = bhk / hkv_enc, hk = bhk % hkv_enc;
   const int n_rep = hq / hkv_enc;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int64_t row0 = (int64_t)b * hq + (int64_t)hk * n_rep;
+  const float sd = sqrtf((float)kHeadDim);
   for (int i = tid; i < kMaxRep * kHeadDim; i += 128) {
     const int r = i >> 7, d = i & (kHeadDim - 1);
-    w_s[r][d] = r < n_rep ? Elem<T>::to_f(w[(row0 + r) * kHeadDim + d]) : 0.f;
+    float wv = r < n_rep ? Elem<T>::to_f(w[(row0 + r) * kHeadDim + d]) : 0.f;
+    if (STEP) {
+      float bp = 0.f;
+      if (r < n_rep) {
+        const int64_t srow = sa.scale_heads == hq ? row0 + r : (int64_t)b * sa.scale_heads + hk;
+        const float sk = Elem<T>::to_f(static_cast<const T*>(sa.scale)[srow * kHeadDim + d]);
+        const float zk = Elem<T>::to_f(static_cast<const T*>(sa.zero_point)[srow * kHeadDim + d]);
+        bp = rnd<T>(rnd<T>(sk * zk) * wv);
+        wv = rnd<T>(wv * sk);
+      }
+      bias_s[STEP ? r : 0][STEP ? d : 0] = bp;
+    }
+    w_s[r][d] = wv;
   }
-  if (tid < (1 << BITS)) lut_s[tid] = Elem<T>::to_f(lut[tid]);
+  if (STEP) {
+    if (tid < 16) lut_s[tid] = (float)tid;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && tid < 16) sa.lut_out[tid] = __half_as_ushort(__float2half_rn((float)tid));
+  } else if (tid < (1 << BITS)) lut_s[tid] = Elem<T>::to_f(lut[tid]);
   __syncthreads();
   for (int r = warp; r < kMaxRep; r += 4) {               // sum_d w[r][d], a warp per head
-    const float s = warp_sum(w_s[r][lane] + w_s[r][lane + 32] + w_s[r][lane + 64] + w_s[r][lane + 96]);
-    if (lane == 0) wsum_s[r] = s;
+    float s = warp_sum(w_s[r][lane] + w_s[r][lane + 32] + w_s[r][lane + 64] + w_s[r][lane + 96]);
+    if (STEP) {       // bias_k: the sum rounds to the data dtype, so does the division
+      const int rr = STEP ? r : 0;
+      const float bsum = warp_sum(bias_s[rr][STEP ? lane : 0] + bias_s[rr][STEP ? lane + 32 : 0] +
+                                  bias_s[rr][STEP ? lane + 64 : 0] + bias_s[rr][STEP ? lane + 96 : 0]);
+      s = rnd<T>(__fdiv_rn(rnd<T>(bsum), sd));
+    }
+    if (lane == 0) wsum_s[r] = s;                          // STEP: bias_k of the head
   }
   const float l0 = lut_s[0], step = lut_s[1] - lut_s[0];
   bool affine = true;
@@ -598,20 +654,29 @@ lut_scores_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const 
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = 2 * c + (e & 1), tt = 16 * mt + g + 8 * (e >> 1);
-        if (r < n_rep) out_s[warp][r][tt] = __float2half_rn(fmaf(step * 1048576.f, acc[e], l0 * wsum_s[r]));
+        if (r < n_rep) {
+          if (STEP) {
+            const float raw = rnd<__half>(acc[e] * 1048576.f);                      // fused_kernel's fp16 output
+            put_score(out_s[warp][r][tt], StepScore<T>::r(rnd<__half>(__fdiv_rn(raw, sd)) - wsum_s[r]));
+          } else {
+            put_score(out_s[warp][r][tt], fmaf(step * 1048576.f, acc[e], l0 * wsum_s[r]));
+          }
+        }
       }
     }
     __syncwarp();
+    SOut* outp = STEP ? static_cast<SOut*>(sa.out) : reinterpret_cast<SOut*>(out);
+    constexpr int PER16 = 16 / (int)sizeof(SOut);          // scores per 16-byte store
     if (vec_ok && t0 + LS_TOK <= t_len) {
-      for (int i = lane; i < n_rep * (LS_TOK / 8); i += 32) {
-        const int r = i / (LS_TOK / 8), ch = i % (LS_TOK / 8);
-        *reinterpret_cast<uint4*>(out + (row0 + r) * t_len + t0 + 8 * ch) =
-            *reinterpret_cast<const uint4*>(&out_s[warp][r][8 * ch]);
+      for (int i = lane; i < n_rep * (LS_TOK / PER16); i += 32) {
+        const int r = i / (LS_TOK / PER16), ch = i % (LS_TOK / PER16);
+        *reinterpret_cast<uint4*>(outp + (row0 + r) * t_len + t0 + PER16 * ch) =
+            *reinterpret_cast<const uint4*>(&out_s[warp][r][PER16 * ch]);
       }
     } else {
       for (int i = lane; i < n_rep * LS_TOK; i += 32) {
         const int r = i / LS_TOK, tt = i % LS_TOK;
-        if (t0 + tt < t_len) out[(row0 + r) * t_len + t0 + tt] = out_s[warp][r][tt];
+        if (t0 + tt < t_len) outp[(row0 + r) * t_len + t0 + tt] = out_s[warp][r][tt];
       }
     }
     __syncwarp();
@@ -752,6 +817,136 @@ lut_out_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const uin
   }
 }
 
+
+
+// ---- fused decode step, launch 2: full-precision scores, calibration, softmax -------------------------------
+// One CTA per (batch, query head).  The whole row [sys | visual | text] lives in shared memory as fp32:
+//   s_fp[t]  = rnd(rnd(q . k_fp[t]) / sqrt(D))                               patch_internvl.py:362-365
+//   s_vis    = calibrated visual scores (every op rounded to the score dtype)                 :376-385
+//   att      = rnd(softmax_fp32(row))                                                        :388-390
+// Outputs: att over the visual span as fp16 (the weights of fused_kernel_wv, :396), att over the fp tokens in
+// the data dtype, and rnd(sum of the visual att) for the zero-point term (:399).
+constexpr int SM_THREADS = 1024;
+
+__device__ __forceinline__ float block_reduce(float v, float* red, int op) {   // op 0: sum, 1: max, 2: min
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = op == 0 ? warp_sum(v) : op == 1 ? warp_max(v) : warp_min(v);
+  __syncthreads();                       // red may still be read from the previous reduction
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int n = (blockDim.x + 31) >> 5;
+  float r = red[0];
+  for (int i = 1; i < n; ++i) r = op == 0 ? r + red[i] : op == 1 ? fmaxf(r, red[i]) : fminf(r, red[i]);
+  return r;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SM_THREADS)
+step_softmax_kernel(const T* __restrict__ q, const T* __restrict__ k_fp, int64_t fp_stride_b, int64_t fp_stride_h,
+                    int hq, int hkv, int t_vis, int t_fp, int t_sys, int calibrate,
+                    const typename StepScore<T>::type* __restrict__ s_vis, const T* __restrict__ mask,
+                    int64_t mask_stride_b, __half* __restrict__ a_vis, T* __restrict__ a_fp,
+                    float* __restrict__ a_sum) {
+  extern __shared__ float row[];         // [t_vis + t_fp], visual scores first
+  __shared__ float red[32];
+  __shared__ float q_s[kHeadDim];
+  using SS = StepScore<T>;
+  const int bh = blockIdx.x, b = bh / hq, h = bh % hq, hk = h / (hq / hkv);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float sd = sqrtf((float)kHeadDim);
+  if (tid < kHeadDim) q_s[tid] = Elem<T>::to_f(q[(int64_t)bh * kHeadDim + tid]);
+  __syncthreads();
+  const T* kb = k_fp + b * fp_stride_b + hk * fp_stride_h;
+  for (int t = warp; t < t_fp; t += SM_THREADS / 32) {
+    const T* kr = kb + (int64_t)t * kHeadDim + lane * 4;
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dot = fmaf(q_s[lane * 4 + i], Elem<T>::to_f(kr[i]), dot);
+    dot = warp_sum(dot);
+    if (lane == 0) row[t_vis + t] = rnd<T>(__fdiv_rn(rnd<T>(dot), sd));
+  }
+  const typename SS::type* sv = s_vis + (int64_t)bh * t_vis;
+  float mx = -INFINITY, mn = INFINITY;
+  for (int t = tid; t < t_vis; t += SM_THREADS) {
+    const float v = SS::load(sv[t]);
+    row[t] = v;
+    mx = fmaxf(mx, v);
+    mn = fminf(mn, v);
+  }
+  if (calibrate && t_vis > 0) {
+    mx = block_reduce(mx, red, 1);
+    mn = block_reduce(mn, red, 2);
+    const float span = SS::r(SS::r(mx + -3.f) - mn);              // tgt_max - tgt_min
+    const float denom = SS::r(SS::r(mx - mn) + 1e-8f);
+    for (int t = tid; t < t_vis; t += SM_THREADS) {
+      const float n = SS::r(__fdiv_rn(SS::r(row[t] - mn), denom));
+      row[t] = SS::r(SS::r(n * span) + mn);
+    }
+  }
+  __syncthreads();
+  if (mask) {                            // additive mask in the original key order [sys | visual | text] (:404-410)
+    const T* mr = mask + b * mask_stride_b;
+    for (int t = tid; t < t_vis; t += SM_THREADS) row[t] = SS::r(row[t] + Elem<T>::to_f(mr[t_sys + t]));
+    for (int t = tid; t < t_fp; t += SM_THREADS)
+      row[t_vis + t] = SS::r(row[t_vis + t] + Elem<T>::to_f(mr[t < t_sys ? t : t_vis + t]));
+    __syncthreads();
+  }
+  const int total = t_vis + t_fp;
+  float m = -INFINITY;
+  for (int t = tid; t < total; t += SM_THREADS) m = fmaxf(m, row[t]);
+  m = block_reduce(m, red, 1);
+  float sum = 0.f;
+  for (int t = tid; t < total; t += SM_THREADS) {
+    const float e = __expf(row[t] - m);
+    row[t] = e;
+    sum += e;
+  }
+  sum = block_reduce(sum, red, 0);
+  const float inv = 1.f / sum;
+  float vs = 0.f;
+  for (int t = tid; t < t_vis; t += SM_THREADS) {
+    const float a = rnd<T>(row[t] * inv);
+    a_vis[(int64_t)bh * t_vis + t] = __float2half_rn(a);
+    vs += a;
+  }
+  for (int t = tid; t < t_fp; t += SM_THREADS) a_fp[(int64_t)bh * t_fp + t] = Elem<T>::from_f(row[t_vis + t] * inv);
+  vs = block_reduce(vs, red, 0);
+  if (tid == 0) a_sum[bh] = rnd<T>(vs);
+}
+
+// ---- fused decode step, launch 4: scale / zero point of V, full-precision tokens, bf16 output -------------
+// o = fused_kernel_wv(...) * scale_v - scale_v*zero_point_v*sum(att_vis) + att_sys @ V_sys + att_txt @ V_txt
+// (patch_internvl.py:396-436), thread = channel.  Products of an fp16 tensor with a bf16 one promote to fp32.
+template <typename T>
+__global__ void __launch_bounds__(kHeadDim)
+step_finish_kernel(const float* __restrict__ partial, int chunks, int n_rows, const T* __restrict__ scale_v,
+                   const T* __restrict__ zp_v, int scale_heads, const T* __restrict__ a_fp,
+                   const float* __restrict__ a_sum, const T* __restrict__ v_fp, int64_t fp_stride_b,
+                   int64_t fp_stride_h, int hq, int hkv, int t_fp, int t_sys, __nv_bfloat16* __restrict__ out) {
+  using SS = StepScore<T>;
+  extern __shared__ float att_s[];       // [t_fp]
+  const int bh = blockIdx.x, b = bh / hq, h = bh % hq, hk = h / (hq / hkv), d = threadIdx.x;
+  for (int t = d; t < t_fp; t += kHeadDim) att_s[t] = Elem<T>::to_f(a_fp[(int64_t)bh * t_fp + t]);
+  float acc = 0.f;
+  for (int c = 0; c < chunks; ++c) acc += partial[((int64_t)c * n_rows + bh) * kHeadDim + d];
+  const int64_t srow = scale_heads == hq ? bh : (int64_t)b * scale_heads + hk;
+  float o = 0.f;
+  if (chunks) {                          // no visual span: nothing quantized to add
+    const float sv = Elem<T>::to_f(scale_v[srow * kHeadDim + d]), zv = Elem<T>::to_f(zp_v[srow * kHeadDim + d]);
+    o = SS::r(rnd<__half>(acc) * sv);
+    o = SS::r(o - rnd<T>(rnd<T>(sv * zv) * a_sum[bh]));
+  }
+  __syncthreads();
+  const T* vb = v_fp + b * fp_stride_b + hk * fp_stride_h + d;
+  float seg = 0.f;
+  const int ts = min(t_sys, t_fp);
+  for (int t = 0; t < ts; ++t) seg = fmaf(att_s[t], Elem<T>::to_f(vb[(int64_t)t * kHeadDim]), seg);
+  o = SS::r(o + rnd<T>(seg));
+  seg = 0.f;
+  for (int t = ts; t < t_fp; ++t) seg = fmaf(att_s[t], Elem<T>::to_f(vb[(int64_t)t * kHeadDim]), seg);
+  o = SS::r(o + rnd<T>(seg));
+  out[(int64_t)bh * kHeadDim + d] = __float2bfloat16_rn(o);
+}
 
 }  // namespace calib
 }  // namespace cq
@@ -938,4 +1133,108 @@ extern "C" int cq_lut_out(const void* lut, const void* weights, const uint8_t* e
   const int64_t total = (int64_t)rows * kHeadDim;
   calib::lut_out_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(ws, static_cast<__half*>(out), chunks, total);
   return check_launch();
+}
+
+// ---- fused decode step on the uint8 format: four launches -------------------------------------------------
+namespace {
+struct StepLayout {
+  size_t scores, a_vis, a_fp, a_sum, lut, partial, total;
+  int chunks;
+};
+StepLayout step_layout(const cq_u8_decode_args* a) {
+  StepLayout l{};
+  const size_t rows = (size_t)a->batch * a->n_q_heads;
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  size_t off = 0;
+  l.scores = off; off = up(off + rows * (size_t)a->t_vis * 4);
+  l.a_vis = off;  off = up(off + rows * (size_t)a->t_vis * 2);
+  l.a_fp = off;   off = up(off + rows * (size_t)a->t_fp * 2);
+  l.a_sum = off;  off = up(off + rows * 4);
+  l.lut = off;    off = up(off + 32);
+  l.chunks = a->bits <= 2 ? (a->t_vis + calib::WO_TOK - 1) / calib::WO_TOK : (a->t_vis + calib::WV_TCHUNK - 1) / calib::WV_TCHUNK;
+  l.partial = off; off = up(off + (size_t)l.chunks * rows * kHeadDim * 4);
+  l.total = off;
+  return l;
+}
+int step_check(const cq_u8_decode_args* a) {
+  if (!a) return CQ_ERR_BAD_ARG;
+  if (a->batch <= 0 || a->n_q_heads <= 0 || a->n_kv_heads <= 0 || a->t_vis < 0 || a->t_fp < 0) return CQ_ERR_BAD_ARG;
+  if (a->t_vis + a->t_fp == 0 || a->t_sys < 0 || a->t_sys > a->t_fp || a->reserved != 0) return CQ_ERR_BAD_ARG;
+  if (a->n_q_heads % a->n_kv_heads || !dtype_ok(a->dtype)) return CQ_ERR_BAD_ARG;
+  if (a->n_scale_heads != a->n_q_heads && a->n_scale_heads != a->n_kv_heads) return CQ_ERR_BAD_ARG;
+  if (!bits_ok(a->bits) || a->head_dim != kHeadDim || a->n_q_heads / a->n_kv_heads > kMaxRep) return CQ_ERR_UNSUPPORTED;
+  if ((int64_t)a->batch * a->n_kv_heads > 65535) return CQ_ERR_UNSUPPORTED;
+  if ((size_t)(a->t_vis + a->t_fp) * 4 > 200 * 1024) return CQ_ERR_UNSUPPORTED;   // the score row must fit shared memory
+  if ((size_t)a->t_fp * 4 > 160 * 1024) return CQ_ERR_UNSUPPORTED;
+  if (!a->q || !a->out) return CQ_ERR_BAD_ARG;
+  if (a->t_vis && (!a->enc_k || !a->enc_v || !a->scale_key || !a->zero_point_key || !a->scale_value || !a->zero_point_value))
+    return CQ_ERR_BAD_ARG;
+  if (a->t_vis && (!aligned16(a->enc_k) || !aligned16(a->enc_v))) return CQ_ERR_BAD_ARG;
+  if (a->t_fp && (!a->k_fp || !a->v_fp)) return CQ_ERR_BAD_ARG;
+  return CQ_OK;
+}
+}  // namespace
+
+extern "C" size_t cq_u8_decode_attn_workspace_bytes(const cq_u8_decode_args* a) {
+  if (step_check(a) != CQ_OK) return 0;
+  return step_layout(a).total;
+}
+
+template <typename T>
+static int launch_step(const cq_u8_decode_args* a, char* ws, cudaStream_t st) {
+  using S = typename calib::StepScore<T>::type;
+  const StepLayout l = step_layout(a);
+  const int B = a->batch, hq = a->n_q_heads, hkv = a->n_kv_heads, rows = B * hq;
+  S* scores = reinterpret_cast<S*>(ws + l.scores);
+  __half* a_vis = reinterpret_cast<__half*>(ws + l.a_vis);
+  T* a_fp = reinterpret_cast<T*>(ws + l.a_fp);
+  float* a_sum = reinterpret_cast<float*>(ws + l.a_sum);
+  uint16_t* lut = reinterpret_cast<uint16_t*>(ws + l.lut);
+  float* partial = reinterpret_cast<float*>(ws + l.partial);
+  const T* q = static_cast<const T*>(a->q);
+  if (a->t_vis) {
+    const int per_cta = 4 * calib::LS_TOK;
+    const int by_work = (a->t_vis + 8 * per_cta - 1) / (8 * per_cta);
+    const int by_fill = (148 * 8 + B * hkv - 1) / (B * hkv);
+    const int max_x = (a->t_vis + per_cta - 1) / per_cta;
+    dim3 grid((unsigned)max(1, min(max_x, max(by_work, by_fill))), (unsigned)(B * hkv));
+    calib::StepScoreArgs sa{a->scale_key, a->zero_point_key, a->n_scale_heads, scores, lut};
+    switch (a->bits) {
+      case 1: calib::lut_scores_mma_kernel<T, 1, true><<<grid, 128, 0, st>>>(nullptr, q, a->enc_k, hq, hkv, a->t_vis, nullptr, sa); break;
+      case 2: calib::lut_scores_mma_kernel<T, 2, true><<<grid, 128, 0, st>>>(nullptr, q, a->enc_k, hq, hkv, a->t_vis, nullptr, sa); break;
+      default: calib::lut_scores_mma_kernel<T, 4, true><<<grid, 128, 0, st>>>(nullptr, q, a->enc_k, hq, hkv, a->t_vis, nullptr, sa); break;
+    }
+  }
+  const size_t row_bytes = (size_t)(a->t_vis + a->t_fp) * 4;
+  if (cudaFuncSetAttribute(calib::step_softmax_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+    return CQ_ERR_LAUNCH;
+  calib::step_softmax_kernel<T><<<rows, calib::SM_THREADS, row_bytes, st>>>(
+      q, static_cast<const T*>(a->k_fp), a->fp_stride_b, a->fp_stride_h, hq, hkv, a->t_vis, a->t_fp, a->t_sys,
+      a->calibrate, scores, static_cast<const T*>(a->mask), a->mask_stride_b, a_vis, a_fp, a_sum);
+  if (a->t_vis) {
+    dim3 grid((unsigned)l.chunks, (unsigned)(B * hkv));
+    const __half* lut_h = reinterpret_cast<const __half*>(lut);
+    if (a->bits == 1)
+      calib::lut_out_mma_kernel<__half, 1><<<grid, 128, 0, st>>>(lut_h, a_vis, a->enc_v, hq, hkv, a->t_vis, partial, rows);
+    else if (a->bits == 2)
+      calib::lut_out_mma_kernel<__half, 2><<<grid, 128, 0, st>>>(lut_h, a_vis, a->enc_v, hq, hkv, a->t_vis, partial, rows);
+    else
+      calib::lut_out_partial_kernel<__half><<<grid, kHeadDim, 0, st>>>(lut_h, a_vis, a->enc_v, hq, hkv, a->t_vis, a->bits, partial, rows);
+  }
+  if (cudaFuncSetAttribute(calib::step_finish_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
+    return CQ_ERR_LAUNCH;
+  calib::step_finish_kernel<T><<<rows, kHeadDim, (size_t)a->t_fp * 4, st>>>(
+      partial, a->t_vis ? l.chunks : 0, rows, static_cast<const T*>(a->scale_value), static_cast<const T*>(a->zero_point_value),
+      a->n_scale_heads, a_fp, a_sum, static_cast<const T*>(a->v_fp), a->fp_stride_b, a->fp_stride_h, hq, hkv, a->t_fp,
+      a->t_sys, static_cast<__nv_bfloat16*>(a->out));
+  return check_launch();
+}
+
+extern "C" int cq_u8_decode_attn(const cq_u8_decode_args* a, void* workspace, size_t workspace_bytes, void* stream) {
+  const int rc = step_check(a);
+  if (rc != CQ_OK) return rc;
+  if (!workspace || workspace_bytes < step_layout(a).total) return CQ_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->dtype == CQ_DTYPE_F16) return launch_step<__half>(a, static_cast<char*>(workspace), st);
+  return launch_step<__nv_bfloat16>(a, static_cast<char*>(workspace), st);
 }

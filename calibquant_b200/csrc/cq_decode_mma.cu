@@ -34,6 +34,7 @@
 #include <stdlib.h>
 
 #include <mutex>
+#include <utility>
 #include <type_traits>
 
 #include "cq_common.cuh"
@@ -210,6 +211,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   const int n_pairs = dm.batch * dm.hkv;
   const int n_items = n_pairs * dm.n_ktiles;
 
+  pdl_launch_dependents();
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], K1_WARPS); }
     mbar_fence_init();
@@ -262,6 +264,10 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   }
   (void)word_in_group;
 
+  // The producer above streams only the packed keys, which no launch of a decode step writes, so it may run
+  // ahead of the kernel before this one in the stream; the query, the appended fp keys and the score buffer
+  // (still read by the previous step) are touched only after that kernel has completed.
+  pdl_wait();
   int cur_pair = -1;
   uint32_t qA[8], qB[8];
   bool failed = false;
@@ -541,7 +547,7 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // channels 32w .. 32w+31.  Writes the (max, sum, acc[128]) partials of the fp slots that k3 merges.
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
-k2_fp_tokens(Dims dm, const T* __restrict__ scores, const T* __restrict__ v_fp,
+k2_fp_tokens(Dims dm, const T* scores, const T* __restrict__ v_fp,   // scores: written by an overlapping launch
              float* __restrict__ partial, float2* __restrict__ ml) {
   constexpr int PF_PITCH = 128 + 8;         // probability row pitch (elements): rows land on different banks
   constexpr int VROW = kHeadDim * 2 + 16;   // staged V row pitch in bytes, for conflict-free ldmatrix
@@ -550,6 +556,8 @@ k2_fp_tokens(Dims dm, const T* __restrict__ scores, const T* __restrict__ v_fp,
   __shared__ __align__(16) T pf_s[kMaxRep * PF_PITCH];    // probabilities, exact in the data dtype
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int n_pairs = dm.batch * dm.hkv;
+  pdl_launch_dependents();
+  pdl_wait();
   const int t_fp = live_t_fp(dm);
   const int n_fp_chunks = (t_fp + 127) / 128;
   for (int it = blockIdx.x; it < n_pairs * n_fp_chunks; it += gridDim.x) {
@@ -644,7 +652,7 @@ k2_fp_tokens(Dims dm, const T* __restrict__ scores, const T* __restrict__ v_fp,
 // the slot of the range's first tile; the other tile slots of the range are marked empty (max = -inf).
 template <typename T, int BITS, int VT>
 __global__ void __launch_bounds__(K2_THREADS, 2)
-k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile_mm,
+k2_attn_v(Dims dm, const T* scores, const float2* tile_mm,   // written by the launch before: no read-only loads
           const int32_t* __restrict__ v_code, const T* __restrict__ v_scale,
           const T* __restrict__ v_mn,
           float* __restrict__ partial, float2* __restrict__ ml, int* __restrict__ status) {
@@ -673,6 +681,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
   const int n_vt = dm.n_chunks;             // tiles per KV head
   const int n_items = n_pairs * n_vt;
 
+  pdl_launch_dependents();
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], K2_WARPS); }
     mbar_fence_init();
@@ -686,12 +695,10 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
   if (warp == K2_WARPS) {
     if (lane == 0) {
       fence_proxy_async_smem();
-      for (int k = 0; it_first + k < it_end; ++k) {
+      // the packed values do not depend on the score launch: the first ring of tiles is requested before
+      // waiting for it, the logit rows of those tiles after
+      auto load_values = [&](int k) {
         const int it = it_first + k, s = k % STAGES;
-        if (k >= STAGES && !mbar_wait_bounded(&empty_bar[s], (uint32_t)((k / STAGES - 1) & 1), WAIT_TRIES)) {
-          atomicExch(status, CQ_ERR_TIMEOUT);
-          break;
-        }
         const int pair = it / n_vt, vt = it % n_vt;
         unsigned char* base = smem + s * STAGE_BYTES;
         const int64_t tok = (int64_t)pair * dm.t_vis + (int64_t)vt * VT;
@@ -700,9 +707,27 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
         bulk_load_1d(base, v_code + tok * WPT, (uint32_t)(nt * TOK_BYTES), &full_bar[s]);
         bulk_load_1d(base + CODE_BYTES, v_scale + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
         bulk_load_1d(base + CODE_BYTES + VT * 8, v_mn + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
+      };
+      auto load_logits = [&](int k) {
+        const int it = it_first + k, s = k % STAGES;
+        const int pair = it / n_vt, vt = it % n_vt;
+        unsigned char* base = smem + s * STAGE_BYTES;
+        const int nt = min(VT, dm.t_vis - vt * VT);
         const T* srow = scores + (int64_t)pair * dm.n_rep * dm.pitch + (int64_t)vt * VT;
         for (int h = 0; h < dm.n_rep; ++h)
           bulk_load_1d(base + LOGIT_OFF + h * LROW, srow + (int64_t)h * dm.pitch, (uint32_t)(nt * 2), &full_bar[s]);
+      };
+      const int n_pre = min(STAGES, it_end - it_first);
+      for (int k = 0; k < n_pre; ++k) load_values(k);
+      pdl_wait();
+      for (int k = 0; k < n_pre; ++k) load_logits(k);
+      for (int k = n_pre; it_first + k < it_end; ++k) {
+        if (!mbar_wait_bounded(&empty_bar[k % STAGES], (uint32_t)((k / STAGES - 1) & 1), WAIT_TRIES)) {
+          atomicExch(status, CQ_ERR_TIMEOUT);
+          break;
+        }
+        load_values(k);
+        load_logits(k);
       }
     }
     return;
@@ -724,6 +749,7 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
     sc1[i] = exp2f((float)(24 - sh - BITS));
   }
 
+  pdl_wait();          // the tile minima / maxima and (through the producer) the logits come from the score launch
   float acc[8][4];
   float cb[4] = {0.f, 0.f, 0.f, 0.f};
   int seg_pair = -1, seg_first = 0, seg_end = 0;     // the run of tiles of one KV head accumulated so far
@@ -956,27 +982,29 @@ k2_attn_v(Dims dm, const T* __restrict__ scores, const float2* __restrict__ tile
 // contexts), 1 when it has a handful (then four times as many rows fit on an SM at once)
 template <typename T, int K3_LANES>
 __global__ void __launch_bounds__(kHeadDim * K3_LANES)
-k3_combine(Dims dm, const float* __restrict__ partial, const float2* __restrict__ ml,
+k3_combine(Dims dm, const float* partial, const float2* ml,   // written by overlapping launches: plain loads only
            T* __restrict__ out) {
   __shared__ float o_s[K3_LANES][kHeadDim];
   __shared__ float l_s[K3_LANES];
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const int d = threadIdx.x & (kHeadDim - 1), sl = threadIdx.x >> 7;
   const float2* r = ml + row * dm.n_slots;
   const int n_live = dm.n_chunks + (live_t_fp(dm) + 127) / 128;   // visual chunks, then fp chunks
   // common maximum: the lanes of every warp share the slots, one or two loads each
   float M = -INFINITY;
-  for (int i = threadIdx.x & 31; i < n_live; i += 32) M = fmaxf(M, __ldg(&r[i]).x);
+  for (int i = threadIdx.x & 31; i < n_live; i += 32) M = fmaxf(M, r[i].x);
   M = warp_max(M);
   float L = 0.f, o = 0.f;
   const float* p = partial + row * dm.n_slots * kHeadDim + d;
 #pragma unroll 8
   for (int i = sl; i < n_live; i += K3_LANES) {
-    const float2 mlv = __ldg(&r[i]);
+    const float2 mlv = r[i];
     if (mlv.x == -INFINITY) continue;      // an empty slot (its run of tiles was accumulated into an earlier one)
     const float w = exp2f((mlv.x - M) * LOG2E);
     L = fmaf(mlv.y, w, L);
-    o = fmaf(__ldg(p + (int64_t)i * kHeadDim), w, o);
+    o = fmaf(p[(int64_t)i * kHeadDim], w, o);
   }
   o_s[sl][d] = o;
   if (d == 0) l_s[sl] = L;
@@ -1096,6 +1124,24 @@ static int sm_count() {      // of the current device
   return v;
 }
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may begin (up to its pdl_wait())
+// while the previous kernel of the stream drains.
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
 template <typename T, int BITS, int VT>
 static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st,
                      cudaEvent_t* ev, int* status_word) {
@@ -1137,8 +1183,9 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
       return CQ_ERR_LAUNCH;
     const int items1 = n_pairs * d.n_ktiles;
     const int grid1 = max(1, min(items1 + n_pairs * ((d.t_fp + 63) / 64), sm_count() * occ1));
-    k1<<<grid1, K1_THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(a->q),
-                                      static_cast<const T*>(a->k_fp), scores, mm, status);
+    if (launch_pdl(k1, dim3(grid1), dim3(K1_THREADS), smem1, st, tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(a->q),
+                   static_cast<const T*>(a->k_fp), scores, mm, status) != cudaSuccess)
+      return CQ_ERR_LAUNCH;
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
   }
@@ -1146,23 +1193,30 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
   {
     const int items2 = n_pairs * d.n_chunks;
     const int grid2 = max(1, min(items2, sm_count() * occ2));
-    k2<<<grid2, K2_THREADS, smem2, st>>>(d, scores, mm, a->v_code, static_cast<const T*>(a->v_scale),
-                                      static_cast<const T*>(a->v_mn), partial, ml, status);
+    if (launch_pdl(k2, dim3(grid2), dim3(K2_THREADS), smem2, st, d, static_cast<const T*>(scores),
+                   static_cast<const float2*>(mm), a->v_code, static_cast<const T*>(a->v_scale),
+                   static_cast<const T*>(a->v_mn), partial, ml, status) != cudaSuccess)
+      return CQ_ERR_LAUNCH;
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
     mark(2);
     if (d.n_fp_chunks > 0) {
-      k2_fp_tokens<T><<<n_pairs * d.n_fp_chunks, THREADS, 0, st>>>(d, scores, static_cast<const T*>(a->v_fp),
-                                                                 partial, ml);
+      if (launch_pdl(k2_fp_tokens<T>, dim3(n_pairs * d.n_fp_chunks), dim3(THREADS), 0, st, d, static_cast<const T*>(scores),
+                     static_cast<const T*>(a->v_fp), partial, ml) != cudaSuccess)
+        return CQ_ERR_LAUNCH;
       rc = check_launch();
       if (rc != CQ_OK) return rc;
     }
     mark(3);
   }
+  cudaError_t e3;
   if (d.n_slots >= 16)
-    k3_combine<T, 4><<<d.batch * d.hq, kHeadDim * 4, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
+    e3 = launch_pdl(k3_combine<T, 4>, dim3(d.batch * d.hq), dim3(kHeadDim * 4), 0, st, d, static_cast<const float*>(partial),
+                    static_cast<const float2*>(ml), static_cast<T*>(a->out));
   else
-    k3_combine<T, 1><<<d.batch * d.hq, kHeadDim, 0, st>>>(d, partial, ml, static_cast<T*>(a->out));
+    e3 = launch_pdl(k3_combine<T, 1>, dim3(d.batch * d.hq), dim3(kHeadDim), 0, st, d, static_cast<const float*>(partial),
+                    static_cast<const float2*>(ml), static_cast<T*>(a->out));
+  if (e3 != cudaSuccess) return CQ_ERR_LAUNCH;
   const int rc3 = check_launch();
   mark(4);
   return rc3;

@@ -150,5 +150,12 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   return r;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may
+// start while the kernel before it in the stream still runs; pdl_wait() blocks the calling thread until that
+// kernel has completed and its writes are visible (a no-op for a normal launch), and
+// pdl_launch_dependents() lets the next kernel in the stream start early once every CTA has called it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 }  // namespace ptx
 }  // namespace cq

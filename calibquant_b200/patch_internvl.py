@@ -34,6 +34,10 @@ from .qjl.qjl_utils import QJLKeyQuantizer, repeat_kv_quant
 
 # global hyperparameters for quantization (same names and defaults as the reference)
 BITS_KV = 1
+# layout of the quantized visual span: "group" (32-element groups, the layout of the reference's qjl kernels)
+# or "uint8" (the reference's calibquant forward: one scale per channel over the whole span, clip factors
+# SCALE_K / SCALE_V, bytes packed most-significant field first); chosen by patch_model(..., kv_format=...)
+KV_FORMAT = "group"
 
 if BITS_KV == 1:
     SCALE_V = 0.3
@@ -232,6 +236,8 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
     bsz, q_len, _ = hidden_states.size()
 
     if q_len == 1 and getattr(self, "_static_decode", False):
+        if getattr(self, "_u8_state", None) is not None:
+            raise NotImplementedError("the graph-replayable decode step serves the group format only")
         # graph-replayable step: everything that changes between steps is read from device memory.
         # One launch splits the projection, rotates q and k and appends k, v at the device-side
         # token count (already advanced by the owner of the counter), one call attends over the
@@ -265,11 +271,17 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
         tc = _TextCache.empty(bsz, n_kv, q_len - n_vis, self.head_dim, hidden_states.dtype, hidden_states.device)
         q, k, v = ops.prefill_rope_split(self.wqkv(hidden_states), cos, sin, position_ids, n_kv, n_rep,
                                          tc.k, tc.v, s0, n_vis)
-        if LOW_BITS:
+        self.k_pack = self.v_pack = self._u8_state = None
+        if LOW_BITS and KV_FORMAT == "uint8":
+            # patch_internvl.py:288-339: whole-span per-channel min-max with the clip factors, codes as bytes
+            from . import calibquant as _cq
+            enc_k, sk, zk = _cq.quant_encode(k[:, s0:s0 + n_vis], BITS_KV, scale=SCALE_K)
+            enc_v, sv, zv = _cq.quant_encode(v[:, s0:s0 + n_vis], BITS_KV, scale=SCALE_V)
+            self._u8_state = {"enc_k": enc_k, "enc_v": enc_v, "scale_key": sk, "zero_point_key": zk,
+                              "scale_value": sv, "zero_point_value": zv}
+        elif LOW_BITS:
             self.k_pack = ops.pack_k_per_channel(k.transpose(1, 2)[:, :, s0:s0 + n_vis], GROUP_SIZE, BITS_KV)
             self.v_pack = ops.pack_v_per_token(v.transpose(1, 2)[:, :, s0:s0 + n_vis], GROUP_SIZE, BITS_KV)
-        else:
-            self.k_pack = self.v_pack = None
         self._text_cache = tc
         past_key_value = tc.views() if use_cache else None
         attn = ops.prefill_attention(q, k, v)
@@ -293,9 +305,14 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
         raise ValueError(f"Attention mask should be of size {(bsz, 1, q_len, kv_seq_len)}, "
                          f"but is {attention_mask.size()}")
     t_sys = self.sprompt_len if LOW_BITS else 0
-    attn = ops.decode_attention(q, self.k_pack, self.v_pack, k_fp, v_fp, t_sys, BITS_KV,
-                                group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
-                                mask=attention_mask)                             # [B,Hq,1,D]
+    if getattr(self, "_u8_state", None) is not None:
+        from . import calibquant as _cq
+        attn = _cq.decode_attention(q, self._u8_state, k_fp, v_fp, BITS_KV, t_sys, normalize=self.normalize,
+                                    mask=attention_mask).to(q.dtype)             # bfloat16 out, as the reference
+    else:
+        attn = ops.decode_attention(q, self.k_pack, self.v_pack, k_fp, v_fp, t_sys, BITS_KV,
+                                    group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
+                                    mask=attention_mask)                         # [B,Hq,1,D]
     local_heads = self.num_heads // _shard_world(self)
     if attn.size() != (bsz, local_heads, q_len, self.head_dim):
         raise ValueError(f"`attn_output` should be of size {(bsz, local_heads, q_len, self.head_dim)}, "
@@ -377,12 +394,20 @@ ATTN_FORWARD_FUNCTIONS = {
 
 def patch_model(model, quant_method="calibquant", **kwargs):
     """Swap the chat model's ``generate`` and the attention class's ``forward`` in place, exactly
-    as ``patch_internvl.py:645-660``; the ``qjl`` settings land on ``model.config.llm_config``."""
+    as ``patch_internvl.py:645-660``; the ``qjl`` settings land on ``model.config.llm_config``.
+    ``kv_format="uint8"`` (with ``"calibquant"``) keeps the visual span in the reference's own byte format
+    and decodes with ``calibquant.decode_attention``; the default ``"group"`` is the 32-element group format."""
     print("Patching InternVLChatModel.generate function ...")
     if hasattr(model, "extract_feature"):
         model.__class__.generate = custom_generate
     print(f"Patching InternLM2FlashAttention2.forward function ... {quant_method}")
     model.language_model.model.layers[0].attention.__class__.forward = ATTN_FORWARD_FUNCTIONS[quant_method]
+    if quant_method == "calibquant":
+        global KV_FORMAT
+        kv_format = kwargs.get("kv_format", "group")
+        if kv_format not in ("group", "uint8"):
+            raise ValueError(f"kv_format must be 'group' or 'uint8', got {kv_format!r}")
+        KV_FORMAT = kv_format
     if quant_method == "qjl":
         cfg = model.config.llm_config
         cfg.k_bits = kwargs.get("k_bits", 2)

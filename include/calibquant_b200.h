@@ -275,6 +275,42 @@ int cq_lut_out(const void* lut, const void* weights, const uint8_t* enc, void* o
                size_t workspace_bytes, void* stream);
 
 /*
+ * cq_u8_decode_attn: one decode step of attention on this format, four launches (no reference entry point
+ * of its own: it replaces the eager sequence patch_internvl.py:356-436 -- scores of the system and text
+ * tokens, `fused_kernel(q * scale_key) / sqrt(D) - bias_k`, logit calibration :376-385, fp32 softmax,
+ * `fused_kernel_wv(att) * scale_value - scale_value*zero_point_value*sum(att)`, the full-precision
+ * products and the final cast to bfloat16 :436).
+ *   q [B,Hq,D]; enc_k, enc_v uint8 [B,Hkv,t_vis,D*bits/8] (16-byte aligned);
+ *   scale_*, zero_point_* [B,Hs,D] in the data dtype with Hs = n_scale_heads = Hq (as the reference keeps
+ *   them, repeated per query head) or Hkv;  k_fp/v_fp as in cq_decode_args, tokens [sys | text];
+ *   out [B,Hq,D] bfloat16 whatever the data dtype.  (t_vis + t_fp) * 4 bytes must fit 200 KB of shared
+ *   memory (51 200 keys); larger requests return CQ_ERR_UNSUPPORTED.
+ */
+typedef struct cq_u8_decode_args {
+  int32_t batch, n_q_heads, n_kv_heads, head_dim;   /* head_dim must be 128 */
+  int32_t t_vis, t_fp, t_sys;                       /* t_sys of the t_fp tokens precede the visual span */
+  int32_t bits, dtype;
+  int32_t calibrate;                                /* 1: remap the visual logits */
+  int32_t n_scale_heads;
+  int32_t reserved;                                 /* must be 0 */
+  const void* q;
+  const uint8_t* enc_k;
+  const uint8_t* enc_v;
+  const void* scale_key;
+  const void* zero_point_key;
+  const void* scale_value;
+  const void* zero_point_value;
+  const void* k_fp;
+  const void* v_fp;
+  int64_t fp_stride_b, fp_stride_h;                 /* in elements */
+  const void* mask;                                 /* optional additive mask [B, t_fp + t_vis] in `dtype`,   */
+  int64_t mask_stride_b;                            /* key order [sys | visual | text]; NULL = none           */
+  void* out;
+} cq_u8_decode_args;
+size_t cq_u8_decode_attn_workspace_bytes(const cq_u8_decode_args* args);
+int cq_u8_decode_attn(const cq_u8_decode_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * ---- decode-step glue around the attention call ---------------------------------------------------
  *
  * cq_rope_split_append replaces, for one decode token per batch row, the QKV split, rotary embedding

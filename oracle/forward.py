@@ -1,7 +1,8 @@
 """Oracle for the patched attention forward (test infrastructure).
 
 CPU restatement of ``forward_internlm2_calibquant`` (``patch_internvl.py:141-484``) with the
-quantized state in the group format, and of the decode arithmetic of ``forward_internlm2_qjl``
+quantized state in the group format or (``kv_format="uint8"``) in the reference's own byte format
+(``:288-339`` prefill, ``:356-436`` decode), and of the decode arithmetic of ``forward_internlm2_qjl``
 (``:544-600``) with per-channel group-quantized keys.  Weights are passed in explicitly; all
 tensor ops run in the weight dtype on CPU, the attention core in the oracle functions of
 ``group_format`` / ``prefill``.
@@ -13,6 +14,7 @@ import math
 
 import torch
 
+from . import calibquant_format as cqf
 from . import group_format as gf
 from . import prefill as pf
 
@@ -42,7 +44,8 @@ class AttentionOracle:
     reference (fp cache of system+text tokens, quantized visual span kept on the object)."""
 
     def __init__(self, wqkv, wo, n_heads, n_kv_heads, head_dim=128, rope_base=1e6, bits=1, sys_len=41,
-                 group_size=32, calibrate=None):
+                 group_size=32, calibrate=None, kv_format="group"):
+        self.kv_format = kv_format
         self.wqkv, self.wo = wqkv, wo
         self.hq, self.hkv, self.d = n_heads, n_kv_heads, head_dim
         self.n_rep = n_heads // n_kv_heads
@@ -64,6 +67,10 @@ class AttentionOracle:
         q, k, v = self._qkv(h, pos, T)
         s0, s1 = self.sys_len, self.sys_len + image_token_num
         self.t_vis = image_token_num
+        if self.kv_format == "uint8":
+            clip_k, clip_v = (0.5, 0.3) if self.bits == 1 else (1, 1)        # patch_internvl.py:22-27
+            self.u8 = cqf.prefill_quantize(k[:, :, s0:s1].transpose(1, 2), v[:, :, s0:s1].transpose(1, 2), self.bits,
+                                           clip_k, clip_v, self.n_rep)
         self.k_pack = gf.quantize_and_pack_last_dim(k[:, :, s0:s1].transpose(2, 3).contiguous(), self.g, self.bits)
         self.v_pack = gf.quantize_and_pack_last_dim(v[:, :, s0:s1].contiguous(), self.g, self.bits)
         self.k_fp = torch.cat([k[:, :, :s0], k[:, :, s1:]], dim=2)
@@ -80,6 +87,9 @@ class AttentionOracle:
         self.k_fp = torch.cat([self.k_fp, k], dim=2)
         self.v_fp = torch.cat([self.v_fp, v], dim=2)
         s = self.sys_len
+        if self.kv_format == "uint8":
+            o = cqf.decode_attention(q, self.u8, self.k_fp, self.v_fp, self.bits, s, normalize=self.calibrate).to(h.dtype)
+            return torch.nn.functional.linear(o.transpose(1, 2).reshape(B, 1, self.hq * self.d), self.wo)
         o = gf.decode_attention(q, self.k_pack, self.v_pack, self.k_fp[:, :, :s], self.k_fp[:, :, s:],
                                 self.v_fp[:, :, :s], self.v_fp[:, :, s:], self.bits, self.g,
                                 calibrated=self.calibrate)

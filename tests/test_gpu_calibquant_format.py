@@ -77,8 +77,13 @@ def test_quant_dequant_paths(cq, bits, dtype):
     # strided input: the [B,T,H,D] view of a [B,H,T,D] cache
     got_s = cq.quant(k.cuda().transpose(1, 2), bits, per_channel=True, scale=0.5, post_scale=True)
     assert bits_equal(got_s[0], ref_q[0])
-    with pytest.raises(NotImplementedError):
-        cq.quant(x.cuda(), bits)
+    # per_channel=False: one scale and zero point for the whole tensor, returned as 0-dim tensors
+    for post in (True, False):
+        ref_t = cqf.quant(x, bits, per_channel=False, scale=0.5, post_scale=post)
+        got_t = cq.quant(x.cuda(), bits, per_channel=False, scale=0.5, post_scale=post)
+        assert got_t[1].dim() == 0 and got_t[2].dim() == 0
+        for a, b in zip(got_t, ref_t):
+            assert bits_equal(a, b)
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
@@ -139,6 +144,78 @@ def test_decode_composition(cq, bits):
     out = cq.decode_attention(q.cuda(), state, k_fp.cuda(), v_fp.cuda(), bits, sys_len)
     assert out.dtype == torch.bfloat16 and out.shape == ref.shape
     assert rel_l2(out, ref) <= 1e-2, rel_l2(out, ref)
+
+
+def _step_inputs(bits, B, Hq, Hkv, sys_len, t_vis, t_txt, dtype, seed):
+    k, v, q = generator.make_kvq(B, Hq, Hkv, sys_len + t_vis + t_txt, seed=seed)
+    k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+    k_sys, k_vis, k_txt = generator.split_spans(k, t_vis, sys_len)
+    v_sys, v_vis, v_txt = generator.split_spans(v, t_vis, sys_len)
+    clip_k, clip_v = (0.5, 0.3) if bits == 1 else (1, 1)
+    state = cqf.prefill_quantize(k_vis.transpose(1, 2), v_vis.transpose(1, 2), bits, clip_k, clip_v, Hq // Hkv)
+    return q, state, torch.cat([k_sys, k_txt], 2), torch.cat([v_sys, v_txt], 2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("bits", [1, 2, 4])
+def test_fused_step_larger_shape_and_kv_head_scales(cq, bits, dtype):
+    """The one-call step at 32 query heads on 8 KV heads and 4 096 visual tokens, against the oracle
+    (tolerance 1e-2 rel-L2, the bar of the step) and against the eager composition around the two code
+    products (2e-3: same arithmetic, different summation order); scale / zero point given once per query
+    head (the reference's layout) and once per KV head must agree bit for bit."""
+    sys_len, t_vis, t_txt, B, Hq, Hkv = 41, 4096, 77, 2, 32, 8
+    q, state, k_fp, v_fp = _step_inputs(bits, B, Hq, Hkv, sys_len, t_vis, t_txt, dtype, seed=70 + bits)
+    ref = cqf.decode_attention(q, state, k_fp, v_fp, bits, sys_len)
+    dev = {n: t.cuda() for n, t in state.items()}
+    out = cq.decode_attention(q.cuda(), dev, k_fp.cuda(), v_fp.cuda(), bits, sys_len)
+    assert out.dtype == torch.bfloat16 and out.shape == ref.shape
+    assert rel_l2(out, ref) <= 1e-2, rel_l2(out, ref)
+    eager = cq.decode_attention_unfused(q.cuda(), dev, k_fp.cuda(), v_fp.cuda(), bits, sys_len)
+    assert rel_l2(out, eager.cpu()) <= 4e-3, rel_l2(out, eager.cpu())
+    per_kv = dict(dev)
+    for n in ("scale_key", "zero_point_key", "scale_value", "zero_point_value"):
+        per_kv[n] = dev[n][:, ::Hq // Hkv].contiguous()                   # [B,Hkv,1,D]
+    out2 = cq.decode_attention(q.cuda(), per_kv, k_fp.cuda(), v_fp.cuda(), bits, sys_len)
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+
+
+def test_fused_step_mask_and_empty_spans(cq):
+    """An additive mask that removes keys must equal the step on the remaining keys' probabilities
+    (checked against the oracle with the same mask); no full-precision tokens and no visual tokens are
+    both legal requests."""
+    bits, sys_len, t_vis, t_txt = 2, 41, 512, 20
+    q, state, k_fp, v_fp = _step_inputs(bits, 1, 8, 2, sys_len, t_vis, t_txt, torch.float16, seed=91)
+    dev = {n: t.cuda() for n, t in state.items()}
+    mask = torch.zeros(1, 1, 1, sys_len + t_vis + t_txt, dtype=torch.float16)
+    mask[..., 5:9] = -60000.0
+    mask[..., sys_len + 100:sys_len + 140] = -60000.0
+    out = cq.decode_attention(q.cuda(), dev, k_fp.cuda(), v_fp.cuda(), bits, sys_len, mask=mask.cuda())
+    # oracle with the mask: the same composition with the mask added before the softmax
+    import math
+    from oracle.group_format import repeat_kv, calibrate
+    n_rep, sd = 4, math.sqrt(128)
+    lut = torch.arange(2 ** bits, dtype=q.dtype)
+    k, v = repeat_kv(k_fp, n_rep), repeat_kv(v_fp, n_rep)
+    s_sys = torch.matmul(q, k[:, :, :sys_len].transpose(2, 3)) / sd
+    s_txt = torch.matmul(q, k[:, :, sys_len:].transpose(2, 3)) / sd
+    bias = torch.sum(state["scale_key"] * state["zero_point_key"] * q, dim=-1, keepdim=True) / sd
+    s_vis = calibrate(cqf.fused_kernel(lut, q * state["scale_key"], repeat_kv(state["enc_k"], n_rep), bits) / sd - bias)
+    att = torch.softmax(torch.cat([s_sys, s_vis, s_txt], -1) + mask, dim=-1, dtype=torch.float32).to(q.dtype)
+    a_vis = att[..., sys_len:sys_len + t_vis]
+    o = cqf.fused_kernel_wv(lut.half(), a_vis.half(), repeat_kv(state["enc_v"], n_rep), bits) * state["scale_value"]
+    o = o - state["scale_value"] * state["zero_point_value"] * a_vis.sum(-1, keepdim=True)
+    o = o + torch.matmul(att[..., :sys_len], v[:, :, :sys_len]) + torch.matmul(att[..., sys_len + t_vis:], v[:, :, sys_len:])
+    assert rel_l2(out, o.to(torch.bfloat16)) <= 1e-2
+    # no full-precision tokens
+    empty = torch.empty(1, 2, 0, 128, dtype=torch.float16)
+    ref = cqf.decode_attention(q, state, empty, empty, bits, 0)
+    out = cq.decode_attention(q.cuda(), dev, empty.cuda(), empty.cuda(), bits, 0)
+    assert rel_l2(out, ref) <= 1e-2
+    # no visual tokens: plain attention over the full-precision tokens
+    none = {n: t[:, :, :0].cuda() if n.startswith("enc") else t.cuda() for n, t in state.items()}
+    out = cq.decode_attention(q.cuda(), none, k_fp.cuda(), v_fp.cuda(), bits, sys_len)
+    att = torch.softmax((torch.matmul(q, k.transpose(2, 3)) / sd).float(), -1).to(q.dtype)
+    assert rel_l2(out, torch.matmul(att, v).to(torch.bfloat16)) <= 1e-2
 
 
 @pytest.mark.parametrize("bits", [1, 2, 4])

@@ -27,16 +27,19 @@ def _layer(hq, hkv, seed, dtype=torch.float16):
     return shell
 
 
+@pytest.mark.parametrize("kv_format", ["group", "uint8"])
 @pytest.mark.parametrize("bits", [1, 2, 4])
-def test_calibquant_forward_matches_oracle(bits):
+def test_calibquant_forward_matches_oracle(bits, kv_format):
     from calibquant_b200 import patch_internvl as pi
     shell = _layer(8, 2, seed=bits)
-    pi.patch_model(shell, "calibquant")
+    pi.patch_model(shell, "calibquant", kv_format=kv_format)
+    assert pi.KV_FORMAT == kv_format
     pi.BITS_KV = bits
+    pi.SCALE_K, pi.SCALE_V = (0.5, 0.3) if bits == 1 else (1, 1)      # as the reference derives them from BITS_KV
     try:
         attn_cpu = shell.language_model.model.layers[0].attention
         oracle = AttentionOracle(attn_cpu.wqkv.weight.detach().clone(), attn_cpu.wo.weight.detach().clone(),
-                                 8, 2, bits=bits)
+                                 8, 2, bits=bits, kv_format=kv_format)
         shell.cuda()
         attn = shell.language_model.model.layers[0].attention
         t_vis, t_txt, B = 256, 13, 2
@@ -58,6 +61,8 @@ def test_calibquant_forward_matches_oracle(bits):
             assert rel_l2(out, ref) <= TOL, (step, rel_l2(out, ref))
     finally:
         pi.BITS_KV = 1
+        pi.SCALE_K, pi.SCALE_V = 0.5, 0.3
+        pi.KV_FORMAT = "group"
 
 
 def test_qjl_forward_structure_and_scores():
