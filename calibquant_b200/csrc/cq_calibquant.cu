@@ -507,6 +507,8 @@ template <> struct StepScore<__nv_bfloat16> {
 
 __device__ __forceinline__ void put_score(__half& dst, float v) { dst = __float2half_rn(v); }
 __device__ __forceinline__ void put_score(float& dst, float v) { dst = v; }
+__device__ __forceinline__ void put_half(__half& dst, __half v) { dst = v; }
+__device__ __forceinline__ void put_half(float& dst, __half v) { dst = __half2float(v); }
 
 // With STEP set this is the visual-score launch of the fused decode step (patch_internvl.py:366-372):
 // `w` is the query, the weights become rnd(q * scale_key), the table is the identity and the epilogue
@@ -535,7 +537,8 @@ lut_scores_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const 
   const int n_rep = hq / hkv_enc;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int64_t row0 = (int64_t)b * hq + (int64_t)hk * n_rep;
-  const float sd = sqrtf((float)kHeadDim);
+  const float sd = sqrtf((float)kHeadDim), inv_sd = 1.f / sd;
+  (void)inv_sd;
   for (int i = tid; i < kMaxRep * kHeadDim; i += 128) {
     const int r = i >> 7, d = i & (kHeadDim - 1);
     float wv = r < n_rep ? Elem<T>::to_f(w[(row0 + r) * kHeadDim + d]) : 0.f;
@@ -651,15 +654,30 @@ lut_scores_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const 
         mma_f16(acc, a0, a1, a2, a3, b0[kb], b1[kb]);
       }
       // acc[0..1] = (token 16mt+g, heads 2c, 2c+1), acc[2..3] = (token 16mt+g+8, same heads)
+      if (STEP && std::is_same<T, __half>::value) {
+        // fp16 data: the three roundings of `fused_kernel(...) / sqrt(D) - bias_k` on packed pairs of heads.
+        // raw / sqrt(D) is a product with the fp32 reciprocal: at most one fp32 ulp from the IEEE quotient,
+        // i.e. after the rounding to fp16 one score in about 4 000 differs, by one fp16 ulp.
+        const __half2 bias2 = __floats2half2_rn(wsum_s[2 * c], wsum_s[2 * c + 1]);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = 2 * c + (e & 1), tt = 16 * mt + g + 8 * (e >> 1);
-        if (r < n_rep) {
-          if (STEP) {
-            const float raw = rnd<__half>(acc[e] * 1048576.f);                      // fused_kernel's fp16 output
-            put_score(out_s[warp][r][tt], StepScore<T>::r(rnd<__half>(__fdiv_rn(raw, sd)) - wsum_s[r]));
-          } else {
-            put_score(out_s[warp][r][tt], fmaf(step * 1048576.f, acc[e], l0 * wsum_s[r]));
+        for (int hf = 0; hf < 2; ++hf) {
+          const float2 raw = __half22float2(__floats2half2_rn(acc[2 * hf] * 1048576.f, acc[2 * hf + 1] * 1048576.f));
+          const __half2 sc = __hsub2(__floats2half2_rn(raw.x * inv_sd, raw.y * inv_sd), bias2);
+          const int tt = 16 * mt + g + 8 * hf;
+          if (2 * c < n_rep) put_half(out_s[warp][2 * c][tt], __low2half(sc));
+          if (2 * c + 1 < n_rep) put_half(out_s[warp][2 * c + 1][tt], __high2half(sc));
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = 2 * c + (e & 1), tt = 16 * mt + g + 8 * (e >> 1);
+          if (r < n_rep) {
+            if (STEP) {
+              const float raw = rnd<__half>(acc[e] * 1048576.f);                      // fused_kernel's fp16 output
+              put_score(out_s[warp][r][tt], StepScore<T>::r(rnd<__half>(raw * inv_sd) - wsum_s[r]));
+            } else {
+              put_score(out_s[warp][r][tt], fmaf(step * 1048576.f, acc[e], l0 * wsum_s[r]));
+            }
           }
         }
       }
@@ -912,6 +930,113 @@ step_softmax_kernel(const T* __restrict__ q, const T* __restrict__ k_fp, int64_t
   for (int t = tid; t < t_fp; t += SM_THREADS) a_fp[(int64_t)bh * t_fp + t] = Elem<T>::from_f(row[t_vis + t] * inv);
   vs = block_reduce(vs, red, 0);
   if (tid == 0) a_sum[bh] = rnd<T>(vs);
+}
+
+// The same launch for fp16 data without a mask and with t_vis % 8 == 0: the visual scores are fp16 numbers and stay
+// fp16 through the calibration (every op of it rounds to fp16), so the row is kept as packed halves (half the
+// shared memory: two CTAs per SM, one wave for 256 heads), the calibration runs on packed fp16 arithmetic, whose
+// single rounding per op is the reference's, and the exponentials are recomputed in the last pass instead of stored.
+constexpr int SMH_THREADS = 512;
+
+__device__ __forceinline__ float ex2_fast(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+__global__ void __launch_bounds__(SMH_THREADS, 2)
+step_softmax_h_kernel(const __half* __restrict__ q, const __half* __restrict__ k_fp, int64_t fp_stride_b,
+                      int64_t fp_stride_h, int hq, int hkv, int t_vis, int t_fp, int calibrate,
+                      const __half* __restrict__ s_vis, __half* __restrict__ a_vis, __half* __restrict__ a_fp,
+                      float* __restrict__ a_sum) {
+  extern __shared__ __align__(16) unsigned char sm_raw[];
+  uint4* rv = reinterpret_cast<uint4*>(sm_raw);                          // t_vis halves
+  float* fprow = reinterpret_cast<float*>(sm_raw + (size_t)t_vis * 2);   // t_fp floats
+  __shared__ float red[32];
+  __shared__ float q_s[kHeadDim];
+  const int bh = blockIdx.x, b = bh / hq, h = bh % hq, hk = h / (hq / hkv);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float sd = sqrtf((float)kHeadDim);
+  if (tid < kHeadDim) q_s[tid] = __half2float(q[(int64_t)bh * kHeadDim + tid]);
+  __syncthreads();
+  const __half* kb = k_fp + b * fp_stride_b + hk * fp_stride_h;
+  float fmx = -INFINITY;
+  for (int t = warp; t < t_fp; t += SMH_THREADS / 32) {
+    const __half* kr = kb + (int64_t)t * kHeadDim + lane * 4;
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dot = fmaf(q_s[lane * 4 + i], __half2float(kr[i]), dot);
+    dot = warp_sum(dot);
+    const float sc = rnd<__half>(__fdiv_rn(rnd<__half>(dot), sd));
+    if (lane == 0) fprow[t] = sc;
+    fmx = fmaxf(fmx, sc);
+  }
+  const int nvec = t_vis >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(s_vis + (int64_t)bh * t_vis);
+  __half2 mx2 = __float2half2_rn(-INFINITY), mn2 = __float2half2_rn(INFINITY);
+  for (int i = tid; i < nvec; i += SMH_THREADS) {
+    const uint4 v = src[i];
+    rv[i] = v;
+    const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { mx2 = __hmax2(mx2, h2[j]); mn2 = __hmin2(mn2, h2[j]); }
+  }
+  float mx = fmaxf(__low2float(mx2), __high2float(mx2));
+  if (calibrate && t_vis > 0) {
+    const float mn = block_reduce(fminf(__low2float(mn2), __high2float(mn2)), red, 2);
+    mx = block_reduce(mx, red, 1);
+    const __half2 span2 = __float2half2_rn(rnd<__half>(rnd<__half>(mx + -3.f) - mn));      // tgt_max - tgt_min
+    const float rden = 1.f / rnd<__half>(rnd<__half>(mx - mn) + 1e-8f);
+    const __half2 mnh = __float2half2_rn(mn);
+    mx2 = __float2half2_rn(-INFINITY);
+    for (int i = tid; i < nvec; i += SMH_THREADS) {
+      uint4 v = rv[i];
+      __half2* h2 = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 d = __half22float2(__hsub2(h2[j], mnh));
+        const __half2 n = __floats2half2_rn(d.x * rden, d.y * rden);
+        h2[j] = __hadd2(__hmul2(n, span2), mnh);
+        mx2 = __hmax2(mx2, h2[j]);
+      }
+      rv[i] = v;
+    }
+    mx = fmaxf(__low2float(mx2), __high2float(mx2));
+  }
+  const float m = block_reduce(fmaxf(mx, fmx), red, 1);      // also orders the row writes before the reads below
+  constexpr float L2E = 1.4426950408889634f;
+  const float ml = m * L2E;
+  float sum = 0.f;
+  for (int i = tid; i < nvec; i += SMH_THREADS) {
+    const uint4 v = rv[i];
+    const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = __half22float2(h2[j]);
+      sum += ex2_fast(fmaf(x.x, L2E, -ml)) + ex2_fast(fmaf(x.y, L2E, -ml));
+    }
+  }
+  for (int t = tid; t < t_fp; t += SMH_THREADS) sum += ex2_fast(fmaf(fprow[t], L2E, -ml));
+  sum = block_reduce(sum, red, 0);
+  const float inv = 1.f / sum;
+  float vs = 0.f;
+  uint4* dst = reinterpret_cast<uint4*>(a_vis + (int64_t)bh * t_vis);
+  for (int i = tid; i < nvec; i += SMH_THREADS) {
+    uint4 v = rv[i];
+    __half2* h2 = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 x = __half22float2(h2[j]);
+      h2[j] = __floats2half2_rn(ex2_fast(fmaf(x.x, L2E, -ml)) * inv, ex2_fast(fmaf(x.y, L2E, -ml)) * inv);
+      const float2 a = __half22float2(h2[j]);
+      vs += a.x + a.y;
+    }
+    dst[i] = v;
+  }
+  for (int t = tid; t < t_fp; t += SMH_THREADS)
+    a_fp[(int64_t)bh * t_fp + t] = __float2half_rn(ex2_fast(fmaf(fprow[t], L2E, -ml)) * inv);
+  vs = block_reduce(vs, red, 0);
+  if (tid == 0) a_sum[bh] = rnd<__half>(vs);
 }
 
 // ---- fused decode step, launch 4: scale / zero point of V, full-precision tokens, bf16 output -------------
@@ -1206,11 +1331,21 @@ static int launch_step(const cq_u8_decode_args* a, char* ws, cudaStream_t st) {
     }
   }
   const size_t row_bytes = (size_t)(a->t_vis + a->t_fp) * 4;
-  if (cudaFuncSetAttribute(calib::step_softmax_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
-    return CQ_ERR_LAUNCH;
-  calib::step_softmax_kernel<T><<<rows, calib::SM_THREADS, row_bytes, st>>>(
-      q, static_cast<const T*>(a->k_fp), a->fp_stride_b, a->fp_stride_h, hq, hkv, a->t_vis, a->t_fp, a->t_sys,
-      a->calibrate, scores, static_cast<const T*>(a->mask), a->mask_stride_b, a_vis, a_fp, a_sum);
+  const size_t row_bytes_h = (size_t)a->t_vis * 2 + (size_t)a->t_fp * 4;
+  if (std::is_same<T, __half>::value && !a->mask && a->t_vis > 0 && a->t_vis % 8 == 0 && row_bytes_h <= 100 * 1024) {
+    if (cudaFuncSetAttribute(calib::step_softmax_h_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
+      return CQ_ERR_LAUNCH;
+    calib::step_softmax_h_kernel<<<rows, calib::SMH_THREADS, row_bytes_h, st>>>(
+        static_cast<const __half*>(a->q), static_cast<const __half*>(a->k_fp), a->fp_stride_b, a->fp_stride_h, hq, hkv,
+        a->t_vis, a->t_fp, a->calibrate, reinterpret_cast<const __half*>(scores), a_vis, reinterpret_cast<__half*>(a_fp),
+        a_sum);
+  } else {
+    if (cudaFuncSetAttribute(calib::step_softmax_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+      return CQ_ERR_LAUNCH;
+    calib::step_softmax_kernel<T><<<rows, calib::SM_THREADS, row_bytes, st>>>(
+        q, static_cast<const T*>(a->k_fp), a->fp_stride_b, a->fp_stride_h, hq, hkv, a->t_vis, a->t_fp, a->t_sys,
+        a->calibrate, scores, static_cast<const T*>(a->mask), a->mask_stride_b, a_vis, a_fp, a_sum);
+  }
   if (a->t_vis) {
     dim3 grid((unsigned)l.chunks, (unsigned)(B * hkv));
     const __half* lut_h = reinterpret_cast<const __half*>(lut);
