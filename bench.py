@@ -44,8 +44,8 @@ L2_BYTES = 126 * 1024 * 1024
 # profiles/: (kernel, bits, context, batch) -> (bytes, the kernel instantiation that was captured, summary file).
 # The figure is reported only while the library still builds that instantiation for the workload.
 NCU_TRAFFIC = {
-    ("attn_v", 1, 32768, 8): (None, "k2_attn_v<__half,1,512>", "profiles/decode_attn_1bit_b8_ctx32768.md"),
-    ("scores", 1, 32768, 8): (None, "k1_scores<__half,1,true>", "profiles/decode_attn_1bit_b8_ctx32768.md"),
+    ("attn_v", 1, 32768, 8): (87492608, "k2_attn_v<__half,1,512>", "profiles/decode_attn_1bit_b8_ctx32768.md"),
+    ("scores", 1, 32768, 8): (71231232, "k1_scores<__half,1,true>", "profiles/decode_attn_1bit_b8_ctx32768.md"),
 }
 KERNEL_NAMES = {"scores": "k1_scores", "attn_v": "k2_attn_v"}
 MIN_TIMED_MS = 50.0      # the device-timed region lasts at least this long, whatever --steps says
@@ -498,8 +498,9 @@ def model_decode(rank, world, device, big=False, batch=None, steps=64, bits=1, e
                        f"tensor parallel by KV head x{world}: wqkv/wo/w1/w3/w2 and the cache sliced with the heads",
         "collectives_per_layer": 0 if world == 1 else 2,
         "collective": None if world == 1 else
-                      "one-shot all-reduce of the [batch, hidden] partial sums: peer stores over NVLink "
-                      "(cq_comm_push) + sum inside the next layer-norm launch (cq_comm_reduce_add_rmsnorm)",
+                      "one launch per all-reduce of the [batch, hidden] partial sums: peer stores over NVLink, bounded wait "
+                      "for the peers' rows, rank-ordered sum + residual + RMSNorm (cq_comm_allreduce_add_rmsnorm); more "
+                      "than 64 rows: cq_comm_push + cq_comm_reduce_add_rmsnorm",
         "decode_loop": "eager launches" if eager else "one CUDA graph replayed per token",
     }
 
