@@ -32,6 +32,7 @@
 // 16-byte aligned operands.
 #include <cuda.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <mutex>
 #include <utility>
@@ -71,7 +72,12 @@ __host__ __device__ constexpr int k1_min_ctas(int bits) {
 __host__ __device__ constexpr int k1_code_row_bytes(int bits) { return TILE_G * bits * 4 < 128 ? TILE_G * bits * 4 : 128; }
 // an attn.V stage: codes, scales, minima, and the logits of kMaxRep heads for the tile's tokens
 // (logit rows are 16 bytes longer than a tile so that the heads fall on different banks)
-__host__ __device__ constexpr int k2_stage_bytes(int bits, int vt) { return vt * (16 * bits + 16) + kMaxRep * (2 * vt + 16); }
+// At 2 and 4 bits the codes arrive as swizzled TMA boxes, whose pattern is a function of the shared-memory
+// address: stages then start on 1 KB boundaries.
+__host__ __device__ constexpr int k2_stage_bytes(int bits, int vt) {
+  return bits == 1 ? vt * (16 * bits + 16) + kMaxRep * (2 * vt + 16)
+                   : (vt * (16 * bits + 16) + kMaxRep * (2 * vt + 16) + 1023) / 1024 * 1024;
+}
 __host__ __device__ constexpr int k2_stages(int bits, int vt) { return 3 * k2_stage_bytes(bits, vt) <= 76 * 1024 ? 3 : 2; }
 __host__ __device__ constexpr int k2_smem_bytes(int bits, int vt) {
   return k2_stages(bits, vt) * k2_stage_bytes(bits, vt) + K2_WARPS * kMaxRep * 136 * 4 + 1024;
@@ -652,7 +658,8 @@ k2_fp_tokens(Dims dm, const T* scores, const T* __restrict__ v_fp,   // scores: 
 // the slot of the range's first tile; the other tile slots of the range are marked empty (max = -inf).
 template <typename T, int BITS, int VT>
 __global__ void __launch_bounds__(K2_THREADS, 2)
-k2_attn_v(Dims dm, const T* scores, const float2* tile_mm,   // written by the launch before: no read-only loads
+k2_attn_v(const __grid_constant__ CUtensorMap tm_v,   // 2 and 4 bits: the value codes as [tokens][row words], swizzled boxes
+          Dims dm, const T* scores, const float2* tile_mm,   // written by the launch before: no read-only loads
           const int32_t* __restrict__ v_code, const T* __restrict__ v_scale,
           const T* __restrict__ v_mn,
           float* __restrict__ partial, float2* __restrict__ ml, int* __restrict__ status) {
@@ -704,7 +711,14 @@ k2_attn_v(Dims dm, const T* scores, const float2* tile_mm,   // written by the l
         const int64_t tok = (int64_t)pair * dm.t_vis + (int64_t)vt * VT;
         const int nt = min(VT, dm.t_vis - vt * VT);
         mbar_expect_tx(&full_bar[s], (uint32_t)(nt * (TOK_BYTES + 16) + dm.n_rep * nt * 2));
-        bulk_load_1d(base, v_code + tok * WPT, (uint32_t)(nt * TOK_BYTES), &full_bar[s]);
+        if (BITS == 1) {
+          bulk_load_1d(base, v_code + tok * WPT, (uint32_t)(nt * TOK_BYTES), &full_bar[s]);
+        } else {
+          // token rows of 32 / 64 bytes: a plain copy would put the rows of a quarter warp's four tokens on the
+          // same banks; the tiled load XORs the 16-byte chunk index with bits of the row number (nt % 256 == 0)
+          for (int r0 = 0; r0 < nt; r0 += 256)
+            tma_load_2d(base + r0 * TOK_BYTES, &tm_v, 0, (int)(tok + r0), &full_bar[s]);
+        }
         bulk_load_1d(base + CODE_BYTES, v_scale + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
         bulk_load_1d(base + CODE_BYTES + VT * 8, v_mn + tok * 4, (uint32_t)(nt * 8), &full_bar[s]);
       };
@@ -766,7 +780,9 @@ k2_attn_v(Dims dm, const T* scores, const float2* tile_mm,   // written by the l
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int i = (BITS == 1) ? (j & 1) : 0;
-      const int ch = BITS == 1 ? 32 * (j >> 1) + Expand<1>::elem(i, g) : 16 * j + 2 * g;
+      // 4 bits: the two m-tiles of a 32-channel group take words {2hi, 2hi+1} of the group's four (hi = g / 4)
+      const int ch = BITS == 1 ? 32 * (j >> 1) + Expand<1>::elem(i, g)
+                   : BITS == 4 ? 32 * (j >> 1) + 16 * (g >> 2) + 8 * (j & 1) + 2 * (g & 3) : 16 * j + 2 * g;
       if (2 * c < dm.n_rep) {
         mine[(2 * c) * RED_STRIDE + ch] = acc[j][0] * sc0[i];
         mine[(2 * c) * RED_STRIDE + ch + 1] = acc[j][2] * sc1[i];
@@ -932,10 +948,27 @@ k2_attn_v(Dims dm, const T* scores, const float2* tile_mm,   // written by the l
       }
       // code words of the lane's four tokens
       const uint32_t tb = code_b + (uint32_t)t0 * TOK_BYTES;
+      if (BITS == 4) {
+        // rows of tokens t0, t0+1, t0+8, t0+9 all carry the chunk XOR c (64-byte swizzle: chunk ^= (row / 2) % 4).
+        // Per 32-channel group q the lane reads the two words (2hi, 2hi+1) of chunk q: m-tiles 2q and 2q+1.
+        const uint32_t hoff = (uint32_t)(g >> 2) * 8u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t off = (uint32_t)((q ^ c) << 4) + hoff;
+          const uint2 wa = lds64(tb + off), wb = lds64(tb + TOK_BYTES + off);
+          const uint2 wc = lds64(tb + 8 * TOK_BYTES + off), wd = lds64(tb + 9 * TOK_BYTES + off);
+          const uint32_t x01a = prmt(wa.x, wb.x, sel[0]), x89a = prmt(wc.x, wd.x, sel[0]);
+          mma_f16(acc[2 * q], x01a & m0[0], x01a & m1[0], x89a & m0[0], x89a & m1[0], bA[q], bB[q]);
+          const uint32_t x01b = prmt(wa.y, wb.y, sel[0]), x89b = prmt(wc.y, wd.y, sel[0]);
+          mma_f16(acc[2 * q + 1], x01b & m0[0], x01b & m1[0], x89b & m0[0], x89b & m1[0], bA[q], bB[q]);
+        }
+      } else {
 #pragma unroll
       for (int part = 0; part < BITS; ++part) {      // 16 bytes of every token row at a time
-        const uint4 wa = lds128(tb + part * 16), wb = lds128(tb + TOK_BYTES + part * 16);
-        const uint4 wc = lds128(tb + 8 * TOK_BYTES + part * 16), wd = lds128(tb + 9 * TOK_BYTES + part * 16);
+        // 2 bits: 32-byte swizzle, chunk ^= (row / 4) % 2 = c / 2 for all four tokens
+        const uint32_t po = BITS == 2 ? (uint32_t)((part ^ (c >> 1)) << 4) : (uint32_t)(part * 16);
+        const uint4 wa = lds128(tb + po), wb = lds128(tb + TOK_BYTES + po);
+        const uint4 wc = lds128(tb + 8 * TOK_BYTES + po), wd = lds128(tb + 9 * TOK_BYTES + po);
         const uint32_t Wa[4] = {wa.x, wa.y, wa.z, wa.w}, Wb[4] = {wb.x, wb.y, wb.z, wb.w};
         const uint32_t Wc[4] = {wc.x, wc.y, wc.z, wc.w}, Wd[4] = {wd.x, wd.y, wd.z, wd.w};
         // m-tiles covered by these 4 words: 128/BITS channels = 8/BITS m-tiles
@@ -949,22 +982,12 @@ k2_attn_v(Dims dm, const T* scores, const float2* tile_mm,   // written by the l
           }
         } else
 #pragma unroll
-        for (int jj = 0; jj < 8 / BITS; ++jj) {
-          const int j = part * (8 / BITS) + jj;          // m-tile = channels 16j .. 16j+15
-          const int gq = j >> 1;                         // 32-channel group -> scale
-          const int wi = BITS == 2 ? jj : 2 * jj + (g >> 2), i = 0;
-          uint32_t a, bw, cw, dw;
-          if (BITS == 4) {
-            const bool hi = g >> 2;
-            a = hi ? Wa[2 * jj + 1] : Wa[2 * jj]; bw = hi ? Wb[2 * jj + 1] : Wb[2 * jj];
-            cw = hi ? Wc[2 * jj + 1] : Wc[2 * jj]; dw = hi ? Wd[2 * jj + 1] : Wd[2 * jj];
-            (void)wi;
-          } else {
-            a = Wa[wi]; bw = Wb[wi]; cw = Wc[wi]; dw = Wd[wi];
-          }
-          const uint32_t x01 = prmt(a, bw, sel[i]), x89 = prmt(cw, dw, sel[i]);
-          mma_f16(acc[j], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bA[gq], bB[gq]);
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j = part * 4 + jj;                   // 2 bits: m-tile = channels 16j .. 16j+15 = word jj of the part
+          const uint32_t x01 = prmt(Wa[jj], Wb[jj], sel[0]), x89 = prmt(Wc[jj], Wd[jj], sel[0]);
+          mma_f16(acc[j], x01 & m0[0], x01 & m1[0], x89 & m0[0], x89 & m1[0], bA[j >> 1], bB[j >> 1]);
         }
+      }
       }
     }
     // the stage has been read: hand it back to the producer
@@ -1040,14 +1063,15 @@ static EncodeTiledFn encode_fn() {
 // A decode loop asks for the same few descriptors at every step (one cache per layer), so the encoded
 // maps are remembered per host thread: a descriptor is a pure function of the key below.
 static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, int elem_bytes,
-                     uint64_t cols, uint64_t rows, CUtensorMapSwizzle sw, uint32_t box_cols) {
-  struct Entry { const void* base; uint64_t cols, rows; int dt, sw; uint32_t box_cols; CUtensorMap map; };
+                     uint64_t cols, uint64_t rows, CUtensorMapSwizzle sw, uint32_t box_cols, uint32_t box_rows = 128) {
+  struct Entry { const void* base; uint64_t cols, rows; int dt, sw; uint32_t box_cols, box_rows; CUtensorMap map; };
   constexpr int N = 256;
   thread_local Entry cache[N];
   thread_local int used = 0, next = 0;
   for (int i = 0; i < used; ++i) {
     const Entry& e = cache[i];
-    if (e.base == base && e.cols == cols && e.rows == rows && e.dt == (int)dt && e.sw == (int)sw && e.box_cols == box_cols) {
+    if (e.base == base && e.cols == cols && e.rows == rows && e.dt == (int)dt && e.sw == (int)sw && e.box_cols == box_cols &&
+        e.box_rows == box_rows) {
       *m = e.map;
       return true;
     }
@@ -1056,16 +1080,25 @@ static bool make_map(CUtensorMap* m, const void* base, CUtensorMapDataType dt, i
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
-  cuuint32_t box[2] = {box_cols, 128};
+  cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   if (fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return false;
   Entry& e = cache[next];
-  e.base = base; e.cols = cols; e.rows = rows; e.dt = (int)dt; e.sw = (int)sw; e.box_cols = box_cols; e.map = *m;
+  e.base = base; e.cols = cols; e.rows = rows; e.dt = (int)dt; e.sw = (int)sw; e.box_cols = box_cols; e.box_rows = box_rows; e.map = *m;
   next = (next + 1) % N;
   if (used < N) ++used;
   return true;
+}
+
+// The value codes of the attn.V kernel at 2 and 4 bits: [tokens of all KV heads][4*BITS words], boxes of 256 token
+// rows swizzled over the row width (32 or 64 bytes).  At 1 bit the kernel copies the rows untiled and ignores the map.
+template <int BITS>
+static bool make_v_map(CUtensorMap* tm_v, const void* code, uint64_t tokens) {
+  if (BITS == 1) { memset(tm_v, 0, sizeof(*tm_v)); return true; }
+  return make_map(tm_v, code, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, 4 * BITS, tokens,
+                  BITS == 4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B, 4 * BITS, 256);
 }
 
 // The three tensor maps of the score kernel: code words (boxes of at most 128 bytes per channel row, swizzled
@@ -1091,8 +1124,10 @@ static Dims make_dims(const cq_decode_args* a) {
   d.t_vis = a->t_vis; d.t_fp = a->t_fp; d.calibrate = a->calibrate ? 1 : 0;
   d.n_groups = d.t_vis / 32;
   d.n_ktiles = (d.n_groups + TILE_G - 1) / TILE_G;
-  // the large tiles only when they give every resident CTA a few of them
-  d.chunk_tok = (int64_t)d.batch * d.hkv * ((d.t_vis + VT_LARGE - 1) / VT_LARGE) >= 2 * K2_RESIDENT ? VT_LARGE : VT_SMALL;
+  // the large tiles only when they give every resident CTA a few of them, and never at 4 bits, where a ring of
+  // large tiles leaves room for one CTA per SM only (the small ones: three stages, two CTAs)
+  d.chunk_tok = a->bits != 4 && (int64_t)d.batch * d.hkv * ((d.t_vis + VT_LARGE - 1) / VT_LARGE) >= 2 * K2_RESIDENT
+                    ? VT_LARGE : VT_SMALL;
   d.n_chunks = (d.t_vis + d.chunk_tok - 1) / d.chunk_tok;
   d.n_fp_chunks = (d.t_fp + 127) / 128;
   d.n_slots = d.n_chunks + d.n_fp_chunks;
@@ -1193,7 +1228,9 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
   {
     const int items2 = n_pairs * d.n_chunks;
     const int grid2 = max(1, min(items2, sm_count() * occ2));
-    if (launch_pdl(k2, dim3(grid2), dim3(K2_THREADS), smem2, st, d, static_cast<const T*>(scores),
+    CUtensorMap tm_v;
+    if (!make_v_map<BITS>(&tm_v, a->v_code, (uint64_t)n_pairs * d.t_vis)) return CQ_ERR_LAUNCH;
+    if (launch_pdl(k2, dim3(grid2), dim3(K2_THREADS), smem2, st, tm_v, d, static_cast<const T*>(scores),
                    static_cast<const float2*>(mm), a->v_code, static_cast<const T*>(a->v_scale),
                    static_cast<const T*>(a->v_mn), partial, ml, status) != cudaSuccess)
       return CQ_ERR_LAUNCH;
@@ -1320,7 +1357,9 @@ static int qbmm_run_t(int kind, const mma::Dims& d, const void* fA, const int32_
       configured[dev] = true;
     }
     const int grid = max(1, min(n_pairs * d.n_chunks, sm_count() * occ[dev]));
-    k2<<<grid, K2_THREADS, smem2, st>>>(d, static_cast<const T*>(fA), nullptr, qB, static_cast<const T*>(scales),
+    CUtensorMap tm_v;
+    if (!make_v_map<BITS>(&tm_v, qB, (uint64_t)n_pairs * d.t_vis)) return CQ_ERR_LAUNCH;
+    k2<<<grid, K2_THREADS, smem2, st>>>(tm_v, d, static_cast<const T*>(fA), nullptr, qB, static_cast<const T*>(scales),
                                      static_cast<const T*>(zeros), partial, ml, status);
     return check_launch();
   };
