@@ -111,12 +111,16 @@ __device__ __forceinline__ int live_t_fp(const Dims& dm) {
 // A lane (g = lane/4) owns rows g and g+8 of a 16-row m-tile; they are mapped to two adjacent
 // packed elements e, e+1 of the 32-element group the m-tile belongs to (m-tile i = 0, 1 of the group).
 // Which element a row stands for is free, as long as the epilogue agrees:
-//   2 and 4 bits: e = 16 i + 2g, so m-tile i is word-aligned in the group;
-//   1 bit:        e = 4g + 2i, so both m-tiles take their bits from the same byte of the same word
-//                 and share one byte permute.
+//   2 bits: e = 16 i + 2g, so m-tile i is one word of the group;
+//   4 bits: e = 16 (g/4) + 8 i + 2 (g%4): the lane's two m-tiles are the adjacent words 2(g/4), 2(g/4)+1 of the
+//           group's four, fetched by one 8-byte load;
+//   1 bit:  e = 4g + 2i, so both m-tiles take their bits from the same byte of the same word
+//           and share one byte permute.
 template <int BITS>
 struct Expand {
-  static __device__ __forceinline__ int elem(int i, int g) { return BITS == 1 ? 4 * g + 2 * i : 16 * i + 2 * g; }
+  static __device__ __forceinline__ int elem(int i, int g) {
+    return BITS == 1 ? 4 * g + 2 * i : BITS == 4 ? 16 * (g >> 2) + 8 * i + 2 * (g & 3) : 16 * i + 2 * g;
+  }
   static __device__ __forceinline__ int bit_off(int i, int g) { return elem(i, g) * BITS; }
 };
 
@@ -354,8 +358,14 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
           for (int rr = 0; rr < 4; ++rr) {
             const int d = 16 * kt + 2 * c + (rr & 1) + 8 * (rr >> 1);
             const int sw = ROW_BYTES == 64 ? ((d >> 1) & 3) : (d & 7);
-            const uint4 v = lds128(code_base + box_off + (uint32_t)(d * ROW_BYTES + ((ch ^ sw) << 4)));
-            W[rr][0] = v.x; W[rr][1] = v.y; W[rr][2] = v.z; W[rr][3] = v.w;
+            const uint32_t waddr = code_base + box_off + (uint32_t)(d * ROW_BYTES + ((ch ^ sw) << 4));
+            if (BITS == 4) {     // the lane's word pair of the group (see Expand)
+              const uint2 v = lds64(waddr + (uint32_t)(g >> 2) * 8u);
+              W[rr][0] = v.x; W[rr][1] = v.y; W[rr][2] = 0u; W[rr][3] = 0u;
+            } else {
+              const uint4 v = lds128(waddr);
+              W[rr][0] = v.x; W[rr][1] = v.y; W[rr][2] = v.z; W[rr][3] = v.w;
+            }
           }
 #pragma unroll
           for (int a = 0; a < GU; ++a) {
@@ -378,12 +388,8 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
 #pragma unroll
               for (int i = 0; i < 2; ++i) {
                 uint32_t w0, w1, w8, w9;
-                if (BITS == 4) {   // the lane's element pair sits in word 2i or 2i+1 of the group
-                  const bool hi = word_in_group[i] & 1;
-                  w0 = hi ? W[0][2 * i + 1] : W[0][2 * i];
-                  w1 = hi ? W[1][2 * i + 1] : W[1][2 * i];
-                  w8 = hi ? W[2][2 * i + 1] : W[2][2 * i];
-                  w9 = hi ? W[3][2 * i + 1] : W[3][2 * i];
+                if (BITS == 4) {   // word i of the pair that was loaded
+                  w0 = W[0][i]; w1 = W[1][i]; w8 = W[2][i]; w9 = W[3][i];
                 } else {
                   const int wi = a * BITS + i;
                   w0 = W[0][wi]; w1 = W[1][wi]; w8 = W[2][wi]; w9 = W[3][wi];
