@@ -48,13 +48,11 @@ namespace mma {
 using namespace ptx;
 
 constexpr int THREADS = 128;
-#ifndef CQ_K1_TILE_G
-#define CQ_K1_TILE_G 32
-#endif
-constexpr int K1_WARPS = 4;            // computing warps of a score CTA; each owns TILE_G / K1_WARPS groups of a K tile
+constexpr int K1_WARPS = 4;            // computing warps of a score CTA; each owns tile_g / K1_WARPS groups of a K tile
 constexpr int K1_THREADS = (K1_WARPS + 1) * 32;   // + the TMA producer warp
-constexpr int TILE_G = CQ_K1_TILE_G;   // 32-token groups per K tile
-constexpr int K1_GPW = TILE_G / K1_WARPS;
+// 32-token groups per K tile: 32, but 16 at 4 bits, where a ring of 32-group tiles (80 KB each) leaves room for
+// one CTA per SM only and the kernel then runs with 1.2 warps per scheduler
+__host__ __device__ constexpr int tile_g(int bits) { return bits == 4 ? 16 : 32; }
 // attn.V work items: CT tokens per item, streamed as tiles of VT tokens.  Two shapes are compiled: the
 // large one for long contexts, the small one when the large one would leave CTAs without work.
 constexpr int VT_LARGE = 512, VT_SMALL = 256;
@@ -64,12 +62,12 @@ constexpr int K2_RESIDENT = 296;       // attn.V CTAs resident on the device (2 
 constexpr uint32_t WAIT_TRIES = 1u << 22;
 constexpr float LOG2E = 1.4426950408889634f;
 
-__host__ __device__ constexpr int k1_stage_bytes(int bits) { return TILE_G * (bits * 512 + 512); }
+__host__ __device__ constexpr int k1_stage_bytes(int bits) { return tile_g(bits) * (bits * 512 + 512); }
 __host__ __device__ constexpr int k1_stages(int bits) { return 3 * k1_stage_bytes(bits) <= 100 * 1024 ? 3 : 2; }
 __host__ __device__ constexpr int k1_min_ctas(int bits) {
   return (220 * 1024) / (k1_stages(bits) * k1_stage_bytes(bits) + 2048) > 4 ? 4 : (220 * 1024) / (k1_stages(bits) * k1_stage_bytes(bits) + 2048);
 }
-__host__ __device__ constexpr int k1_code_row_bytes(int bits) { return TILE_G * bits * 4 < 128 ? TILE_G * bits * 4 : 128; }
+__host__ __device__ constexpr int k1_code_row_bytes(int bits) { return tile_g(bits) * bits * 4 < 128 ? tile_g(bits) * bits * 4 : 128; }
 // an attn.V stage: codes, scales, minima, and the logits of kMaxRep heads for the tile's tokens
 // (logit rows are 16 bytes longer than a tile so that the heads fall on different banks)
 // At 2 and 4 bits the codes arrive as swizzled TMA boxes, whose pattern is a function of the shared-memory
@@ -86,7 +84,7 @@ __host__ __device__ constexpr int k2_smem_bytes(int bits, int vt) {
 struct Dims {
   int batch, hq, hkv, n_rep, t_vis, t_fp, calibrate;
   int n_groups;        // t_vis / 32
-  int n_ktiles;        // ceil(n_groups / 32)
+  int n_ktiles;        // ceil(n_groups / tile_g(bits))
   int chunk_tok;       // tokens per attn.V tile: VT_LARGE or VT_SMALL
   int n_chunks;        // tiles per KV head: ceil(t_vis / chunk_tok); one partial slot each
   int n_fp_chunks;     // ceil(t_fp / 128)
@@ -204,6 +202,8 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   using T2 = typename D16<T>::T2;
   constexpr int STAGES = k1_stages(BITS);
   constexpr int STAGE_BYTES = k1_stage_bytes(BITS);
+  constexpr int TILE_G = tile_g(BITS);
+  constexpr int K1_GPW = TILE_G / K1_WARPS;
   constexpr int CODE_BYTES = TILE_G * BITS * 512;
   constexpr int KS_BYTES = TILE_G * 256;
   constexpr int ROW_BYTES = k1_code_row_bytes(BITS);   // bytes of a channel row inside one TMA box
@@ -1108,11 +1108,12 @@ static bool make_v_map(CUtensorMap* tm_v, const void* code, uint64_t tokens) {
 }
 
 // The three tensor maps of the score kernel: code words (boxes of at most 128 bytes per channel row, swizzled
-// over their width), scales and minima (one box of TILE_G values per channel row, swizzled over its width).
+// over their width), scales and minima (one box of tile_g values per channel row, swizzled over its width).
 template <int BITS>
 static bool make_k_maps(CUtensorMap* tm_code, CUtensorMap* tm_ks, CUtensorMap* tm_kmn, const void* code,
                         const void* ks, const void* kmn, uint64_t n_groups, uint64_t rows) {
   constexpr int row = k1_code_row_bytes(BITS);
+  constexpr int TILE_G = tile_g(BITS);
   const CUtensorMapSwizzle sw_ks = TILE_G * 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
   return make_map(tm_code, code, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, n_groups * BITS, rows,
                   row == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, row / 4) &&
@@ -1129,7 +1130,7 @@ static Dims make_dims(const cq_decode_args* a) {
   d.batch = a->batch; d.hq = a->n_q_heads; d.hkv = a->n_kv_heads; d.n_rep = d.hq / d.hkv;
   d.t_vis = a->t_vis; d.t_fp = a->t_fp; d.calibrate = a->calibrate ? 1 : 0;
   d.n_groups = d.t_vis / 32;
-  d.n_ktiles = (d.n_groups + TILE_G - 1) / TILE_G;
+  d.n_ktiles = (d.n_groups + tile_g(a->bits) - 1) / tile_g(a->bits);
   // the large tiles only when they give every resident CTA a few of them, and never at 4 bits, where a ring of
   // large tiles leaves room for one CTA per SM only (the small ones: three stages, two CTAs)
   d.chunk_tok = a->bits != 4 && (int64_t)d.batch * d.hkv * ((d.t_vis + VT_LARGE - 1) / VT_LARGE) >= 2 * K2_RESIDENT
@@ -1321,9 +1322,12 @@ size_t mma_qbmm_workspace_bytes(int batch, int n_q_heads, int64_t K, int64_t N) 
 }
 
 template <typename T, int BITS>
-static int qbmm_run_t(int kind, const mma::Dims& d, const void* fA, const int32_t* qB, const void* scales,
+static int qbmm_run_t(int kind, const mma::Dims& d_in, const void* fA, const int32_t* qB, const void* scales,
                       const void* zeros, void* out, unsigned char* ws, cudaStream_t st) {
   using namespace mma;
+  Dims d = d_in;                       // built without the bit width: the K tiling depends on it
+  d.n_ktiles = (d.n_groups + tile_g(BITS) - 1) / tile_g(BITS);
+  d.n_mm = d.n_ktiles * K1_WARPS;
   int* status = reinterpret_cast<int*>(ws);
   const int n_pairs = d.batch * d.hkv;
   int dev = 0;
