@@ -197,8 +197,7 @@ template <typename T, int BITS, bool SPLIT>
 __global__ void __launch_bounds__(K1_THREADS, k1_min_ctas(BITS))
 k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ CUtensorMap tm_ks,
           const __grid_constant__ CUtensorMap tm_kmn, Dims dm, const T* __restrict__ q,
-          const T* __restrict__ k_fp, T* __restrict__ scores, float2* __restrict__ tile_mm,
-          int* __restrict__ status) {
+          T* __restrict__ scores, float2* __restrict__ tile_mm, int* __restrict__ status) {
   using T2 = typename D16<T>::T2;
   constexpr int STAGES = k1_stages(BITS);
   constexpr int STAGE_BYTES = k1_stage_bytes(BITS);
@@ -275,7 +274,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   (void)word_in_group;
 
   // The producer above streams only the packed keys, which no launch of a decode step writes, so it may run
-  // ahead of the kernel before this one in the stream; the query, the appended fp keys and the score buffer
+  // ahead of the kernel before this one in the stream; the query and the score buffer
   // (still read by the previous step) are touched only after that kernel has completed.
   pdl_wait();
   int cur_pair = -1;
@@ -478,44 +477,6 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   }
   if (failed) return;
 
-  // ---- full-precision tokens: one 16-token m-tile per warp, K rows straight from global memory
-  // as A fragments (all loads of a tile are independent), query heads as B; MMA in the data dtype.
-  const int t_fp = live_t_fp(dm);
-  const int n_fp_tiles = (t_fp + 15) / 16;
-  for (int it = blockIdx.x * K1_WARPS + warp; it < n_pairs * n_fp_tiles; it += gridDim.x * K1_WARPS) {   // (the producer warp has left)
-    const int pair = it / n_fp_tiles, t0 = (it % n_fp_tiles) * 16;
-    const int b = pair / dm.hkv, hk = pair % dm.hkv;
-    const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
-    const T* qrow = q + (row0 + (g < dm.n_rep ? g : 0)) * kHeadDim + 2 * c;
-    const T* kf = k_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h + 2 * c;
-    const T* k_lo = kf + (int64_t)min(t0 + g, t_fp - 1) * kHeadDim;        // rows past the end repeat the last
-    const T* k_hi = kf + (int64_t)min(t0 + g + 8, t_fp - 1) * kHeadDim;    // token; their scores are not stored
-    uint32_t a[8][4], bq[8][2];
-#pragma unroll
-    for (int kt = 0; kt < 8; ++kt) {
-      a[kt][0] = __ldg(reinterpret_cast<const uint32_t*>(k_lo + kt * 16));
-      a[kt][1] = __ldg(reinterpret_cast<const uint32_t*>(k_hi + kt * 16));
-      a[kt][2] = __ldg(reinterpret_cast<const uint32_t*>(k_lo + kt * 16 + 8));
-      a[kt][3] = __ldg(reinterpret_cast<const uint32_t*>(k_hi + kt * 16 + 8));
-      bq[kt][0] = g < dm.n_rep ? __ldg(reinterpret_cast<const uint32_t*>(qrow + kt * 16)) : 0u;
-      bq[kt][1] = g < dm.n_rep ? __ldg(reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 8)) : 0u;
-    }
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int kt = 0; kt < 8; ++kt) {
-      if constexpr (std::is_same<T, __nv_bfloat16>::value)
-        mma_bf16(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], bq[kt][0], bq[kt][1]);
-      else
-        mma_f16(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], bq[kt][0], bq[kt][1]);
-    }
-    // acc[0..1] = (token t0+g, heads 2c, 2c+1), acc[2..3] = (token t0+g+8, same heads)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int h = 2 * c + (e & 1), t = t0 + g + 8 * (e >> 1);
-      if (h < dm.n_rep && t < t_fp)
-        scores[(row0 + h) * dm.pitch + dm.t_vis + t] = Elem<T>::from_f(__fdiv_rn(rnd<T>(acc[e]), 11.313708498984761f));
-    }
-  }
 }
 
 // =================================================================================================
@@ -553,19 +514,23 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return r;
 }
 
-// Full-precision tokens of attn.V, chunks of 128, as a launch of its own next to k2_attn_v:
-// out[h][d] = sum_t p[h][t] V[t][d] on the warp MMA in the data dtype.  A = probabilities (rows = heads,
-// from shared memory), B = V rows staged in shared memory and read through ldmatrix.trans; warp w owns
-// channels 32w .. 32w+31.  Writes the (max, sum, acc[128]) partials of the fp slots that k3 merges.
+// Full-precision tokens (system + text), chunks of 128, as a launch of its own that depends on nothing the other
+// launches of a step write: it computes its own scores, so it can run beside k1_scores and k2_attn_v.
+//   scores: s[h][t] = rnd(rnd(q_h . k_t) / sqrt(D)), 16-token MMA tiles with the K rows as A fragments straight
+//           from global memory and the query heads as B, in the data dtype;
+//   softmax partial of the chunk and out[h][d] = sum_t p[h][t] V[t][d] on the warp MMA: A = probabilities (rows =
+//           heads, from shared memory), B = V rows staged in shared memory and read through ldmatrix.trans; warp w
+//           owns channels 32w .. 32w+31.
+// Writes the (max, sum, acc[128]) partials of the fp slots that k3 merges.
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
-k2_fp_tokens(Dims dm, const T* scores, const T* __restrict__ v_fp,   // scores: written by an overlapping launch
+k2_fp_tokens(Dims dm, const T* __restrict__ q, const T* __restrict__ k_fp, const T* __restrict__ v_fp,
              float* __restrict__ partial, float2* __restrict__ ml) {
   constexpr int PF_PITCH = 128 + 8;         // probability row pitch (elements): rows land on different banks
   constexpr int VROW = kHeadDim * 2 + 16;   // staged V row pitch in bytes, for conflict-free ldmatrix
   constexpr int FP_SUB = 128;               // tokens staged at a time
   __shared__ __align__(16) unsigned char smem[FP_SUB * VROW];
-  __shared__ __align__(16) T pf_s[kMaxRep * PF_PITCH];    // probabilities, exact in the data dtype
+  __shared__ __align__(16) T pf_s[kMaxRep * PF_PITCH];    // scores, then probabilities, exact in the data dtype
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
   const int n_pairs = dm.batch * dm.hkv;
   pdl_launch_dependents();
@@ -577,9 +542,51 @@ k2_fp_tokens(Dims dm, const T* scores, const T* __restrict__ v_fp,   // scores: 
     const int b = pair / dm.hkv, hk = pair % dm.hkv;
     const int64_t row0 = (int64_t)b * dm.hq + (int64_t)hk * dm.n_rep;
     const int t0 = fc * 128, nt = min(128, t_fp - t0);
+    __syncthreads();                        // the previous item's probabilities have been consumed
+    // ---- scores of the chunk: warp w takes the 16-token tiles w and w + 4
+    {
+      const T* qrow = q + (row0 + (g < dm.n_rep ? g : 0)) * kHeadDim + 2 * c;
+      const T* kf = k_fp + (int64_t)b * dm.fp_stride_b + (int64_t)hk * dm.fp_stride_h + 2 * c;
+      uint32_t bq[8][2];
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
+        bq[kt][0] = g < dm.n_rep ? __ldg(reinterpret_cast<const uint32_t*>(qrow + kt * 16)) : 0u;
+        bq[kt][1] = g < dm.n_rep ? __ldg(reinterpret_cast<const uint32_t*>(qrow + kt * 16 + 8)) : 0u;
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const int tt = (warp + 4 * mt) * 16;             // first token of the tile inside the chunk
+        if (tt >= nt) break;
+        const T* k_lo = kf + (int64_t)(t0 + min(tt + g, nt - 1)) * kHeadDim;       // rows past the end repeat the last
+        const T* k_hi = kf + (int64_t)(t0 + min(tt + g + 8, nt - 1)) * kHeadDim;   // token; their scores are not kept
+        uint32_t a[8][4];
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) {
+          a[kt][0] = __ldg(reinterpret_cast<const uint32_t*>(k_lo + kt * 16));
+          a[kt][1] = __ldg(reinterpret_cast<const uint32_t*>(k_hi + kt * 16));
+          a[kt][2] = __ldg(reinterpret_cast<const uint32_t*>(k_lo + kt * 16 + 8));
+          a[kt][3] = __ldg(reinterpret_cast<const uint32_t*>(k_hi + kt * 16 + 8));
+        }
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) {
+          if constexpr (std::is_same<T, __nv_bfloat16>::value)
+            mma_bf16(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], bq[kt][0], bq[kt][1]);
+          else
+            mma_f16(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], bq[kt][0], bq[kt][1]);
+        }
+        // acc[0..1] = (token tt+g, heads 2c, 2c+1), acc[2..3] = (token tt+g+8, same heads)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h = 2 * c + (e & 1), t = tt + g + 8 * (e >> 1);
+          if (h < dm.n_rep && t < nt)
+            pf_s[h * PF_PITCH + t] = Elem<T>::from_f(__fdiv_rn(rnd<T>(acc[e]), 11.313708498984761f));
+        }
+      }
+    }
     __syncthreads();
     for (int h = warp; h < dm.n_rep; h += 4) {
-      const T* srow = scores + (row0 + h) * dm.pitch + dm.t_vis + t0;
+      const T* srow = pf_s + h * PF_PITCH;               // overwritten in place by the probabilities (same lanes)
       const T* mrow = dm.mask ? static_cast<const T*>(dm.mask) + (int64_t)b * dm.mask_stride_b : nullptr;
       float xv[4], m_true = -INFINITY;
 #pragma unroll
@@ -1131,8 +1138,10 @@ static Dims make_dims(const cq_decode_args* a) {
   d.t_vis = a->t_vis; d.t_fp = a->t_fp; d.calibrate = a->calibrate ? 1 : 0;
   d.n_groups = d.t_vis / 32;
   d.n_ktiles = (d.n_groups + tile_g(a->bits) - 1) / tile_g(a->bits);
-  // the large tiles only when they give every resident CTA a few of them, and never at 4 bits, where a ring of
-  // large tiles leaves room for one CTA per SM only (the small ones: three stages, two CTAs)
+  // the large tiles only when they give every resident CTA a few of them (measured on the 7B step's shape, batch
+  // 16 x 3328 tokens: 18.4 us with three to four large tiles per CTA against 19.4 us with five to six small
+  // ones), and never at 4 bits, where a ring of large tiles leaves room for one CTA per SM only (the small ones:
+  // three stages, two CTAs)
   d.chunk_tok = a->bits != 4 && (int64_t)d.batch * d.hkv * ((d.t_vis + VT_LARGE - 1) / VT_LARGE) >= 2 * K2_RESIDENT
                     ? VT_LARGE : VT_SMALL;
   d.n_chunks = (d.t_vis + d.chunk_tok - 1) / d.chunk_tok;
@@ -1184,6 +1193,25 @@ static cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
+// A side stream and two events per host thread and device: the launch for the full-precision tokens depends on
+// nothing the other launches of a step write, so it is forked off the caller's stream before the score launch and
+// joined before the combine launch (a pattern that stream capture records as two parallel branches).
+struct ForkSet { cudaStream_t side = nullptr; cudaEvent_t fork = nullptr, join = nullptr; };
+static ForkSet* fork_set(int dev) {
+  thread_local ForkSet sets[64];
+  ForkSet& f = sets[dev];
+  if (!f.side) {
+    if (cudaStreamCreateWithFlags(&f.side, cudaStreamNonBlocking) != cudaSuccess) { f.side = nullptr; return nullptr; }
+    if (cudaEventCreateWithFlags(&f.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&f.join, cudaEventDisableTiming) != cudaSuccess) {
+      cudaStreamDestroy(f.side);
+      f.side = nullptr;
+      return nullptr;
+    }
+  }
+  return &f;
+}
+
 template <typename T, int BITS, int VT>
 static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned char* ws, cudaStream_t st,
                      cudaEvent_t* ev, int* status_word) {
@@ -1215,8 +1243,24 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ2, k2, K2_THREADS, smem2) != cudaSuccess || occ2 < 1) return CQ_ERR_LAUNCH;
     configured = true;
   }
-  // `ev` (profiling entry point only): five events recorded around the four launches
+  // `ev` (profiling entry point only): five events recorded around the four launches, which then run one after
+  // the other on the caller's stream
   auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], st); };
+  auto launch_fp = [&](cudaStream_t s) -> int {
+    k2_fp_tokens<T><<<n_pairs * d.n_fp_chunks, THREADS, 0, s>>>(d, static_cast<const T*>(a->q), static_cast<const T*>(a->k_fp),
+                                                               static_cast<const T*>(a->v_fp), partial, ml);
+    return check_launch();
+  };
+  ForkSet* fk = nullptr;
+  if (d.n_fp_chunks > 0 && !ev) {
+    fk = fork_set(dev);
+    if (!fk) return CQ_ERR_LAUNCH;
+    if (cudaEventRecord(fk->fork, st) != cudaSuccess || cudaStreamWaitEvent(fk->side, fk->fork, 0) != cudaSuccess)
+      return CQ_ERR_LAUNCH;
+    const int rc = launch_fp(fk->side);
+    if (rc != CQ_OK) return rc;
+    if (cudaEventRecord(fk->join, fk->side) != cudaSuccess) return CQ_ERR_LAUNCH;
+  }
   mark(0);
   if (d.t_vis > 0) {
     CUtensorMap tm_code, tm_ks, tm_kmn;
@@ -1224,9 +1268,9 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
     if (!make_k_maps<BITS>(&tm_code, &tm_ks, &tm_kmn, a->k_code, a->k_scale, a->k_mn, (uint64_t)d.n_groups, rows))
       return CQ_ERR_LAUNCH;
     const int items1 = n_pairs * d.n_ktiles;
-    const int grid1 = max(1, min(items1 + n_pairs * ((d.t_fp + 63) / 64), sm_count() * occ1));
+    const int grid1 = max(1, min(items1, sm_count() * occ1));
     if (launch_pdl(k1, dim3(grid1), dim3(K1_THREADS), smem1, st, tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(a->q),
-                   static_cast<const T*>(a->k_fp), scores, mm, status) != cudaSuccess)
+                   scores, mm, status) != cudaSuccess)
       return CQ_ERR_LAUNCH;
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
@@ -1245,11 +1289,12 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
     if (rc != CQ_OK) return rc;
     mark(2);
     if (d.n_fp_chunks > 0) {
-      if (launch_pdl(k2_fp_tokens<T>, dim3(n_pairs * d.n_fp_chunks), dim3(THREADS), 0, st, d, static_cast<const T*>(scores),
-                     static_cast<const T*>(a->v_fp), partial, ml) != cudaSuccess)
-        return CQ_ERR_LAUNCH;
-      rc = check_launch();
-      if (rc != CQ_OK) return rc;
+      if (fk) {
+        if (cudaStreamWaitEvent(st, fk->join, 0) != cudaSuccess) return CQ_ERR_LAUNCH;
+      } else {
+        rc = launch_fp(st);
+        if (rc != CQ_OK) return rc;
+      }
     }
     mark(3);
   }
@@ -1349,7 +1394,7 @@ static int qbmm_run_t(int kind, const mma::Dims& d_in, const void* fA, const int
     const uint64_t rows = (uint64_t)n_pairs * kHeadDim;
     if (!make_k_maps<BITS>(&tm_code, &tm_ks, &tm_kmn, qB, scales, zeros, (uint64_t)d.n_groups, rows)) return CQ_ERR_LAUNCH;
     const int grid = max(1, min(n_pairs * d.n_ktiles, sm_count() * occ[dev][variant]));
-    k1<<<grid, K1_THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(fA), nullptr,
+    k1<<<grid, K1_THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(fA),
                                         static_cast<T*>(out), nullptr, status);
     return check_launch();
   }

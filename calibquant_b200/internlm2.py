@@ -286,7 +286,7 @@ class GraphedDecoder:
         torch.cuda.synchronize()
         self._reset(state0, start_pos)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, stream=side):     # the warm-up's stream: its scratch buffers are reused
             self._step()
         self._reset(state0, start_pos)
 

@@ -63,8 +63,16 @@ _decode_ws_bytes = {}      # problem extents -> bytes, so a decode loop asks the
 def _workspace(nbytes: int, device, stream_handle=None) -> torch.Tensor:
     """Grow-only scratch buffer per (device, stream), zeroed when created: its first word is
     the sticky device status the decode kernels set when a bounded wait runs out."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream if stream_handle is None else stream_handle)
+    # A capture reuses the buffer an eager warm-up call created (a fixed address the replays can use).  A buffer
+    # that has to be created while a CUDA graph is being captured lives in that graph's memory pool: it is kept
+    # for captures only, eager calls on the same stream never see it.
+    stream = torch.cuda.current_stream(device).cuda_stream if stream_handle is None else stream_handle
+    capturing = bool(torch.cuda.is_current_stream_capturing())
+    key = (device.index, stream, False)
     buf = _workspaces.get(key)
+    if capturing and (buf is None or buf.numel() < nbytes):
+        key = (device.index, stream, True)
+        buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         new = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
         if buf is not None:
@@ -77,11 +85,13 @@ def device_status(device=None) -> int:
     """Sticky status word of the current stream's decode workspace (0 = no device-side wait has
     timed out since the workspace was created).  Synchronises the stream."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
-    buf = _workspaces.get(key)
-    if buf is None:
-        return 0
-    return int(buf[:4].view(torch.int32).item())
+    stream = torch.cuda.current_stream(device).cuda_stream
+    status = 0
+    for capturing in (False, True):
+        buf = _workspaces.get((device.index, stream, capturing))
+        if buf is not None and status == 0:
+            status = int(buf[:4].view(torch.int32).item())
+    return status
 
 
 def pack_last_dim(data: torch.Tensor, group_size: int, bits: int):

@@ -177,6 +177,14 @@ typedef struct cq_decode_args {
                                  /* (tensor-core path only, otherwise CQ_ERR_UNSUPPORTED)          */
 } cq_decode_args;
 
+/*
+ * Stream semantics: everything the call enqueues is ordered after the work already in `stream` and before
+ * anything enqueued in it afterwards.  With full-precision tokens present, the tensor-core path runs their launch
+ * on an internal side stream (one per host thread and device, created on first use) between two events recorded
+ * in `stream` and in the side stream; under stream capture this records two parallel branches that join before the
+ * last launch.  Make the first call on a device outside any capture.  The launches carry the
+ * programmatic-stream-serialization attribute (they overlap their heads with the previous launch's tail).
+ */
 size_t cq_decode_attn_workspace_bytes(const cq_decode_args* args);
 int cq_decode_attn(const cq_decode_args* args, void* workspace, size_t workspace_bytes,
                    void* stream);
