@@ -715,10 +715,10 @@ template <typename T, int BITS>
 __global__ void __launch_bounds__(128)
 lut_out_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const uint8_t* __restrict__ enc,
                    int hq, int hkv_enc, int t_len, float* __restrict__ partial, int n_rows) {
-  static_assert(BITS == 1 || BITS == 2, "4-bit codes take the scalar kernel");
-  constexpr int ROW_BYTES = kHeadDim * BITS / 8;          // 16 / 32
-  constexpr int WORDS = ROW_BYTES / 4;                    // 4 / 8
-  constexpr int MT_PER_WORD = 2 / BITS;                   // m-tiles (16 channels) per code word: 2 / 1
+  constexpr int ROW_BYTES = kHeadDim * BITS / 8;          // 16 / 32 / 64
+  constexpr int WORDS = ROW_BYTES / 4;                    // 4 / 8 / 16
+  // m-tiles (16 channels) per code word: 2 / 1; at 4 bits an m-tile spans two words and takes its own code path
+  constexpr int MT_PER_WORD = BITS == 4 ? 1 : 2 / BITS;
   __shared__ __align__(16) __half w_s[kMaxRep][WO_TOK + 8];
   __shared__ float red_s[4][kMaxRep][kHeadDim + 4];
   __shared__ float wsum_s[kMaxRep];
@@ -792,6 +792,34 @@ lut_out_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const uin
   for (int ks = 0; ks < WO_TOK / 4 / 16; ++ks) {
     const int tk = tw0 + ks * 16;                          // first token of the k-step inside the CTA's span
     if (tk >= nt) break;
+    const __half* wr = &w_s[g < n_rep ? g : 0][tk + 2 * c];
+    uint32_t bq0 = *reinterpret_cast<const uint32_t*>(wr), bq1 = *reinterpret_cast<const uint32_t*>(wr + 8);
+    if (g >= n_rep) { bq0 = 0u; bq1 = 0u; }
+    if constexpr (BITS == 4) {
+      // A byte is two channels (first one in the high nibble).  Lane g takes byte g%4 of the words 4q + 2(g/4) and
+      // 4q + 2(g/4) + 1 of every 32-channel quarter q (one 8-byte load per token row): rows g / g+8 of the m-tiles
+      // 2q and 2q+1 are the low / high nibble of that byte, i.e. channels 8W + 2(g%4) + 1 and 8W + 2(g%4).
+      const int last = nt - 1;
+      const uint8_t* pa = base + (int64_t)min(tk + 2 * c, last) * ROW_BYTES + 8 * (g >> 2);
+      const uint8_t* pb = base + (int64_t)min(tk + 2 * c + 1, last) * ROW_BYTES + 8 * (g >> 2);
+      const uint8_t* pc = base + (int64_t)min(tk + 2 * c + 8, last) * ROW_BYTES + 8 * (g >> 2);
+      const uint8_t* pd = base + (int64_t)min(tk + 2 * c + 9, last) * ROW_BYTES + 8 * (g >> 2);
+      const uint32_t sel4 = (uint32_t)((g & 3) | ((g & 3) << 4) | ((4 + (g & 3)) << 8) | ((4 + (g & 3)) << 12));
+      uint2 va[4], vb[4], vc[4], vd[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        va[q] = __ldg(reinterpret_cast<const uint2*>(pa + 16 * q)); vb[q] = __ldg(reinterpret_cast<const uint2*>(pb + 16 * q));
+        vc[q] = __ldg(reinterpret_cast<const uint2*>(pc + 16 * q)); vd[q] = __ldg(reinterpret_cast<const uint2*>(pd + 16 * q));
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t x01a = prmt(va[q].x, vb[q].x, sel4), x89a = prmt(vc[q].x, vd[q].x, sel4);
+        mma_f16(acc[2 * q], x01a & 0x000f000fu, x01a & 0x00f000f0u, x89a & 0x000f000fu, x89a & 0x00f000f0u, bq0, bq1);
+        const uint32_t x01b = prmt(va[q].y, vb[q].y, sel4), x89b = prmt(vc[q].y, vd[q].y, sel4);
+        mma_f16(acc[2 * q + 1], x01b & 0x000f000fu, x01b & 0x00f000f0u, x89b & 0x000f000fu, x89b & 0x00f000f0u, bq0, bq1);
+      }
+      continue;
+    }
     // token rows 2c, 2c+1, 2c+8, 2c+9 of the k-step (clamped: tokens past the end have w = 0)
     uint32_t Wa[WORDS], Wb[WORDS], Wc[WORDS], Wd[WORDS];
     {
@@ -809,9 +837,6 @@ lut_out_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const uin
         Wd[4 * q4] = vd.x; Wd[4 * q4 + 1] = vd.y; Wd[4 * q4 + 2] = vd.z; Wd[4 * q4 + 3] = vd.w;
       }
     }
-    const __half* wr = &w_s[g < n_rep ? g : 0][tk + 2 * c];
-    uint32_t bq0 = *reinterpret_cast<const uint32_t*>(wr), bq1 = *reinterpret_cast<const uint32_t*>(wr + 8);
-    if (g >= n_rep) { bq0 = 0u; bq1 = 0u; }
 #pragma unroll
     for (int wd = 0; wd < WORDS; ++wd) {
       const uint32_t x01 = prmt(Wa[wd], Wb[wd], sel), x89 = prmt(Wc[wd], Wd[wd], sel);
@@ -824,9 +849,15 @@ lut_out_mma_kernel(const T* __restrict__ lut, const T* __restrict__ w, const uin
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int i = j % MT_PER_WORD, span = (j / MT_PER_WORD) * (32 / BITS);   // channels covered by the word
-    const int d0 = span + ch0[i], d1 = span + ch1[i];
-    if (2 * c < n_rep) { red_s[warp][2 * c][d0] = acc[j][0] * sc0[i]; red_s[warp][2 * c][d1] = acc[j][2] * sc1[i]; }
-    if (2 * c + 1 < n_rep) { red_s[warp][2 * c + 1][d0] = acc[j][1] * sc0[i]; red_s[warp][2 * c + 1][d1] = acc[j][3] * sc1[i]; }
+    int d0 = span + ch0[i], d1 = span + ch1[i];
+    float s0 = sc0[i], s1 = sc1[i];
+    if (BITS == 4) {                     // rows g / g+8 = low / high nibble of byte g%4 of word W
+      const int W = 4 * (j >> 1) + 2 * (g >> 2) + (j & 1);
+      d0 = 8 * W + 2 * (g & 3) + 1; d1 = 8 * W + 2 * (g & 3);
+      s0 = 16777216.f; s1 = 1048576.f;   // 2^24 for a field at bit 0, 2^20 at bit 4
+    }
+    if (2 * c < n_rep) { red_s[warp][2 * c][d0] = acc[j][0] * s0; red_s[warp][2 * c][d1] = acc[j][2] * s1; }
+    if (2 * c + 1 < n_rep) { red_s[warp][2 * c + 1][d0] = acc[j][1] * s0; red_s[warp][2 * c + 1][d1] = acc[j][3] * s1; }
   }
   __syncthreads();
   for (int r = 0; r < n_rep; ++r) {
@@ -1230,14 +1261,14 @@ extern "C" int cq_lut_out(const void* lut, const void* weights, const uint8_t* e
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* ws = static_cast<float*>(workspace);
   const int rows = batch * n_q_heads;
-  if (bits <= 2 && aligned16(enc)) {     // tensor-core kernel: WO_TOK tokens per CTA (fewer partials than the scalar one)
+  if (aligned16(enc)) {     // tensor-core kernel: WO_TOK tokens per CTA (fewer partials than the scalar one)
     const int chunks = (t_len + calib::WO_TOK - 1) / calib::WO_TOK;
     dim3 grid((unsigned)chunks, (unsigned)(batch * n_enc_heads));
 #define CQ_LUT_OUT(T, B)                                                                                      \
   calib::lut_out_mma_kernel<T, B><<<grid, 128, 0, st>>>(static_cast<const T*>(lut), static_cast<const T*>(weights), enc, \
                                                        n_q_heads, n_enc_heads, t_len, ws, rows)
-    if (dtype == CQ_DTYPE_F16) { if (bits == 1) CQ_LUT_OUT(__half, 1); else CQ_LUT_OUT(__half, 2); }
-    else { if (bits == 1) CQ_LUT_OUT(__nv_bfloat16, 1); else CQ_LUT_OUT(__nv_bfloat16, 2); }
+    if (dtype == CQ_DTYPE_F16) { if (bits == 1) CQ_LUT_OUT(__half, 1); else if (bits == 2) CQ_LUT_OUT(__half, 2); else CQ_LUT_OUT(__half, 4); }
+    else { if (bits == 1) CQ_LUT_OUT(__nv_bfloat16, 1); else if (bits == 2) CQ_LUT_OUT(__nv_bfloat16, 2); else CQ_LUT_OUT(__nv_bfloat16, 4); }
 #undef CQ_LUT_OUT
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
@@ -1276,7 +1307,7 @@ StepLayout step_layout(const cq_u8_decode_args* a) {
   l.a_fp = off;   off = up(off + rows * (size_t)a->t_fp * 2);
   l.a_sum = off;  off = up(off + rows * 4);
   l.lut = off;    off = up(off + 32);
-  l.chunks = a->bits <= 2 ? (a->t_vis + calib::WO_TOK - 1) / calib::WO_TOK : (a->t_vis + calib::WV_TCHUNK - 1) / calib::WV_TCHUNK;
+  l.chunks = (a->t_vis + calib::WO_TOK - 1) / calib::WO_TOK;
   l.partial = off; off = up(off + (size_t)l.chunks * rows * kHeadDim * 4);
   l.total = off;
   return l;
@@ -1354,7 +1385,7 @@ static int launch_step(const cq_u8_decode_args* a, char* ws, cudaStream_t st) {
     else if (a->bits == 2)
       calib::lut_out_mma_kernel<__half, 2><<<grid, 128, 0, st>>>(lut_h, a_vis, a->enc_v, hq, hkv, a->t_vis, partial, rows);
     else
-      calib::lut_out_partial_kernel<__half><<<grid, kHeadDim, 0, st>>>(lut_h, a_vis, a->enc_v, hq, hkv, a->t_vis, a->bits, partial, rows);
+      calib::lut_out_mma_kernel<__half, 4><<<grid, 128, 0, st>>>(lut_h, a_vis, a->enc_v, hq, hkv, a->t_vis, partial, rows);
   }
   if (cudaFuncSetAttribute(calib::step_finish_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess)
     return CQ_ERR_LAUNCH;
