@@ -911,30 +911,57 @@ k2_attn_v(const __grid_constant__ CUtensorMap tm_v,   // 2 and 4 bits: the value
     if (!(dm.raw && std::is_same<T, __half>::value)) {
       const uint32_t q_b = code_b + LOGIT_OFF + (uint32_t)(warp * QTOK) * 2u;
       const uint32_t cal_b = smem_u32(&cal_w[warp][0][0]);
-#pragma unroll 2
-      for (int h = 0; h < dm.n_rep; ++h) {
-        const uint4 cw = lds128(cal_b + (uint32_t)h * 32u);
-        const float mneg = __uint_as_float(lds32(cal_b + (uint32_t)h * 32u + 16u));
-        CalibH<T> ch;
-        ch.mn = *reinterpret_cast<const T2*>(&cw.x); ch.range = *reinterpret_cast<const T2*>(&cw.y);
-        ch.rdenom = *reinterpret_cast<const T2*>(&cw.z); ch.rdenom_lo = *reinterpret_cast<const T2*>(&cw.w);
+      // Four heads at a time, in three sweeps: all loads, all arithmetic, all stores.  The shared-memory accesses are
+      // volatile asm statements, which the compiler keeps in program order: written as load-compute-store per
+      // element, the eight chains of a lane (4 heads x 2 token pairs) ran one after the other, ~1950 cycles per tile
+      // (cycle counters); as sweeps they overlap.
+      constexpr int NJ = QTOK / 64;
+      for (int h0 = 0; h0 < dm.n_rep; h0 += 4) {
+        uint4 cw[4];
+        float mneg[4];
+        uint32_t xin[4][NJ];
 #pragma unroll
-        for (int j = 0; j < QTOK / 64; ++j) {
-          const int tp = (j * 32 + lane) * 2;                 // first token of the pair, within the quarter
-          if (warp * QTOK + tp < nt_tile) {
-            const uint32_t addr = q_b + (uint32_t)(h * LROW + tp * 2);
-            const uint32_t x = lds32(addr);
-            uint32_t pp;
-            if (dm.raw) {                                     // plain product: the row holds the weights themselves
-              pp = D16<T>::to_h2(x);
+        for (int hh = 0; hh < 4; ++hh) {
+          const int h = min(h0 + hh, dm.n_rep - 1);            // heads past the last repeat it; their results are dropped
+          cw[hh] = lds128(cal_b + (uint32_t)h * 32u);
+          mneg[hh] = __uint_as_float(lds32(cal_b + (uint32_t)h * 32u + 16u));
+#pragma unroll
+          for (int j = 0; j < NJ; ++j) {
+            const int tp = (j * 32 + lane) * 2;                 // first token of the pair, within the quarter
+            xin[hh][j] = lds32(q_b + (uint32_t)(h * LROW + tp * 2));
+          }
+        }
+        uint32_t pp[4][NJ];
+#pragma unroll
+        for (int hh = 0; hh < 4; ++hh) {
+          CalibH<T> ch;
+          ch.mn = *reinterpret_cast<const T2*>(&cw[hh].x); ch.range = *reinterpret_cast<const T2*>(&cw[hh].y);
+          ch.rdenom = *reinterpret_cast<const T2*>(&cw[hh].z); ch.rdenom_lo = *reinterpret_cast<const T2*>(&cw[hh].w);
+#pragma unroll
+          for (int j = 0; j < NJ; ++j) {
+            const int tp = (j * 32 + lane) * 2;
+            if (dm.raw) {                                       // plain product: the row holds the weights themselves
+              pp[hh][j] = D16<T>::to_h2(xin[hh][j]);
             } else {
-              T2 v = *reinterpret_cast<const T2*>(&x);
+              T2 v = *reinterpret_cast<const T2*>(&xin[hh][j]);
               if (dm.calibrate) v = calibrate2<T>(v, ch);
-              if (mvis) v = __hadd2(v, D16<T>::pair2(mvis[warp * QTOK + tp], mvis[warp * QTOK + tp + 1]));
+              if (mvis && warp * QTOK + tp < nt_tile)
+                v = __hadd2(v, D16<T>::pair2(mvis[warp * QTOK + tp], mvis[warp * QTOK + tp + 1]));
               const float2 f = D16<T>::to_f2(v);
-              pp = D16<T>::prob_pair(ex2_approx(fmaf(f.x, LOG2E, mneg)), ex2_approx(fmaf(f.y, LOG2E, mneg)));
+              pp[hh][j] = D16<T>::prob_pair(ex2_approx(fmaf(f.x, LOG2E, mneg[hh])), ex2_approx(fmaf(f.y, LOG2E, mneg[hh])));
             }
-            asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(pp) : "memory");
+          }
+        }
+#pragma unroll
+        for (int hh = 0; hh < 4; ++hh) {
+          const int h = h0 + hh;
+#pragma unroll
+          for (int j = 0; j < NJ; ++j) {
+            const int tp = (j * 32 + lane) * 2;
+            if (h < dm.n_rep && warp * QTOK + tp < nt_tile) {
+              const uint32_t addr = q_b + (uint32_t)(h * LROW + tp * 2);
+              asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(pp[hh][j]) : "memory");
+            }
           }
         }
       }
