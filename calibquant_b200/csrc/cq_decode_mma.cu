@@ -969,66 +969,74 @@ k2_attn_v(const __grid_constant__ CUtensorMap tm_v,   // 2 and 4 bits: the value
     }
     const uint32_t zoff = (uint32_t)(g < 4 ? g : 0) * 4u;   // this lane's column of the minima MMA
     const uint32_t z_and = g < 4 ? 0xffffffffu : 0u, z_or = g == 4 ? 0x3c003c00u : 0u;   // column 4 = ones
-#pragma unroll
-    for (int kq = 0; kq < QTOK / 16; ++kq) {
-      if (warp * QTOK + kq * 16 >= nt_tile) break;
+    // One k-step = 16 tokens.  Its shared-memory operands are fetched one k-step ahead of their use (the loads are
+    // volatile asm statements and stay where they are written): probabilities, scale pairs, minima, code words of
+    // the lane's four tokens (t0, t0+1, t0+8, t0+9).
+    constexpr int NW = BITS == 1 ? 4 : 8;        // code words per token the lane uses
+    struct StepRegs { uint32_t pp0, pp1, zb0, zb1; uint4 s0, s1; uint32_t cw[4][NW]; };
+    auto load_step = [&](int kq, StepRegs& R) {
       const int t0 = warp * QTOK + kq * 16 + 2 * c;   // token (in tile) of the lane's first k pair
-      uint32_t pp0 = lds32(lg_b + (uint32_t)t0 * 2u), pp1 = lds32(lg_b + (uint32_t)(t0 + 8) * 2u);
-      if (g >= dm.n_rep) { pp0 = 0u; pp1 = 0u; }
+      R.pp0 = lds32(lg_b + (uint32_t)t0 * 2u);
+      R.pp1 = lds32(lg_b + (uint32_t)(t0 + 8) * 2u);
       // scale pairs of tokens (t0, t0+1) and (t0+8, t0+9), one register per channel group
-      const uint4 s0 = lds128(vs_b + (uint32_t)t0 * 8u), s1 = lds128(vs_b + (uint32_t)(t0 + 8) * 8u);
-      uint32_t bA[4], bB[4];
-      bA[0] = hmul2_u32(pp0, s0.x); bA[1] = hmul2_u32(pp0, s0.y); bA[2] = hmul2_u32(pp0, s0.z); bA[3] = hmul2_u32(pp0, s0.w);
-      bB[0] = hmul2_u32(pp1, s1.x); bB[1] = hmul2_u32(pp1, s1.y); bB[2] = hmul2_u32(pp1, s1.z); bB[3] = hmul2_u32(pp1, s1.w);
-      // minima + row sum: A = p (rows = heads), B column n = g: n<4 -> vmn[.][n], n==4 -> 1
-      {
-        const uint32_t zb0 = (lds32(vmn_b + (uint32_t)t0 * 8u + zoff) & z_and) | z_or;
-        const uint32_t zb1 = (lds32(vmn_b + (uint32_t)(t0 + 8) * 8u + zoff) & z_and) | z_or;
-        mma_f16(cb, pp0, 0u, pp1, 0u, zb0, zb1);
-      }
-      // code words of the lane's four tokens
+      R.s0 = lds128(vs_b + (uint32_t)t0 * 8u);
+      R.s1 = lds128(vs_b + (uint32_t)(t0 + 8) * 8u);
+      R.zb0 = lds32(vmn_b + (uint32_t)t0 * 8u + zoff);
+      R.zb1 = lds32(vmn_b + (uint32_t)(t0 + 8) * 8u + zoff);
       const uint32_t tb = code_b + (uint32_t)t0 * TOK_BYTES;
-      if (BITS == 4) {
-        // rows of tokens t0, t0+1, t0+8, t0+9 all carry the chunk XOR c (64-byte swizzle: chunk ^= (row / 2) % 4).
-        // Per 32-channel group q the lane reads the two words (2hi, 2hi+1) of chunk q: m-tiles 2q and 2q+1.
-        const uint32_t hoff = (uint32_t)(g >> 2) * 8u;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t off = (uint32_t)((q ^ c) << 4) + hoff;
-          const uint2 wa = lds64(tb + off), wb = lds64(tb + TOK_BYTES + off);
-          const uint2 wc = lds64(tb + 8 * TOK_BYTES + off), wd = lds64(tb + 9 * TOK_BYTES + off);
-          const uint32_t x01a = prmt(wa.x, wb.x, sel[0]), x89a = prmt(wc.x, wd.x, sel[0]);
-          mma_f16(acc[2 * q], x01a & m0[0], x01a & m1[0], x89a & m0[0], x89a & m1[0], bA[q], bB[q]);
-          const uint32_t x01b = prmt(wa.y, wb.y, sel[0]), x89b = prmt(wc.y, wd.y, sel[0]);
-          mma_f16(acc[2 * q + 1], x01b & m0[0], x01b & m1[0], x89b & m0[0], x89b & m1[0], bA[q], bB[q]);
-        }
-      } else {
+      for (int r = 0; r < 4; ++r) {
+        const uint32_t row = tb + (uint32_t)((r & 1) + 8 * (r >> 1)) * TOK_BYTES;
+        if (BITS == 4) {
+          // rows of tokens t0, t0+1, t0+8, t0+9 all carry the chunk XOR c (64-byte swizzle: chunk ^= (row / 2) % 4).
+          // Per 32-channel group q the lane reads the two words (2hi, 2hi+1) of chunk q: m-tiles 2q and 2q+1.
 #pragma unroll
-      for (int part = 0; part < BITS; ++part) {      // 16 bytes of every token row at a time
-        // 2 bits: 32-byte swizzle, chunk ^= (row / 4) % 2 = c / 2 for all four tokens
-        const uint32_t po = BITS == 2 ? (uint32_t)((part ^ (c >> 1)) << 4) : (uint32_t)(part * 16);
-        const uint4 wa = lds128(tb + po), wb = lds128(tb + TOK_BYTES + po);
-        const uint4 wc = lds128(tb + 8 * TOK_BYTES + po), wd = lds128(tb + 9 * TOK_BYTES + po);
-        const uint32_t Wa[4] = {wa.x, wa.y, wa.z, wa.w}, Wb[4] = {wb.x, wb.y, wb.z, wb.w};
-        const uint32_t Wc[4] = {wc.x, wc.y, wc.z, wc.w}, Wd[4] = {wd.x, wd.y, wd.z, wd.w};
-        // m-tiles covered by these 4 words: 128/BITS channels = 8/BITS m-tiles
-        if (BITS == 1) {      // word m = channels 32m .. 32m+31 = m-tiles 2m, 2m+1, one byte permute for both
-#pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const uint32_t x01 = prmt(Wa[m], Wb[m], sel[0]), x89 = prmt(Wc[m], Wd[m], sel[0]);
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-              mma_f16(acc[2 * m + i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bA[m], bB[m]);
+          for (int q = 0; q < 4; ++q) {
+            const uint2 w = lds64(row + (uint32_t)((q ^ c) << 4) + (uint32_t)(g >> 2) * 8u);
+            R.cw[r][2 * q] = w.x; R.cw[r][2 * q + 1] = w.y;
           }
-        } else
+        } else {
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const int j = part * 4 + jj;                   // 2 bits: m-tile = channels 16j .. 16j+15 = word jj of the part
-          const uint32_t x01 = prmt(Wa[jj], Wb[jj], sel[0]), x89 = prmt(Wc[jj], Wd[jj], sel[0]);
+          for (int part = 0; part < BITS; ++part) {      // 16 bytes of the token row at a time
+            // 2 bits: 32-byte swizzle, chunk ^= (row / 4) % 2 = c / 2 for all four tokens
+            const uint32_t po = BITS == 2 ? (uint32_t)((part ^ (c >> 1)) << 4) : (uint32_t)(part * 16);
+            const uint4 w = lds128(row + po);
+            R.cw[r][4 * part] = w.x; R.cw[r][4 * part + 1] = w.y; R.cw[r][4 * part + 2] = w.z; R.cw[r][4 * part + 3] = w.w;
+          }
+        }
+      }
+    };
+    auto compute_step = [&](const StepRegs& R) {
+      uint32_t pp0 = R.pp0, pp1 = R.pp1;
+      if (g >= dm.n_rep) { pp0 = 0u; pp1 = 0u; }
+      uint32_t bA[4], bB[4];
+      bA[0] = hmul2_u32(pp0, R.s0.x); bA[1] = hmul2_u32(pp0, R.s0.y); bA[2] = hmul2_u32(pp0, R.s0.z); bA[3] = hmul2_u32(pp0, R.s0.w);
+      bB[0] = hmul2_u32(pp1, R.s1.x); bB[1] = hmul2_u32(pp1, R.s1.y); bB[2] = hmul2_u32(pp1, R.s1.z); bB[3] = hmul2_u32(pp1, R.s1.w);
+      // minima + row sum: A = p (rows = heads), B column n = g: n<4 -> vmn[.][n], n==4 -> 1
+      mma_f16(cb, pp0, 0u, pp1, 0u, (R.zb0 & z_and) | z_or, (R.zb1 & z_and) | z_or);
+      if (BITS == 1) {        // word m = channels 32m .. 32m+31 = m-tiles 2m, 2m+1, one byte permute for both
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          const uint32_t x01 = prmt(R.cw[0][m], R.cw[1][m], sel[0]), x89 = prmt(R.cw[2][m], R.cw[3][m], sel[0]);
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            mma_f16(acc[2 * m + i], x01 & m0[i], x01 & m1[i], x89 & m0[i], x89 & m1[i], bA[m], bB[m]);
+        }
+      } else {                // 2 bits: m-tile j = word j of the row; 4 bits: m-tiles 2q, 2q+1 = the pair loaded for q
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t x01 = prmt(R.cw[0][j], R.cw[1][j], sel[0]), x89 = prmt(R.cw[2][j], R.cw[3][j], sel[0]);
           mma_f16(acc[j], x01 & m0[0], x01 & m1[0], x89 & m0[0], x89 & m1[0], bA[j >> 1], bB[j >> 1]);
         }
       }
-      }
+    };
+    StepRegs R[2];
+    load_step(0, R[0]);
+#pragma unroll
+    for (int kq = 0; kq < QTOK / 16; ++kq) {
+      if (warp * QTOK + kq * 16 >= nt_tile) break;
+      if (kq + 1 < QTOK / 16) load_step(kq + 1, R[(kq + 1) & 1]);
+      compute_step(R[kq & 1]);
     }
     // the stage has been read: hand it back to the producer
     __syncwarp();
