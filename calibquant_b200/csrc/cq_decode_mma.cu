@@ -846,7 +846,17 @@ k2_attn_v(const __grid_constant__ CUtensorMap tm_v,   // 2 and 4 bits: the value
       float lo = INFINITY, hi = -INFINITY;
       if (g < dm.n_rep && !dm.raw) {
         const float2* mm = tile_mm + ((int64_t)pair * dm.n_rep + g) * dm.n_mm;
-        for (int i = c; i < dm.n_mm; i += 4) {
+        // eight entries in flight per lane: the loads are L2 round trips, one after the other they cost the
+        // CTA several thousand cycles at every change of KV head
+        int i = c;
+        for (; i + 28 < dm.n_mm; i += 32) {
+          float2 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) v[u] = mm[i + 4 * u];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) { lo = fminf(lo, v[u].x); hi = fmaxf(hi, v[u].y); }
+        }
+        for (; i < dm.n_mm; i += 4) {
           const float2 v = mm[i];
           lo = fminf(lo, v.x);
           hi = fmaxf(hi, v.y);
