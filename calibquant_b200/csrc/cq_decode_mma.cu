@@ -475,8 +475,6 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
             make_float2(INFINITY, -INFINITY);
     }
   }
-  if (failed) return;
-
 }
 
 // =================================================================================================
