@@ -59,6 +59,7 @@ class U8DecodeArgs(_c.Structure):
         ("fp_stride_b", _i64), ("fp_stride_h", _i64),
         ("mask", _vp), ("mask_stride_b", _i64),
         ("out", _vp),
+        ("t_fp_dev", _vp),
     ]
 
 

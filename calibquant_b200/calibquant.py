@@ -141,7 +141,7 @@ def fused_kernel_wv(unique_values, weights, features_enc, BITS=BITS_KV, DATUM_PE
     return out
 
 
-def decode_attention(q, state, k_fp, v_fp, bits, sys_len, normalize=None, mask=None):
+def decode_attention(q, state, k_fp, v_fp, bits, sys_len, normalize=None, mask=None, t_fp_dev=None):
     """Decode step of the reference's calibquant forward (``patch_internvl.py:356-436``) on the uint8
     format as ONE library call of four launches: post-scaling (scale folded into the query, zero point
     into a scalar bias), logit calibration, fp32 softmax, the two code products, the full-precision
@@ -149,6 +149,8 @@ def decode_attention(q, state, k_fp, v_fp, bits, sys_len, normalize=None, mask=N
     zero_point_key, scale_value, zero_point_value`` as [B,Hq,1,D] (the reference's repeated layout) or
     [B,1,Hkv,D] / [B,Hkv,1,D] (one row per KV head).  ``k_fp``/``v_fp`` [B,Hkv,T_fp,D] hold
     [system | text]; ``mask`` is the optional additive mask [B,1,1,T] over [system | visual | text].
+    With ``t_fp_dev`` (int32 device scalar) the live number of full-precision tokens is read on the device and
+    ``k_fp``/``v_fp`` are the whole pre-allocated buffers, so that a captured CUDA graph serves every step.
     Returns [B,Hq,1,D] in bfloat16 as the reference does."""
     from ._lib import U8DecodeArgs
     _need_cuda(q, k_fp, v_fp)
@@ -180,7 +182,8 @@ def decode_attention(q, state, k_fp, v_fp, bits, sys_len, normalize=None, mask=N
                      k_fp=k_fp.data_ptr() if t_fp else None, v_fp=v_fp.data_ptr() if t_fp else None,
                      fp_stride_b=k_fp.stride(0), fp_stride_h=k_fp.stride(1),
                      mask=mask2.data_ptr() if mask2 is not None else None,
-                     mask_stride_b=mask2.stride(0) if mask2 is not None else 0, out=out.data_ptr())
+                     mask_stride_b=mask2.stride(0) if mask2 is not None else 0, out=out.data_ptr(),
+                     t_fp_dev=t_fp_dev.data_ptr() if t_fp_dev is not None else None)
     if k_fp.stride() != v_fp.stride():
         raise ValueError("k_fp and v_fp must share strides")
     nbytes = lib().cq_u8_decode_attn_workspace_bytes(ctypes.byref(a))

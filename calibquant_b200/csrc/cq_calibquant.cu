@@ -895,7 +895,8 @@ step_softmax_kernel(const T* __restrict__ q, const T* __restrict__ k_fp, int64_t
                     int hq, int hkv, int t_vis, int t_fp, int t_sys, int calibrate,
                     const typename StepScore<T>::type* __restrict__ s_vis, const T* __restrict__ mask,
                     int64_t mask_stride_b, __half* __restrict__ a_vis, T* __restrict__ a_fp,
-                    float* __restrict__ a_sum) {
+                    float* __restrict__ a_sum, const int32_t* __restrict__ t_fp_dev, int t_fp_cap) {
+  if (t_fp_dev) t_fp = min(*t_fp_dev, t_fp_cap);      // live count kept on the device; rows of a_fp stay t_fp_cap apart
   extern __shared__ float row[];         // [t_vis + t_fp], visual scores first
   __shared__ float red[32];
   __shared__ float q_s[kHeadDim];
@@ -958,7 +959,7 @@ step_softmax_kernel(const T* __restrict__ q, const T* __restrict__ k_fp, int64_t
     a_vis[(int64_t)bh * t_vis + t] = __float2half_rn(a);
     vs += a;
   }
-  for (int t = tid; t < t_fp; t += SM_THREADS) a_fp[(int64_t)bh * t_fp + t] = Elem<T>::from_f(row[t_vis + t] * inv);
+  for (int t = tid; t < t_fp; t += SM_THREADS) a_fp[(int64_t)bh * t_fp_cap + t] = Elem<T>::from_f(row[t_vis + t] * inv);
   vs = block_reduce(vs, red, 0);
   if (tid == 0) a_sum[bh] = rnd<T>(vs);
 }
@@ -979,7 +980,8 @@ __global__ void __launch_bounds__(SMH_THREADS, 2)
 step_softmax_h_kernel(const __half* __restrict__ q, const __half* __restrict__ k_fp, int64_t fp_stride_b,
                       int64_t fp_stride_h, int hq, int hkv, int t_vis, int t_fp, int calibrate,
                       const __half* __restrict__ s_vis, __half* __restrict__ a_vis, __half* __restrict__ a_fp,
-                      float* __restrict__ a_sum) {
+                      float* __restrict__ a_sum, const int32_t* __restrict__ t_fp_dev, int t_fp_cap) {
+  if (t_fp_dev) t_fp = min(*t_fp_dev, t_fp_cap);
   extern __shared__ __align__(16) unsigned char sm_raw[];
   uint4* rv = reinterpret_cast<uint4*>(sm_raw);                          // t_vis halves
   float* fprow = reinterpret_cast<float*>(sm_raw + (size_t)t_vis * 2);   // t_fp floats
@@ -1065,7 +1067,7 @@ step_softmax_h_kernel(const __half* __restrict__ q, const __half* __restrict__ k
     dst[i] = v;
   }
   for (int t = tid; t < t_fp; t += SMH_THREADS)
-    a_fp[(int64_t)bh * t_fp + t] = __float2half_rn(ex2_fast(fmaf(fprow[t], L2E, -ml)) * inv);
+    a_fp[(int64_t)bh * t_fp_cap + t] = __float2half_rn(ex2_fast(fmaf(fprow[t], L2E, -ml)) * inv);
   vs = block_reduce(vs, red, 0);
   if (tid == 0) a_sum[bh] = rnd<__half>(vs);
 }
@@ -1078,11 +1080,14 @@ __global__ void __launch_bounds__(kHeadDim)
 step_finish_kernel(const float* __restrict__ partial, int chunks, int n_rows, const T* __restrict__ scale_v,
                    const T* __restrict__ zp_v, int scale_heads, const T* __restrict__ a_fp,
                    const float* __restrict__ a_sum, const T* __restrict__ v_fp, int64_t fp_stride_b,
-                   int64_t fp_stride_h, int hq, int hkv, int t_fp, int t_sys, __nv_bfloat16* __restrict__ out) {
+                   int64_t fp_stride_h, int hq, int hkv, int t_fp, int t_sys, __nv_bfloat16* __restrict__ out,
+                   const int32_t* __restrict__ t_fp_dev) {
   using SS = StepScore<T>;
+  const int t_fp_cap = t_fp;
+  if (t_fp_dev) t_fp = min(*t_fp_dev, t_fp_cap);
   extern __shared__ float att_s[];       // [t_fp]
   const int bh = blockIdx.x, b = bh / hq, h = bh % hq, hk = h / (hq / hkv), d = threadIdx.x;
-  for (int t = d; t < t_fp; t += kHeadDim) att_s[t] = Elem<T>::to_f(a_fp[(int64_t)bh * t_fp + t]);
+  for (int t = d; t < t_fp; t += kHeadDim) att_s[t] = Elem<T>::to_f(a_fp[(int64_t)bh * t_fp_cap + t]);
   float acc = 0.f;
   for (int c = 0; c < chunks; ++c) acc += partial[((int64_t)c * n_rows + bh) * kHeadDim + d];
   const int64_t srow = scale_heads == hq ? bh : (int64_t)b * scale_heads + hk;
@@ -1369,13 +1374,13 @@ static int launch_step(const cq_u8_decode_args* a, char* ws, cudaStream_t st) {
     calib::step_softmax_h_kernel<<<rows, calib::SMH_THREADS, row_bytes_h, st>>>(
         static_cast<const __half*>(a->q), static_cast<const __half*>(a->k_fp), a->fp_stride_b, a->fp_stride_h, hq, hkv,
         a->t_vis, a->t_fp, a->calibrate, reinterpret_cast<const __half*>(scores), a_vis, reinterpret_cast<__half*>(a_fp),
-        a_sum);
+        a_sum, a->t_fp_dev, a->t_fp);
   } else {
     if (cudaFuncSetAttribute(calib::step_softmax_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
       return CQ_ERR_LAUNCH;
     calib::step_softmax_kernel<T><<<rows, calib::SM_THREADS, row_bytes, st>>>(
         q, static_cast<const T*>(a->k_fp), a->fp_stride_b, a->fp_stride_h, hq, hkv, a->t_vis, a->t_fp, a->t_sys,
-        a->calibrate, scores, static_cast<const T*>(a->mask), a->mask_stride_b, a_vis, a_fp, a_sum);
+        a->calibrate, scores, static_cast<const T*>(a->mask), a->mask_stride_b, a_vis, a_fp, a_sum, a->t_fp_dev, a->t_fp);
   }
   if (a->t_vis) {
     dim3 grid((unsigned)l.chunks, (unsigned)(B * hkv));
@@ -1392,7 +1397,7 @@ static int launch_step(const cq_u8_decode_args* a, char* ws, cudaStream_t st) {
   calib::step_finish_kernel<T><<<rows, kHeadDim, (size_t)a->t_fp * 4, st>>>(
       partial, a->t_vis ? l.chunks : 0, rows, static_cast<const T*>(a->scale_value), static_cast<const T*>(a->zero_point_value),
       a->n_scale_heads, a_fp, a_sum, static_cast<const T*>(a->v_fp), a->fp_stride_b, a->fp_stride_h, hq, hkv, a->t_fp,
-      a->t_sys, static_cast<__nv_bfloat16*>(a->out));
+      a->t_sys, static_cast<__nv_bfloat16*>(a->out), a->t_fp_dev);
   return check_launch();
 }
 

@@ -236,8 +236,6 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
     bsz, q_len, _ = hidden_states.size()
 
     if q_len == 1 and getattr(self, "_static_decode", False):
-        if getattr(self, "_u8_state", None) is not None:
-            raise NotImplementedError("the graph-replayable decode step serves the group format only")
         # graph-replayable step: everything that changes between steps is read from device memory.
         # One launch splits the projection, rotates q and k and appends k, v at the device-side
         # token count (already advanced by the owner of the counter), one call attends over the
@@ -248,9 +246,14 @@ def forward_internlm2_calibquant(self, hidden_states: torch.Tensor,
         q = ops.rope_split_append(self.wqkv(hidden_states), cos, sin, position_ids,
                                   self.wqkv.out_features // ((n_rep + 2) * self.head_dim), n_rep,
                                   tc.k, tc.v, t_fp_dev=tc.len_dev)
-        attn = ops.decode_attention(q, self.k_pack, self.v_pack, tc.k, tc.v, self.sprompt_len if LOW_BITS else 0,
-                                    BITS_KV, group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
-                                    t_fp_dev=tc.len_dev)
+        if getattr(self, "_u8_state", None) is not None:
+            from . import calibquant as _cq
+            attn = _cq.decode_attention(q, self._u8_state, tc.k, tc.v, BITS_KV, self.sprompt_len,
+                                        normalize=self.normalize, t_fp_dev=tc.len_dev).to(q.dtype)
+        else:
+            attn = ops.decode_attention(q, self.k_pack, self.v_pack, tc.k, tc.v, self.sprompt_len if LOW_BITS else 0,
+                                        BITS_KV, group_size=GROUP_SIZE, calibrate=self.normalize and LOW_BITS,
+                                        t_fp_dev=tc.len_dev)
         attn = _gather_heads(self, attn.transpose(1, 2).reshape(bsz, q_len, -1))
         return self.wo(attn.reshape(bsz, q_len, -1)), None, past_key_value
 

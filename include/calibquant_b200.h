@@ -314,6 +314,8 @@ typedef struct cq_u8_decode_args {
   const void* mask;                                 /* optional additive mask [B, t_fp + t_vis] in `dtype`,   */
   int64_t mask_stride_b;                            /* key order [sys | visual | text]; NULL = none           */
   void* out;
+  const int32_t* t_fp_dev;                          /* optional device counter of live fp tokens, as in       */
+                                                    /* cq_decode_args: t_fp is then the capacity of k_fp/v_fp */
 } cq_u8_decode_args;
 size_t cq_u8_decode_attn_workspace_bytes(const cq_u8_decode_args* args);
 int cq_u8_decode_attn(const cq_u8_decode_args* args, void* workspace, size_t workspace_bytes, void* stream);

@@ -131,16 +131,17 @@ def test_tiny_model_generates_and_is_deterministic():
     assert a.shape == (2, 5) and torch.equal(a, b)
 
 
-def test_graph_replayed_decode_matches_eager():
+@pytest.mark.parametrize("kv_format", ["group", "uint8"])
+def test_graph_replayed_decode_matches_eager(kv_format):
     """The decode step captured in a CUDA graph (device-side token, position and cache-length
-    counters) must generate exactly the tokens of the eager loop."""
+    counters) must generate exactly the tokens of the eager loop, in both formats of the visual span."""
     from calibquant_b200 import patch_internvl as pi
     from calibquant_b200.internlm2 import ChatModelShell, GraphedDecoder, InternLM2Config, init_weights_
     cfg = InternLM2Config(hidden_size=512, num_attention_heads=4, num_key_value_heads=1,
                           intermediate_size=1024, num_hidden_layers=2, vocab_size=128)
     shell = ChatModelShell(cfg).half()
     init_weights_(shell, 7, std=0.05)
-    pi.patch_model(shell, "calibquant")
+    pi.patch_model(shell, "calibquant", kv_format=kv_format)
     shell.cuda()
     lm = shell.language_model
     g = torch.Generator().manual_seed(2)
@@ -155,5 +156,6 @@ def test_graph_replayed_decode_matches_eager():
     dec = GraphedDecoder(lm, past, first, T, n_new)
     toks = dec.run(n_new - 1)
     dec.close()
+    pi.KV_FORMAT = "group"
     assert torch.equal(first, eager[:, 0])
     assert torch.equal(toks, eager[:, 1:])
