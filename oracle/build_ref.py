@@ -2,15 +2,17 @@
 
     python oracle/build_ref.py [path/to/reference]
 
-Compiles ``qjl/csrc/quantization.cu`` of ActiveSky/calibquant, unchanged and where it lies in the reference
-checkout (default ``/root/reference``), with the flags of the reference's ``qjl/setup.py:5-15`` plus the
-sm_100a code generation flag, into ``oracle/_ref/quantization.so``.  Nothing of the reference is copied into
+Compiles ``qjl/csrc/quantization.cu``, ``qjl_quant_kernel.cu`` and ``qjl_gqa_score_kernel.cu`` of
+ActiveSky/calibquant, unchanged and where they lie in the reference checkout (default ``/root/reference``), with
+the flags of the reference's ``qjl/setup.py:5-15`` plus the sm_100a code generation flag, into
+``oracle/_ref/<module>.so``.  Nothing of the reference is copied into
 this repository: ``oracle/_ref/`` is ignored by git and holds build outputs only.
 
 The extension is the only executable definition of ``cuda_quantized_bmm_dynamic``'s arithmetic
 (``qjl/csrc/quantization.cu:67-169``).  ``tests/test_gpu_ref_pin.py`` runs it on a GPU for 2 and 4 bits (its
 ``psum[16]`` array cannot hold the 32 codes of a 1-bit word) and compares it with the CPU oracle and with
-``cq_qbmm``.  The product never loads it.
+``cq_qbmm``; ``tests/test_gpu_ref_pin_qjl.py`` does the same for the two QJL kernels
+(``qjl_quant_kernel.cu:53-168``, ``qjl_gqa_score_kernel.cu:40-180``).  The product never loads any of them.
 """
 
 from __future__ import annotations
@@ -22,21 +24,39 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = False) -> str | None:
-    src = os.path.join(reference_root, "qjl", "csrc", "quantization.cu")
-    target = os.path.join(OUT, "quantization.so")
+# extension name -> source file under qjl/csrc (the module names the reference's qjl/setup.py:18-57 gives them)
+EXTENSIONS = {
+    "quantization": "quantization.cu",
+    "cuda_qjl_quant": "qjl_quant_kernel.cu",
+    "cuda_qjl_gqa_score": "qjl_gqa_score_kernel.cu",
+}
+
+
+def build_one(name: str, reference_root: str = "/root/reference", verbose: bool = False) -> str | None:
+    src = os.path.join(reference_root, "qjl", "csrc", EXTENSIONS[name])
+    target = os.path.join(OUT, name + ".so")
     if not os.path.exists(src):
         return target if os.path.exists(target) else None
     if os.path.exists(target) and os.path.getmtime(target) >= os.path.getmtime(src):
         return target
-    os.makedirs(OUT, exist_ok=True)
+    out_dir = os.path.join(OUT, "_build_" + name)
+    os.makedirs(out_dir, exist_ok=True)
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")      # no GPU is needed to compile
     from torch.utils.cpp_extension import load
-    load(name="quantization", sources=[src], build_directory=OUT, verbose=verbose,
+    load(name=name, sources=[src], build_directory=out_dir, verbose=verbose,
          extra_cflags=["-O3"],
          extra_cuda_cflags=["-O3", "-std=c++17", "--expt-relaxed-constexpr", "--expt-extended-lambda",
                             "--use_fast_math", "-gencode", "arch=compute_100a,code=sm_100a"])
+    built = os.path.join(out_dir, name + ".so")
+    if os.path.exists(built):
+        os.replace(built, target)
     return target if os.path.exists(target) else None
+
+
+def build(reference_root: str = "/root/reference", verbose: bool = False) -> str | None:
+    """Build every extension; returns the path of ``quantization.so`` (None if it could not be built)."""
+    paths = {name: build_one(name, reference_root, verbose) for name in EXTENSIONS}
+    return paths["quantization"]
 
 
 if __name__ == "__main__":

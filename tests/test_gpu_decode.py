@@ -227,6 +227,50 @@ def test_host_buffer_entry_point(ops, t_vis, pinned):
     assert ops.device_status() == 0
 
 
+def test_two_host_threads_share_the_library(ops):
+    """The entry points may be called from several host threads, each on a stream of its own: two threads run the
+    same decode step (tensor-core path with full-precision tokens, i.e. with the forked side-stream launch) forty
+    times each while the other does the same, and every result must be bit-identical to the one a single thread
+    computed beforehand."""
+    import threading
+    sys_len, t_vis, t_txt, bits = 41, 512, 23, 1
+    cases = []
+    for seed in (61, 62):
+        k, v, q = generator.make_kvq(2, 8, 2, sys_len + t_vis + t_txt, seed=seed)
+        k_sys, k_vis, k_txt = generator.split_spans(k, t_vis, sys_len)
+        v_sys, v_vis, v_txt = generator.split_spans(v, t_vis, sys_len)
+        k_pack = _cuda(gf.quantize_and_pack_last_dim(k_vis.transpose(2, 3).contiguous(), 32, bits))
+        v_pack = _cuda(gf.quantize_and_pack_last_dim(v_vis.contiguous(), 32, bits))
+        k_fp, v_fp = torch.cat([k_sys, k_txt], 2).cuda(), torch.cat([v_sys, v_txt], 2).cuda()
+        args = (q.cuda(), k_pack, v_pack, k_fp, v_fp, sys_len, bits)
+        want = ops.decode_attention(*args).clone()
+        cases.append((args, want))
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker(i):
+        try:
+            args, want = cases[i]
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                for _ in range(40):
+                    out = ops.decode_attention(*args)
+                    stream.synchronize()
+                    if not torch.equal(out.view(torch.int16), want.view(torch.int16)):
+                        errors.append(f"thread {i}: result differs")
+                        return
+        except Exception as e:          # surfaced in the main thread
+            errors.append(f"thread {i}: {type(e).__name__}: {e}")
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not any(t.is_alive() for t in threads), "a worker thread did not finish"
+    assert not errors, errors
+
+
 def test_timed_out_device_wait_is_reported(ops):
     """A bounded device-side wait that runs out leaves CQ_ERR_TIMEOUT in the first word of the workspace.
     No kernel is made to hang here: the word is preset by the host, and the entry points that promise to
