@@ -12,8 +12,11 @@ the restatements here are pinned against *outputs of the reference's own
 functions executed on CPU* (``qjl/new_pack.py`` and ``calibquant.py`` under the
 Triton interpreter, ``calibquant.quant`` / ``encode`` natively).  The script
 ``tests/golden/make_golden.py`` runs the reference and writes the fixtures that
-``tests/test_oracle_golden.py`` replays.  Two pieces have no runnable reference
-on CPU and are "parity unpinned" by the reference itself:
+``tests/test_oracle_golden.py`` replays.  The reference's CUDA extensions
+(``quantization``, ``cuda_qjl_quant``, ``cuda_qjl_gqa_score``) are built unchanged by
+``oracle/build_ref.py`` and run on a GPU by ``tests/test_gpu_ref_pin*.py``, which pins
+``group_format.qbmm`` at 2 and 4 bits, the decode composition and ``qjl.py``.  Two pieces
+have no runnable reference at all and are "parity unpinned" by the reference itself:
 
 * ``group_format.qbmm`` at 1 bit (the reference CUDA kernel cannot run 1-bit:
   ``qjl/matmul.py:24`` asserts bits in [2, 4]); it follows the dequantize-and-

@@ -9,8 +9,9 @@
   (``:170-177``), with ``S q_out`` rebuilt from the group's outlier channels (``:118-127``).
 * ``build_groups``   <- ``qjl/qjl_utils.py:115-134`` (grouping, top-k outlier channels by group norm).
 
-Parity unpinned: the reference kernels need a GPU to run, the reference has no test vectors for them;
-this file follows the kernel sources line by line.  One deliberate difference: ``|k_in|`` uses
+Parity pinned on a GPU: the reference has no test vectors for these kernels, so ``oracle/build_ref.py`` builds
+the two reference extensions unchanged and ``tests/test_gpu_ref_pin_qjl.py`` compares this file (and the library)
+with their outputs on seeded inputs.  This file follows the kernel sources line by line.  One deliberate difference: ``|k_in|`` uses
 ``max(|k|^2 - |k_out|^2, 0)`` where the kernel takes the square root of the raw difference.
 """
 
