@@ -630,10 +630,35 @@ def time_prefill(device, world, B=16, T=3392, HQ=32, steps=5, warmup=3):
     return ms, flops / ms / 1e9, peak, which, (2 * q.numel() + 2 * k.numel()) * 2 / 1e6
 
 
+def time_flash_attn_library(device, B=16, T=3392, HQ=32, steps=5):
+    """The same shape through the third-party flash_attn package the reference calls for its prefill
+    (patch_internvl.py:464-468): TFLOP/s of one GPU, or None where the package is missing or has no kernels for
+    this GPU.  A library baseline beside the number, never part of it."""
+    try:
+        from flash_attn import flash_attn_func
+        g = torch.Generator(device=device).manual_seed(3)
+        q = torch.randn(B, T, HQ, D, generator=g, device=device).to(torch.bfloat16)
+        k = torch.randn(B, T, HKV, D, generator=g, device=device).to(torch.bfloat16)
+        v = torch.randn(B, T, HKV, D, generator=g, device=device).to(torch.bfloat16)
+        for _ in range(3):
+            flash_attn_func(q, k, v, causal=True)
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            flash_attn_func(q, k, v, causal=True)
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1) / steps
+        return round(4.0 * B * HQ * T * T * D / 2 / ms / 1e9, 1)
+    except Exception:
+        return None
+
+
 def prefill_key(device, world):
     """The `prefill` entry of the default line: config 2's prefill attention, batch 16 x 3392 tokens, 5 passes."""
     ms, tf, peak, which, mb = time_prefill(device, world)
-    return {"metric": "prefill_attn_TFLOPs", "value": round(tf * world, 1), "unit": "TFLOP/s", "ms_per_pass": round(ms, 4),
+    return {"flash_attn_library_TFLOPs_per_gpu": time_flash_attn_library(device),"metric": "prefill_attn_TFLOPs", "value": round(tf * world, 1), "unit": "TFLOP/s", "ms_per_pass": round(ms, 4),
             "config": "causal prefill attention, batch 16/GPU, 3392 tokens, 32q/8kv heads, head_dim 128, bf16; 5 passes "
                       f"after 3 warm-up; q+k+v+out = {mb:.0f} MB per pass (> L2)",
             "flops": "4*B*Hq*T^2*D/2 (causal half)", "kernel": "prefill_tc_kernel",

@@ -22,7 +22,8 @@ have no runnable reference at all and are "parity unpinned" by the reference its
   ``qjl/matmul.py:24`` asserts bits in [2, 4]); it follows the dequantize-and-
   accumulate arithmetic of ``qjl/csrc/quantization.cu:108-123``.
 * ``prefill.causal_attention`` (the reference calls the third-party flash_attn
-  library, ``patch_internvl.py:464-468``); it is plain fp32 softmax attention.
+  library, ``patch_internvl.py:464-468``); it is plain fp32 softmax attention, compared
+  with that library on a GPU where it is installed (``tests/test_gpu_prefill.py``).
 """
 
 from . import generator, group_format, calibquant_format, prefill, forward  # noqa: F401

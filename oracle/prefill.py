@@ -5,8 +5,10 @@ The reference delegates prefill attention to the third-party flash_attn library
 ``:606-609``), in 1024-query chunks against the growing K/V prefix, which is just
 causal attention.  flash_attn is not part of the reference tree and needs a GPU, so
 this file restates the published definition -- softmax(Q K^T / sqrt(D) + causal
-mask) V with GQA head sharing -- in fp32.  Parity for prefill is therefore
-"unpinned" by any reference test or run; tolerance is set against this fp32 form.
+mask) V with GQA head sharing -- in fp32.  The reference has no test or vector for it;
+where the flash_attn package is installed and runs on the test GPU,
+``tests/test_gpu_prefill.py::test_against_the_flash_attn_library`` pins this file and the
+library's kernel to ``flash_attn_func(causal=True)`` on seeded tensors.
 """
 
 from __future__ import annotations

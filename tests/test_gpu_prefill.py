@@ -104,3 +104,23 @@ def test_growing_logits_force_row_rescales(ops, dtype, tol):
     out = ops.prefill_attention(q.cuda(), k.cuda(), v.cuda())
     assert torch.isfinite(out.float()).all()
     assert rel_l2(out, ref) <= tol, rel_l2(out, ref)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float16, 5e-3), (torch.bfloat16, 1e-2)])
+def test_against_the_flash_attn_library(ops, dtype, tol):
+    """The reference's prefill is a call into the third-party flash_attn package (patch_internvl.py:464-468,
+    :606-609).  Where that package is installed and has kernels for this GPU, its causal attention on the same
+    seeded tensors pins both the library's prefill kernel and the fp32 oracle; otherwise the test is skipped."""
+    try:
+        from flash_attn import flash_attn_func
+    except Exception as e:                      # not installed / not importable here
+        pytest.skip(f"flash_attn not importable: {type(e).__name__}")
+    q, k, v = _qkv(2, 700, 8, 2, dtype, seed=33)
+    try:
+        ref = flash_attn_func(q.cuda(), k.cuda(), v.cuda(), causal=True)
+        torch.cuda.synchronize()
+    except Exception as e:                      # e.g. no kernel image for this architecture
+        pytest.skip(f"flash_attn cannot run on this GPU: {type(e).__name__}: {str(e)[:80]}")
+    out = ops.prefill_attention(q.cuda(), k.cuda(), v.cuda())
+    assert rel_l2(out, ref.cpu()) <= tol
+    assert rel_l2(oracle_prefill.causal_attention(q, k, v), ref.cpu()) <= tol
