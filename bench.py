@@ -26,6 +26,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -397,6 +398,61 @@ def cpu_baseline(args, reps, rows=1):
                       f"({sec * 1e3:.1f} ms per pass)", "ms_per_sample": round(sec * 1e3, 2)}
 
 
+def reference_gpu_decode(args, reps=5):
+    """The reference's OWN CUDA path for this step, on this GPU, beside the CPU number of the reference arm: its
+    extension `quantization` (qjl/csrc/quantization.cu, built unchanged into oracle/_ref/ by oracle/build_ref.py)
+    called as qjl/matmul.py:4-35 calls it (three transposed copies of the packed operand per call) on operands
+    expanded to the query heads as qjl/qjl_utils.py:6-11 does, with the eager calibration and softmax of
+    patch_internvl.py:376-385, 413.  2 bits: the reference kernel cannot run 1-bit codes (matmul.py:24,
+    quantization.cu:89).  Returns None where the extension or a GPU is missing."""
+    so = os.path.join(ROOT, "oracle", "_ref", "quantization.so")
+    if not (torch.cuda.is_available() and os.path.exists(so)):
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("quantization", so)
+    ext = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ext)
+    bits, batch, t_vis = 2, args.batch, args.context
+    device = torch.device("cuda", 0)
+    (kp, vp, _, _), = build_caches(batch, t_vis, 0, bits, 1, device, 5)       # set-up only, outside the timed step
+    q = torch.randn(batch, HQ, 1, D, device=device).half()
+    n_rep = HQ // HKV
+
+    def rep(t):                                                             # repeat_kv_quant: a materialised copy
+        b, h, a, c = t.shape
+        return t[:, :, None].expand(b, h, n_rep, a, c).reshape(b, h * n_rep, a, c)
+
+    def bmm(fA, qB, scales, zeros):                                         # qjl/matmul.py:12-31
+        B, nh, M, K = fA.shape
+        a = fA.view(-1, M, K).contiguous()
+        w = qB.reshape(-1, K, qB.shape[-1]).transpose(1, 2).contiguous()
+        sc = scales.view(B * nh, scales.shape[-2], scales.shape[-1]).transpose(1, 2).contiguous()
+        z = zeros.view(B * nh, zeros.shape[-2], zeros.shape[-1]).transpose(1, 2).contiguous()
+        out = ext.batchedQuantizedMultiplyAccumulate_half(a, w, sc, z, bits, GROUP, nh, False)
+        return out.view(B, nh, out.shape[-2], out.shape[-1])
+
+    def step():
+        s = bmm(q, rep(kp[0]), rep(kp[1]), rep(kp[2])) / math.sqrt(D)
+        mx, mn = s.amax(dim=(2, 3), keepdim=True), s.amin(dim=(2, 3), keepdim=True)
+        s = (s - mn) / (mx - mn + 1e-8) * ((mx + (-3)) - mn) + mn
+        att = torch.softmax(s, dim=-1, dtype=torch.float32).to(q.dtype)
+        return bmm(att, rep(vp[0]), rep(vp[1]), rep(vp[2]))
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(reps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / reps
+    return {"what": "the reference's own CUDA kernel and wrappers for the decode step on this GPU (informational; the "
+                    "reference arm's value is the CPU number)", "bits": bits, "ms_per_step": round(ms, 3),
+            "GBps": round(algorithmic_bytes(batch, t_vis, 0, bits) / (ms * 1e-3) / 1e9, 2), "reps": reps}
+
+
 def run_reference(args, rank, world):
     """Reference arm: the reference's decode-step arithmetic on this host's CPU cores (its CUDA
     extension and Triton kernels need a GPU toolchain that the port replaces; the CPU oracle is
@@ -419,8 +475,16 @@ def run_reference(args, rank, world):
                               "extrapolates the sampled rows to the full batch"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "reference_gpu": _safe(lambda: reference_gpu_decode(args)),
         "wall_s": round(time.perf_counter() - t0, 1),
     }
+
+
+def _safe(fn):
+    try:
+        return fn()
+    except Exception as e:
+        return {"error": f"{type(e).__name__}: {e}"[:200]}
 
 
 def model_decode(rank, world, device, big=False, batch=None, steps=64, bits=1, eager=False):
