@@ -45,8 +45,8 @@ L2_BYTES = 126 * 1024 * 1024
 # profiles/: (kernel, bits, context, batch) -> (bytes, the kernel instantiation that was captured, summary file).
 # The figure is reported only while the library still builds that instantiation for the workload.
 NCU_TRAFFIC = {
-    ("attn_v", 1, 32768, 8): (87492608, "k2_attn_v<__half,1,512>", "profiles/decode_attn_1bit_b8_ctx32768.md"),
-    ("scores", 1, 32768, 8): (71231232, "k1_scores<__half,1,true>", "profiles/decode_attn_1bit_b8_ctx32768.md"),
+    ("attn_v", 1, 32768, 8): (87126272, "k2_attn_v<__half,1,512>", "profiles/decode_attn_1bit_b8_ctx32768.md"),
+    ("scores", 1, 32768, 8): (70148352, "k1_scores<__half,1,true>", "profiles/decode_attn_1bit_b8_ctx32768.md"),
 }
 KERNEL_NAMES = {"scores": "k1_scores", "attn_v": "k2_attn_v"}
 MIN_TIMED_MS = 50.0      # the device-timed region lasts at least this long, whatever --steps says
