@@ -3,7 +3,8 @@
     python oracle/build_ref.py [path/to/reference]
 
 Compiles ``qjl/csrc/quantization.cu``, ``qjl_quant_kernel.cu`` and ``qjl_gqa_score_kernel.cu`` of
-ActiveSky/calibquant, unchanged and where they lie in the reference checkout (default ``/root/reference``), with
+ActiveSky/calibquant, unchanged and where they lie in the reference checkout (default: the directory
+``reference`` beside this repository), with
 the flags of the reference's ``qjl/setup.py:5-15`` plus the sm_100a code generation flag, into
 ``oracle/_ref/<module>.so``.  Nothing of the reference is copied into
 this repository: ``oracle/_ref/`` is ignored by git and holds build outputs only.
@@ -22,6 +23,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
+DEFAULT_REFERENCE = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 # extension name -> source file under qjl/csrc (the module names the reference's qjl/setup.py:18-57 gives them)
@@ -32,7 +34,7 @@ EXTENSIONS = {
 }
 
 
-def build_one(name: str, reference_root: str = "/root/reference", verbose: bool = False) -> str | None:
+def build_one(name: str, reference_root: str = DEFAULT_REFERENCE, verbose: bool = False) -> str | None:
     src = os.path.join(reference_root, "qjl", "csrc", EXTENSIONS[name])
     target = os.path.join(OUT, name + ".so")
     if not os.path.exists(src):
@@ -53,7 +55,7 @@ def build_one(name: str, reference_root: str = "/root/reference", verbose: bool 
     return target if os.path.exists(target) else None
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = False) -> str | None:
+def build(reference_root: str = DEFAULT_REFERENCE, verbose: bool = False) -> str | None:
     """Build every extension; returns the path of ``quantization.so`` (None if it could not be built)."""
     paths = {name: build_one(name, reference_root, verbose) for name in EXTENSIONS}
     return paths["quantization"]
