@@ -74,6 +74,46 @@ def test_argument_validation_needs_no_gpu(handle):
     assert lib.cq_decode_attn(ctypes.byref(a), None, 0, None) == _lib.CQ_ERR_WORKSPACE
 
 
+def test_argument_validation_of_the_newer_entry_points(handle):
+    """Prefill split + RoPE, strided V pack, the uint8-format decode step and the peer-buffer collectives reject bad
+    arguments on the host, before any CUDA call."""
+    from calibquant_b200 import _lib
+    lib = _lib.lib()
+    buf = ctypes.create_string_buffer(4096)
+    p16 = ctypes.c_void_p((ctypes.cast(buf, ctypes.c_void_p).value + 15) // 16 * 16)
+    # cq_prefill_rope_split: empty prompt is a no-op, null operands / a span past the prompt / odd strides are not
+    args = lambda **kw: [kw.get("qkv", p16), kw.get("sb", 6 * 128 * 8), kw.get("st", 6 * 128), p16, p16, 64, None,
+                         kw.get("batch", 1), kw.get("t_len", 8), 1, 4, kw.get("head_dim", 128), p16, p16, None, None,
+                         0, 0, 0, kw.get("vis_start", 0), kw.get("vis_len", 0), 0, None]
+    assert lib.cq_prefill_rope_split(*args(batch=0)) == _lib.CQ_OK
+    assert lib.cq_prefill_rope_split(*args(qkv=None)) == _lib.CQ_ERR_BAD_ARG
+    assert lib.cq_prefill_rope_split(*args(vis_start=4, vis_len=8)) == _lib.CQ_ERR_BAD_ARG
+    assert lib.cq_prefill_rope_split(*args(st=6 * 128 + 4)) == _lib.CQ_ERR_BAD_ARG
+    assert lib.cq_prefill_rope_split(*args(head_dim=64)) == _lib.CQ_ERR_UNSUPPORTED
+    # cq_pack_v_per_token
+    assert lib.cq_pack_v_per_token(p16, 0, 2, 8, 128, 0, 0, 0, 32, 1, 0, p16, p16, p16, None) == _lib.CQ_OK
+    assert lib.cq_pack_v_per_token(None, 1, 2, 8, 128, 2048, 128, 256, 32, 1, 0, p16, p16, p16, None) == _lib.CQ_ERR_BAD_ARG
+    assert lib.cq_pack_v_per_token(p16, 1, 2, 8, 128, 2048, 128, 256, 32, 3, 0, p16, p16, p16, None) == _lib.CQ_ERR_UNSUPPORTED
+    assert lib.cq_pack_v_per_token(p16, 1, 2, 8, 128, 2044, 128, 256, 32, 1, 0, p16, p16, p16, None) == _lib.CQ_ERR_BAD_ARG
+    # cq_u8_decode_attn
+    a = _lib.U8DecodeArgs()
+    assert lib.cq_u8_decode_attn_workspace_bytes(ctypes.byref(a)) == 0
+    assert lib.cq_u8_decode_attn(ctypes.byref(a), None, 0, None) == _lib.CQ_ERR_BAD_ARG
+    a.batch, a.n_q_heads, a.n_kv_heads, a.head_dim = 1, 4, 1, 128
+    a.t_vis, a.t_fp, a.t_sys, a.bits, a.dtype, a.n_scale_heads = 64, 0, 0, 1, 0, 4
+    for f in ("q", "out", "enc_k", "enc_v", "scale_key", "zero_point_key", "scale_value", "zero_point_value"):
+        setattr(a, f, p16.value)
+    assert lib.cq_u8_decode_attn_workspace_bytes(ctypes.byref(a)) > 0
+    assert lib.cq_u8_decode_attn(ctypes.byref(a), None, 0, None) == _lib.CQ_ERR_WORKSPACE
+    a.n_scale_heads = 3
+    assert lib.cq_u8_decode_attn(ctypes.byref(a), None, 0, None) == _lib.CQ_ERR_BAD_ARG
+    a.n_scale_heads, a.t_vis = 4, 60000                       # more keys than a shared-memory row holds
+    assert lib.cq_u8_decode_attn(ctypes.byref(a), None, 0, None) == _lib.CQ_ERR_UNSUPPORTED
+    # peer-buffer sizes
+    assert lib.cq_comm_buffer_bytes(2, 8192) > 2 * 2 * 8192
+    assert lib.cq_comm_buffer_bytes(0, 8192) == 0 or lib.cq_comm_buffer_bytes(9, 8192) == 0
+
+
 def test_cpu_tensors_are_rejected():
     import torch
     from calibquant_b200 import ops
