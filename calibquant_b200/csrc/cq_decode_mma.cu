@@ -193,11 +193,18 @@ template <> struct D16<__nv_bfloat16> {
 // Warps 0-3 compute, warp 4 is the TMA producer: stages are handed over through a full barrier (bytes
 // landed) and an empty barrier (one arrival per computing warp), so no warp waits for another warp's
 // arithmetic, only for data.
-template <typename T, int BITS, bool SPLIT>
+// LDG: the variant for token counts that are not a multiple of 256.  The row pitches of the packed keys
+// (T*bits/8 bytes) and of their scales and minima (T/16 bytes) are then no multiples of 16 bytes, which a tensor
+// map cannot describe: the producer warp copies the code words with 4-byte cp.async into the same swizzled layout
+// (words past the last group are zero-filled), the computing warps read their scale and minimum fragments straight
+// from global memory, and groups past the end are neither stored nor counted in the min/max.
+template <typename T, int BITS, bool SPLIT, bool LDG = false>
 __global__ void __launch_bounds__(K1_THREADS, k1_min_ctas(BITS))
 k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ CUtensorMap tm_ks,
           const __grid_constant__ CUtensorMap tm_kmn, Dims dm, const T* __restrict__ q,
-          T* __restrict__ scores, float2* __restrict__ tile_mm, int* __restrict__ status) {
+          T* __restrict__ scores, float2* __restrict__ tile_mm, int* __restrict__ status,
+          const int32_t* __restrict__ code_g = nullptr, const T* __restrict__ ks_g = nullptr,
+          const T* __restrict__ kmn_g = nullptr) {
   using T2 = typename D16<T>::T2;
   constexpr int STAGES = k1_stages(BITS);
   constexpr int STAGE_BYTES = k1_stage_bytes(BITS);
@@ -222,7 +229,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
 
   pdl_launch_dependents();
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], K1_WARPS); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], LDG ? 32 : 1); mbar_init(&empty_bar[s], K1_WARPS); }
     mbar_fence_init();
   }
   __syncthreads();
@@ -232,6 +239,32 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
   const int it_first = (int)(((int64_t)blockIdx.x * n_items) / gridDim.x);
   const int it_end = (int)(((int64_t)(blockIdx.x + 1) * n_items) / gridDim.x);
 
+  if (LDG && warp == K1_WARPS) {
+    // ---- producer, all 32 lanes: 4-byte asynchronous copies of the tile's code words into the swizzled boxes
+    constexpr int WPR = TILE_G * BITS;                 // words of a channel row inside a tile
+    const int64_t row_words = (int64_t)dm.n_groups * BITS;
+    for (int k = 0; it_first + k < it_end; ++k) {
+      const int it = it_first + k, s = k % STAGES;
+      if (k >= STAGES && !mbar_wait_bounded(&empty_bar[s], (uint32_t)((k / STAGES - 1) & 1), WAIT_TRIES)) {
+        if (lane == 0) atomicExch(status, CQ_ERR_TIMEOUT);
+        break;
+      }
+      const int pair = it / dm.n_ktiles, tile = it % dm.n_ktiles;
+      const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
+      const int valid = min(TILE_G, dm.n_groups - tile * TILE_G) * BITS;     // live words of a row
+      const int32_t* src0 = code_g + (int64_t)pair * kHeadDim * row_words + (int64_t)tile * WPR;
+      for (int i = lane; i < kHeadDim * WPR; i += 32) {
+        const int d = i / WPR, w = i % WPR;
+        const int cb = (w * 4) % ROW_BYTES, box = (w * 4) / ROW_BYTES;
+        const int sw = ROW_BYTES == 64 ? ((d >> 1) & 3) : (d & 7);
+        const uint32_t dst = base + (uint32_t)(box * (128 * ROW_BYTES) + d * ROW_BYTES + (((cb >> 4) ^ sw) << 4) + (cb & 15));
+        const bool live = w < valid;
+        cp_async4_zfill(dst, src0 + (int64_t)d * row_words + (live ? w : 0), live ? 4u : 0u);
+      }
+      cp_async_mbar_arrive_noinc(&full_bar[s]);
+    }
+    return;
+  }
   if (warp == K1_WARPS) {
     // ---- producer: one thread streams the CTA's tiles through the ring
     if (lane == 0) {
@@ -317,7 +350,27 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
       const int col8 = (warp * K1_GPW) >> 3, g_in_col = (warp * K1_GPW) & 7;
       uint32_t ksA[8], ksB[8];
       float cb[4] = {0.f, 0.f, 0.f, 0.f};   // bias[G = 8*col8+g][columns 2c, 2c+1]
-      {
+      if (LDG) {
+        // fragments straight from global memory: lane (g, c) holds, for k-tile kt, the pairs of channels
+        // 16kt + 2c (+1) and 16kt + 8 + 2c (+1) of group G = first group of the warp's eight + g
+        const int G = tile * TILE_G + col8 * 8 + g;
+        const bool live = G < dm.n_groups;
+        const T* ksr = ks_g + (int64_t)pair * kHeadDim * dm.n_groups + (live ? G : 0);
+        const T* mnr = kmn_g + (int64_t)pair * kHeadDim * dm.n_groups + (live ? G : 0);
+        uint32_t zA[8], zB[8];
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) {
+          const int64_t d0 = (int64_t)(16 * kt + 2 * c) * dm.n_groups, d1 = (int64_t)(16 * kt + 8 + 2 * c) * dm.n_groups;
+          const T2 a = D16<T>::pair2(ksr[d0], ksr[d0 + dm.n_groups]), b2 = D16<T>::pair2(ksr[d1], ksr[d1 + dm.n_groups]);
+          const T2 za = D16<T>::pair2(mnr[d0], mnr[d0 + dm.n_groups]), zb = D16<T>::pair2(mnr[d1], mnr[d1 + dm.n_groups]);
+          ksA[kt] = live ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(&a)) : 0u;
+          ksB[kt] = live ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(&b2)) : 0u;
+          zA[kt] = live ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(&za)) : 0u;
+          zB[kt] = live ? D16<T>::to_h2(*reinterpret_cast<const uint32_t*>(&zb)) : 0u;
+        }
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) mma_f16(cb, zA[kt], 0u, zB[kt], 0u, qA[kt], qB[kt]);
+      } else {
         const int mat = lane >> 3, r = lane & 7;
 #pragma unroll
         for (int kp = 0; kp < 4; ++kp) {
@@ -407,6 +460,7 @@ k1_scores(const __grid_constant__ CUtensorMap tm_code, const __grid_constant__ C
           const float bias0 = __shfl_sync(0xffffffffu, cb[0], 4 * gi + c);
           const float bias1 = SPLIT ? 0.f : __shfl_sync(0xffffffffu, cb[1], 4 * gi + c);
           const int tokg = (tile * TILE_G + col8 * 8 + gi) * 32;
+          if (LDG && tokg >= dm.t_vis) continue;      // a group past the end of a ragged last tile
           if (SPLIT) {      // one head per lane: columns 2c, 2c+1 are its two terms
             T2 sa[2];
 #pragma unroll
@@ -721,7 +775,10 @@ k2_attn_v(const __grid_constant__ CUtensorMap tm_v,   // 2 and 4 bits: the value
         unsigned char* base = smem + s * STAGE_BYTES;
         const int64_t tok = (int64_t)pair * dm.t_vis + (int64_t)vt * VT;
         const int nt = min(VT, dm.t_vis - vt * VT);
-        mbar_expect_tx(&full_bar[s], (uint32_t)(nt * (TOK_BYTES + 16) + dm.n_rep * nt * 2));
+        // a tiled load always delivers whole boxes of 256 rows (rows past the last token of the KV head are the
+        // next head's, or zero past the end of the array; nobody reads them)
+        const int code_rows = BITS == 1 ? nt : (nt + 255) / 256 * 256;
+        mbar_expect_tx(&full_bar[s], (uint32_t)(code_rows * TOK_BYTES + nt * 16 + dm.n_rep * nt * 2));
         if (BITS == 1) {
           bulk_load_1d(base, v_code + tok * WPT, (uint32_t)(nt * TOK_BYTES), &full_bar[s]);
         } else {
@@ -1265,17 +1322,20 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
   float* partial = reinterpret_cast<float*>(ws + l.partial_off);
   const int n_pairs = d.batch * d.hkv;
 
-  auto k1 = d.n_rep <= 4 ? k1_scores<T, BITS, true> : k1_scores<T, BITS, false>;
+  // token counts that are not a multiple of 256: row pitches a tensor map cannot describe (see k1_scores)
+  const bool ldg = d.t_vis % 256 != 0;
+  auto k1 = ldg ? (d.n_rep <= 4 ? k1_scores<T, BITS, true, true> : k1_scores<T, BITS, false, true>)
+                : (d.n_rep <= 4 ? k1_scores<T, BITS, true> : k1_scores<T, BITS, false>);
   auto k2 = k2_attn_v<T, BITS, VT>;
   const int smem1 = k1_stages(BITS) * k1_stage_bytes(BITS) + 1024;
   const int smem2 = k2_smem_bytes(BITS, VT);
-  static bool configured_dev[64][2] = {};   // per template instance, device and score-kernel variant
-  static int occ1_dev[64][2], occ2_dev[64][2];
+  static bool configured_dev[64][4] = {};   // per template instance, device and score-kernel variant
+  static int occ1_dev[64][4], occ2_dev[64][4];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return CQ_ERR_LAUNCH;
   static std::mutex config_mu;                // host threads may share a device
   std::lock_guard<std::mutex> config_lock(config_mu);
-  const int variant = d.n_rep <= 4 ? 1 : 0;
+  const int variant = (d.n_rep <= 4 ? 1 : 0) + (ldg ? 2 : 0);
   bool& configured = configured_dev[dev][variant];
   int& occ1 = occ1_dev[dev][variant];
   int& occ2 = occ2_dev[dev][variant];
@@ -1308,12 +1368,16 @@ static int run_shape(const cq_decode_args* a, const Dims& d, const Layout& l, un
   if (d.t_vis > 0) {
     CUtensorMap tm_code, tm_ks, tm_kmn;
     const uint64_t rows = (uint64_t)n_pairs * kHeadDim;
-    if (!make_k_maps<BITS>(&tm_code, &tm_ks, &tm_kmn, a->k_code, a->k_scale, a->k_mn, (uint64_t)d.n_groups, rows))
+    if (ldg) {
+      memset(&tm_code, 0, sizeof(tm_code)); memset(&tm_ks, 0, sizeof(tm_ks)); memset(&tm_kmn, 0, sizeof(tm_kmn));
+    } else if (!make_k_maps<BITS>(&tm_code, &tm_ks, &tm_kmn, a->k_code, a->k_scale, a->k_mn, (uint64_t)d.n_groups, rows)) {
       return CQ_ERR_LAUNCH;
+    }
     const int items1 = n_pairs * d.n_ktiles;
     const int grid1 = max(1, min(items1, sm_count() * occ1));
     if (launch_pdl(k1, dim3(grid1), dim3(K1_THREADS), smem1, st, tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(a->q),
-                   scores, mm, status) != cudaSuccess)
+                   scores, mm, status, a->k_code, static_cast<const T*>(a->k_scale),
+                   static_cast<const T*>(a->k_mn)) != cudaSuccess)
       return CQ_ERR_LAUNCH;
     int rc = check_launch();
     if (rc != CQ_OK) return rc;
@@ -1364,7 +1428,7 @@ static int run(const cq_decode_args* a, const Dims& d, const Layout& l, unsigned
 }  // namespace mma
 
 bool mma_path_eligible(const cq_decode_args* a) {
-  if (a->t_vis <= 0 || a->t_vis % 256 != 0) return false;
+  if (a->t_vis <= 0 || a->t_vis % 32 != 0) return false;
   if (a->bits != 1 && a->bits != 2 && a->bits != 4) return false;
   const void* ptrs[] = {a->q, a->k_code, a->k_scale, a->k_mn, a->v_code, a->v_scale, a->v_mn};
   for (const void* p : ptrs)
@@ -1438,7 +1502,7 @@ static int qbmm_run_t(int kind, const mma::Dims& d_in, const void* fA, const int
     if (!make_k_maps<BITS>(&tm_code, &tm_ks, &tm_kmn, qB, scales, zeros, (uint64_t)d.n_groups, rows)) return CQ_ERR_LAUNCH;
     const int grid = max(1, min(n_pairs * d.n_ktiles, sm_count() * occ[dev][variant]));
     k1<<<grid, K1_THREADS, smem1, st>>>(tm_code, tm_ks, tm_kmn, d, static_cast<const T*>(fA),
-                                        static_cast<T*>(out), nullptr, status);
+                                        static_cast<T*>(out), nullptr, status, nullptr, nullptr, nullptr);
     return check_launch();
   }
   float2* ml = reinterpret_cast<float2*>(ws + 256);

@@ -37,6 +37,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// 4-byte asynchronous copy global -> shared; src_bytes < 4 zero-fills the rest (0: nothing is read).
+__device__ __forceinline__ void cp_async4_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// The mbarrier receives one arrival when all cp.async copies this thread has issued so far have completed; the
+// arrival is counted against the barrier's expected count (no increment of the pending count).
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // Bounded wait: returns false when the phase did not complete within `max_tries` polls.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t max_tries) {
   for (uint32_t i = 0; i < max_tries; ++i) {

@@ -194,7 +194,7 @@ int cq_decode_attn(const cq_decode_args* args, void* workspace, size_t workspace
  * timers).  Runs the step exactly as cq_decode_attn does, with CUDA events recorded on `stream` between
  * its launches, waits for the last one and fills launch_ms[4] = {scores, attn.V, attn.V of the
  * full-precision tokens, combine} in milliseconds.  Only for requests the tensor-core kernels take
- * (t_vis a multiple of 256, 16-byte aligned operands); CQ_ERR_UNSUPPORTED otherwise.  Synchronises.
+ * (t_vis > 0, 16-byte aligned operands); CQ_ERR_UNSUPPORTED otherwise.  Synchronises.
  */
 int cq_decode_attn_profile(const cq_decode_args* args, void* workspace, size_t workspace_bytes,
                            void* stream, float* launch_ms);

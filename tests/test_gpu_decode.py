@@ -159,6 +159,43 @@ def test_without_calibration_and_with_mask(ops):
     assert rel_l2(out, ref) <= TOL_ATTN
 
 
+@pytest.mark.parametrize("bits", [1, 2, 4])
+@pytest.mark.parametrize("t_vis,t_txt,n_rep,dtype", [(32, 0, 4, torch.float16), (96, 3, 4, torch.float16),
+                                                     (1056, 17, 4, torch.float16), (3360, 64, 4, torch.float16),
+                                                     (2080, 9, 6, torch.float16), (800, 30, 8, torch.float16),
+                                                     (1312, 21, 4, torch.bfloat16)])
+def test_tensor_core_path_any_multiple_of_32(ops, bits, t_vis, t_txt, n_rep, dtype):
+    """Visual spans that are a multiple of 32 but not of 256: the rows of the packed keys, scales and minima then
+    have pitches no tensor map can describe, and the score launch takes its cp.async / global-load variant; the
+    last K tile and the last V tile are ragged down to a single group (1056 = 33 groups, 3360 = 105)."""
+    out, ref = _run_case(ops, 2, 2 * n_rep, 2, t_vis, t_txt, bits, dtype, seed=70 + bits + t_vis)
+    # bf16: 2e-2 as on the other tensor-core shapes, 3e-2 at 1 bit, where the calibrated logits span the widest range
+    # and a one-ulp flip (0.25 at |s| = 40) of a head's extreme logit moves every logit of that head (measured 2.2e-2)
+    tol = TOL_ATTN if dtype == torch.float16 else (3e-2 if bits == 1 else 2e-2)
+    assert rel_l2(out, ref) <= tol, rel_l2(out, ref)
+    assert ops.device_status() == 0
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4])
+def test_cuda_core_kernels_on_an_unaligned_query(ops, bits):
+    """Operands that are not 16-byte aligned cannot go through TMA / 16-byte loads: the request is served by the
+    CUDA-core kernels (the only route left to them besides requests without visual tokens).  Same bar."""
+    sys_len, t_vis, t_txt = 41, 544, 70
+    k, v, q = generator.make_kvq(3, 8, 2, sys_len + t_vis + t_txt, seed=50 + bits)
+    k_sys, k_vis, k_txt = generator.split_spans(k, t_vis, sys_len)
+    v_sys, v_vis, v_txt = generator.split_spans(v, t_vis, sys_len)
+    k_pack = gf.quantize_and_pack_last_dim(k_vis.transpose(2, 3).contiguous(), 32, bits)
+    v_pack = gf.quantize_and_pack_last_dim(v_vis.contiguous(), 32, bits)
+    ref = gf.decode_attention(q, k_pack, v_pack, k_sys, k_txt, v_sys, v_txt, bits)
+    flat = torch.empty(q.numel() + 4, dtype=q.dtype, device="cuda")
+    q_dev = flat[4:].view(q.shape)                            # 8 bytes off a 16-byte boundary
+    q_dev.copy_(q)
+    assert q_dev.data_ptr() % 16 == 8
+    out = ops.decode_attention(q_dev, _cuda(k_pack), _cuda(v_pack), torch.cat([k_sys, k_txt], 2).cuda(),
+                               torch.cat([v_sys, v_txt], 2).cuda(), sys_len, bits)
+    assert rel_l2(out.cpu(), ref) <= TOL_ATTN
+
+
 def test_edge_segments(ops):
     # no text tokens yet, a single group of visual tokens
     out, ref = _run_case(ops, 1, 4, 1, 32, 0, 1, torch.float16, seed=6)
