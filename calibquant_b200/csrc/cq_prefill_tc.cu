@@ -17,6 +17,8 @@
 // Lazy maximum: a row keeps its reference maximum until the true one exceeds it by more than 2^8, and
 // only then are that row's O columns and running sum rescaled (tcgen05.ld / st between two PV
 // products); probabilities stay below 256 and O is read back once, at the end.
+// Epilogue: the normalised rows of a tile are staged in its Q buffer (swizzled box layout) and written
+// with two tiled TMA stores, which also clip the rows past the end of the sequence.
 // TMEM columns: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512).  Operand tiles in shared
 // memory use the 128-byte swizzle: a [128 rows x 64 elements] TMA box lands directly in the
 // canonical UMMA layout (8-row atoms of 1024 bytes).
@@ -45,9 +47,7 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr float RESCALE_LOG2 = 8.f;          // a row is rescaled when its maximum grew by more than 2^8
 
 struct Params {
-  void* out;
   int t_len, hq, hkv;
-  int64_t o_sb, o_st, o_sh;
   float scale_log2;
   uint32_t idesc_s, idesc_pv;
   int is_bf16;
@@ -123,6 +123,21 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const void* tmap, int c0,
       : "memory");
 }
 
+// 4-D tiled store shared -> global (rows past the tensor's extent are clipped), tracked by the thread's bulk group
+__device__ __forceinline__ void tma_store_4d(const void* tmap, const void* src, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
+      ::"l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(src))
+      : "memory");
+}
+// closes the thread's bulk group and waits until its stores have read their shared-memory source
+__device__ __forceinline__ void tma_store_commit_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// barrier among the four softmax warps of one query tile
+__device__ __forceinline__ void tile_barrier(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
+
 // Shared-memory matrix descriptor, 128-byte swizzle, version 1 (Blackwell).
 // K-major operands: lbo is unused (1), sbo = 1024 B between 8-row atoms.
 // MN-major operands: lbo = bytes between 64-element MN blocks, sbo = 1024 B between 8-row K groups.
@@ -177,7 +192,7 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 template <bool IS_BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                  const __grid_constant__ CUtensorMap tm_v, Params p) {
+                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   unsigned char* q_s = smem;                    // tiles A, B
@@ -384,24 +399,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       } else {
         tc_fence_after();
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        unsigned char* dst = reinterpret_cast<unsigned char*>(p.out) +
-                             2 * ((int64_t)b * p.o_sb + (int64_t)row * p.o_st + (int64_t)h * p.o_sh);
+        // The normalised rows go through the tile's Q buffer (every S_x has completed before the last P.V, so
+        // nothing reads Q_x any more) in the layout of a 128-byte-swizzled TMA box, and leave as two tiled stores:
+        // a thread's row is 256 contiguous bytes in global memory, but the 32 rows of a warp are a row pitch
+        // apart, and direct 16-byte stores from the registers cost the CTA ~5000 cycles.
+        unsigned char* stage = q_s + x * TILE_BYTES;
 #pragma unroll 1
         for (int cc = 0; cc < 4; ++cc) {
           uint32_t r[32];
-          tmem_ld32(tO + cc * 32, r);                   // warp-collective: rows past the end load too
-          if (row < p.t_len) {
+          tmem_ld32(tO + cc * 32, r);
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 w;
-              w.x = pack16<IS_BF16>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-              w.y = pack16<IS_BF16>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-              w.z = pack16<IS_BF16>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-              w.w = pack16<IS_BF16>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-              *reinterpret_cast<uint4*>(dst + (cc * 32 + i) * 2) = w;
-            }
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack16<IS_BF16>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+            w.y = pack16<IS_BF16>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+            w.z = pack16<IS_BF16>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+            w.w = pack16<IS_BF16>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+            const int chunk = (cc & 1) * 4 + (i >> 3);          // 16-byte chunk of the 128-byte panel row
+            *reinterpret_cast<uint4*>(stage + (cc >> 1) * PANEL_BYTES + r_in * 128 + ((chunk ^ (r_in & 7)) << 4)) = w;
           }
         }
+      }
+      fence_proxy_async_smem();
+      tile_barrier(1 + x);
+      if (ok && quarter == 0 && lane == 0) {
+        tma_store_4d(&tm_o, q_s + x * TILE_BYTES, 0, h, qx0, b);
+        tma_store_4d(&tm_o, q_s + x * TILE_BYTES + PANEL_BYTES, 64, h, qx0, b);
+        tma_store_commit_wait_read();
       }
     }
   }
@@ -469,9 +493,9 @@ int prefill_tc_run(const void* q, const void* k, const void* v, void* out, int b
                    const int64_t* qs, const int64_t* ks, const int64_t* vs, const int64_t* os, int is_bf16,
                    int* status, cudaStream_t st) {
   using namespace prefill_tc;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tq, tk, tv, to;
   if (!make_map(&tq, q, is_bf16, batch, t_len, hq, qs) || !make_map(&tk, k, is_bf16, batch, t_len, hkv, ks) ||
-      !make_map(&tv, v, is_bf16, batch, t_len, hkv, vs))
+      !make_map(&tv, v, is_bf16, batch, t_len, hkv, vs) || !make_map(&to, out, is_bf16, batch, t_len, hq, os))
     return CQ_ERR_LAUNCH;
   static bool configured[64] = {};
   int dev = 0;
@@ -483,16 +507,15 @@ int prefill_tc_run(const void* q, const void* k, const void* v, void* out, int b
     configured[dev] = true;
   }
   Params p;
-  p.out = out; p.t_len = t_len; p.hq = hq; p.hkv = hkv;
-  p.o_sb = os[0]; p.o_st = os[1]; p.o_sh = os[2];
+  p.t_len = t_len; p.hq = hq; p.hkv = hkv;
   p.scale_log2 = 1.4426950408889634f / sqrtf(128.f);
   p.idesc_s = make_idesc(is_bf16, 0);
   p.idesc_pv = make_idesc(is_bf16, 1);
   p.is_bf16 = is_bf16;
   p.status = status;
   dim3 grid((unsigned)((t_len + 2 * BM - 1) / (2 * BM)), (unsigned)hq, (unsigned)batch);
-  if (is_bf16) prefill_tc_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
-  else prefill_tc_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, p);
+  if (is_bf16) prefill_tc_kernel<true><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, to, p);
+  else prefill_tc_kernel<false><<<grid, THREADS, SMEM_BYTES, st>>>(tq, tk, tv, to, p);
   return check_launch();
 }
 
