@@ -39,7 +39,7 @@ using namespace ptx;
 constexpr int BM = 128, BN = 128;
 constexpr int PANEL_BYTES = 128 * 128;          // [128 rows][64 x 16-bit]
 constexpr int TILE_BYTES = 2 * PANEL_BYTES;     // [128 rows][128 x 16-bit]
-constexpr int SMEM_BYTES = TILE_BYTES * 6 + 1024;   // Q x2, K x2, V x2 (+ alignment slack)
+constexpr int SMEM_BYTES = TILE_BYTES * 7 + 1024;   // Q x2, K x2, V x2, output staging (+ alignment slack)
 constexpr int SOFTMAX_THREADS = 256, MMA_WARP = 8, TMA_WARP = 9, THREADS = SOFTMAX_THREADS + 64;
 constexpr uint32_t WAIT_TRIES = 1u << 22;
 constexpr long long WAIT_CYCLES = 1ll << 30;     // ~0.5 s: bound of the waits on the S / P hand-offs
@@ -135,6 +135,37 @@ __device__ __forceinline__ void tma_store_commit_wait_read() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// Cluster launch control: a running CTA asks for the grid's next CTA that has not been launched yet.  On success
+// that CTA is never launched and the 16-byte response names its block index, so the caller does its work: the
+// hardware's own launch order and load balance, without the launch gap and the set-up of a new CTA.
+// After a request has failed (nothing left to cancel) no further request may be issued.
+__device__ __forceinline__ void clc_try_cancel(void* resp, uint64_t* bar) {
+  asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+               ::"r"(smem_u32(resp)), "r"(smem_u32(bar)) : "memory");
+}
+// decodes a response; false: the request failed, there is no further work
+__device__ __forceinline__ bool clc_read(const void* resp, int& bx, int& by, int& bz) {
+  uint32_t valid = 0, x = 0, y = 0, z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p1;\n\t.reg .b128 r;\n\t"
+      "ld.shared.b128 r, [%4];\n\t"
+      "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p1, r;\n\t"
+      "selp.u32 %3, 1, 0, p1;\n\t"
+      "@p1 clusterlaunchcontrol.query_cancel.get_first_ctaid.v4.b32.b128 {%0, %1, %2, _}, r;\n\t}"
+      : "+r"(x), "+r"(y), "+r"(z), "+r"(valid)
+      : "r"(smem_u32(resp))
+      : "memory");
+  fence_proxy_async_smem();       // the slot is written again through the async proxy
+  bx = (int)x; by = (int)y; bz = (int)z;
+  return valid != 0;
+}
+// barrier among the four softmax warps of one query tile that also tells whether ALL of them passed `flag`
+__device__ __forceinline__ bool tile_all(int id, bool flag) {
+  uint32_t out;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(out) : "r"((uint32_t)flag), "r"(id) : "memory");
+  return out != 0;
+}
 // barrier among the four softmax warps of one query tile
 __device__ __forceinline__ void tile_barrier(int id) { asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory"); }
 
@@ -189,6 +220,28 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// One work item = 256 queries of one (batch, query head) = one block index of the grid (x: 256-query block,
+// longest rows first; y: query head; z: batch row).  A CTA starts with its own index and then takes over blocks
+// that have not been launched yet (cluster launch control), in the order the hardware would have launched them:
+// neighbouring CTAs keep working on the query blocks and heads of one KV head, whose K/V tiles stay in L2.
+struct Item {
+  int h, b, hk, q0, n_a, n_b, n_max;
+};
+__device__ __forceinline__ Item decode_item(const Params& p, int bx, int by, int bz) {
+  Item w;
+  const int qt = (int)gridDim.x - 1 - bx;         // longest rows first
+  w.h = by;
+  w.b = bz;
+  w.hk = w.h / (p.hq / p.hkv);
+  w.q0 = qt * 2 * BM;
+  const int t_tiles = (p.t_len + BN - 1) / BN;
+  // key tiles of query tile X = 0 (A), 1 (B); B may lie wholly past the end
+  w.n_a = min((w.q0 + BM + BN - 1) / BN, t_tiles);
+  w.n_b = w.q0 + BM < p.t_len ? min((w.q0 + 2 * BM + BN - 1) / BN, t_tiles) : 0;
+  w.n_max = max(w.n_a, w.n_b);
+  return w;
+}
+
 template <bool IS_BF16>
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -198,32 +251,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   unsigned char* q_s = smem;                    // tiles A, B
   unsigned char* k_s = q_s + 2 * TILE_BYTES;    // 2 stages
   unsigned char* v_s = k_s + 2 * TILE_BYTES;    // 2 stages
-  // per query tile X: bar_s (S_X ready), bar_p[X][half] (P_X of keys 0-63 / 64-127 stored, 128 arrivals
-  // each), bar_pv (O_X += P_X V done); each completes once per key tile of X
-  __shared__ __align__(8) uint64_t bar_q, bar_kv_full[2], bar_kv_free[2], bar_s[2], bar_p[2][2], bar_pv[2];
+  unsigned char* o_s = v_s + 2 * TILE_BYTES;    // output staging, used by the two tiles in turn
+  // Barriers.  Their phases run on across the CTA's items: every role keeps the count of completions it has seen.
+  //   bar_q[X]       Q_X of an item has landed                         (once per item)
+  //   bar_q_free[X]  the last S_X of an item has completed: Q_X may be overwritten   (once per item)
+  //   bar_kv_full/free[stage]   K/V ring                               (once per key tile of the CTA)
+  //   bar_s[X]       S_X ready;  bar_p[X][half]  P_X of keys 0-63 / 64-127 stored (128 arrivals);
+  //   bar_pv[X]      O_X += P_X V done                                 (once per key tile of X)
+  //   bar_stage      a tile's output stores have read the staging buffer   (once per tile with rows)
+  //   bar_clc_full/free[slot]   the response naming the CTA's next item has arrived / has been read by the MMA
+  //                  thread and the eight softmax warps (item i's successor travels through slot i % 2)
+  __shared__ __align__(8) uint64_t bar_q[2], bar_q_free[2], bar_kv_full[2], bar_kv_free[2], bar_s[2], bar_p[2][2],
+      bar_pv[2], bar_stage, bar_clc_full[2], bar_clc_free[2];
+  __shared__ __align__(16) uint4 clc_resp[2];
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qt = gridDim.x - 1 - blockIdx.x;    // longest rows first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int hk = h / (p.hq / p.hkv);
-  const int q0 = qt * 2 * BM;
-  const int t_tiles = (p.t_len + BN - 1) / BN;
-  // key tiles of query tile X = 0 (A), 1 (B); B may lie wholly past the end
-  const int n_a = min((q0 + BM + BN - 1) / BN, t_tiles);
-  const int n_b = q0 + BM < p.t_len ? min((q0 + 2 * BM + BN - 1) / BN, t_tiles) : 0;
-  const int n_max = max(n_a, n_b);
 
   if (tid == 0) {
-    mbar_init(&bar_q, 1);
     for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar_q[s], 1);
+      mbar_init(&bar_q_free[s], 1);
       mbar_init(&bar_kv_full[s], 1);
       mbar_init(&bar_kv_free[s], 1);
       mbar_init(&bar_s[s], 1);
       mbar_init(&bar_p[s][0], SOFTMAX_THREADS / 2);
       mbar_init(&bar_p[s][1], SOFTMAX_THREADS / 2);
       mbar_init(&bar_pv[s], 1);
+      mbar_init(&bar_clc_full[s], 1);
+      mbar_init(&bar_clc_free[s], 1 + SOFTMAX_THREADS / 32);
     }
+    mbar_init(&bar_stage, 1);
     mbar_fence_init();
   }
   if (warp == MMA_WARP) tmem_alloc(&tmem_base_s, TMEM_COLS);
@@ -235,22 +293,40 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (warp == TMA_WARP) {
     // ================= TMA producer (one lane) =================
     if (lane == 0) {
-      mbar_expect_tx(&bar_q, 2 * TILE_BYTES);
-#pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        tma_load_4d(q_s + x * TILE_BYTES, &tm_q, 0, h, q0 + x * BM, b, &bar_q);
-        tma_load_4d(q_s + x * TILE_BYTES + PANEL_BYTES, &tm_q, 64, h, q0 + x * BM, b, &bar_q);
-      }
       bool ok = true;
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int s = j & 1;
-        if (j >= 2) ok = mbar_wait_bounded(&bar_kv_free[s], (uint32_t)(((j - 2) >> 1) & 1), WAIT_TRIES);
+      uint32_t kv = 0;                          // K/V tiles this CTA has loaded so far
+      int bx = blockIdx.x, by = blockIdx.y, bz = blockIdx.z;
+      for (uint32_t it = 0; ok; ++it) {         // items of this CTA
+        const Item w = decode_item(p, bx, by, bz);
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          // Q_x of the previous item is read until its last S_x has completed
+          if (it > 0) ok = ok && mbar_wait_bounded(&bar_q_free[x], (it - 1) & 1, WAIT_TRIES);
+          if (!ok) break;
+          mbar_expect_tx(&bar_q[x], TILE_BYTES);
+          tma_load_4d(q_s + x * TILE_BYTES, &tm_q, 0, w.h, w.q0 + x * BM, w.b, &bar_q[x]);
+          tma_load_4d(q_s + x * TILE_BYTES + PANEL_BYTES, &tm_q, 64, w.h, w.q0 + x * BM, w.b, &bar_q[x]);
+        }
+        for (int j = 0; j < w.n_max && ok; ++j, ++kv) {
+          const uint32_t s = kv & 1;
+          if (kv >= 2) ok = mbar_wait_bounded(&bar_kv_free[s], ((kv - 2) >> 1) & 1, WAIT_TRIES);
+          if (!ok) break;
+          mbar_expect_tx(&bar_kv_full[s], 2 * TILE_BYTES);
+          tma_load_4d(k_s + s * TILE_BYTES, &tm_k, 0, w.hk, j * BN, w.b, &bar_kv_full[s]);
+          tma_load_4d(k_s + s * TILE_BYTES + PANEL_BYTES, &tm_k, 64, w.hk, j * BN, w.b, &bar_kv_full[s]);
+          tma_load_4d(v_s + s * TILE_BYTES, &tm_v, 0, w.hk, j * BN, w.b, &bar_kv_full[s]);
+          tma_load_4d(v_s + s * TILE_BYTES + PANEL_BYTES, &tm_v, 64, w.hk, j * BN, w.b, &bar_kv_full[s]);
+        }
         if (!ok) break;
-        mbar_expect_tx(&bar_kv_full[s], 2 * TILE_BYTES);
-        tma_load_4d(k_s + s * TILE_BYTES, &tm_k, 0, hk, j * BN, b, &bar_kv_full[s]);
-        tma_load_4d(k_s + s * TILE_BYTES + PANEL_BYTES, &tm_k, 64, hk, j * BN, b, &bar_kv_full[s]);
-        tma_load_4d(v_s + s * TILE_BYTES, &tm_v, 0, hk, j * BN, b, &bar_kv_full[s]);
-        tma_load_4d(v_s + s * TILE_BYTES + PANEL_BYTES, &tm_v, 64, hk, j * BN, b, &bar_kv_full[s]);
+        // All loads of this item are on their way (the other roles are about two key tiles behind): ask for the
+        // item's successor now, not earlier, so that a CTA does not sit on a block another CTA could start.
+        const uint32_t slot = it & 1;
+        if (it >= 2) ok = mbar_wait_bounded(&bar_clc_free[slot], ((it >> 1) - 1) & 1, WAIT_TRIES);
+        if (!ok) break;
+        mbar_expect_tx(&bar_clc_full[slot], 16);
+        clc_try_cancel(&clc_resp[slot], &bar_clc_full[slot]);
+        ok = mbar_wait_bounded(&bar_clc_full[slot], (it >> 1) & 1, WAIT_TRIES);
+        if (!ok || !clc_read(&clc_resp[slot], bx, by, bz)) break;
       }
       if (!ok) atomicExch(p.status, CQ_ERR_TIMEOUT);
     }
@@ -264,54 +340,73 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const uint64_t kd[2] = {smem_desc(smem_u32(k_s), 16, 1024), smem_desc(smem_u32(k_s + TILE_BYTES), 16, 1024)};
       const uint64_t vd[2] = {smem_desc(smem_u32(v_s), PANEL_BYTES, 1024),
                               smem_desc(smem_u32(v_s + TILE_BYTES), PANEL_BYTES, 1024)};
-      auto issue_s = [&](int x, int j) {        // S_x(j) = Q_x K(j)^T; the K tile is known to be there
+      auto issue_s = [&](int x, uint32_t stage) {   // S_x = Q_x K^T on the K tile of that stage, known to be there
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {        // 16 channels per step; panel = ks/4, 32 B per step
           const uint64_t off = (uint64_t)(((ks >> 2) * PANEL_BYTES + (ks & 3) * 32) >> 4);
-          umma(tmem + (uint32_t)x * 128u, qd[x] + off, kd[j & 1] + off, p.idesc_s, ks > 0);
+          umma(tmem + (uint32_t)x * 128u, qd[x] + off, kd[stage] + off, p.idesc_s, ks > 0);
         }
         umma_commit(&bar_s[x]);
       };
-      bool ok = mbar_wait_bounded(&bar_q, 0, WAIT_TRIES);
-      ok = ok && mbar_wait_bounded(&bar_kv_full[0], 0, WAIT_TRIES);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0, 0);
-        if (n_b > 0) issue_s(1, 0);
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int s = j & 1;
-        bool next_k_ready = false;
+      bool ok = true;
+      uint32_t kv = 0, cnt[2] = {0, 0};           // K/V tiles, key tiles of A / B done so far
+      int bx = blockIdx.x, by = blockIdx.y, bz = blockIdx.z;
+      for (uint32_t it = 0; ok; ++it) {
+        const Item w = decode_item(p, bx, by, bz);
+        const int n_x[2] = {w.n_a, w.n_b};
+        ok = mbar_wait_bounded(&bar_kv_full[kv & 1], (kv >> 1) & 1, WAIT_TRIES);
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-          if (j >= (x == 0 ? n_a : n_b)) continue;
-          // O_x += P_x(j) V(j), 16 keys = 8 TMEM columns per step; the first four steps start as soon as
-          // the probabilities of keys 0-63 are stored, while the softmax warps work on keys 64-127
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
-            ok = mbar_wait_cycles(&bar_p[x][hf], (uint32_t)(j & 1), WAIT_CYCLES);
-            if (!ok) break;
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 4 * hf; ks < 4 * hf + 4; ++ks)
-              umma_ts(tmem + 256u + (uint32_t)x * 128u, tmem + (uint32_t)x * 128u + (uint32_t)ks * 8u,
-                      vd[s] + (uint64_t)(ks * 2048 >> 4), p.idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-          }
+          ok = ok && mbar_wait_bounded(&bar_q[x], it & 1, WAIT_TRIES);
           if (!ok) break;
-          umma_commit(&bar_pv[x]);
-          // S_x(j+1) overwrites the columns P_x(j) lives in; the tensor pipe runs in issue order
-          if (j + 1 < (x == 0 ? n_a : n_b)) {
-            if (!next_k_ready) {
-              ok = mbar_wait_bounded(&bar_kv_full[s ^ 1], (uint32_t)(((j + 1) >> 1) & 1), WAIT_TRIES);
+          tc_fence_after();
+          if (n_x[x] > 0) issue_s(x, kv & 1);
+          if (n_x[x] <= 1) umma_commit(&bar_q_free[x]);     // that was the item's last S_x (or it has none)
+        }
+        for (int j = 0; j < w.n_max && ok; ++j) {
+          const uint32_t s = (kv + j) & 1;
+          bool next_k_ready = false;
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            if (j >= n_x[x]) continue;
+            // O_x += P_x(j) V(j), 16 keys = 8 TMEM columns per step; the first four steps start as soon as
+            // the probabilities of keys 0-63 are stored, while the softmax warps work on keys 64-127
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+              ok = mbar_wait_cycles(&bar_p[x][hf], (cnt[x] + j) & 1, WAIT_CYCLES);
               if (!ok) break;
               tc_fence_after();
-              next_k_ready = true;
+#pragma unroll
+              for (int ks = 4 * hf; ks < 4 * hf + 4; ++ks)
+                umma_ts(tmem + 256u + (uint32_t)x * 128u, tmem + (uint32_t)x * 128u + (uint32_t)ks * 8u,
+                        vd[s] + (uint64_t)(ks * 2048 >> 4), p.idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
             }
-            issue_s(x, j + 1);
+            if (!ok) break;
+            umma_commit(&bar_pv[x]);
+            // S_x(j+1) overwrites the columns P_x(j) lives in; the tensor pipe runs in issue order
+            if (j + 1 < n_x[x]) {
+              if (!next_k_ready) {
+                ok = mbar_wait_bounded(&bar_kv_full[s ^ 1], ((kv + j + 1) >> 1) & 1, WAIT_TRIES);
+                if (!ok) break;
+                tc_fence_after();
+                next_k_ready = true;
+              }
+              issue_s(x, s ^ 1);
+              if (j + 2 == n_x[x]) umma_commit(&bar_q_free[x]);   // the item's last S_x
+            }
           }
+          if (!ok) break;
+          umma_commit(&bar_kv_free[s]);             // K(j), V(j) are free once everything issued so far has drained
         }
+        kv += (uint32_t)w.n_max;
+        cnt[0] += (uint32_t)w.n_a;
+        cnt[1] += (uint32_t)w.n_b;
         if (!ok) break;
-        umma_commit(&bar_kv_free[s]);             // K(j), V(j) are free once everything issued so far has drained
+        ok = mbar_wait_bounded(&bar_clc_full[it & 1], (it >> 1) & 1, WAIT_TRIES);
+        if (!ok) break;
+        const bool more = clc_read(&clc_resp[it & 1], bx, by, bz);
+        mbar_arrive(&bar_clc_free[it & 1]);
+        if (!more) break;
       }
       if (!ok) atomicExch(p.status, CQ_ERR_TIMEOUT);
     }
@@ -319,114 +414,133 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   } else {
     // ===== softmax: warps 0-3 tile A, 4-7 tile B; thread = one query row =====
     const int x = warp >> 2, quarter = warp & 3;
-    const int n_x = x == 0 ? n_a : n_b;
     const int r_in = quarter * 32 + lane;               // row inside the tile = TMEM lane
-    const int qx0 = q0 + x * BM;
-    const int row = qx0 + r_in;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const uint32_t tS = tmem + (uint32_t)x * 128u + lane_off;
     const uint32_t tO = tmem + 256u + (uint32_t)x * 128u + lane_off;
-    float m_ref = -INFINITY, l_run = 0.f;               // reference maximum (log2 units), row sum
     bool ok = true;                                     // stays false after a timeout; later waits are skipped
-    for (int j = 0; j < n_x; ++j) {
-      const int key0 = j * BN;
-      const bool need_mask = (key0 + BN - 1 > qx0) || (key0 + BN > p.t_len);
-      if (ok) ok = mbar_wait_cycles(&bar_s[x], (uint32_t)(j & 1), WAIT_CYCLES);
-      tc_fence_after();
-      uint32_t sv[4][32];                               // this row's 128 logits, read once
+    uint32_t cnt = 0, uses = 0;                         // key tiles of this tile / uses of the staging buffer so far
+    int bx = blockIdx.x, by = blockIdx.y, bz = blockIdx.z;
+    for (uint32_t it = 0;; ++it) {
+      const Item w = decode_item(p, bx, by, bz);
+      const int n_x = x == 0 ? w.n_a : w.n_b;
+      const int qx0 = w.q0 + x * BM;
+      const int row = qx0 + r_in;
+      float m_ref = -INFINITY, l_run = 0.f;             // reference maximum (log2 units), row sum
+      for (int j = 0; j < n_x; ++j) {
+        const int key0 = j * BN;
+        const bool need_mask = (key0 + BN - 1 > qx0) || (key0 + BN > p.t_len);
+        if (ok) ok = mbar_wait_cycles(&bar_s[x], (cnt + j) & 1, WAIT_CYCLES);
+        tc_fence_after();
+        uint32_t sv[4][32];                             // this row's 128 logits, read once
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) tmem_ld32_nowait(tS + cc * 32, sv[cc]);
-      tmem_ld_wait();
-      if (need_mask) {                                  // diagonal and last key tiles only
-        const int lim = min(row, p.t_len - 1) - key0;   // columns above lim are masked
+        for (int cc = 0; cc < 4; ++cc) tmem_ld32_nowait(tS + cc * 32, sv[cc]);
+        tmem_ld_wait();
+        if (need_mask) {                                // diagonal and last key tiles only
+          const int lim = min(row, p.t_len - 1) - key0; // columns above lim are masked
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (cc * 32 + i > lim) sv[cc][i] = 0xff800000u;   // -inf
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (cc * 32 + i > lim) sv[cc][i] = 0xff800000u;   // -inf
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc)
-#pragma unroll
-        for (int i = 0; i < 32; i += 2)
-          mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1]));
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float m_true = fmaxf(m_ref, mx * p.scale_log2);
-      const bool grow = m_true - m_ref > RESCALE_LOG2;  // also true for the first tile (m_ref = -inf)
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // O_x holds the products of tiles 0..j-1; the last of them must have completed
-        if (ok) ok = mbar_wait_bounded(&bar_pv[x], (uint32_t)((j - 1) & 1), WAIT_TRIES);
-        tc_fence_after();
-        const float alpha = grow ? exp2f(m_ref - m_true) : 1.f;
+          for (int i = 0; i < 32; i += 2)
+            mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], __uint_as_float(sv[cc][i]), __uint_as_float(sv[cc][i + 1]));
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float m_true = fmaxf(m_ref, mx * p.scale_log2);
+        const bool grow = m_true - m_ref > RESCALE_LOG2;  // also true for the first tile (m_ref = -inf)
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          // O_x holds the products of tiles 0..j-1; the last of them must have completed
+          if (ok) ok = mbar_wait_bounded(&bar_pv[x], (cnt + j - 1) & 1, WAIT_TRIES);
+          tc_fence_after();
+          const float alpha = grow ? exp2f(m_ref - m_true) : 1.f;
 #pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t r[32];
-          tmem_ld32(tO + cc * 32, r);
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tmem_ld32(tO + cc * 32, r);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(tO + cc * 32, r);
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(tO + cc * 32, r);
+          }
+          l_run *= alpha;
         }
-        l_run *= alpha;
-      }
-      if (grow) m_ref = m_true;
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (grow) m_ref = m_true;
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+        float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int cc = 0; cc < 4; cc += 2) {
-        uint32_t w[32];                                 // 64 probabilities as 16-bit pairs = 32 TMEM columns
+        for (int cc = 0; cc < 4; cc += 2) {
+          uint32_t wv[32];                              // 64 probabilities as 16-bit pairs = 32 TMEM columns
 #pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          // masked logits are -inf: ex2 gives 0
-          float x0, x1;
-          fma_pair(x0, x1, __uint_as_float(sv[cc + (i >> 5)][i & 31]), __uint_as_float(sv[cc + (i >> 5)][(i & 31) + 1]),
-                   p.scale_log2, -m_use);
-          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-          add_pair(rs4[i & 2], rs4[(i & 2) + 1], p0, p1);
-          w[i >> 1] = pack16<IS_BF16>(p0, p1);
+          for (int i = 0; i < 64; i += 2) {
+            // masked logits are -inf: ex2 gives 0
+            float x0, x1;
+            fma_pair(x0, x1, __uint_as_float(sv[cc + (i >> 5)][i & 31]), __uint_as_float(sv[cc + (i >> 5)][(i & 31) + 1]),
+                     p.scale_log2, -m_use);
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            add_pair(rs4[i & 2], rs4[(i & 2) + 1], p0, p1);
+            wv[i >> 1] = pack16<IS_BF16>(p0, p1);
+          }
+          tmem_st32(tS + (cc >> 1) * 32, wv);           // over the first 64 columns of S_x
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&bar_p[x][cc >> 1]);
         }
-        tmem_st32(tS + (cc >> 1) * 32, w);              // over the first 64 columns of S_x
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(&bar_p[x][cc >> 1]);
+        l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       }
-      l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
-    }
-    if (n_x > 0) {
-      if (ok) ok = mbar_wait_bounded(&bar_pv[x], (uint32_t)((n_x - 1) & 1), WAIT_TRIES);
-      if (!ok) {
-        atomicExch(p.status, CQ_ERR_TIMEOUT);
-      } else {
-        tc_fence_after();
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        // The normalised rows go through the tile's Q buffer (every S_x has completed before the last P.V, so
-        // nothing reads Q_x any more) in the layout of a 128-byte-swizzled TMA box, and leave as two tiled stores:
-        // a thread's row is 256 contiguous bytes in global memory, but the 32 rows of a warp are a row pitch
-        // apart, and direct 16-byte stores from the registers cost the CTA ~5000 cycles.
-        unsigned char* stage = q_s + x * TILE_BYTES;
+      if (n_x > 0) {
+        if (ok) ok = mbar_wait_bounded(&bar_pv[x], (cnt + n_x - 1) & 1, WAIT_TRIES);
+        // the staging buffer is used by A, then B, of every item: wait until the use before this one has been read
+        const uint32_t use = uses + (x == 1 && w.n_a > 0 ? 1u : 0u);
+        if (ok && use > 0) ok = mbar_wait_bounded(&bar_stage, (use - 1) & 1, WAIT_TRIES);
+        if (ok) {
+          tc_fence_after();
+          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          // The normalised rows go through shared memory in the layout of a 128-byte-swizzled TMA box and leave
+          // as two tiled stores: a thread's row is 256 contiguous bytes in global memory, but the 32 rows of a
+          // warp are a row pitch apart, and direct 16-byte stores from the registers cost the CTA ~5000 cycles.
 #pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t r[32];
-          tmem_ld32(tO + cc * 32, r);
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tmem_ld32(tO + cc * 32, r);
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            w.x = pack16<IS_BF16>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-            w.y = pack16<IS_BF16>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-            w.z = pack16<IS_BF16>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-            w.w = pack16<IS_BF16>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-            const int chunk = (cc & 1) * 4 + (i >> 3);          // 16-byte chunk of the 128-byte panel row
-            *reinterpret_cast<uint4*>(stage + (cc >> 1) * PANEL_BYTES + r_in * 128 + ((chunk ^ (r_in & 7)) << 4)) = w;
+            for (int i = 0; i < 32; i += 8) {
+              uint4 wq;
+              wq.x = pack16<IS_BF16>(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+              wq.y = pack16<IS_BF16>(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+              wq.z = pack16<IS_BF16>(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+              wq.w = pack16<IS_BF16>(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+              const int chunk = (cc & 1) * 4 + (i >> 3);        // 16-byte chunk of the 128-byte panel row
+              *reinterpret_cast<uint4*>(o_s + (cc >> 1) * PANEL_BYTES + r_in * 128 + ((chunk ^ (r_in & 7)) << 4)) = wq;
+            }
           }
         }
+        tc_fence_before();                              // O_x has been read: the next item's first P.V may overwrite it
+        fence_proxy_async_smem();
+        tile_barrier(1 + x);
+        if (quarter == 0 && lane == 0) {
+          if (ok) {
+            tma_store_4d(&tm_o, o_s, 0, w.h, qx0, w.b);
+            tma_store_4d(&tm_o, o_s + PANEL_BYTES, 64, w.h, qx0, w.b);
+            tma_store_commit_wait_read();
+          } else {
+            atomicExch(p.status, CQ_ERR_TIMEOUT);
+          }
+          mbar_arrive(&bar_stage);                      // also after a timeout, so that nobody waits for this use
+        }
       }
-      fence_proxy_async_smem();
-      tile_barrier(1 + x);
-      if (ok && quarter == 0 && lane == 0) {
-        tma_store_4d(&tm_o, q_s + x * TILE_BYTES, 0, h, qx0, b);
-        tma_store_4d(&tm_o, q_s + x * TILE_BYTES + PANEL_BYTES, 64, h, qx0, b);
-        tma_store_commit_wait_read();
-      }
+      cnt += (uint32_t)n_x;
+      uses += (w.n_a > 0 ? 1u : 0u) + (w.n_b > 0 ? 1u : 0u);
+      // the next item, if there is one
+      if (ok) ok = mbar_wait_bounded(&bar_clc_full[it & 1], (it >> 1) & 1, WAIT_TRIES);
+      bool more = ok && clc_read(&clc_resp[it & 1], bx, by, bz);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_clc_free[it & 1]);
+      more = tile_all(1 + x, more);                     // the tile's four warps go on, or leave, together
+      if (!more) break;
     }
   }
   tc_fence_before();
