@@ -1,8 +1,11 @@
 // Dense causal prefill attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
 //
-// One CTA = 256 queries of one (batch, query head), as two 128-row tiles A and B that share the
-// K/V stream.  Roles:
-//   warp 9 (one lane)  TMA producer: Q tiles once, then 128-key K/V tiles through a two-stage ring
+// One work item = 256 queries of one (batch, query head), as two 128-row tiles A and B that share the
+// K/V stream.  One CTA per SM; it starts with the item of its own block index and then takes over blocks of the
+// grid that have not been launched yet (cluster launch control), so tensor memory, barriers and the pipeline
+// are set up once per SM and the hardware's launch order and load balance are kept.  Roles:
+//   warp 9 (one lane)  TMA producer: the item's Q tiles, then its 128-key K/V tiles through a two-stage ring
+//                        that runs on across items; asks for the next block when an item's loads are issued
 //   warp 8 (one lane)  MMA issuer:
 //        S_X = Q_X K^T   tcgen05.mma kind::f16, A = Q_X and B = K from shared memory (K-major), D in the
 //                        tile's 128 TMEM columns
@@ -11,17 +14,20 @@
 //                        the tile's O columns over all key tiles
 //   warps 0-3 / 4-7    softmax of tile A / B: thread = one query row (= TMEM lane).  It reads its 128
 //                        logits once (tcgen05.ld), applies scale, causal mask and the online softmax
-//                        with a lazy maximum, and stores P back to TMEM (tcgen05.st).  No shared memory,
-//                        no cross-thread exchange: the two tiles run out of phase, so one tile's
+//                        with a lazy maximum, and stores P back to TMEM (tcgen05.st).  No cross-thread
+//                        exchange: the two tiles run out of phase, so one tile's
 //                        exponentials overlap the other tile's products on the tensor pipe.
 // Lazy maximum: a row keeps its reference maximum until the true one exceeds it by more than 2^8, and
 // only then are that row's O columns and running sum rescaled (tcgen05.ld / st between two PV
 // products); probabilities stay below 256 and O is read back once, at the end.
-// Epilogue: the normalised rows of a tile are staged in its Q buffer (swizzled box layout) and written
+// Epilogue: the normalised rows of a tile are staged in shared memory (swizzled box layout) and written
 // with two tiled TMA stores, which also clip the rows past the end of the sequence.
 // TMEM columns: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512).  Operand tiles in shared
 // memory use the 128-byte swizzle: a [128 rows x 64 elements] TMA box lands directly in the
 // canonical UMMA layout (8-row atoms of 1024 bytes).
+// Measured on B200: one M128 N128 K16 product takes 85 cycles of the tensor pipe whether A comes from shared or
+// tensor memory (98 with the softmax warps' TMEM traffic beside it), so the 32 products of a key tile bound a
+// CTA at ~3100 cycles per key tile; the loop runs at ~3400.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA records CQ_ERR_TIMEOUT in the status word,
 // skips its remaining waits, frees its TMEM and returns.
@@ -159,6 +165,20 @@ __device__ __forceinline__ bool clc_read(const void* resp, int& bx, int& by, int
   bx = (int)x; by = (int)y; bz = (int)z;
   return valid != 0;
 }
+// A use counter in shared memory (monotonic, so a waiter may be any number of uses behind or ahead, which the
+// parity of an mbarrier phase cannot express): bounded wait until it has reached `target`.
+__device__ __forceinline__ bool wait_count(const uint32_t* ctr, uint32_t target, uint32_t max_tries) {
+  for (uint32_t i = 0; i < max_tries; ++i) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(ctr)) : "memory");
+    if (v >= target) return true;
+    if (i > 64) __nanosleep(64);
+  }
+  return false;
+}
+__device__ __forceinline__ void publish_count(uint32_t* ctr, uint32_t v) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(ctr)), "r"(v) : "memory");
+}
 // barrier among the four softmax warps of one query tile that also tells whether ALL of them passed `flag`
 __device__ __forceinline__ bool tile_all(int id, bool flag) {
   uint32_t out;
@@ -258,12 +278,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   //   bar_kv_full/free[stage]   K/V ring                               (once per key tile of the CTA)
   //   bar_s[X]       S_X ready;  bar_p[X][half]  P_X of keys 0-63 / 64-127 stored (128 arrivals);
   //   bar_pv[X]      O_X += P_X V done                                 (once per key tile of X)
-  //   bar_stage      a tile's output stores have read the staging buffer   (once per tile with rows)
+  //   stage_done     (a counter, not a barrier) uses of the staging buffer whose stores have read it
   //   bar_clc_full/free[slot]   the response naming the CTA's next item has arrived / has been read by the MMA
   //                  thread and the eight softmax warps (item i's successor travels through slot i % 2)
   __shared__ __align__(8) uint64_t bar_q[2], bar_q_free[2], bar_kv_full[2], bar_kv_free[2], bar_s[2], bar_p[2][2],
-      bar_pv[2], bar_stage, bar_clc_full[2], bar_clc_free[2];
+      bar_pv[2], bar_clc_full[2], bar_clc_free[2];
   __shared__ __align__(16) uint4 clc_resp[2];
+  __shared__ uint32_t stage_done;
   __shared__ uint32_t tmem_base_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -281,7 +302,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(&bar_clc_full[s], 1);
       mbar_init(&bar_clc_free[s], 1 + SOFTMAX_THREADS / 32);
     }
-    mbar_init(&bar_stage, 1);
+    stage_done = 0;
     mbar_fence_init();
   }
   if (warp == MMA_WARP) tmem_alloc(&tmem_base_s, TMEM_COLS);
@@ -495,7 +516,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (ok) ok = mbar_wait_bounded(&bar_pv[x], (cnt + n_x - 1) & 1, WAIT_TRIES);
         // the staging buffer is used by A, then B, of every item: wait until the use before this one has been read
         const uint32_t use = uses + (x == 1 && w.n_a > 0 ? 1u : 0u);
-        if (ok && use > 0) ok = mbar_wait_bounded(&bar_stage, (use - 1) & 1, WAIT_TRIES);
+        if (ok) ok = wait_count(&stage_done, use, WAIT_TRIES);
         if (ok) {
           tc_fence_after();
           const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -529,7 +550,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           } else {
             atomicExch(p.status, CQ_ERR_TIMEOUT);
           }
-          mbar_arrive(&bar_stage);                      // also after a timeout, so that nobody waits for this use
+          publish_count(&stage_done, use + 1);          // also after a timeout, so that nobody waits for this use
         }
       }
       cnt += (uint32_t)n_x;
