@@ -504,6 +504,15 @@ namespace cq {
 static size_t host_stage_bytes(const cq_decode_args* a) {
   return align_up((size_t)a->batch * a->n_q_heads * kHeadDim * 2, 256);
 }
+// Page-locked query rows -> their device staging rows, 16 bytes per thread, read over the host link by the kernel
+// itself.  The score launch that follows is a programmatic dependent launch: it sets up its barriers and streams its
+// first key tiles while this copy runs, and touches the query only after it (griddepcontrol.wait); behind a
+// copy-engine transfer it could not start early.
+__global__ void stage_query_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int n) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[i];
+}
 // device-visible address of a page-locked host buffer, or nullptr for pageable memory (asked on every
 // call: an address can change from page-locked to pageable between calls)
 static void* mapped_host_ptr(const void* p) {
@@ -567,7 +576,14 @@ extern "C" int cq_decode_attn_host(const cq_decode_args* args, const void* q_hos
   void* q_dev = ws + base_al;
   void* out_stage = ws + base_al + stage;
   const size_t bytes = (size_t)a.batch * a.n_q_heads * cq::kHeadDim * 2;
-  if (cudaMemcpyAsync(q_dev, q_host, bytes, cudaMemcpyHostToDevice, st) != cudaSuccess) return CQ_ERR_LAUNCH;
+  const void* q_map = cq::aligned16(q_host) ? cq::mapped_host_ptr(q_host) : nullptr;
+  if (q_map) {
+    const int n16 = (int)(bytes / 16);
+    cq::stage_query_kernel<<<(n16 + 255) / 256, 256, 0, st>>>(static_cast<const uint4*>(q_map), static_cast<uint4*>(q_dev), n16);
+    if (cudaGetLastError() != cudaSuccess) return CQ_ERR_LAUNCH;
+  } else if (cudaMemcpyAsync(q_dev, q_host, bytes, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+    return CQ_ERR_LAUNCH;
+  }
   // page-locked result buffer: the last launch stores straight into it; pageable: staged copy
   void* out_map = cq::aligned16(out_host) ? cq::mapped_host_ptr(out_host) : nullptr;
   a.q = q_dev;
