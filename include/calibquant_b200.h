@@ -211,7 +211,9 @@ int cq_workspace_status(const void* workspace, void* stream);
 /*
  * The same step for a caller whose query and result live in HOST memory (the serving loop of
  * patch_internvl.py:556-592 samples the next token on the host): `args->q` and `args->out` are
- * ignored, q_host [B,Hq,D] is copied into the workspace, the last launch stores the result
+ * ignored, q_host [B,Hq,D] is copied into the workspace (by a small kernel that reads the buffer
+ * when it is page-locked, so that the score launch starts under the copy; by a copy-engine transfer
+ * otherwise), the last launch stores the result
  * straight into out_host when that buffer is page-locked (cudaHostAlloc / cudaHostRegister; a
  * staged copy otherwise), and the call returns after the stream has drained, i.e. with out_host
  * valid.
