@@ -73,6 +73,16 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
+def agree_max(n, world, device):
+    """The same iteration count on every rank: the largest any rank asked for.  Each rank sizes its timed
+    region from a probe of its own; the job's time is the slowest rank's total, and it is divided by this count."""
+    if world == 1:
+        return int(n)
+    t = torch.tensor([int(n)], device=device, dtype=torch.int64)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return int(t.item())
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while the timed region runs."""
 
@@ -254,10 +264,7 @@ def run_ours(args, rank, world, device):
     ev_a.record(); graph.replay(); ev_b.record(); torch.cuda.synchronize()
     n_replays = max(1, int(-(-MIN_TIMED_MS // max(ev_a.elapsed_time(ev_b), 1e-3))))
     n_replays = min(n_replays, 2000)
-    if world > 1:      # every rank times the same number of replays: the slowest rank's total is divided by it
-        t = torch.tensor([n_replays], device=device, dtype=torch.int64)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        n_replays = int(t.item())
+    n_replays = agree_max(n_replays, world, device)
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(n_replays + 1)]
     sampler = ClockSampler(device.index)
     barrier()
@@ -297,10 +304,7 @@ def run_ours(args, rank, world, device):
     if not torch.equal(o_host.view(torch.int16), step(n_w - 1, q_dev).view(batch, HQ, D).cpu().view(torch.int16)):
         raise RuntimeError("host-buffer decode step differs from the device-buffer one")
     n_e2e = args.steps * max(1, min(n_replays, int(-(-MIN_TIMED_MS // max(ms / n_replays, 1e-3)))))
-    if world > 1:      # the same number of host calls on every rank, for the same reason
-        t = torch.tensor([n_e2e], device=device, dtype=torch.int64)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        n_e2e = int(t.item())
+    n_e2e = agree_max(n_e2e, world, device)
     barrier()
     ev_a.record()
     for i in range(n_e2e):

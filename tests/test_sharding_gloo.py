@@ -113,6 +113,31 @@ def _tp_worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
+def _count_worker(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import bench
+        # each rank sizes its timed region from its own probe (7 and 8 replays here); all must time the larger
+        # count, or the slowest rank's total would be divided by another rank's count
+        n = bench.agree_max(7 + rank, world, torch.device("cpu"))
+        assert n == 8
+        total_ms = torch.tensor([8 * 7.15], dtype=torch.float64)        # this rank's time for n replays of 100 steps
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+        assert abs(total_ms.item() / (100 * n) - 0.0715) < 1e-12
+        assert bench.agree_max(5, 1, torch.device("cpu")) == 5          # single rank: no collective
+        open(os.path.join(out_dir, f"n{rank}"), "w").close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_time_the_same_number_of_replays(tmp_path):
+    world = 2
+    mp.spawn(_count_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"n{r}").exists() for r in range(world))
+
+
 def test_two_rank_tensor_parallel_slices(tmp_path):
     world = 2
     mp.spawn(_tp_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
