@@ -242,8 +242,9 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 
 // One work item = 256 queries of one (batch, query head) = one block index of the grid (x: 256-query block,
 // longest rows first; y: query head; z: batch row).  A CTA starts with its own index and then takes over blocks
-// that have not been launched yet (cluster launch control), in the order the hardware would have launched them:
-// neighbouring CTAs keep working on the query blocks and heads of one KV head, whose K/V tiles stay in L2.
+// that have not been launched yet (cluster launch control).  Measured, the CTAs running at the same time keep
+// working on the query blocks and heads of a few KV heads, whose K/V tiles stay in L2, as with one CTA per block;
+// a static assignment of items sorted by length lost that and ran 6 % slower.
 struct Item {
   int h, b, hk, q0, n_a, n_b, n_max;
 };
